@@ -1,0 +1,236 @@
+/*
+ * C ABI of libq4t_moe_b200.so: a B200 (sm_100a) implementation of the
+ * qwen4-thor NVFP4 W4A4 MoE layer operators.
+ *
+ * Every entry point takes plain device/host pointers and sizes, enqueues its
+ * work on the caller's CUDA stream (passed as void*, i.e. a cudaStream_t; NULL
+ * is the default stream), performs no host synchronisation and returns 0 on
+ * success or a negative q4t_status.  q4t_last_error() returns the message of
+ * the calling thread's last failure.  There is no CPU fallback: on a machine
+ * without a usable sm_100 device the compute entry points fail.
+ *
+ * Each declaration names the reference interface (file:line in the
+ * qwen4-thor tree) whose behaviour it reproduces.  The C++ shims in
+ * qwen4-thor_b200/host/ rebuild those C++ signatures on top of this ABI.
+ *
+ * Data formats (unchanged from the reference engine):
+ *   packed NVFP4  : row-major [rows, K/2] bytes, two e2m1 codes per byte, low
+ *                   nibble = even element;
+ *   block scales  : one unsigned e4m3 byte per 16 elements along K, stored in
+ *                   128-row x 4-group atoms of 512 bytes (byte (r%32)*16 +
+ *                   ((r%128)/32)*4 + g%4 of atom (r/128)*ceil(K/64) + g/4);
+ *   global scales : one fp32 per tensor (weight_scale_2, input_scale);
+ *   bf16          : uint16_t bit patterns.
+ */
+#ifndef Q4T_MOE_B200_H_
+#define Q4T_MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  Q4T_OK = 0,
+  Q4T_ERR_INVALID = -1,    /* bad dimensions or null pointers            */
+  Q4T_ERR_WORKSPACE = -2,  /* workspace too small                        */
+  Q4T_ERR_CUDA = -3,       /* a CUDA call failed                         */
+  Q4T_ERR_DEVICE = -4,     /* no sm_100 device / driver entry point      */
+  Q4T_ERR_KERNEL = -5      /* a kernel reported a bounded wait that ran out */
+} q4t_status;
+
+/* Message of the calling thread's last failing call ("" if none). */
+const char* q4t_last_error(void);
+/* Library version string. */
+const char* q4t_version(void);
+
+/* One layer's routed-expert weights on the device: the POD image of
+ * q4t::quant::MoEWeightLayout (include/q4t/quant/moe_weights.h:43-109).
+ * Expert e's gate/up codes start at gu_packed + e*moe_is*hs (gate rows, then
+ * up rows), its gate/up scale block at gu_sf + e*q4t_sf_buffer_size(2*moe_is,
+ * hs); likewise dn_packed + e*hs*moe_is/2 and dn_sf.                         */
+typedef struct {
+  int32_t E, hs, moe_is;
+  int32_t slot_mode;             /* carried for the host shim; not interpreted */
+  const uint8_t* gu_packed;
+  const uint8_t* gu_sf;
+  const uint8_t* dn_packed;
+  const uint8_t* dn_sf;
+  const float* gu_w_scale2;      /* [E] device */
+  const float* gu_input_scale;   /* [E] device */
+  const float* dn_w_scale2;      /* [E] device */
+  const float* dn_input_scale;   /* [E] device */
+} q4t_routed_weights;
+
+/* Router and shared-expert BF16 weights on the device: the POD image of
+ * q4t::model::MoEExtraWeights (include/q4t/model/moe.h:39-56), without the
+ * optional FP8 shadows.                                                       */
+typedef struct {
+  int32_t E, hs, shared_is;
+  const uint16_t* gate;               /* [E, hs]            */
+  const uint16_t* shared_gu;          /* [2*shared_is, hs]  */
+  const uint16_t* shared_down;        /* [hs, shared_is]    */
+  const uint16_t* shared_gate_scalar; /* [hs]               */
+} q4t_extra_weights;
+
+/* ---- layout helpers: SfNumGtiles / SfBufferSize / SfOffset
+ *      (include/q4t/quant/swizzle.h:34-57)                                   */
+int32_t q4t_sf_num_gtiles(int32_t K);
+size_t q4t_sf_buffer_size(int32_t rows, int32_t K);
+size_t q4t_sf_offset(int32_t row, int32_t group, int32_t num_g_tiles);
+
+/* ---- host-side packer: the per-expert body of LoadMoEWeights
+ * (src/quant/moe_weights.cpp:163-291).  Copies one expert's checkpoint tensors
+ * (gate/up/down codes unchanged; gate then up scale rows concatenated and
+ * swizzled; down scales swizzled) into HOST staging images of the device
+ * layout.  gate_w/up_w: [moe_is, hs/2]; down_w: [hs, moe_is/2]; *_s row-major
+ * e4m3 [rows, K/16].  The four destination pointers address expert e's slice.
+ * Enforces the loader's divisibility rules (moe_weights.cpp:49-57).           */
+int32_t q4t_pack_expert_host(const uint8_t* gate_w, const uint8_t* up_w,
+                             const uint8_t* down_w, const uint8_t* gate_s,
+                             const uint8_t* up_s, const uint8_t* down_s,
+                             int32_t hs, int32_t moe_is, uint8_t* gu_packed_e,
+                             uint8_t* gu_sf_e, uint8_t* dn_packed_e,
+                             uint8_t* dn_sf_e);
+
+/* ---- QuantizeActivationToFp4Async (include/q4t/quant/act_quant.h:30-34,
+ * src/quant/act_quant.cu:47-108).  bf16 [M,K] -> codes [M,K/2] + swizzled
+ * scales (>= q4t_sf_buffer_size(M,K) bytes; only bytes of real rows/groups
+ * are written).  K % 16 == 0.                                                */
+int32_t q4t_quantize_activation_fp4(const uint16_t* bf16, uint8_t* packed_out,
+                                    uint8_t* sf_out, int32_t M, int32_t K,
+                                    float global_scale, void* stream);
+
+/* ---- DequantFp4ToBf16Async (include/q4t/quant/dequant.h:22-25,
+ * src/quant/dequant.cu:31-71).  Row-major (not swizzled) scales.             */
+int32_t q4t_dequant_fp4_to_bf16(const uint8_t* packed, const uint8_t* group_scale,
+                                uint16_t* bf16_out, float inv_global_scale,
+                                int32_t N, int32_t K, void* stream);
+
+/* ---- Fp4Gemm<OutT> (include/q4t/quant/fp4_gemm.h:58-213): out[M,N] =
+ * (inv_w_global*inv_a_global) * A[M,K] . W[N,K]^T with swizzled block scales
+ * on both operands.  out_is_bf16 selects uint16_t (bf16) or float output.
+ * N % 128 == 0, K % 64 == 0.  The reference's cuBLASLt workspace arguments are
+ * accepted by the C++ shim and ignored.                                       */
+int32_t q4t_fp4_gemm(const uint8_t* w_packed, const uint8_t* w_sf,
+                     const uint8_t* a_packed, const uint8_t* a_sf, void* out,
+                     int32_t out_is_bf16, int32_t M, int32_t N, int32_t K,
+                     float inv_w_global, float inv_a_global, void* stream);
+
+/* ---- RouterTopkKernel (src/model/moe.cu:134-212): logits bf16 [T,E] ->
+ * ids int32 [T,k], weights fp32 [T,k]; selection by (value desc, id asc),
+ * softmax over the selected k in selection order.  E <= 512, k <= 16.        */
+int32_t q4t_router_topk(const uint16_t* logits, int32_t* expert_ids,
+                        float* router_w, int32_t T, int32_t E, int32_t k,
+                        void* stream);
+
+/* ---- Bf16Gemm (include/q4t/model/linear.h:103-180): y[M,N] = bf16(x[M,K] .
+ * w[N,K]^T).  For M <= 8 the accumulation order is the reference's warp-per-
+ * output GEMV order (src/model/gemv.cu:56-119), bit for bit; larger M runs on
+ * the tensor cores (order unspecified, as with the reference's library call).
+ * N % 128 == 0 and K % 64 == 0 for M > 8; K % 8 == 0 otherwise.               */
+int32_t q4t_bf16_linear(const uint16_t* x, const uint16_t* w, uint16_t* y,
+                        int32_t M, int32_t N, int32_t K, void* stream);
+
+/* ---- MoEWorkspace::RequiredBytes (include/q4t/quant/moe_gemm.h:34-53).
+ * The first four regions keep the reference's order and sizes (a_packed,
+ * a_sf, gu_out, dn_out); this implementation's routing tables and tile-local
+ * scale blocks follow them, so the total is larger than the reference's.      */
+size_t q4t_moe_routed_workspace_bytes(int32_t M, int32_t k, int32_t hs,
+                                      int32_t moe_is, int32_t E);
+/* Byte offsets of the regions inside a routed workspace.  Rows of the
+ * expert-grouped buffers are cut into row tiles of at most 128 rows that
+ * never span two experts; scale bytes of grouped rows live in tile-local
+ * atoms: tile t, scale tile g/4 at (t*ceil(K/64) + g/4)*512, row index inside
+ * the atom = row - tile_row0[t].                                              */
+typedef struct {
+  size_t a_packed, a_sf, gu_out, dn_out;   /* reference regions (a_sf unused)  */
+  size_t counts;                           /* int32 [E]   rows per expert      */
+  size_t offsets;                          /* int32 [E+1] first grouped row    */
+  size_t row_of_flat;                      /* int32 [M*k] grouped row of (token,slot), -1 if skipped */
+  size_t flat_of_row;                      /* int32 [M*k] inverse map          */
+  size_t row_tile;                         /* int32 [M*k] row tile of a grouped row */
+  size_t ntiles;                           /* int32 [1]   number of row tiles  */
+  size_t tile_expert, tile_row0, tile_nrows; /* int32 [max_tiles]              */
+  size_t a_sf_tiles;                       /* input scales, tile-local atoms   */
+  size_t inter_packed;                     /* [M*k, moe_is/2] intermediate codes */
+  size_t inter_sf_tiles;                   /* intermediate scales, tile-local  */
+  size_t status;                           /* int32 [4] kernel status words    */
+  size_t max_tiles;                        /* capacity of the tile tables      */
+  size_t total;
+} q4t_routed_ws_layout;
+int32_t q4t_moe_routed_workspace_layout(int32_t M, int32_t k, int32_t hs,
+                                        int32_t moe_is, int32_t E,
+                                        q4t_routed_ws_layout* out);
+
+/* ---- MoERoutedForward (include/q4t/quant/moe_gemm.h:55-74,
+ * src/quant/moe_gemm.cu:314-621).  y fp32 [M,hs] must be zeroed by the caller
+ * and is accumulated into.  After the call the workspace's dn_out region
+ * holds the bf16 down-projection rows in grouped order (expert ascending,
+ * then (token,slot) ascending) and row_of_flat maps (token,slot) to its row.
+ * Expert ids outside [0,E) are skipped.  flags: bit 0 = also materialise the
+ * bf16 gate/up outputs in gu_out (parity/debug; slower).                      */
+int32_t q4t_moe_routed_forward(const uint16_t* x, const int32_t* expert_ids,
+                               const float* router_w, float* y,
+                               const q4t_routed_weights* weights,
+                               void* workspace, size_t workspace_bytes,
+                               int32_t M, int32_t k, uint32_t flags,
+                               void* stream);
+
+/* ---- MoEForwardWorkspaceBytes (include/q4t/model/moe.h:72-76,
+ * src/model/moe.cu:403-417).                                                  */
+size_t q4t_moe_forward_workspace_bytes(int32_t T, int32_t k, int32_t hs,
+                                       int32_t moe_is, int32_t shared_is,
+                                       int32_t E);
+/* Offsets of the regions MoEForward leaves readable (src/model/moe.cu:449-469):
+ * the routed workspace first, then logits, ids, router weights, routed fp32,
+ * shared gate/up, shared activation, shared down.                             */
+typedef struct {
+  size_t routed_ws, logits, expert_ids, router_w, routed, shared_gu,
+      shared_act, shared_down, total;
+} q4t_forward_ws_layout;
+int32_t q4t_moe_forward_workspace_layout(int32_t T, int32_t k, int32_t hs,
+                                         int32_t moe_is, int32_t shared_is,
+                                         int32_t E, q4t_forward_ws_layout* out);
+
+/* ---- MoEForward (include/q4t/model/moe.h:78-114, src/model/moe.cu:427-976):
+ * router logits + top-k, routed NVFP4 experts, BF16 shared expert, sigmoid-
+ * gated combine; y bf16 [T,hs], no residual add.  T <= 0 is a no-op; k must
+ * be in [1,16] ("k out of range"); a short workspace fails with "workspace
+ * too small".  fixed_ids (may be NULL) replaces the selected experts by a
+ * caller-supplied int32 [T,k] table while the weights are still the softmax of
+ * the current logits at those ids (the replay hook, moe.cu:214-237).          */
+int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
+                        const q4t_extra_weights* extra, uint16_t* y, int32_t T,
+                        int32_t k, void* workspace, size_t workspace_bytes,
+                        const int32_t* fixed_ids, uint32_t flags, void* stream);
+
+/* Reads the kernel status words of a workspace after the stream has been
+ * synchronised by the caller: 0 = clean, otherwise a bounded device-side wait
+ * ran out (the output is then undefined).  Copies with cudaMemcpy.            */
+int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k,
+                                 int32_t hs, int32_t moe_is, int32_t E);
+
+/* ---- device self-checks used by the GPU tests (no reference counterpart):
+ * sweep float bit patterns [first, first+count) through the kernels' hardware
+ * encoders and through a compare-chain restatement of format.h and return the
+ * number of disagreements in *mismatches (host pointer).  which: 0 = e2m1,
+ * 1 = ue4m3 (non-negative inputs only).  Synchronises the stream.             */
+int32_t q4t_selftest_encoders(int32_t which, uint64_t first, uint64_t count,
+                              uint64_t* mismatches, uint32_t* first_bad,
+                              void* stream);
+/* Exact-arithmetic NVFP4 GEMM on CUDA cores (fp32 out = float(exact * alpha),
+ * alpha = inv_w_global * inv_a_global); the device twin of the CPU oracle's
+ * exact mode, for checking the tensor-core path at sizes the CPU cannot
+ * reach.  Same operand layout as q4t_fp4_gemm, any N, K % 16 == 0.            */
+int32_t q4t_fp4_gemm_check(const uint8_t* w_packed, const uint8_t* w_sf,
+                           const uint8_t* a_packed, const uint8_t* a_sf,
+                           float* out, int32_t M, int32_t N, int32_t K,
+                           float inv_w_global, float inv_a_global, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q4T_MOE_B200_H_ */

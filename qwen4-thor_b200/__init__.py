@@ -1,0 +1,288 @@
+"""Python binding of libq4t_moe_b200.so (C ABI in include/q4t_moe_b200.h).
+
+PyTorch is used only for plumbing: device buffers, streams and (in the
+benchmark) torch.distributed.  Every compute call goes through the C ABI into
+the hand-written sm_100a kernels; there is no eager/PyTorch fallback, and the
+calls raise if the shared library or a B200-class device is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libq4t_moe_b200.so")
+
+
+class Q4TError(RuntimeError):
+    pass
+
+
+class RoutedWeights(C.Structure):
+    """q4t_routed_weights: POD image of MoEWeightLayout."""
+    _fields_ = [("E", C.c_int32), ("hs", C.c_int32), ("moe_is", C.c_int32), ("slot_mode", C.c_int32),
+                ("gu_packed", C.c_void_p), ("gu_sf", C.c_void_p), ("dn_packed", C.c_void_p),
+                ("dn_sf", C.c_void_p), ("gu_w_scale2", C.c_void_p), ("gu_input_scale", C.c_void_p),
+                ("dn_w_scale2", C.c_void_p), ("dn_input_scale", C.c_void_p)]
+
+
+class ExtraWeights(C.Structure):
+    """q4t_extra_weights: POD image of MoEExtraWeights."""
+    _fields_ = [("E", C.c_int32), ("hs", C.c_int32), ("shared_is", C.c_int32),
+                ("gate", C.c_void_p), ("shared_gu", C.c_void_p), ("shared_down", C.c_void_p),
+                ("shared_gate_scalar", C.c_void_p)]
+
+
+class RoutedWsLayout(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in (
+        "a_packed", "a_sf", "gu_out", "dn_out", "counts", "offsets", "row_of_flat", "flat_of_row",
+        "row_tile", "ntiles", "tile_expert", "tile_row0", "tile_nrows", "a_sf_tiles", "inter_packed",
+        "inter_sf_tiles", "status", "max_tiles", "total")]
+
+
+class ForwardWsLayout(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in (
+        "routed_ws", "logits", "expert_ids", "router_w", "routed", "shared_gu", "shared_act",
+        "shared_down", "total")]
+
+
+EXPORTS = [
+    "q4t_last_error", "q4t_version", "q4t_sf_num_gtiles", "q4t_sf_buffer_size", "q4t_sf_offset",
+    "q4t_pack_expert_host", "q4t_quantize_activation_fp4", "q4t_dequant_fp4_to_bf16", "q4t_fp4_gemm",
+    "q4t_fp4_gemm_check", "q4t_router_topk", "q4t_bf16_linear", "q4t_moe_routed_workspace_bytes",
+    "q4t_moe_routed_workspace_layout", "q4t_moe_routed_forward", "q4t_moe_forward_workspace_bytes",
+    "q4t_moe_forward_workspace_layout", "q4t_moe_forward", "q4t_moe_workspace_status",
+    "q4t_selftest_encoders",
+]
+
+_lib = None
+
+
+def load():
+    """Loads the shared library (no device needed for this step)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise Q4TError(f"{LIB_PATH} is missing: build it with `python qwen4-thor_b200/build.py` "
+                       "(there is no fallback path)")
+    L = C.CDLL(LIB_PATH)
+    L.q4t_last_error.restype = C.c_char_p
+    L.q4t_version.restype = C.c_char_p
+    L.q4t_sf_num_gtiles.restype = C.c_int32
+    L.q4t_sf_buffer_size.restype = C.c_size_t
+    L.q4t_sf_buffer_size.argtypes = [C.c_int32, C.c_int32]
+    L.q4t_sf_offset.restype = C.c_size_t
+    L.q4t_sf_offset.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+    L.q4t_moe_routed_workspace_bytes.restype = C.c_size_t
+    L.q4t_moe_routed_workspace_bytes.argtypes = [C.c_int32] * 5
+    L.q4t_moe_forward_workspace_bytes.restype = C.c_size_t
+    L.q4t_moe_forward_workspace_bytes.argtypes = [C.c_int32] * 6
+    vp, i32, f32, u32, sz = C.c_void_p, C.c_int32, C.c_float, C.c_uint32, C.c_size_t
+    L.q4t_pack_expert_host.argtypes = [vp] * 6 + [i32, i32] + [vp] * 4
+    L.q4t_quantize_activation_fp4.argtypes = [vp, vp, vp, i32, i32, f32, vp]
+    L.q4t_dequant_fp4_to_bf16.argtypes = [vp, vp, vp, f32, i32, i32, vp]
+    L.q4t_fp4_gemm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, vp]
+    L.q4t_fp4_gemm_check.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, f32, f32, vp]
+    L.q4t_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    L.q4t_bf16_linear.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    L.q4t_moe_routed_workspace_layout.argtypes = [i32] * 5 + [C.POINTER(RoutedWsLayout)]
+    L.q4t_moe_routed_forward.argtypes = [vp, vp, vp, vp, C.POINTER(RoutedWeights), vp, sz, i32, i32, u32, vp]
+    L.q4t_moe_forward_workspace_layout.argtypes = [i32] * 6 + [C.POINTER(ForwardWsLayout)]
+    L.q4t_moe_forward.argtypes = [vp, C.POINTER(RoutedWeights), C.POINTER(ExtraWeights), vp, i32, i32,
+                                  vp, sz, vp, u32, vp]
+    L.q4t_moe_workspace_status.argtypes = [vp, i32, i32, i32, i32, i32]
+    L.q4t_selftest_encoders.argtypes = [i32, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64),
+                                        C.POINTER(C.c_uint32), vp]
+    _lib = L
+    return L
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise Q4TError(f"[{rc}] {load().q4t_last_error().decode()}")
+
+
+def _stream_ptr(stream=None):
+    import torch
+    s = torch.cuda.current_stream() if stream is None else stream
+    return C.c_void_p(s.cuda_stream)
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+# --------------------------------------------------------------------- layouts
+def routed_ws_layout(M, k, hs, moe_is, E) -> RoutedWsLayout:
+    L = RoutedWsLayout()
+    check(load().q4t_moe_routed_workspace_layout(M, k, hs, moe_is, E, C.byref(L)))
+    return L
+
+
+def forward_ws_layout(T, k, hs, moe_is, shared_is, E) -> ForwardWsLayout:
+    F = ForwardWsLayout()
+    check(load().q4t_moe_forward_workspace_layout(T, k, hs, moe_is, shared_is, E, C.byref(F)))
+    return F
+
+
+# ------------------------------------------------------------- device weights
+class DeviceLayer:
+    """One MoE layer resident in HBM, in the reference's device layout.
+
+    Built from any object with the oracle Layer's attributes (numpy arrays) or
+    directly from torch CUDA tensors."""
+
+    ROUTED = ("gu_packed", "gu_sf", "dn_packed", "dn_sf", "gu_w_scale2", "gu_input_scale",
+              "dn_w_scale2", "dn_input_scale")
+    EXTRA = ("gate", "shared_gu", "shared_down", "shared_gate_scalar")
+
+    def __init__(self, E, hs, moe_is, shared_is, tensors: dict):
+        self.E, self.hs, self.moe_is, self.shared_is = E, hs, moe_is, shared_is
+        self.t = tensors  # keeps the device buffers alive
+        self.routed = RoutedWeights(E, hs, moe_is, 0, *[self._p(n) for n in self.ROUTED])
+        self.extra = ExtraWeights(E, hs, shared_is, *[self._p(n) for n in self.EXTRA])
+
+    def _p(self, name):
+        t = self.t.get(name)
+        return None if t is None else t.data_ptr()
+
+    @classmethod
+    def from_host(cls, layer, device="cuda"):
+        import numpy as np
+        import torch
+        tensors = {}
+        for n in cls.ROUTED + cls.EXTRA:
+            a = getattr(layer, n, None)
+            if a is None:
+                continue
+            if a.dtype == np.uint16:   # bf16 bit patterns
+                tensors[n] = torch.from_numpy(a.view(np.int16)).to(device)
+            else:
+                tensors[n] = torch.from_numpy(a).to(device)
+        return cls(layer.E, layer.hs, layer.moe_is, layer.shared_is, tensors)
+
+
+# ------------------------------------------------------------------ operators
+def quantize_activation_fp4(x_bf16, global_scale: float, stream=None):
+    """x: CUDA tensor [M, K] of bf16 (torch.bfloat16 or int16 bit patterns)."""
+    import torch
+    M, K = x_bf16.shape
+    packed = torch.empty((M, K // 2), dtype=torch.uint8, device=x_bf16.device)
+    sf = torch.zeros(load().q4t_sf_buffer_size(M, K), dtype=torch.uint8, device=x_bf16.device)
+    check(load().q4t_quantize_activation_fp4(_ptr(x_bf16), _ptr(packed), _ptr(sf), M, K,
+                                             float(global_scale), _stream_ptr(stream)))
+    return packed, sf
+
+
+def dequant_fp4_to_bf16(packed, group_scale, inv_global: float, stream=None):
+    import torch
+    N, K2 = packed.shape
+    out = torch.empty((N, K2 * 2), dtype=torch.bfloat16, device=packed.device)
+    check(load().q4t_dequant_fp4_to_bf16(_ptr(packed), _ptr(group_scale), _ptr(out), float(inv_global),
+                                         N, K2 * 2, _stream_ptr(stream)))
+    return out
+
+
+def fp4_gemm(w_packed, w_sf, a_packed, a_sf, M, N, K, inv_w, inv_a, out_bf16=False, check_kernel=False,
+             stream=None):
+    import torch
+    dt = torch.bfloat16 if out_bf16 else torch.float32
+    out = torch.empty((M, N), dtype=dt, device=w_packed.device)
+    if check_kernel:
+        check(load().q4t_fp4_gemm_check(_ptr(w_packed), _ptr(w_sf), _ptr(a_packed), _ptr(a_sf), _ptr(out),
+                                        M, N, K, float(inv_w), float(inv_a), _stream_ptr(stream)))
+    else:
+        check(load().q4t_fp4_gemm(_ptr(w_packed), _ptr(w_sf), _ptr(a_packed), _ptr(a_sf), _ptr(out),
+                                  1 if out_bf16 else 0, M, N, K, float(inv_w), float(inv_a),
+                                  _stream_ptr(stream)))
+    return out
+
+
+def router_topk(logits_bf16, k: int, stream=None):
+    import torch
+    T, E = logits_bf16.shape
+    ids = torch.empty((T, k), dtype=torch.int32, device=logits_bf16.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits_bf16.device)
+    check(load().q4t_router_topk(_ptr(logits_bf16), _ptr(ids), _ptr(w), T, E, k, _stream_ptr(stream)))
+    return ids, w
+
+
+def bf16_linear(x, w, stream=None):
+    import torch
+    M, K = x.shape
+    N = w.shape[0]
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    check(load().q4t_bf16_linear(_ptr(x), _ptr(w), _ptr(y), M, N, K, _stream_ptr(stream)))
+    return y
+
+
+class RoutedForward:
+    """MoERoutedForward with a caller-owned workspace (allocated once here)."""
+
+    def __init__(self, layer: DeviceLayer, M: int, k: int, device="cuda"):
+        import torch
+        self.layer, self.M, self.k = layer, M, k
+        self.layout = routed_ws_layout(M, k, layer.hs, layer.moe_is, layer.E)
+        self.ws = torch.empty(self.layout.total, dtype=torch.uint8, device=device)
+
+    def __call__(self, x, ids, rw, y, flags=0, stream=None):
+        check(load().q4t_moe_routed_forward(_ptr(x), _ptr(ids), _ptr(rw), _ptr(y), C.byref(self.layer.routed),
+                                            _ptr(self.ws), self.layout.total, self.M, self.k, flags,
+                                            _stream_ptr(stream)))
+        return y
+
+    def region(self, name, dtype, count):
+        import torch
+        off = getattr(self.layout, name)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        return self.ws[off:off + nbytes].view(dtype)
+
+    def status(self):
+        import torch
+        torch.cuda.synchronize()
+        check(load().q4t_moe_workspace_status(_ptr(self.ws), self.M, self.k, self.layer.hs,
+                                              self.layer.moe_is, self.layer.E))
+
+
+class MoEForward:
+    """MoEForward (router + routed experts + shared expert + gated combine)."""
+
+    def __init__(self, layer: DeviceLayer, T: int, k: int, device="cuda"):
+        import torch
+        self.layer, self.T, self.k = layer, T, k
+        self.layout = forward_ws_layout(T, k, layer.hs, layer.moe_is, layer.shared_is, layer.E)
+        self.routed_layout = routed_ws_layout(T, k, layer.hs, layer.moe_is, layer.E)
+        self.ws = torch.empty(self.layout.total, dtype=torch.uint8, device=device)
+
+    def __call__(self, x, y, fixed_ids=None, flags=0, stream=None):
+        check(load().q4t_moe_forward(_ptr(x), C.byref(self.layer.routed), C.byref(self.layer.extra), _ptr(y),
+                                     self.T, self.k, _ptr(self.ws), self.layout.total, _ptr(fixed_ids),
+                                     flags, _stream_ptr(stream)))
+        return y
+
+    def region(self, name, dtype, count):
+        import torch
+        off = getattr(self.layout, name)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        return self.ws[off:off + nbytes].view(dtype)
+
+    def routed_region(self, name, dtype, count):
+        import torch
+        off = self.layout.routed_ws + getattr(self.routed_layout, name)
+        nbytes = count * torch.empty((), dtype=dtype).element_size()
+        return self.ws[off:off + nbytes].view(dtype)
+
+    def status(self):
+        import torch
+        torch.cuda.synchronize()
+        ws = self.ws[self.layout.routed_ws:]
+        check(load().q4t_moe_workspace_status(_ptr(ws), self.T, self.k, self.layer.hs, self.layer.moe_is,
+                                              self.layer.E))
+
+
+def selftest_encoders(which: int, first: int, count: int):
+    m = C.c_uint64(0)
+    b = C.c_uint32(0)
+    check(load().q4t_selftest_encoders(which, first, count, C.byref(m), C.byref(b), _stream_ptr()))
+    return m.value, b.value

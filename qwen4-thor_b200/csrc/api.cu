@@ -1,0 +1,589 @@
+// C ABI of libq4t_moe_b200 (include/q4t_moe_b200.h): argument checking,
+// workspace carving, TMA descriptor construction and kernel sequencing.  All
+// device work goes to the caller's stream; nothing here synchronises except
+// the self-check and status helpers that say so.
+#include "../../include/q4t_moe_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "kernels.h"
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(int code, const std::string& msg) {
+  g_error = msg;
+  return code;
+}
+int fail_cuda(const char* what, cudaError_t e) {
+  g_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return Q4T_ERR_CUDA;
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  int num_sms = 0;
+  EncodeFn encode = nullptr;
+};
+constexpr int kMaxDevices = 16;
+DeviceState g_dev[kMaxDevices];
+std::mutex g_dev_mutex;
+
+// Per-device one-time set-up: architecture check, driver entry point for the
+// tensor-map encoder, shared-memory attribute of the GEMM kernels.
+int device_state(const DeviceState** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(Q4T_ERR_DEVICE, std::string("no CUDA device: ") + cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(Q4T_ERR_DEVICE, "device index out of range");
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceState& s = g_dev[dev];
+  if (!s.ready) {
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) return fail_cuda("cudaGetDeviceProperties", e);
+    if (prop.major != 10)
+      return fail(Q4T_ERR_DEVICE, "libq4t_moe_b200 needs an sm_100 device (found sm_" +
+                                      std::to_string(prop.major) + std::to_string(prop.minor) + ")");
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess)
+      return fail(Q4T_ERR_DEVICE, "cuTensorMapEncodeTiled entry point unavailable");
+    if ((e = q4t::gemm_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+    s.encode = reinterpret_cast<EncodeFn>(fn);
+    s.num_sms = prop.multiProcessorCount;
+    s.ready = true;
+  }
+  *out = &s;
+  return Q4T_OK;
+}
+
+// 2-D K-major tensor map whose box is 128 bytes x 128 rows, 128-byte swizzled.
+int make_tmap(const DeviceState* ds, CUtensorMap* tm, bool bf16, const void* base, uint64_t inner_elems,
+              uint64_t rows, uint64_t pitch_bytes) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (pitch_bytes & 15u))
+    return fail(Q4T_ERR_INVALID, "operand base and row pitch must be 16-byte aligned");
+  cuuint64_t dims[2] = {inner_elems, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {bf16 ? 64u : 128u, 128u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = ds->encode(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(Q4T_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+  return Q4T_OK;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+size_t sf_buffer_size(int rows, int K) {
+  return static_cast<size_t>((rows + 127) / 128) * static_cast<size_t>((K / 16 + 3) / 4) * 512;
+}
+
+void routed_layout(int M, int k, int hs, int is, int E, q4t_routed_ws_layout* L) {
+  const size_t R = static_cast<size_t>(M) * k;
+  const size_t max_tiles = R / 128 + (R < static_cast<size_t>(E) ? R : static_cast<size_t>(E)) + 1;
+  const size_t nblk = (R + q4t::kPlanChunk - 1) / q4t::kPlanChunk;
+  size_t off = 0;
+  auto take = [&](size_t bytes, size_t align = 256) {
+    off = align_up(off, align);
+    const size_t at = off;
+    off += bytes;
+    return at;
+  };
+  // reference regions, packed back to back as in MoEWorkspace::Init
+  L->a_packed = take(R * (hs / 2), 1);
+  L->a_sf = take(sf_buffer_size(static_cast<int>(R), hs), 1);
+  L->gu_out = take(R * 2 * is * 2, 1);
+  L->dn_out = take(R * hs * 2, 1);
+  L->counts = take(static_cast<size_t>(E) * 4);
+  L->offsets = take(static_cast<size_t>(E + 1) * 4);
+  L->row_of_flat = take(R * 4);
+  L->flat_of_row = take(R * 4);
+  L->row_tile = take(R * 4);
+  L->ntiles = take(256);
+  L->tile_expert = take(max_tiles * 4);
+  L->tile_row0 = take(max_tiles * 4);
+  L->tile_nrows = take(max_tiles * 4);
+  L->a_sf_tiles = take(max_tiles * static_cast<size_t>((hs + 63) / 64) * 512);
+  L->inter_packed = take(R * (is / 2));
+  L->inter_sf_tiles = take(max_tiles * static_cast<size_t>((is + 63) / 64) * 512);
+  L->status = take(256);
+  // planning scratch that callers never read: tile_off [E+1], blk_counts [nblk, E]
+  take(static_cast<size_t>(E + 1) * 4);
+  take(nblk * static_cast<size_t>(E) * 4);
+  L->max_tiles = max_tiles;
+  L->total = align_up(off, 256);
+}
+
+void forward_layout(int T, int k, int hs, int is, int sis, int E, q4t_forward_ws_layout* F) {
+  q4t_routed_ws_layout R;
+  routed_layout(T, k, hs, is, E, &R);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    off = align_up(off, 256);
+    const size_t at = off;
+    off += bytes;
+    return at;
+  };
+  F->routed_ws = take(R.total);
+  F->logits = take(static_cast<size_t>(T) * E * 2);
+  F->expert_ids = take(static_cast<size_t>(T) * k * 4);
+  F->router_w = take(static_cast<size_t>(T) * k * 4);
+  F->routed = take(static_cast<size_t>(T) * hs * 4);
+  F->shared_gu = take(static_cast<size_t>(T) * 2 * sis * 2);
+  F->shared_act = take(static_cast<size_t>(T) * sis * 2);
+  F->shared_down = take(static_cast<size_t>(T) * hs * 2);
+  F->total = align_up(off, 256);
+}
+
+bool routed_dims_ok(int E, int hs, int is) {
+  // hs and 2*is multiples of 128 (per-expert scale blocks), is a multiple of
+  // 128 (gate and up rows of one tile come from whole scale atoms), E within
+  // the planning kernel's single-block scan.
+  return E > 0 && E <= 1024 && hs > 0 && is > 0 && hs % 128 == 0 && is % 128 == 0;
+}
+
+struct RoutedPtrs {
+  q4t_routed_ws_layout L;
+  uint8_t* base;
+  template <typename T>
+  T* at(size_t off) const { return reinterpret_cast<T*>(base + off); }
+};
+
+// Steps shared by the routed entry point and the full layer: permutation,
+// gather-quantise, gate/up GEMM with fused SwiGLU + requantisation, down GEMM.
+int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids,
+                    const q4t_routed_weights* w, const RoutedPtrs& P, int M, int k, uint32_t flags,
+                    cudaStream_t st) {
+  const int E = w->E, hs = w->hs, is = w->moe_is;
+  const int R = M * k;
+  const q4t_routed_ws_layout& L = P.L;
+  cudaError_t e;
+  if ((e = cudaMemsetAsync(P.at<int32_t>(L.status), 0, 16, st)) != cudaSuccess) return fail_cuda("memset status", e);
+
+  q4t::PlanTables pt;
+  pt.counts = P.at<int32_t>(L.counts);
+  pt.offsets = P.at<int32_t>(L.offsets);
+  pt.row_of_flat = P.at<int32_t>(L.row_of_flat);
+  pt.flat_of_row = P.at<int32_t>(L.flat_of_row);
+  pt.row_tile = P.at<int32_t>(L.row_tile);
+  pt.ntiles = P.at<int32_t>(L.ntiles);
+  pt.tile_expert = P.at<int32_t>(L.tile_expert);
+  pt.tile_row0 = P.at<int32_t>(L.tile_row0);
+  pt.tile_nrows = P.at<int32_t>(L.tile_nrows);
+  pt.tile_off = P.at<int32_t>(align_up(L.status + 256, 256));
+  pt.blk_counts = P.at<int32_t>(align_up(align_up(L.status + 256, 256) + static_cast<size_t>(E + 1) * 4, 256));
+  if ((e = q4t::launch_plan(ids, R, E, static_cast<int>(L.max_tiles), pt, st)) != cudaSuccess)
+    return fail_cuda("plan launch", e);
+
+  uint8_t* a_packed = P.at<uint8_t>(L.a_packed);
+  uint8_t* a_sf_tiles = P.at<uint8_t>(L.a_sf_tiles);
+  if ((e = q4t::launch_gather_quantize(x, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, ids,
+                                       w->gu_input_scale, pt.row_tile, pt.tile_row0, k, E, st)) != cudaSuccess)
+    return fail_cuda("gather-quantise launch", e);
+
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  // gate/up: A = grouped input codes [R, hs/2], B = all experts' gate|up rows
+  if ((rc = make_tmap(ds, &tm_a, false, a_packed, hs / 2, R, hs / 2)) != Q4T_OK) return rc;
+  if ((rc = make_tmap(ds, &tm_b, false, w->gu_packed, hs / 2, static_cast<uint64_t>(E) * 2 * is, hs / 2)) != Q4T_OK)
+    return rc;
+  q4t::GemmArgs g{};
+  g.K = hs;
+  g.n_tiles = is / 128;
+  g.n_per_tile = 128;
+  g.up_row_offset = is;
+  g.b_rows_per_group = 2 * is;
+  g.b_rows_valid = is;
+  g.ntiles_dev = pt.ntiles;
+  g.tile_expert = pt.tile_expert;
+  g.tile_row0 = pt.tile_row0;
+  g.tile_nrows = pt.tile_nrows;
+  g.total_rows = R;
+  g.sfa_tiles = a_sf_tiles;
+  g.sfb = w->gu_sf;
+  g.sfb_group_stride = sf_buffer_size(2 * is, hs);
+  g.out = P.at<uint8_t>(L.inter_packed);
+  g.ldo = is / 2;
+  g.alpha_w = w->gu_w_scale2;
+  g.alpha_a = w->gu_input_scale;
+  g.next_scale = w->dn_input_scale;
+  g.out_sf_tiles = P.at<uint8_t>(L.inter_sf_tiles);
+  g.gu_dump = (flags & 1u) ? P.at<uint16_t>(L.gu_out) : nullptr;
+  g.gu_dump_ld = 2 * is;
+  g.status = P.at<int32_t>(L.status);
+  if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, g, q4t::Epilogue::kSwigluQuant, ds->num_sms, st)) != cudaSuccess)
+    return fail_cuda("gate/up GEMM launch", e);
+
+  // down: A = intermediate codes [R, is/2], B = all experts' down rows
+  if ((rc = make_tmap(ds, &tm_a, false, P.at<uint8_t>(L.inter_packed), is / 2, R, is / 2)) != Q4T_OK) return rc;
+  if ((rc = make_tmap(ds, &tm_b, false, w->dn_packed, is / 2, static_cast<uint64_t>(E) * hs, is / 2)) != Q4T_OK)
+    return rc;
+  q4t::GemmArgs d{};
+  d.K = is;
+  d.n_tiles = (hs + 255) / 256;
+  d.n_per_tile = 256;
+  d.b_rows_per_group = hs;
+  d.b_rows_valid = hs;
+  d.ntiles_dev = pt.ntiles;
+  d.tile_expert = pt.tile_expert;
+  d.tile_row0 = pt.tile_row0;
+  d.tile_nrows = pt.tile_nrows;
+  d.total_rows = R;
+  d.sfa_tiles = P.at<uint8_t>(L.inter_sf_tiles);
+  d.sfb = w->dn_sf;
+  d.sfb_group_stride = sf_buffer_size(hs, is);
+  d.out = P.at<uint16_t>(L.dn_out);
+  d.ldo = hs;
+  d.alpha_w = w->dn_w_scale2;
+  d.alpha_a = w->dn_input_scale;
+  d.status = P.at<int32_t>(L.status);
+  if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, d, q4t::Epilogue::kStoreBf16, ds->num_sms, st)) != cudaSuccess)
+    return fail_cuda("down GEMM launch", e);
+  return Q4T_OK;
+}
+
+// y[M,N] = bf16(x . w^T): exact-order warp GEMV for M <= 8, tensor cores above.
+int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
+                    int K, cudaStream_t st) {
+  cudaError_t e;
+  if (M <= 8) {
+    if (K % 8) return fail(Q4T_ERR_INVALID, "K must be a multiple of 8");
+    if ((e = q4t::launch_small_m_linear(x, w, y, M, N, K, st)) != cudaSuccess) return fail_cuda("linear launch", e);
+    return Q4T_OK;
+  }
+  if (K % 16 || N % 16) return fail(Q4T_ERR_INVALID, "K and N must be multiples of 16");
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = make_tmap(ds, &ta, true, x, K, M, static_cast<uint64_t>(K) * 2)) != Q4T_OK) return rc;
+  if ((rc = make_tmap(ds, &tb, true, w, K, N, static_cast<uint64_t>(K) * 2)) != Q4T_OK) return rc;
+  q4t::GemmArgs g{};
+  g.K = K;
+  g.n_tiles = (N + 255) / 256;
+  g.n_per_tile = 256;
+  g.b_rows_valid = N;
+  g.ntiles_host = (M + 127) / 128;
+  g.total_rows = M;
+  g.out = y;
+  g.ldo = N;
+  g.alpha_const = 1.0f;
+  if ((e = q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kStoreBf16, ds->num_sms, st)) != cudaSuccess)
+    return fail_cuda("bf16 GEMM launch", e);
+  return Q4T_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* q4t_last_error(void) { return g_error.c_str(); }
+const char* q4t_version(void) { return "q4t-moe-b200 0.1 (sm_100a)"; }
+
+int32_t q4t_sf_num_gtiles(int32_t K) { return (K / 16 + 3) / 4; }
+size_t q4t_sf_buffer_size(int32_t rows, int32_t K) { return sf_buffer_size(rows, K); }
+size_t q4t_sf_offset(int32_t row, int32_t group, int32_t num_g_tiles) {
+  return static_cast<size_t>(row % 32) * 16 + static_cast<size_t>((row % 128) / 32) * 4 + group % 4 +
+         static_cast<size_t>(group / 4) * 512 + static_cast<size_t>(row / 128) * num_g_tiles * 512;
+}
+
+int32_t q4t_pack_expert_host(const uint8_t* gate_w, const uint8_t* up_w, const uint8_t* down_w,
+                             const uint8_t* gate_s, const uint8_t* up_s, const uint8_t* down_s,
+                             int32_t hs, int32_t moe_is, uint8_t* gu_packed_e, uint8_t* gu_sf_e,
+                             uint8_t* dn_packed_e, uint8_t* dn_sf_e) {
+  if (hs <= 0 || moe_is <= 0) return fail(Q4T_ERR_INVALID, "invalid MoE dims");
+  if (hs % 32 || moe_is % 32) return fail(Q4T_ERR_INVALID, "hs and moe_is must be multiples of 32 (FP4 GEMM)");
+  if ((2 * moe_is) % 128 || hs % 128)
+    return fail(Q4T_ERR_INVALID, "2*moe_is and hs must be multiples of 128 (per-expert SF blocks)");
+  if (!gate_w || !up_w || !down_w || !gate_s || !up_s || !down_s || !gu_packed_e || !gu_sf_e || !dn_packed_e ||
+      !dn_sf_e)
+    return fail(Q4T_ERR_INVALID, "null tensor pointer");
+  const size_t gw = static_cast<size_t>(moe_is) * (hs / 2);
+  std::memcpy(gu_packed_e, gate_w, gw);
+  std::memcpy(gu_packed_e + gw, up_w, gw);
+  std::memcpy(dn_packed_e, down_w, static_cast<size_t>(hs) * (moe_is / 2));
+  const int ggu = hs / 16, gdn = moe_is / 16;
+  const int ntgu = (ggu + 3) / 4, ntdn = (gdn + 3) / 4;
+  std::memset(gu_sf_e, 0, sf_buffer_size(2 * moe_is, hs));
+  std::memset(dn_sf_e, 0, sf_buffer_size(hs, moe_is));
+  for (int r = 0; r < 2 * moe_is; ++r) {
+    const uint8_t* src = r < moe_is ? gate_s + static_cast<size_t>(r) * ggu
+                                    : up_s + static_cast<size_t>(r - moe_is) * ggu;
+    for (int g = 0; g < ggu; ++g) gu_sf_e[q4t_sf_offset(r, g, ntgu)] = src[g];
+  }
+  for (int r = 0; r < hs; ++r)
+    for (int g = 0; g < gdn; ++g) dn_sf_e[q4t_sf_offset(r, g, ntdn)] = down_s[static_cast<size_t>(r) * gdn + g];
+  return Q4T_OK;
+}
+
+int32_t q4t_quantize_activation_fp4(const uint16_t* bf16, uint8_t* packed_out, uint8_t* sf_out, int32_t M,
+                                    int32_t K, float global_scale, void* stream) {
+  if (M < 0 || K <= 0 || K % 16) return fail(Q4T_ERR_INVALID, "K must be a positive multiple of 16");
+  if (M == 0) return Q4T_OK;
+  if (!bf16 || !packed_out || !sf_out) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (reinterpret_cast<uintptr_t>(bf16) & 15u) return fail(Q4T_ERR_INVALID, "input must be 16-byte aligned");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaError_t e = q4t::launch_quantize(bf16, packed_out, sf_out, M, K, global_scale, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("quantise launch", e);
+}
+
+int32_t q4t_dequant_fp4_to_bf16(const uint8_t* packed, const uint8_t* group_scale, uint16_t* bf16_out,
+                                float inv_global_scale, int32_t N, int32_t K, void* stream) {
+  if (N < 0 || K <= 0 || K % 16) return fail(Q4T_ERR_INVALID, "K must be a positive multiple of 16");
+  if (N == 0) return Q4T_OK;
+  if (!packed || !group_scale || !bf16_out) return fail(Q4T_ERR_INVALID, "null pointer");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaError_t e = q4t::launch_dequant(packed, group_scale, bf16_out, inv_global_scale, N, K,
+                                      static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("dequant launch", e);
+}
+
+int32_t q4t_fp4_gemm(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t* a_packed,
+                     const uint8_t* a_sf, void* out, int32_t out_is_bf16, int32_t M, int32_t N, int32_t K,
+                     float inv_w_global, float inv_a_global, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(Q4T_ERR_INVALID, "invalid GEMM dims");
+  if (K % 64 || N % 16) return fail(Q4T_ERR_INVALID, "K must be a multiple of 64 and N of 16");
+  if (!w_packed || !w_sf || !a_packed || !a_sf || !out) return fail(Q4T_ERR_INVALID, "null pointer");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  CUtensorMap ta, tb;
+  if ((rc = make_tmap(ds, &ta, false, a_packed, K / 2, M, K / 2)) != Q4T_OK) return rc;
+  if ((rc = make_tmap(ds, &tb, false, w_packed, K / 2, N, K / 2)) != Q4T_OK) return rc;
+  q4t::GemmArgs g{};
+  g.K = K;
+  g.n_tiles = (N + 255) / 256;
+  g.n_per_tile = 256;
+  g.b_rows_valid = N;
+  g.ntiles_host = (M + 127) / 128;
+  g.total_rows = M;
+  g.sfa_tiles = a_sf;
+  g.sfb = w_sf;
+  g.out = out;
+  g.ldo = N;
+  g.alpha_const = inv_w_global * inv_a_global;  // include/q4t/quant/fp4_gemm.h:205
+  cudaError_t e = q4t::launch_gemm_nvf4(ta, tb, g, out_is_bf16 ? q4t::Epilogue::kStoreBf16 : q4t::Epilogue::kStoreF32,
+                                        ds->num_sms, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("NVFP4 GEMM launch", e);
+}
+
+int32_t q4t_fp4_gemm_check(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t* a_packed,
+                           const uint8_t* a_sf, float* out, int32_t M, int32_t N, int32_t K,
+                           float inv_w_global, float inv_a_global, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % 16) return fail(Q4T_ERR_INVALID, "invalid GEMM dims");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaError_t e = q4t::launch_fp4_gemm_check(w_packed, w_sf, a_packed, a_sf, out, M, N, K,
+                                             inv_w_global * inv_a_global, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("check GEMM launch", e);
+}
+
+int32_t q4t_router_topk(const uint16_t* logits, int32_t* expert_ids, float* router_w, int32_t T, int32_t E,
+                        int32_t k, void* stream) {
+  if (T <= 0) return Q4T_OK;
+  if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");
+  if (E <= 0 || E > 512 || k > E) return fail(Q4T_ERR_INVALID, "E out of range (1..512, >= k)");
+  if (!logits || !expert_ids || !router_w) return fail(Q4T_ERR_INVALID, "null pointer");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaError_t e = q4t::launch_topk(logits, nullptr, expert_ids, router_w, T, E, k, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("topk launch", e);
+}
+
+int32_t q4t_bf16_linear(const uint16_t* x, const uint16_t* w, uint16_t* y, int32_t M, int32_t N, int32_t K,
+                        void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(Q4T_ERR_INVALID, "invalid GEMM dims");
+  if (!x || !w || !y) return fail(Q4T_ERR_INVALID, "null pointer");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  return run_bf16_linear(ds, x, w, y, M, N, K, static_cast<cudaStream_t>(stream));
+}
+
+size_t q4t_moe_routed_workspace_bytes(int32_t M, int32_t k, int32_t hs, int32_t moe_is, int32_t E) {
+  if (M <= 0 || k <= 0 || hs <= 0 || moe_is <= 0 || E <= 0) return 0;
+  q4t_routed_ws_layout L;
+  routed_layout(M, k, hs, moe_is, E, &L);
+  return L.total;
+}
+
+int32_t q4t_moe_routed_workspace_layout(int32_t M, int32_t k, int32_t hs, int32_t moe_is, int32_t E,
+                                        q4t_routed_ws_layout* out) {
+  if (M <= 0 || k <= 0 || hs <= 0 || moe_is <= 0 || E <= 0 || !out) return fail(Q4T_ERR_INVALID, "invalid MoE forward dims");
+  routed_layout(M, k, hs, moe_is, E, out);
+  return Q4T_OK;
+}
+
+int32_t q4t_moe_routed_forward(const uint16_t* x, const int32_t* expert_ids, const float* router_w, float* y,
+                               const q4t_routed_weights* w, void* workspace, size_t workspace_bytes, int32_t M,
+                               int32_t k, uint32_t flags, void* stream) {
+  if (!w) return fail(Q4T_ERR_INVALID, "null weights");
+  if (M <= 0 || k <= 0 || w->E <= 0 || w->hs <= 0 || w->moe_is <= 0)
+    return fail(Q4T_ERR_INVALID, "invalid MoE forward dims");  // src/quant/moe_gemm.cu:321-323
+  if (!routed_dims_ok(w->E, w->hs, w->moe_is))
+    return fail(Q4T_ERR_INVALID, "hs and moe_is must be multiples of 128 and E <= 1024");
+  if (!x || !expert_ids || !router_w || !y || !workspace) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(Q4T_ERR_INVALID, "workspace must be 256-byte aligned");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  RoutedPtrs P;
+  routed_layout(M, k, w->hs, w->moe_is, w->E, &P.L);
+  if (workspace_bytes < P.L.total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");
+  P.base = static_cast<uint8_t*>(workspace);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((rc = run_routed_core(ds, x, expert_ids, w, P, M, k, flags, st)) != Q4T_OK) return rc;
+  cudaError_t e = q4t::launch_routed_combine(P.at<uint16_t>(P.L.dn_out), P.at<int32_t>(P.L.row_of_flat), router_w,
+                                             y, M, k, w->hs, st);
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("combine launch", e);
+}
+
+size_t q4t_moe_forward_workspace_bytes(int32_t T, int32_t k, int32_t hs, int32_t moe_is, int32_t shared_is,
+                                       int32_t E) {
+  if (T <= 0 || k <= 0 || hs <= 0 || moe_is <= 0 || shared_is <= 0 || E <= 0) return 0;
+  q4t_forward_ws_layout F;
+  forward_layout(T, k, hs, moe_is, shared_is, E, &F);
+  return F.total;
+}
+
+int32_t q4t_moe_forward_workspace_layout(int32_t T, int32_t k, int32_t hs, int32_t moe_is, int32_t shared_is,
+                                         int32_t E, q4t_forward_ws_layout* out) {
+  if (T <= 0 || k <= 0 || hs <= 0 || moe_is <= 0 || shared_is <= 0 || E <= 0 || !out)
+    return fail(Q4T_ERR_INVALID, "invalid MoE forward dims");
+  forward_layout(T, k, hs, moe_is, shared_is, E, out);
+  return Q4T_OK;
+}
+
+int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, const q4t_extra_weights* extra,
+                        uint16_t* y, int32_t T, int32_t k, void* workspace, size_t workspace_bytes,
+                        const int32_t* fixed_ids, uint32_t flags, void* stream) {
+  if (T <= 0) return Q4T_OK;                                           // src/model/moe.cu:442
+  if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");  // moe.cu:443
+  if (!routed || !extra) return fail(Q4T_ERR_INVALID, "null weights");
+  const int E = extra->E, hs = extra->hs, sis = extra->shared_is, is = routed->moe_is;
+  if (routed->E != E || routed->hs != hs) return fail(Q4T_ERR_INVALID, "routed and extra weights disagree on E/hs");
+  if (!routed_dims_ok(E, hs, is) || E > 512 || k > E || sis <= 0 || sis % 128)
+    return fail(Q4T_ERR_INVALID, "unsupported dims (hs, moe_is, shared_is multiples of 128; E <= 512)");
+  q4t_forward_ws_layout F;
+  forward_layout(T, k, hs, is, sis, E, &F);
+  if (workspace_bytes < F.total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");  // moe.cu:444-447
+  if (!x || !y || !workspace) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(Q4T_ERR_INVALID, "workspace must be 256-byte aligned");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  uint16_t* logits = reinterpret_cast<uint16_t*>(base + F.logits);
+  int32_t* ids = reinterpret_cast<int32_t*>(base + F.expert_ids);
+  float* rw = reinterpret_cast<float*>(base + F.router_w);
+  float* routed_f32 = reinterpret_cast<float*>(base + F.routed);
+  uint16_t* sgu = reinterpret_cast<uint16_t*>(base + F.shared_gu);
+  uint16_t* sact = reinterpret_cast<uint16_t*>(base + F.shared_act);
+  uint16_t* sdown = reinterpret_cast<uint16_t*>(base + F.shared_down);
+  cudaError_t e;
+
+  // 1-2. router logits and top-k
+  if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, E, hs, st)) != Q4T_OK) return rc;
+  if ((e = q4t::launch_topk(logits, fixed_ids, ids, rw, T, E, k, st)) != cudaSuccess) return fail_cuda("topk launch", e);
+
+  // 3. routed experts
+  RoutedPtrs P;
+  routed_layout(T, k, hs, is, E, &P.L);
+  P.base = base + F.routed_ws;
+  if ((rc = run_routed_core(ds, x, ids, routed, P, T, k, flags, st)) != Q4T_OK) return rc;
+
+  // 4-6. shared expert
+  if (T <= 8) {
+    if ((rc = run_bf16_linear(ds, x, extra->shared_gu, sgu, T, 2 * sis, hs, st)) != Q4T_OK) return rc;
+    if ((e = q4t::launch_swiglu(sgu, sact, T, sis, st)) != cudaSuccess) return fail_cuda("swiglu launch", e);
+  } else {
+    CUtensorMap ta, tb;
+    if ((rc = make_tmap(ds, &ta, true, x, hs, T, static_cast<uint64_t>(hs) * 2)) != Q4T_OK) return rc;
+    if ((rc = make_tmap(ds, &tb, true, extra->shared_gu, hs, 2 * sis, static_cast<uint64_t>(hs) * 2)) != Q4T_OK)
+      return rc;
+    q4t::GemmArgs g{};
+    g.K = hs;
+    g.n_tiles = sis / 128;
+    g.n_per_tile = 128;
+    g.up_row_offset = sis;
+    g.b_rows_valid = sis;
+    g.ntiles_host = (T + 127) / 128;
+    g.total_rows = T;
+    g.out = sact;
+    g.ldo = sis;
+    g.alpha_const = 1.0f;
+    g.gu_dump = (flags & 1u) ? sgu : nullptr;
+    g.gu_dump_ld = 2 * sis;
+    if ((e = q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kSwigluBf16, ds->num_sms, st)) != cudaSuccess)
+      return fail_cuda("shared gate/up GEMM launch", e);
+  }
+  if ((rc = run_bf16_linear(ds, sact, extra->shared_down, sdown, T, hs, sis, st)) != Q4T_OK) return rc;
+
+  // 7. routed sum + sigmoid-gated shared expert
+  if ((e = q4t::launch_final_combine(P.at<uint16_t>(P.L.dn_out), P.at<int32_t>(P.L.row_of_flat), rw, sdown, x,
+                                     extra->shared_gate_scalar, routed_f32, y, T, k, hs, st)) != cudaSuccess)
+    return fail_cuda("combine launch", e);
+  return Q4T_OK;
+}
+
+int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k, int32_t hs, int32_t moe_is,
+                                 int32_t E) {
+  if (!workspace || M <= 0 || k <= 0) return fail(Q4T_ERR_INVALID, "invalid arguments");
+  q4t_routed_ws_layout L;
+  routed_layout(M, k, hs, moe_is, E, &L);
+  int32_t word = 0;
+  cudaError_t e = cudaMemcpy(&word, static_cast<const uint8_t*>(workspace) + L.status, 4, cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail_cuda("status read", e);
+  if (word != 0) return fail(Q4T_ERR_KERNEL, "a bounded device-side wait ran out (role " + std::to_string(word) + ")");
+  return Q4T_OK;
+}
+
+int32_t q4t_selftest_encoders(int32_t which, uint64_t first, uint64_t count, uint64_t* mismatches,
+                              uint32_t* first_bad, void* stream) {
+  if (!mismatches || !first_bad) return fail(Q4T_ERR_INVALID, "null pointer");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  unsigned long long* d_m = nullptr;
+  uint32_t* d_b = nullptr;
+  cudaError_t e;
+  if ((e = cudaMalloc(&d_m, 8)) != cudaSuccess) return fail_cuda("cudaMalloc", e);
+  if ((e = cudaMalloc(&d_b, 4)) != cudaSuccess) {
+    cudaFree(d_m);
+    return fail_cuda("cudaMalloc", e);
+  }
+  cudaMemsetAsync(d_m, 0, 8, st);
+  cudaMemsetAsync(d_b, 0xff, 4, st);
+  e = q4t::launch_encoder_selftest(which, first, count, d_m, d_b, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  unsigned long long m = 0;
+  if (e == cudaSuccess) e = cudaMemcpy(&m, d_m, 8, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaMemcpy(first_bad, d_b, 4, cudaMemcpyDeviceToHost);
+  cudaFree(d_m);
+  cudaFree(d_b);
+  if (e != cudaSuccess) return fail_cuda("encoder self-check", e);
+  *mismatches = m;
+  return Q4T_OK;
+}
+
+}  // extern "C"

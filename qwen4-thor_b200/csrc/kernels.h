@@ -1,0 +1,109 @@
+// Internal launch interface between the C ABI (api.cu) and the kernel files.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace q4t {
+
+constexpr int kTileM = 128;        // rows of one GEMM tile (tokens of one expert)
+constexpr int kPlanChunk = 2048;   // (token,slot) entries handled by one planning block
+
+// ---- quantise / dequantise (quant_kernels.cu)
+cudaError_t launch_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf, int M, int K,
+                            float global_scale, cudaStream_t stream);
+cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int R,
+                                   int K, const int32_t* flat_of_row, const int32_t* expert_ids,
+                                   const float* input_scale, const int32_t* row_tile,
+                                   const int32_t* tile_row0, int k, int E, cudaStream_t stream);
+cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,
+                           float inv_global, int N, int K, cudaStream_t stream);
+cudaError_t launch_encoder_selftest(int which, uint64_t first, uint64_t count,
+                                    unsigned long long* d_mismatches, uint32_t* d_first_bad,
+                                    cudaStream_t stream);
+
+// ---- routing, permutation, combine (routing_kernels.cu)
+// Tables produced by the planning step, all in the routed workspace.
+struct PlanTables {
+  int32_t* blk_counts;   // [nblk, E] scratch
+  int32_t* counts;       // [E]
+  int32_t* offsets;      // [E+1]
+  int32_t* tile_off;     // [E+1]
+  int32_t* tile_expert;  // [max_tiles]
+  int32_t* tile_row0;    // [max_tiles]
+  int32_t* tile_nrows;   // [max_tiles]
+  int32_t* ntiles;       // [1]
+  int32_t* row_of_flat;  // [R]
+  int32_t* flat_of_row;  // [R]
+  int32_t* row_tile;     // [R]
+};
+cudaError_t launch_small_m_linear(const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
+                                  int K, cudaStream_t stream);
+cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw,
+                        int T, int E, int k, cudaStream_t stream);
+cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
+                        cudaStream_t stream);
+cudaError_t launch_routed_combine(const uint16_t* dn_out, const int32_t* row_of_flat,
+                                  const float* rw, float* y, int T, int k, int hs,
+                                  cudaStream_t stream);
+cudaError_t launch_swiglu(const uint16_t* gu, uint16_t* out, int T, int inner, cudaStream_t stream);
+cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,
+                                 const uint16_t* shared_down, const uint16_t* x,
+                                 const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
+                                 int k, int hs, cudaStream_t stream);
+
+// ---- tensor-core GEMMs (tc_gemm.cu)
+enum class Epilogue : int {
+  kStoreBf16 = 0,     // out[row, n] = bf16(alpha * acc)
+  kStoreF32 = 1,      // out[row, n] = alpha * acc
+  kSwigluBf16 = 2,    // gate|up tile -> bf16((g*sig(g))*u), g/u rounded to bf16 first
+  kSwigluQuant = 3    // as above, then NVFP4 quantisation with the expert's down input scale
+};
+struct GemmArgs {
+  // problem
+  int K;                 // reduction length (elements)
+  int n_tiles;           // column tiles per row tile
+  int n_per_tile;        // output columns produced per tile (256, or 128 for the SwiGLU epilogues)
+  int up_row_offset;     // SwiGLU: row distance between a gate row and its up row in B
+  int b_rows_per_group;  // rows of B belonging to one expert (0 for a dense GEMM)
+  int b_rows_valid;      // output columns that exist (N); columns beyond are neither loaded as scales nor stored
+  // row tiles: dense (tile t = rows [128 t, ..)) when tile_expert == nullptr
+  const int32_t* ntiles_dev;   // device count of row tiles (grouped) or nullptr
+  int ntiles_host;             // row tiles (dense)
+  const int32_t* tile_expert;
+  const int32_t* tile_row0;
+  const int32_t* tile_nrows;
+  int total_rows;              // dense: M
+  // block scales (NVFP4 only)
+  const uint8_t* sfa_tiles;    // tile-local atoms: tile t at t * ceil(K/64) * 512
+  const uint8_t* sfb;          // standard swizzled buffer per group
+  size_t sfb_group_stride;     // bytes between groups' scale buffers
+  // epilogue
+  void* out;                   // bf16 / f32 / packed codes
+  int ldo;                     // leading dimension of out, in elements (bytes for codes)
+  const float* alpha_w;        // per-group weight scale (grouped) or nullptr
+  const float* alpha_a;        // per-group activation scale or nullptr
+  float alpha_const;           // used when alpha_w == nullptr
+  const float* next_scale;     // kSwigluQuant: per-group input scale of the next GEMM
+  uint8_t* out_sf_tiles;       // kSwigluQuant: tile-local scale atoms of the intermediate
+  uint16_t* gu_dump;           // optional bf16 [rows, 2*inner] copy of the rounded gate|up values
+  int gu_dump_ld;
+  int32_t* status;             // device status word (non-zero = a bounded wait ran out)
+};
+// tmap_a: [rows, K] operand A; tmap_b: [all groups' rows, K] operand B (K-major, 128-byte boxes).
+cudaError_t launch_gemm_nvf4(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmArgs& a,
+                             Epilogue epi, int num_sms, cudaStream_t stream);
+cudaError_t launch_gemm_bf16(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmArgs& a,
+                             Epilogue epi, int num_sms, cudaStream_t stream);
+cudaError_t gemm_set_attributes();
+
+// ---- verification GEMM on CUDA cores (simt_check.cu): exact integer dot,
+// out = float(exact * alpha); used by tests to check the tensor-core path at
+// sizes the CPU oracle cannot reach.  Swizzled scales on both sides.
+cudaError_t launch_fp4_gemm_check(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t* a_packed,
+                                  const uint8_t* a_sf, float* out, int M, int N, int K, float alpha,
+                                  cudaStream_t stream);
+
+}  // namespace q4t

@@ -1,0 +1,181 @@
+// NVFP4 quantise / dequantise kernels: the standalone activation quantiser,
+// the expert-grouped gather-quantiser that feeds the gate/up GEMM, the
+// dequantiser, and the encoder self-check.
+#include "kernels.h"
+#include "q4t_device.cuh"
+
+namespace q4t {
+
+namespace {
+
+// One thread per group of 16 values; 4 neighbouring threads (the 4 groups of
+// one scale atom column block) merge their scale bytes into one 32-bit store.
+// ROWMAP: rows are gathered (source row = flat_of_row[r] / k, scale =
+// input_scale[expert of r]) and scales go to tile-local atoms; otherwise plain
+// row order, one global scale, scales in the standard swizzled buffer.
+template <bool ROWMAP>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(
+    const uint16_t* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_out,
+    int rows, int K, float global_scale,
+    // ROWMAP only:
+    const int32_t* __restrict__ flat_of_row, const int32_t* __restrict__ expert_ids,
+    const float* __restrict__ input_scale, const int32_t* __restrict__ row_tile,
+    const int32_t* __restrict__ tile_row0, int k, int E) {
+  const int groups = K >> 4;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(rows) * groups;
+  // groups is a multiple of 4, so the 4 lanes of a quad share one row
+  const bool live = idx < total;
+  const int row = live ? static_cast<int>(idx / groups) : 0;
+  const int g = live ? static_cast<int>(idx % groups) : 0;
+
+  int src_row = row;
+  float gs = global_scale;
+  size_t sf_base = 0;
+  uint32_t sf_row = row;
+  if constexpr (ROWMAP) {
+    if (live) {
+      const int flat = flat_of_row[row];
+      src_row = flat / k;
+      const int e = expert_ids[flat];
+      gs = input_scale[e];
+      const int t = row_tile[row];
+      sf_base = static_cast<size_t>(t) * (static_cast<size_t>((groups + 3) >> 2) * 512u);
+      sf_row = static_cast<uint32_t>(row - tile_row0[t]);
+    }
+  }
+  uint32_t sf = 0;
+  if (live) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(src_row) * K + g * 16);
+    const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float a[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      a[2 * j] = bf16x2_lo(w[j]);
+      a[2 * j + 1] = bf16x2_hi(w[j]);
+    }
+    uint32_t lo, hi;
+    sf = quantize_group16(a, gs, lo, hi);
+    *reinterpret_cast<uint2*>(packed + (static_cast<size_t>(row) * groups + g) * 8) = make_uint2(lo, hi);
+  }
+  if ((groups & 3) == 0) {
+    // merge the quad's scale bytes: groups g..g+3 of one row, g % 4 == 0 at the leader
+    const uint32_t lane = threadIdx.x & 31u;
+    uint32_t word = sf;
+    word |= __shfl_down_sync(0xffffffffu, sf, 1) << 8;
+    word |= __shfl_down_sync(0xffffffffu, sf, 2) << 16;
+    word |= __shfl_down_sync(0xffffffffu, sf, 3) << 24;
+    if (live && (lane & 3u) == 0) {
+      size_t off;
+      if constexpr (ROWMAP)
+        off = sf_base + static_cast<size_t>(g >> 2) * 512u + sf_in_atom(sf_row, 0);
+      else
+        off = sf_offset(sf_row, g, groups >> 2);
+      *reinterpret_cast<uint32_t*>(sf_out + off) = word;
+    }
+  } else if (live) {
+    if constexpr (ROWMAP)
+      sf_out[sf_base + static_cast<size_t>(g >> 2) * 512u + sf_in_atom(sf_row, g)] = sf;
+    else
+      sf_out[sf_offset(sf_row, g, (groups + 3) >> 2)] = sf;
+  }
+}
+
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ packed,
+                                                      const uint8_t* __restrict__ group_scale,
+                                                      uint16_t* __restrict__ out, float inv_global,
+                                                      int N, int K) {
+  const int groups = K >> 4;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(N) * groups) return;
+  const uint2 c = *reinterpret_cast<const uint2*>(packed + idx * 8);
+  // reference order: decode(scale) * inv_global, then code * that, then bf16
+  const float scale = e4m3_decode(group_scale[idx]) * inv_global;
+  const uint32_t w[2] = {c.x, c.y};
+  uint32_t o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t b = (w[j >> 2] >> (8 * (j & 3))) & 0xffu;
+    const uint32_t lo = b & 0xfu, hi = b >> 4;
+    // e2m1 magnitude: 0,.5,1,1.5,2,3,4,6
+    const float ml = (lo & 6u) ? __uint_as_float((((lo >> 1) & 3u) + 126u) << 23 | (lo & 1u) << 22)
+                               : 0.5f * static_cast<float>(lo & 1u);
+    const float mh = (hi & 6u) ? __uint_as_float((((hi >> 1) & 3u) + 126u) << 23 | (hi & 1u) << 22)
+                               : 0.5f * static_cast<float>(hi & 1u);
+    const float vl = ((lo & 8u) ? -ml : ml) * scale;
+    const float vh = ((hi & 8u) ? -mh : mh) * scale;
+    o[j] = f32x2_to_bf16x2(vl, vh);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + idx * 16);
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+__global__ void encoder_selftest_kernel(int which, uint64_t first, uint64_t count,
+                                        unsigned long long* mismatches, uint32_t* first_bad) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+  unsigned long long bad = 0;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) {
+    const uint32_t bits = static_cast<uint32_t>(first + i);
+    const float f = __uint_as_float(bits);
+    if (f != f) continue;
+    bool differ;
+    if (which == 0) {
+      const uint32_t hw = e2m1x2_encode_hw(f, -f);
+      const uint32_t sw = e2m1_encode_sw(f) | (e2m1_encode_sw(-f) << 4);
+      differ = hw != sw;
+    } else {
+      if (f < 0.0f || bits == 0x80000000u) continue;
+      differ = e4m3_encode_hw(f) != e4m3_encode_sw(f);
+    }
+    if (differ) {
+      ++bad;
+      atomicMin(first_bad, bits);
+    }
+  }
+  if (bad) atomicAdd(mismatches, bad);
+}
+
+}  // namespace
+
+cudaError_t launch_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf, int M, int K,
+                            float global_scale, cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(M) * (K / 16);
+  if (total == 0) return cudaSuccess;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  quantize_rows_kernel<false><<<blocks, 256, 0, stream>>>(x, packed, sf, M, K, global_scale, nullptr,
+                                                          nullptr, nullptr, nullptr, nullptr, 1, 0);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int R,
+                                   int K, const int32_t* flat_of_row, const int32_t* expert_ids,
+                                   const float* input_scale, const int32_t* row_tile,
+                                   const int32_t* tile_row0, int k, int E, cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(R) * (K / 16);
+  if (total == 0) return cudaSuccess;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  quantize_rows_kernel<true><<<blocks, 256, 0, stream>>>(x, packed, sf_tiles, R, K, 0.0f, flat_of_row,
+                                                         expert_ids, input_scale, row_tile, tile_row0,
+                                                         k, E);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,
+                           float inv_global, int N, int K, cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(N) * (K / 16);
+  if (total == 0) return cudaSuccess;
+  dequant_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      packed, group_scale, out, inv_global, N, K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_encoder_selftest(int which, uint64_t first, uint64_t count,
+                                    unsigned long long* d_mismatches, uint32_t* d_first_bad,
+                                    cudaStream_t stream) {
+  encoder_selftest_kernel<<<1184, 256, 0, stream>>>(which, first, count, d_mismatches, d_first_bad);
+  return cudaGetLastError();
+}
+
+}  // namespace q4t

@@ -1,0 +1,380 @@
+// Router, token->expert permutation, SwiGLU and combine kernels.
+#include "kernels.h"
+#include "q4t_device.cuh"
+
+namespace q4t {
+
+namespace {
+
+// y[m, n] = bf16(x[m,:] . w[n,:]) for M <= 8 with the accumulation order of
+// the reference's warp-per-output GEMV (src/model/gemv.cu:56-119 and the
+// small-M kernel it is documented bit-identical to, src/model/small_m_gemm.cu:
+// 57-113): lane l owns the 8-element chunks l, l+32, ...; inside a chunk even
+// elements feed one accumulator and odd elements another by fused multiply-
+// add; the two are added; lanes fold by shuffle-down 16..1; bf16 round.
+template <int MAXM>
+__global__ void __launch_bounds__(256) small_m_linear_kernel(const uint16_t* __restrict__ x,
+                                                             const uint16_t* __restrict__ w,
+                                                             uint16_t* __restrict__ y, int M, int N,
+                                                             int K) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const uint4* wrow = reinterpret_cast<const uint4*>(w + static_cast<size_t>(n) * K);
+  float ax[MAXM], ay[MAXM];
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m) ax[m] = ay[m] = 0.0f;
+  const int k8 = K >> 3;
+  for (int i = lane; i < k8; i += 32) {
+    const uint4 wv = __ldg(wrow + i);
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m) {
+      if (m < M) {
+        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * K) + i);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          ax[m] = fmaf(bf16x2_lo(xw[j]), bf16x2_lo(ww[j]), ax[m]);
+          ay[m] = fmaf(bf16x2_hi(xw[j]), bf16x2_hi(ww[j]), ay[m]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m) {
+    if (m < M) {
+      float s = ax[m] + ay[m];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) s += __shfl_down_sync(0xffffffffu, s, off);
+      if (lane == 0) y[static_cast<size_t>(m) * N + n] = f32_to_bf16(1.0f * s);
+    }
+  }
+}
+
+// Top-k + softmax over the selected logits, one warp per token
+// (RouterTopkKernel, src/model/moe.cu:134-212): k rounds of arg-max by
+// (value desc, id asc) with the winner masked to -1e30; then, in selection
+// order, e_i = __expf(v_i - max), sum, w_i = e_i * (1/sum).
+__global__ void __launch_bounds__(256) topk_kernel(const uint16_t* __restrict__ logits,
+                                                   const int32_t* __restrict__ fixed_ids,
+                                                   int32_t* __restrict__ ids, float* __restrict__ rw,
+                                                   int T, int E, int k) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const uint16_t* row = logits + static_cast<size_t>(t) * E;
+  float sel_v = 0.0f;  // lane i < k keeps the i-th selected value
+  int sel_i = 0;
+  if (fixed_ids != nullptr) {
+    if (lane < k) {
+      sel_i = fixed_ids[static_cast<size_t>(t) * k + lane];
+      sel_v = bf16_to_f32(row[sel_i]);
+    }
+  } else {
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = lane + 32 * i;
+      v[i] = e < E ? bf16_to_f32(row[e]) : -INFINITY;  // never beats the -1e30 start value
+    }
+    for (int r = 0; r < k; ++r) {
+      float m = -1e30f;
+      int mid = 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int e = lane + 32 * i;
+        if (v[i] > m || (v[i] == m && e < mid)) {
+          m = v[i];
+          mid = e;
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m, off);
+        const int oid = __shfl_xor_sync(0xffffffffu, mid, off);
+        if (om > m || (om == m && oid < mid)) {
+          m = om;
+          mid = oid;
+        }
+      }
+      if (lane == r) {
+        sel_v = m;
+        sel_i = mid;
+      }
+      if ((mid & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i == (mid >> 5)) v[i] = -1e30f;
+      }
+    }
+  }
+  // softmax in selection order, evaluated redundantly by every lane
+  float mx = __shfl_sync(0xffffffffu, sel_v, 0);
+  for (int i = 1; i < k; ++i) mx = fmaxf(mx, __shfl_sync(0xffffffffu, sel_v, i));
+  const float ev = __expf(sel_v - mx);
+  float sum = 0.0f;
+  for (int i = 0; i < k; ++i) sum += __shfl_sync(0xffffffffu, ev, i);
+  const float inv = __frcp_rn(sum);  // == 1.0f / sum under IEEE division
+  if (lane < k) {
+    ids[static_cast<size_t>(t) * k + lane] = sel_i;
+    rw[static_cast<size_t>(t) * k + lane] = ev * inv;
+  }
+}
+
+// ---- permutation: stable counting sort of the (token,slot) entries by expert.
+__global__ void __launch_bounds__(256) plan_hist_kernel(const int32_t* __restrict__ ids, int R, int E,
+                                                        int32_t* __restrict__ blk_counts) {
+  extern __shared__ int32_t hist[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int base = blockIdx.x * kPlanChunk;
+  for (int i = threadIdx.x; i < kPlanChunk; i += blockDim.x) {
+    const int f = base + i;
+    if (f < R) {
+      const int e = ids[f];
+      if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) blk_counts[static_cast<size_t>(blockIdx.x) * E + e] = hist[e];
+}
+
+// One block of 1024 threads, E <= 1024.  Turns the per-block counts into
+// per-block bases, builds offsets[E+1], the row-tile list and its count.
+__global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int max_tiles, PlanTables p) {
+  __shared__ int32_t s_rows[1024];
+  __shared__ int32_t s_tiles[1024];
+  const int e = threadIdx.x;
+  int32_t c = 0;
+  if (e < E) {
+    for (int b = 0; b < nblk; ++b) {
+      const int32_t v = p.blk_counts[static_cast<size_t>(b) * E + e];
+      p.blk_counts[static_cast<size_t>(b) * E + e] = c;
+      c += v;
+    }
+    p.counts[e] = c;
+  }
+  const int32_t tiles = (c + kTileM - 1) / kTileM;
+  s_rows[e] = c;
+  s_tiles[e] = tiles;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {  // inclusive Hillis-Steele scan of both arrays
+    int32_t a = 0, b = 0;
+    if (e >= off) {
+      a = s_rows[e - off];
+      b = s_tiles[e - off];
+    }
+    __syncthreads();
+    s_rows[e] += a;
+    s_tiles[e] += b;
+    __syncthreads();
+  }
+  const int32_t row_base = s_rows[e] - c, tile_base = s_tiles[e] - tiles;
+  if (e < E) {
+    p.offsets[e] = row_base;
+    p.tile_off[e] = tile_base;
+    for (int i = 0; i < tiles; ++i) {
+      const int t = tile_base + i;
+      if (t < max_tiles) {
+        p.tile_expert[t] = e;
+        p.tile_row0[t] = row_base + i * kTileM;
+        p.tile_nrows[t] = min(kTileM, c - i * kTileM);
+      }
+    }
+  }
+  if (e == E - 1) {
+    p.offsets[E] = s_rows[e];
+    p.tile_off[E] = s_tiles[e];
+    p.ntiles[0] = min(s_tiles[e], max_tiles);
+  }
+}
+
+__global__ void __launch_bounds__(256) plan_scatter_kernel(const int32_t* __restrict__ ids, int R, int E,
+                                                           PlanTables p) {
+  extern __shared__ int32_t cursor[];  // next grouped row of each expert for this block
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    cursor[e] = p.offsets[e] + p.blk_counts[static_cast<size_t>(blockIdx.x) * E + e];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int base = blockIdx.x * kPlanChunk;
+  for (int round = 0; round < kPlanChunk / 256; ++round) {
+    const int f = base + round * 256 + threadIdx.x;
+    const int e = f < R ? ids[f] : -1;
+    const bool valid = e >= 0 && e < E;
+    for (int w = 0; w < 8; ++w) {  // warps take turns so that positions follow the flat order
+      if (warp == w) {
+        const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);
+        if (valid) {
+          const int rank = __popc(peers & ((1u << lane) - 1u));
+          const int row = cursor[e] + rank;
+          __syncwarp(peers);
+          if (rank == 0) cursor[e] += __popc(peers);
+          p.row_of_flat[f] = row;
+          p.flat_of_row[row] = f;
+          p.row_tile[row] = p.tile_off[e] + (row - p.offsets[e]) / kTileM;
+        } else if (f < R) {
+          p.row_of_flat[f] = -1;
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// y[t, c] += sum over slots, in slot order, of w * bf16 row value, accumulated
+// by fused multiply-add from 0 (CombineGroupedKernel, src/quant/moe_gemm.cu:
+// 273-288).  One thread per 8 columns.
+__global__ void __launch_bounds__(256) routed_combine_kernel(const uint16_t* __restrict__ dn_out,
+                                                             const int32_t* __restrict__ row_of_flat,
+                                                             const float* __restrict__ rw,
+                                                             float* __restrict__ y, int T, int k, int hs) {
+  const int per_row = hs >> 3;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(T) * per_row) return;
+  const int t = static_cast<int>(idx / per_row), c8 = static_cast<int>(idx % per_row);
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  for (int s = 0; s < k; ++s) {
+    const int r = row_of_flat[t * k + s];
+    if (r < 0) continue;
+    const float wgt = rw[t * k + s];
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(r) * hs) + c8);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc[2 * j] = fmaf(wgt, bf16x2_lo(w[j]), acc[2 * j]);
+      acc[2 * j + 1] = fmaf(wgt, bf16x2_hi(w[j]), acc[2 * j + 1]);
+    }
+  }
+  float4* dst = reinterpret_cast<float4*>(y + static_cast<size_t>(t) * hs) + c8 * 2;
+  float4 a = dst[0], b = dst[1];
+  a.x += acc[0]; a.y += acc[1]; a.z += acc[2]; a.w += acc[3];
+  b.x += acc[4]; b.y += acc[5]; b.z += acc[6]; b.w += acc[7];
+  dst[0] = a;
+  dst[1] = b;
+}
+
+// out[t, c] = bf16((g * sigmoid(g)) * u) (SwiGLUKernel, src/model/moe.cu:276-287).
+__global__ void __launch_bounds__(256) swiglu_kernel(const uint16_t* __restrict__ gu,
+                                                     uint16_t* __restrict__ out, int T, int inner) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(T) * inner) return;
+  const int t = static_cast<int>(idx / inner), c = static_cast<int>(idx % inner);
+  const float g = bf16_to_f32(gu[static_cast<size_t>(t) * 2 * inner + c]);
+  const float u = bf16_to_f32(gu[static_cast<size_t>(t) * 2 * inner + inner + c]);
+  const float sig = __frcp_rn(1.0f + __expf(-g));
+  out[idx] = f32_to_bf16((g * sig) * u);
+}
+
+// One block of 256 threads per token: routed sum (slot order), gate =
+// sigmoid(x . gate_scalar) with the reference's 256 strided fused partials and
+// halving tree, y = bf16(fma(gate, shared_down, routed)) (MoECombineKernel,
+// src/model/moe.cu:291-321).  Also leaves the fp32 routed sum in `routed`.
+__global__ void __launch_bounds__(256) final_combine_kernel(
+    const uint16_t* __restrict__ dn_out, const int32_t* __restrict__ row_of_flat,
+    const float* __restrict__ rw, const uint16_t* __restrict__ shared_down,
+    const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate_scalar,
+    float* __restrict__ routed, uint16_t* __restrict__ y, int T, int k, int hs) {
+  __shared__ float part[256];
+  __shared__ int s_row[16];
+  __shared__ float s_w[16];
+  const int t = blockIdx.x;
+  if (threadIdx.x < k) {
+    s_row[threadIdx.x] = row_of_flat[t * k + threadIdx.x];
+    s_w[threadIdx.x] = rw[t * k + threadIdx.x];
+  }
+  float acc = 0.0f;
+  for (int c = threadIdx.x; c < hs; c += 256)
+    acc = fmaf(bf16_to_f32(x[static_cast<size_t>(t) * hs + c]), bf16_to_f32(gate_scalar[c]), acc);
+  part[threadIdx.x] = acc;
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if (threadIdx.x < off) part[threadIdx.x] += part[threadIdx.x + off];
+    __syncthreads();
+  }
+  const float gate = __frcp_rn(1.0f + __expf(-part[0]));
+  for (int c8 = threadIdx.x; c8 < (hs >> 3); c8 += 256) {
+    float a[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = 0.0f;
+    for (int s = 0; s < k; ++s) {
+      const int r = s_row[s];
+      if (r < 0) continue;
+      const float wgt = s_w[s];
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(r) * hs) + c8);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a[2 * j] = fmaf(wgt, bf16x2_lo(w[j]), a[2 * j]);
+        a[2 * j + 1] = fmaf(wgt, bf16x2_hi(w[j]), a[2 * j + 1]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = 0.0f + a[j];  // the reference adds into a zeroed buffer
+    float4* rdst = reinterpret_cast<float4*>(routed + static_cast<size_t>(t) * hs) + c8 * 2;
+    rdst[0] = make_float4(a[0], a[1], a[2], a[3]);
+    rdst[1] = make_float4(a[4], a[5], a[6], a[7]);
+    const uint4 sv = __ldg(reinterpret_cast<const uint4*>(shared_down + static_cast<size_t>(t) * hs) + c8);
+    const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = f32x2_to_bf16x2(fmaf(gate, bf16x2_lo(sw[j]), a[2 * j]),
+                             fmaf(gate, bf16x2_hi(sw[j]), a[2 * j + 1]));
+    *(reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * hs) + c8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_small_m_linear(const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
+                                  int K, cudaStream_t stream) {
+  const unsigned blocks = static_cast<unsigned>((N + 7) / 8);
+  if (M <= 1) small_m_linear_kernel<1><<<blocks, 256, 0, stream>>>(x, w, y, M, N, K);
+  else if (M <= 4) small_m_linear_kernel<4><<<blocks, 256, 0, stream>>>(x, w, y, M, N, K);
+  else small_m_linear_kernel<8><<<blocks, 256, 0, stream>>>(x, w, y, M, N, K);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw,
+                        int T, int E, int k, cudaStream_t stream) {
+  topk_kernel<<<static_cast<unsigned>((T + 7) / 8), 256, 0, stream>>>(logits, fixed_ids, ids, rw, T, E, k);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
+                        cudaStream_t stream) {
+  const int nblk = (R + kPlanChunk - 1) / kPlanChunk;
+  plan_hist_kernel<<<nblk, 256, E * sizeof(int32_t), stream>>>(ids, R, E, p.blk_counts);
+  plan_scan_kernel<<<1, 1024, 0, stream>>>(nblk, E, max_tiles, p);
+  plan_scatter_kernel<<<nblk, 256, E * sizeof(int32_t), stream>>>(ids, R, E, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_routed_combine(const uint16_t* dn_out, const int32_t* row_of_flat,
+                                  const float* rw, float* y, int T, int k, int hs,
+                                  cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(T) * (hs / 8);
+  routed_combine_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      dn_out, row_of_flat, rw, y, T, k, hs);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu(const uint16_t* gu, uint16_t* out, int T, int inner, cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(T) * inner;
+  swiglu_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(gu, out, T, inner);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,
+                                 const uint16_t* shared_down, const uint16_t* x,
+                                 const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
+                                 int k, int hs, cudaStream_t stream) {
+  final_combine_kernel<<<T, 256, 0, stream>>>(dn_out, row_of_flat, rw, shared_down, x, gate_scalar,
+                                              routed, y, T, k, hs);
+  return cudaGetLastError();
+}
+
+}  // namespace q4t

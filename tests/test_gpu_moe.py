@@ -1,0 +1,203 @@
+"""GPU parity of the routed-expert path and the whole layer against the
+oracle's device-order mode, through the C ABI, including the reference's
+error behaviour and batch-independence properties at large T."""
+import numpy as np
+import pytest
+import torch
+
+import synth
+from gpu_util import bf16_ulp_diff, dev, host
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _tile_local_sf(buf, row_tile, tile_row0, rows, K):
+    """Row-major [rows, K/16] view of tile-local scale atoms."""
+    g = np.arange(K // 16)[None, :]
+    ntk = (K + 63) // 64
+    r = (np.arange(rows) - tile_row0[row_tile])[:, None]
+    off = (row_tile[:, None] * ntk + g // 4) * 512 + (r % 32) * 16 + (r // 32) * 4 + g % 4
+    return buf[off]
+
+
+def _run_routed(q4t, L, T, k, seed, flags=1):
+    dl = q4t.DeviceLayer.from_host(L)
+    x = synth.make_x(T, L.hs, seed=seed)
+    ids, rw = synth.random_routing(T, k, L.E, seed=seed + 1)
+    rf = q4t.RoutedForward(dl, T, k)
+    y = torch.zeros((T, L.hs), dtype=torch.float32, device="cuda")
+    rf(dev(x), dev(ids), dev(rw), y, flags=flags)
+    rf.status()
+    return x, ids, rw, rf, host(y)
+
+
+@pytest.mark.parametrize("E,hs,is_,T,k", [(16, 512, 256, 9, 4), (32, 2048, 512, 16, 10),
+                                          (8, 2560, 640, 300, 3), (64, 256, 128, 1, 10)])
+def test_routed_forward_vs_oracle(q4t, gpu_lib, E, hs, is_, T, k):
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=128, seed=E + T, per_expert_input_scale=True)
+    x, ids, rw, rf, y = _run_routed(q4t, L, T, k, seed=T)
+    want_y, taps = O.routed_forward(x, ids, rw, L, 1, want_taps=True)
+    R = T * k
+    counts, offsets, rof, fofr = O.permutation(ids, E)
+    # input quantisation: bit-exact codes and scales
+    assert np.array_equal(host(rf.region("a_packed", torch.uint8, R * hs // 2)).reshape(R, -1), taps["a_packed"])
+    row_tile = host(rf.region("row_tile", torch.int32, R))
+    nt = int(host(rf.region("ntiles", torch.int32, 1))[0])
+    tile_row0 = host(rf.region("tile_row0", torch.int32, nt))
+    a_sf = host(rf.region("a_sf_tiles", torch.uint8, rf.layout.max_tiles * ((hs + 63) // 64) * 512))
+    assert np.array_equal(_tile_local_sf(a_sf, row_tile, tile_row0, R, hs), taps["a_sf"])
+    # gate/up projection rounded to bf16
+    gu = host(rf.region("gu_out", torch.int16, R * 2 * is_)).reshape(R, -1)
+    ulp = bf16_ulp_diff(gu, taps["gu_out"])
+    print(f"gu_out mismatches {(ulp > 0).sum()} of {ulp.size}, max ulp {ulp.max()}")
+    assert ulp.max() <= 1 and (ulp > 0).mean() < 1e-3
+    # intermediate codes/scales: equal except where a bf16 mismatch or the
+    # device exp intrinsic moved a value across a rounding boundary
+    ip = host(rf.region("inter_packed", torch.uint8, R * is_ // 2)).reshape(R, -1)
+    byte_mismatch = (ip != taps["i_packed"]).mean()
+    i_sf = host(rf.region("inter_sf_tiles", torch.uint8, rf.layout.max_tiles * ((is_ + 63) // 64) * 512))
+    sf_mismatch = (_tile_local_sf(i_sf, row_tile, tile_row0, R, is_) != taps["i_sf"]).mean()
+    print(f"intermediate code bytes differing: {byte_mismatch:.2e}, scales differing: {sf_mismatch:.2e}")
+    assert byte_mismatch < 2e-3 and sf_mismatch < 2e-3
+    # down projection rows and the combined output
+    dn = host(rf.region("dn_out", torch.int16, R * hs)).reshape(R, -1)
+    dn_f, want_dn = O.bf16_to_f32(dn), O.bf16_to_f32(taps["dn_out"])
+    assert np.abs(dn_f - want_dn).max() <= 2e-2 * np.abs(want_dn).max()
+    scale = np.abs(want_y).max()
+    err = np.abs(y - want_y).max() / scale
+    print(f"routed output: max |diff| / max |ref| = {err:.3e}")
+    assert err <= 2e-3      # north-star tolerance on the layer output
+
+
+def test_routed_accumulates_and_is_deterministic(q4t, gpu_lib):
+    L = synth.make_layer(E=16, hs=512, moe_is=256, shared_is=128, seed=2)
+    dl = q4t.DeviceLayer.from_host(L)
+    T, k = 33, 4
+    x = dev(synth.make_x(T, L.hs))
+    ids_h, rw_h = synth.random_routing(T, k, L.E)
+    ids, rw = dev(ids_h), dev(rw_h)
+    rf = q4t.RoutedForward(dl, T, k)
+    y0 = torch.zeros((T, L.hs), dtype=torch.float32, device="cuda")
+    rf(x, ids, rw, y0)
+    y1 = torch.full((T, L.hs), 0.25, dtype=torch.float32, device="cuda")
+    rf(x, ids, rw, y1)
+    y2 = torch.zeros((T, L.hs), dtype=torch.float32, device="cuda")
+    rf(x, ids, rw, y2)
+    rf.status()
+    assert torch.equal(y0, y2)
+    assert torch.equal(y1, y0 + 0.25)
+
+
+@pytest.mark.parametrize("T", [2, 16, 130])
+def test_moe_forward_vs_oracle(q4t, gpu_lib, T):
+    """T = 2 takes the exact-order GEMV projections, T >= 16 the tensor cores."""
+    E, hs, is_, sis, k = 64, 1024, 256, 256, 6
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=40 + T, per_expert_input_scale=True)
+    dl = q4t.DeviceLayer.from_host(L)
+    x = synth.make_x(T, hs, seed=T)
+    fwd = q4t.MoEForward(dl, T, k)
+    y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    fwd(dev(x), y, flags=1)
+    fwd.status()
+    logits = host(fwd.region("logits", torch.int16, T * E)).reshape(T, E)
+    ids = host(fwd.region("expert_ids", torch.int32, T * k)).reshape(T, k)
+    rw = host(fwd.region("router_w", torch.float32, T * k)).reshape(T, k)
+    # 1. logits: exact for T <= 8, within one bf16 ulp of the exact product above
+    want_logits = O.bf16_linear(x, L.gate, 1)
+    ulp = bf16_ulp_diff(logits, want_logits)
+    if T <= 8:
+        assert ulp.max() == 0
+    else:
+        assert ulp.max() <= 1
+    # 2. selection and weights from OUR logits must equal the oracle's on the same logits
+    want_ids, want_rw = O.router_topk(logits, k)
+    assert np.array_equal(ids, want_ids)
+    assert np.abs(rw - want_rw).max() <= 2e-6
+    # 3. experts + shared expert + combine, with the routing fixed to ours
+    routed = O.routed_forward(x, ids, rw, L, 1)
+    want_y = O.bf16_to_f32(O.shared_combine(x, routed, L, 1))
+    got_routed = host(fwd.region("routed", torch.float32, T * hs)).reshape(T, hs)
+    assert np.abs(got_routed - routed).max() <= 2e-3 * np.abs(routed).max()
+    got_y = O.bf16_to_f32(host(y))
+    err = np.abs(got_y - want_y).max() / np.abs(want_y).max()
+    print(f"layer output T={T}: max |diff| / max |ref| = {err:.3e}")
+    assert err <= 2e-3 + 2.0 ** -8      # bf16 output grid on top of the 2e-3 bound
+
+
+def test_moe_forward_fixed_ids_and_errors(q4t, gpu_lib):
+    E, hs, is_, sis, k, T = 32, 512, 128, 128, 4, 5
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=77)
+    dl = q4t.DeviceLayer.from_host(L)
+    x = dev(synth.make_x(T, hs))
+    fwd = q4t.MoEForward(dl, T, k)
+    y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    fixed, _ = synth.random_routing(T, k, E, seed=5)
+    fwd(x, y, fixed_ids=dev(fixed))
+    fwd.status()
+    assert np.array_equal(host(fwd.region("expert_ids", torch.int32, T * k)).reshape(T, k), fixed)
+    rw = host(fwd.region("router_w", torch.float32, T * k)).reshape(T, k)
+    assert np.allclose(rw.sum(axis=1), 1.0, atol=1e-5)
+    import ctypes as C
+    lib = q4t.load()
+    rc = lib.q4t_moe_forward(x.data_ptr(), C.byref(dl.routed), C.byref(dl.extra), y.data_ptr(), T, 17,
+                             fwd.ws.data_ptr(), fwd.layout.total, None, 0, None)
+    assert rc != 0 and lib.q4t_last_error() == b"k out of range"
+    rc = lib.q4t_moe_forward(x.data_ptr(), C.byref(dl.routed), C.byref(dl.extra), y.data_ptr(), T, k,
+                             fwd.ws.data_ptr(), 4096, None, 0, None)
+    assert rc != 0 and lib.q4t_last_error() == b"workspace too small"
+
+
+def test_batch_independence_at_scale(q4t, gpu_lib):
+    """Size-independent property (the reference's suffix-independence check,
+    tests/mtp_moe_path_test.cpp:264-304): a token's output does not depend on
+    which other tokens share the batch.  Rows of a 4096-token forward must be
+    bit-identical to the same rows run in a 64-token forward."""
+    E, hs, is_, sis, k = 512, 2048, 512, 512, 10
+    torch.manual_seed(0)
+    dl = synth_device_layer(q4t, E, hs, is_, sis)
+    T = 4096
+    x = torch.randn((T, hs), device="cuda").to(torch.bfloat16)
+    big = q4t.MoEForward(dl, T, k)
+    y_big = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    big(x, y_big)
+    big.status()
+    pick = torch.arange(0, T, 64, device="cuda")
+    small = q4t.MoEForward(dl, pick.numel(), k)
+    y_small = torch.empty((pick.numel(), hs), dtype=torch.bfloat16, device="cuda")
+    ids_big = big.region("expert_ids", torch.int32, T * k).view(T, k)[pick].contiguous()
+    small(x[pick].contiguous(), y_small, fixed_ids=ids_big)
+    small.status()
+    assert torch.isfinite(y_big.float()).all()
+    a, b = y_big[pick].view(torch.int16), y_small.view(torch.int16)
+    diff = (a != b).float().mean().item()
+    print(f"rows differing between T=4096 and T=64 batches: {diff:.3e}")
+    assert diff == 0.0
+
+
+def synth_device_layer(q4t, E, hs, is_, sis, seed=0):
+    """Full-size synthetic layer built on the device: bf16 N(0, 0.02) weights
+    quantised by the library's own quantiser (itself checked bit-exact above)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    t = {}
+    def quant(rows, K):
+        w = (torch.randn((rows, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+        gs = float(w.float().abs().max()) / (6.0 * 448.0)
+        p, s = q4t.quantize_activation_fp4(w, gs)
+        return p, s, gs
+    gu_p, gu_s, gu_g, dn_p, dn_s, dn_g = [], [], [], [], [], []
+    for e in range(E):
+        p, s, gs = quant(2 * is_, hs)
+        gu_p.append(p); gu_s.append(s); gu_g.append(gs)
+        p, s, gs = quant(hs, is_)
+        dn_p.append(p); dn_s.append(s); dn_g.append(gs)
+    t["gu_packed"] = torch.cat(gu_p); t["gu_sf"] = torch.cat(gu_s)
+    t["dn_packed"] = torch.cat(dn_p); t["dn_sf"] = torch.cat(dn_s)
+    t["gu_w_scale2"] = torch.tensor(gu_g, dtype=torch.float32, device="cuda")
+    t["dn_w_scale2"] = torch.tensor(dn_g, dtype=torch.float32, device="cuda")
+    t["gu_input_scale"] = torch.full((E,), 5.0 / (6 * 448), dtype=torch.float32, device="cuda")
+    t["dn_input_scale"] = torch.full((E,), 2.0 / (6 * 448), dtype=torch.float32, device="cuda")
+    for n, shape in (("gate", (E, hs)), ("shared_gu", (2 * sis, hs)), ("shared_down", (hs, sis)),
+                     ("shared_gate_scalar", (hs,))):
+        t[n] = (torch.randn(shape, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    return q4t.DeviceLayer(E, hs, is_, sis, t)
