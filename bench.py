@@ -1,0 +1,331 @@
+"""Benchmark of the NVFP4 MoE layer (router + routed experts + shared expert +
+combine) through the library's C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N = 1 (default): the decode-shaped layer microbenchmark — hidden 2048, 512
+experts, top-10, intermediate 512, shared expert 512, T = 128 tokens per step,
+uniform-random routing, NVFP4 weights ~ N(0, 0.02).  Each step runs one layer
+forward; successive steps rotate over several independent layer weight sets
+and inputs so that no step finds its weights in L2.  The line also carries the
+sweep over T in {1, 8, 32, 64} and the 16384-token Zipf-skewed prefill layer
+under "also".
+
+N > 1 (launched by torchrun, one rank per GPU): the expert-parallel prefill
+layer, T = 32768 tokens per step sharded by rank, 512/N experts per GPU,
+all-to-all dispatch and return over NCCL.
+
+--impl reference times the reference's CPU formulation of the layer (the CPU
+oracle's restatement of the reference's host-side MoE) on the host cores.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HS, E, K_TOP, MOE_IS, SHARED_IS = 2048, 512, 10, 512, 512
+EXPERT_BYTES = 1_048_576 + 131_072 + 524_288 + 65_536 + 16      # codes + scales + 4 scalars
+LAYER_FIXED_BYTES = 2_097_152 + 6_295_552                         # router + bf16 shared expert
+GU_EXPERT_BYTES = 1_048_576 + 131_072                             # gate/up codes + scales
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                sm.append(int(float(r[0])))
+                mx = max(mx, int(float(r[1])))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=mx or None, reasons=sorted(reasons),
+                    samples=len(sm))
+
+
+def time_steps(torch, fn, steps, warmup, barrier=None):
+    """W untimed steps, then exactly K timed steps between CUDA events on the
+    current stream, with a synchronise (and barrier) on both sides."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    t1.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return t0.elapsed_time(t1) / steps
+
+
+def unique_experts(torch, fwd, T):
+    ids = fwd.region("expert_ids", torch.int32, T * K_TOP)
+    return int(torch.unique(ids).numel())
+
+
+def layer_bytes(U, T):
+    return U * EXPERT_BYTES + LAYER_FIXED_BYTES + 2 * T * HS * 2
+
+
+def run_decode_point(torch, q4t, layers, T, steps, warmup, n_inputs=8, with_e2e=False, with_stages=False):
+    syn = importlib.import_module("qwen4-thor_b200.synthetic")
+    xs = [syn.make_x(T, HS, seed=100 + i) for i in range(n_inputs)]
+    fwds = [q4t.MoEForward(l, T, K_TOP) for l in layers]
+    y = torch.empty((T, HS), dtype=torch.bfloat16, device="cuda")
+    counter = {"launches": 0}
+
+    def step(i):
+        fwds[i % len(fwds)](xs[i % n_inputs], y)
+
+    ms = time_steps(torch, step, steps, warmup)
+    fwds[0].status()
+    # distinct experts per step (algorithmic bytes), averaged over the rotation
+    us = []
+    for i in range(min(len(fwds) * 2, 8)):
+        step(i)
+        torch.cuda.synchronize()
+        us.append(unique_experts(torch, fwds[i % len(fwds)], T))
+    U = sum(us) / len(us)
+    out = dict(T=T, ms_per_step=ms, tokens_per_s=T / (ms * 1e-3), unique_experts=U,
+               layer_bytes=layer_bytes(U, T), layer_gbs=layer_bytes(U, T) / (ms * 1e-3) / 1e9)
+    if with_stages:
+        q4t.stage_timing(True)
+        acc = {}
+        n = max(steps, 8)
+        for i in range(n):
+            step(i)
+            for kname, v in q4t.stage_timing_read().items():
+                acc[kname] = acc.get(kname, 0.0) + v
+        q4t.stage_timing(False)
+        out["stage_ms"] = {kname: v / n for kname, v in acc.items()}
+    if with_e2e:
+        hx = [x.cpu().pin_memory() for x in xs]
+        hy = torch.empty((T, HS), dtype=torch.bfloat16).pin_memory()
+        dx = torch.empty((T, HS), dtype=torch.bfloat16, device="cuda")
+
+        def step_e2e(i):
+            dx.copy_(hx[i % n_inputs], non_blocking=True)
+            fwds[i % len(fwds)](dx, y)
+            hy.copy_(y, non_blocking=True)
+
+        ms_e = time_steps(torch, step_e2e, steps, warmup)
+        out["e2e"] = dict(value=T / (ms_e * 1e-3), unit="tokens/s", ms_per_step=ms_e,
+                          h2d_bytes_per_step=T * HS * 2, d2h_bytes_per_step=T * HS * 2)
+    del fwds
+    return out
+
+
+def run_prefill_point(torch, q4t, T, steps, warmup, seed=7):
+    syn = importlib.import_module("qwen4-thor_b200.synthetic")
+    layer = syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=seed, zipf_s=1.1)
+    xs = [syn.make_x(T, HS, seed=200 + i, bias_column=True) for i in range(2)]
+    fwd = q4t.MoEForward(layer, T, K_TOP)
+    y = torch.empty((T, HS), dtype=torch.bfloat16, device="cuda")
+    ms = time_steps(torch, lambda i: fwd(xs[i % 2], y), steps, warmup)
+    fwd.status()
+    counts = fwd.routed_region("counts", torch.int32, E).float()
+    q4t.stage_timing(True)
+    acc = {}
+    for i in range(3):
+        fwd(xs[i % 2], y)
+        for kname, v in q4t.stage_timing_read().items():
+            acc[kname] = acc.get(kname, 0.0) + v / 3
+    q4t.stage_timing(False)
+    flops = 6.0 * T * K_TOP * HS * MOE_IS
+    out = dict(T=T, ms_per_step=ms, tokens_per_s=T / (ms * 1e-3), routed_tflops=flops / (ms * 1e-3) / 1e12,
+               rows_per_expert_max=float(counts.max()), rows_per_expert_mean=float(counts.mean()),
+               stage_ms=acc, routing="zipf(s=1.1) bias on router column 0")
+    del fwd, layer
+    return out
+
+
+def cpu_reference_run(q4t_layer_host, T, steps, warmup):
+    """Times the CPU formulation (oracle 'test twin' mode: dequantise, fp32
+    sequential dots, expf) on all host threads; returns (tokens/s, ms, threads)."""
+    from oracle import oracle as O
+    import numpy as np
+    rng = np.random.default_rng(5)
+    x = O.f32_to_bf16(rng.standard_normal((T, HS), dtype=np.float32))
+    for _ in range(warmup):
+        O.moe_forward(x, q4t_layer_host, K_TOP, 0, 0, 0)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.moe_forward(x, q4t_layer_host, K_TOP, 0, 0, 0)
+    dt = (time.perf_counter() - t0) / steps
+    return T / dt, dt * 1e3, O.num_threads()
+
+
+def host_layer_from_device(torch, dl):
+    from oracle import oracle as O
+    import numpy as np
+    arrs = {}
+    for n, t in dl.t.items():
+        a = t.view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy()
+        arrs[n] = a
+    return O.Layer(dl.E, dl.hs, dl.moe_is, dl.shared_is, **arrs)
+
+
+def pick_cpu_tokens(layer_host, budget_s=4.0):
+    """Largest T <= 128 whose CPU step is expected to stay near budget_s."""
+    _, ms8, _ = cpu_reference_run(layer_host, 8, 1, 0)
+    per_tok = ms8 / 8.0 / 1e3
+    T = int(max(1, min(128, budget_s / max(per_tok, 1e-6))))
+    return T
+
+
+def main_single(args):
+    import torch
+    q4t = importlib.import_module("qwen4-thor_b200")
+    syn = importlib.import_module("qwen4-thor_b200.synthetic")
+    q4t.load()
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    n_layers = 1 if args.impl == "reference" else 4
+    layers = [syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=20260921 + 1000 + i) for i in range(n_layers)]
+
+    if args.impl == "reference":
+        host_layer = host_layer_from_device(torch, layers[0])
+        T = pick_cpu_tokens(host_layer)
+        tps, ms, threads = cpu_reference_run(host_layer, T, args.steps, min(args.warmup, 1))
+        line = dict(impl="reference", metric="moe_layer_tokens_per_s", value=tps, unit="tokens/s", n_gpus=1,
+                    steps=args.steps, warmup=min(args.warmup, 1), ms_per_step=ms, higher_is_better=True,
+                    scaling="weak", vs_baseline=None, dtype="nvfp4 (e2m1 x ue4m3) weights and activations, fp32 accumulate",
+                    data="synthetic",
+                    config=dict(workload="decode-shaped MoE layer, hs=2048 E=512 top-10 is=512 shared=512", tokens=T),
+                    cpu_baseline=dict(value=tps, unit="tokens/s", cores=threads, kind="port",
+                                      sample=f"one layer forward of {T} tokens per step"),
+                    e2e=dict(value=tps, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+        print(json.dumps(line))
+        return
+
+    T = 128
+    with ClockSampler(0) as clocks:
+        main = run_decode_point(torch, q4t, layers, T, args.steps, args.warmup, with_e2e=True, with_stages=True)
+    clk = clocks.summary()
+    also = {}
+    if not args.quick:
+        sweep = []
+        for t in (1, 8, 32, 64):
+            r = run_decode_point(torch, q4t, layers, t, max(args.steps, 20), args.warmup, with_stages=True)
+            r["hbm_frac_of_measured"] = r["layer_gbs"] / peaks["hbm_gbs"]
+            sweep.append(r)
+        also["decode_sweep"] = sweep
+        also["prefill_T16384"] = run_prefill_point(torch, q4t, 16384, max(3, min(args.steps, 10)), 3)
+        pf = also["prefill_T16384"]
+        pf["frac_of_4x_measured_bf16"] = pf["routed_tflops"] / (4 * peaks["bf16_tflops"])
+        pf["frac_of_9pf_nominal"] = pf["routed_tflops"] / 9000.0
+
+    # roofline of the dominant kernel (gate/up GEMM with fused SwiGLU + requantise)
+    st = main["stage_ms"]
+    R = T * K_TOP
+    gu_bytes = main["unique_experts"] * GU_EXPERT_BYTES + R * (HS // 2 + HS // 16) + R * (MOE_IS // 2 + MOE_IS // 16)
+    gu_gbs = gu_bytes / (st["gate_up_gemm"] * 1e-3) / 1e9
+    roofline = dict(bound="hbm", kernel="gate_up_gemm (tcgen05 NVFP4 grouped GEMM + SwiGLU + requantise)",
+                    achieved=gu_gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gu_gbs / peaks["hbm_gbs"],
+                    peak_source=peaks["source"], traffic=None, algorithmic_bytes=gu_bytes,
+                    kernel_ms=st["gate_up_gemm"],
+                    layer=dict(achieved=main["layer_gbs"], frac=main["layer_gbs"] / peaks["hbm_gbs"],
+                               frac_of_8tbs=main["layer_gbs"] / 8000.0, bytes=main["layer_bytes"]))
+
+    cpu = None
+    if not args.no_cpu:
+        host_layer = host_layer_from_device(torch, layers[0])
+        Tc = pick_cpu_tokens(host_layer)
+        tps, ms_c, threads = cpu_reference_run(host_layer, Tc, 2, 1)
+        cpu = dict(value=tps, unit="tokens/s", cores=threads, kind="port",
+                   sample=f"2 layer forwards of {Tc} tokens (oracle restatement of the reference's host-side MoE)")
+
+    launches_per_step = 3 + 3 + 1 + 1 + 1 + 1 + 1 + 1   # logits, topk, plan x3, quant, gu, dn, shared x2, combine
+    line = dict(metric="moe_layer_tokens_per_s", value=main["tokens_per_s"], unit="tokens/s", n_gpus=1,
+                steps=args.steps, warmup=args.warmup, ms_per_step=main["ms_per_step"], higher_is_better=True,
+                scaling="weak", vs_baseline=None,
+                dtype="nvfp4 (e2m1 x ue4m3, fp32 accumulate); bf16 router and shared expert", data="synthetic",
+                config=dict(workload="decode-shaped MoE layer microbench, T=128", hidden=HS, experts=E, top_k=K_TOP,
+                            moe_intermediate=MOE_IS, shared_intermediate=SHARED_IS,
+                            l2="4 layer weight sets (3.6 GB) and 8 inputs rotated per step; one step touches ~840 MB > L2",
+                            unique_experts_per_step=main["unique_experts"]),
+                clocks=clk, e2e={k: v for k, v in main["e2e"].items() if k != "ms_per_step"},
+                gpu_launches=launches_per_step * args.steps, roofline=roofline, cpu_baseline=cpu,
+                stage_ms=st, also=also)
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--quick", action="store_true", help="headline point only (no sweep, no prefill)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 or args.gpus > 1:
+        from importlib import import_module
+        ep = import_module("qwen4-thor_b200.ep_bench")
+        ep.main_multi(args)
+        return
+    main_single(args)
+
+
+if __name__ == "__main__":
+    main()

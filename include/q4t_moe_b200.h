@@ -213,6 +213,18 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
 int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k,
                                  int32_t hs, int32_t moe_is, int32_t E);
 
+/* ---- stage timer, after MoESubTiming (include/q4t/quant/moe_subtiming.h:
+ * 14-97): when enabled, q4t_moe_forward / q4t_moe_routed_forward record CUDA
+ * events on the caller's stream between their stages.  q4t_stage_timing_read
+ * synchronises on the last event of the calling thread's most recent call and
+ * writes the elapsed milliseconds of the Q4T_NUM_STAGES stages:
+ *   0 router logits, 1 top-k, 2 permutation tables, 3 gather-quantise,
+ *   4 gate/up GEMM (+SwiGLU, requantise), 5 down GEMM, 6 shared expert,
+ *   7 combine.  Stages a call does not run read as 0.  Off by default.        */
+#define Q4T_NUM_STAGES 8
+int32_t q4t_stage_timing_enable(int32_t enable);
+int32_t q4t_stage_timing_read(float* ms_out);
+
 /* ---- device self-checks used by the GPU tests (no reference counterpart):
  * sweep float bit patterns [first, first+count) through the kernels' hardware
  * encoders and through a compare-chain restatement of format.h and return the

@@ -52,7 +52,7 @@ EXPORTS = [
     "q4t_fp4_gemm_check", "q4t_router_topk", "q4t_bf16_linear", "q4t_moe_routed_workspace_bytes",
     "q4t_moe_routed_workspace_layout", "q4t_moe_routed_forward", "q4t_moe_forward_workspace_bytes",
     "q4t_moe_forward_workspace_layout", "q4t_moe_forward", "q4t_moe_workspace_status",
-    "q4t_selftest_encoders",
+    "q4t_selftest_encoders", "q4t_stage_timing_enable", "q4t_stage_timing_read",
 ]
 
 _lib = None
@@ -279,6 +279,20 @@ class MoEForward:
         ws = self.ws[self.layout.routed_ws:]
         check(load().q4t_moe_workspace_status(_ptr(ws), self.T, self.k, self.layer.hs, self.layer.moe_is,
                                               self.layer.E))
+
+
+STAGES = ("router_logits", "topk", "permutation", "gather_quantise", "gate_up_gemm", "down_gemm",
+          "shared_expert", "combine")
+
+
+def stage_timing(enable: bool) -> None:
+    check(load().q4t_stage_timing_enable(1 if enable else 0))
+
+
+def stage_timing_read() -> dict:
+    ms = (C.c_float * len(STAGES))()
+    check(load().q4t_stage_timing_read(ms))
+    return dict(zip(STAGES, [float(v) for v in ms]))
 
 
 def selftest_encoders(which: int, first: int, count: int):

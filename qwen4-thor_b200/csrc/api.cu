@@ -87,6 +87,26 @@ int make_tmap(const DeviceState* ds, CUtensorMap* tm, bool bf16, const void* bas
   return Q4T_OK;
 }
 
+// Optional event marks between stages (off by default).
+struct StageTimer {
+  bool enabled = false;
+  cudaEvent_t ev[Q4T_NUM_STAGES + 1] = {};
+  bool marked[Q4T_NUM_STAGES + 1] = {};
+};
+thread_local StageTimer g_timer;
+void stage_begin(cudaStream_t st) {
+  if (!g_timer.enabled) return;
+  for (bool& m : g_timer.marked) m = false;
+  cudaEventRecord(g_timer.ev[0], st);
+  g_timer.marked[0] = true;
+}
+// Marks the end of stage `i` (its event is ev[i + 1]).
+void stage_end(int i, cudaStream_t st) {
+  if (!g_timer.enabled) return;
+  cudaEventRecord(g_timer.ev[i + 1], st);
+  g_timer.marked[i + 1] = true;
+}
+
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 size_t sf_buffer_size(int rows, int K) {
   return static_cast<size_t>((rows + 127) / 128) * static_cast<size_t>((K / 16 + 3) / 4) * 512;
@@ -188,12 +208,14 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   pt.blk_counts = P.at<int32_t>(align_up(align_up(L.status + 256, 256) + static_cast<size_t>(E + 1) * 4, 256));
   if ((e = q4t::launch_plan(ids, R, E, static_cast<int>(L.max_tiles), pt, st)) != cudaSuccess)
     return fail_cuda("plan launch", e);
+  stage_end(2, st);
 
   uint8_t* a_packed = P.at<uint8_t>(L.a_packed);
   uint8_t* a_sf_tiles = P.at<uint8_t>(L.a_sf_tiles);
   if ((e = q4t::launch_gather_quantize(x, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, ids,
-                                       w->gu_input_scale, pt.row_tile, pt.tile_row0, k, E, st)) != cudaSuccess)
+                                       w->gu_input_scale, pt.row_tile, pt.tile_row0, pt.offsets + E, k, E, st)) != cudaSuccess)
     return fail_cuda("gather-quantise launch", e);
+  stage_end(3, st);
 
   CUtensorMap tm_a, tm_b;
   int rc;
@@ -227,6 +249,7 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   g.status = P.at<int32_t>(L.status);
   if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, g, q4t::Epilogue::kSwigluQuant, ds->num_sms, st)) != cudaSuccess)
     return fail_cuda("gate/up GEMM launch", e);
+  stage_end(4, st);
 
   // down: A = intermediate codes [R, is/2], B = all experts' down rows
   if ((rc = make_tmap(ds, &tm_a, false, P.at<uint8_t>(L.inter_packed), is / 2, R, is / 2)) != Q4T_OK) return rc;
@@ -253,6 +276,7 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   d.status = P.at<int32_t>(L.status);
   if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, d, q4t::Epilogue::kStoreBf16, ds->num_sms, st)) != cudaSuccess)
     return fail_cuda("down GEMM launch", e);
+  stage_end(5, st);
   return Q4T_OK;
 }
 
@@ -450,9 +474,13 @@ int32_t q4t_moe_routed_forward(const uint16_t* x, const int32_t* expert_ids, con
   if (workspace_bytes < P.L.total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");
   P.base = static_cast<uint8_t*>(workspace);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  stage_begin(st);
+  stage_end(1, st);
   if ((rc = run_routed_core(ds, x, expert_ids, w, P, M, k, flags, st)) != Q4T_OK) return rc;
   cudaError_t e = q4t::launch_routed_combine(P.at<uint16_t>(P.L.dn_out), P.at<int32_t>(P.L.row_of_flat), router_w,
                                              y, M, k, w->hs, st);
+  stage_end(6, st);
+  stage_end(7, st);
   return e == cudaSuccess ? Q4T_OK : fail_cuda("combine launch", e);
 }
 
@@ -502,8 +530,11 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
   cudaError_t e;
 
   // 1-2. router logits and top-k
+  stage_begin(st);
   if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, E, hs, st)) != Q4T_OK) return rc;
+  stage_end(0, st);
   if ((e = q4t::launch_topk(logits, fixed_ids, ids, rw, T, E, k, st)) != cudaSuccess) return fail_cuda("topk launch", e);
+  stage_end(1, st);
 
   // 3. routed experts
   RoutedPtrs P;
@@ -537,11 +568,13 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
       return fail_cuda("shared gate/up GEMM launch", e);
   }
   if ((rc = run_bf16_linear(ds, sact, extra->shared_down, sdown, T, hs, sis, st)) != Q4T_OK) return rc;
+  stage_end(6, st);
 
   // 7. routed sum + sigmoid-gated shared expert
   if ((e = q4t::launch_final_combine(P.at<uint16_t>(P.L.dn_out), P.at<int32_t>(P.L.row_of_flat), rw, sdown, x,
                                      extra->shared_gate_scalar, routed_f32, y, T, k, hs, st)) != cudaSuccess)
     return fail_cuda("combine launch", e);
+  stage_end(7, st);
   return Q4T_OK;
 }
 
@@ -554,6 +587,39 @@ int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k, in
   cudaError_t e = cudaMemcpy(&word, static_cast<const uint8_t*>(workspace) + L.status, 4, cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return fail_cuda("status read", e);
   if (word != 0) return fail(Q4T_ERR_KERNEL, "a bounded device-side wait ran out (role " + std::to_string(word) + ")");
+  return Q4T_OK;
+}
+
+int32_t q4t_stage_timing_enable(int32_t enable) {
+  StageTimer& t = g_timer;
+  if (enable && !t.enabled) {
+    for (auto& ev : t.ev)
+      if (cudaEventCreate(&ev) != cudaSuccess) return fail(Q4T_ERR_CUDA, "cudaEventCreate failed");
+    t.enabled = true;
+  } else if (!enable && t.enabled) {
+    for (auto& ev : t.ev) cudaEventDestroy(ev);
+    t.enabled = false;
+  }
+  return Q4T_OK;
+}
+
+int32_t q4t_stage_timing_read(float* ms_out) {
+  StageTimer& t = g_timer;
+  if (!ms_out) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (!t.enabled || !t.marked[0]) return fail(Q4T_ERR_INVALID, "stage timing is not enabled or nothing was recorded");
+  int last = 0;
+  for (int i = 0; i <= Q4T_NUM_STAGES; ++i)
+    if (t.marked[i]) last = i;
+  cudaError_t e = cudaEventSynchronize(t.ev[last]);
+  if (e != cudaSuccess) return fail_cuda("cudaEventSynchronize", e);
+  int prev = 0;
+  for (int i = 0; i < Q4T_NUM_STAGES; ++i) {
+    ms_out[i] = 0.0f;
+    if (!t.marked[i + 1]) continue;
+    if ((e = cudaEventElapsedTime(&ms_out[i], t.ev[prev], t.ev[i + 1])) != cudaSuccess)
+      return fail_cuda("cudaEventElapsedTime", e);
+    prev = i + 1;
+  }
   return Q4T_OK;
 }
 

@@ -17,7 +17,8 @@ cudaError_t launch_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf, int
 cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int R,
                                    int K, const int32_t* flat_of_row, const int32_t* expert_ids,
                                    const float* input_scale, const int32_t* row_tile,
-                                   const int32_t* tile_row0, int k, int E, cudaStream_t stream);
+                                   const int32_t* tile_row0, const int32_t* rows_dev, int k, int E,
+                                   cudaStream_t stream);
 cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,
                            float inv_global, int N, int K, cudaStream_t stream);
 cudaError_t launch_encoder_selftest(int which, uint64_t first, uint64_t count,

@@ -20,9 +20,11 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(
     // ROWMAP only:
     const int32_t* __restrict__ flat_of_row, const int32_t* __restrict__ expert_ids,
     const float* __restrict__ input_scale, const int32_t* __restrict__ row_tile,
-    const int32_t* __restrict__ tile_row0, int k, int E) {
+    const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ rows_dev, int k, int E) {
   const int groups = K >> 4;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // grouped rows past the device-side count belong to skipped (token,slot) entries
+  if (ROWMAP) rows = min(rows, *rows_dev);
   const int64_t total = static_cast<int64_t>(rows) * groups;
   // groups is a multiple of 4, so the 4 lanes of a quad share one row
   const bool live = idx < total;
@@ -145,20 +147,21 @@ cudaError_t launch_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf, int
   if (total == 0) return cudaSuccess;
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
   quantize_rows_kernel<false><<<blocks, 256, 0, stream>>>(x, packed, sf, M, K, global_scale, nullptr,
-                                                          nullptr, nullptr, nullptr, nullptr, 1, 0);
+                                                          nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0);
   return cudaGetLastError();
 }
 
 cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int R,
                                    int K, const int32_t* flat_of_row, const int32_t* expert_ids,
                                    const float* input_scale, const int32_t* row_tile,
-                                   const int32_t* tile_row0, int k, int E, cudaStream_t stream) {
+                                   const int32_t* tile_row0, const int32_t* rows_dev, int k, int E,
+                                   cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(R) * (K / 16);
   if (total == 0) return cudaSuccess;
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
   quantize_rows_kernel<true><<<blocks, 256, 0, stream>>>(x, packed, sf_tiles, R, K, 0.0f, flat_of_row,
                                                          expert_ids, input_scale, row_tile, tile_row0,
-                                                         k, E);
+                                                         rows_dev, k, E);
   return cudaGetLastError();
 }
 

@@ -103,13 +103,15 @@ def test_moe_forward_vs_oracle(q4t, gpu_lib, T):
     logits = host(fwd.region("logits", torch.int16, T * E)).reshape(T, E)
     ids = host(fwd.region("expert_ids", torch.int32, T * k)).reshape(T, k)
     rw = host(fwd.region("router_w", torch.float32, T * k)).reshape(T, k)
-    # 1. logits: exact for T <= 8, within one bf16 ulp of the exact product above
-    want_logits = O.bf16_linear(x, L.gate, 1)
-    ulp = bf16_ulp_diff(logits, want_logits)
+    # 1. logits: exact for T <= 8 (reference GEMV order); on the tensor cores
+    #    one bf16 rounding away from the exact product, up to fp32 summation noise
     if T <= 8:
-        assert ulp.max() == 0
+        assert np.array_equal(logits, O.bf16_linear(x, L.gate, 1))
     else:
-        assert ulp.max() <= 1
+        xf, gf = O.bf16_to_f32(x).astype(np.float64), O.bf16_to_f32(L.gate).astype(np.float64)
+        ref = xf @ gf.T
+        tol = 2.0 ** -8 * np.abs(ref) + 1e-5 * (np.abs(xf) @ np.abs(gf).T)
+        assert np.all(np.abs(O.bf16_to_f32(logits) - ref) <= tol)
     # 2. selection and weights from OUR logits must equal the oracle's on the same logits
     want_ids, want_rw = O.router_topk(logits, k)
     assert np.array_equal(ids, want_ids)
@@ -155,7 +157,8 @@ def test_batch_independence_at_scale(q4t, gpu_lib):
     bit-identical to the same rows run in a 64-token forward."""
     E, hs, is_, sis, k = 512, 2048, 512, 512, 10
     torch.manual_seed(0)
-    dl = synth_device_layer(q4t, E, hs, is_, sis)
+    import importlib
+    dl = importlib.import_module("qwen4-thor_b200.synthetic").device_layer(q4t, E, hs, is_, sis)
     T = 4096
     x = torch.randn((T, hs), device="cuda").to(torch.bfloat16)
     big = q4t.MoEForward(dl, T, k)
@@ -173,31 +176,3 @@ def test_batch_independence_at_scale(q4t, gpu_lib):
     diff = (a != b).float().mean().item()
     print(f"rows differing between T=4096 and T=64 batches: {diff:.3e}")
     assert diff == 0.0
-
-
-def synth_device_layer(q4t, E, hs, is_, sis, seed=0):
-    """Full-size synthetic layer built on the device: bf16 N(0, 0.02) weights
-    quantised by the library's own quantiser (itself checked bit-exact above)."""
-    g = torch.Generator(device="cuda").manual_seed(seed)
-    t = {}
-    def quant(rows, K):
-        w = (torch.randn((rows, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
-        gs = float(w.float().abs().max()) / (6.0 * 448.0)
-        p, s = q4t.quantize_activation_fp4(w, gs)
-        return p, s, gs
-    gu_p, gu_s, gu_g, dn_p, dn_s, dn_g = [], [], [], [], [], []
-    for e in range(E):
-        p, s, gs = quant(2 * is_, hs)
-        gu_p.append(p); gu_s.append(s); gu_g.append(gs)
-        p, s, gs = quant(hs, is_)
-        dn_p.append(p); dn_s.append(s); dn_g.append(gs)
-    t["gu_packed"] = torch.cat(gu_p); t["gu_sf"] = torch.cat(gu_s)
-    t["dn_packed"] = torch.cat(dn_p); t["dn_sf"] = torch.cat(dn_s)
-    t["gu_w_scale2"] = torch.tensor(gu_g, dtype=torch.float32, device="cuda")
-    t["dn_w_scale2"] = torch.tensor(dn_g, dtype=torch.float32, device="cuda")
-    t["gu_input_scale"] = torch.full((E,), 5.0 / (6 * 448), dtype=torch.float32, device="cuda")
-    t["dn_input_scale"] = torch.full((E,), 2.0 / (6 * 448), dtype=torch.float32, device="cuda")
-    for n, shape in (("gate", (E, hs)), ("shared_gu", (2 * sis, hs)), ("shared_down", (hs, sis)),
-                     ("shared_gate_scalar", (hs,))):
-        t[n] = (torch.randn(shape, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
-    return q4t.DeviceLayer(E, hs, is_, sis, t)

@@ -56,11 +56,14 @@ def test_tensor_core_linear(q4t, gpu_lib, M, N, K):
     x = O.f32_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
     w = O.f32_to_bf16((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
     got = host(q4t.bf16_linear(dev(x), dev(w)))
-    ref = O.bf16_to_f32(x).astype(np.float64) @ O.bf16_to_f32(w).astype(np.float64).T
-    want = O.f32_to_bf16(ref.astype(np.float32))
-    ulp = bf16_ulp_diff(got, want)
-    # fp32 accumulation then one bf16 rounding: at most one ulp off the exact result
-    assert ulp.max() <= 1, f"max ulp {ulp.max()}, mean {ulp.mean()}"
+    xf, wf = O.bf16_to_f32(x).astype(np.float64), O.bf16_to_f32(w).astype(np.float64)
+    ref = xf @ wf.T
+    # one bf16 rounding (2^-9 relative) on top of fp32 accumulation noise, which
+    # is bounded relative to the sum of the terms' magnitudes, not to the result
+    tol = 2.0 ** -8 * np.abs(ref) + 1e-5 * (np.abs(xf) @ np.abs(wf).T)
+    err = np.abs(O.bf16_to_f32(got).astype(np.float64) - ref)
+    assert np.all(err <= tol), f"worst excess {np.max(err - tol)}"
+    ulp = bf16_ulp_diff(got, O.f32_to_bf16(ref.astype(np.float32)))
     assert (ulp > 0).mean() < 0.02
 
 
