@@ -238,7 +238,7 @@ def main_single(args):
     q4t.load()
     torch.cuda.set_device(0)
     peaks = load_peaks()
-    n_layers = 1 if args.impl == "reference" else 4
+    n_layers = 1 if args.impl == "reference" else args.layers
     layers = [syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=20260921 + 1000 + i) for i in range(n_layers)]
 
     if args.impl == "reference":
@@ -300,7 +300,7 @@ def main_single(args):
                 dtype="nvfp4 (e2m1 x ue4m3, fp32 accumulate); bf16 router and shared expert", data="synthetic",
                 config=dict(workload="decode-shaped MoE layer microbench, T=128", hidden=HS, experts=E, top_k=K_TOP,
                             moe_intermediate=MOE_IS, shared_intermediate=SHARED_IS,
-                            l2="4 layer weight sets (3.6 GB) and 8 inputs rotated per step; one step touches ~840 MB > L2",
+                            l2=f"{args.layers} layer weight sets (0.9 GB each) and 8 inputs rotated per step; one step touches ~840 MB > L2",
                             unique_experts_per_step=main["unique_experts"]),
                 clocks=clk, e2e={k: v for k, v in main["e2e"].items() if k != "ms_per_step"},
                 gpu_launches=launches_per_step * args.steps, roofline=roofline, cpu_baseline=cpu,
@@ -316,6 +316,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--quick", action="store_true", help="headline point only (no sweep, no prefill)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", type=int, default=4, help="independent layer weight sets rotated per step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -62,6 +63,7 @@ int device_state(const DeviceState** out) {
     if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess)
       return fail(Q4T_ERR_DEVICE, "cuTensorMapEncodeTiled entry point unavailable");
     if ((e = q4t::gemm_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+    if ((e = q4t::routing_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     s.encode = reinterpret_cast<EncodeFn>(fn);
     s.num_sms = prop.multiProcessorCount;
     s.ready = true;
@@ -70,14 +72,14 @@ int device_state(const DeviceState** out) {
   return Q4T_OK;
 }
 
-// 2-D K-major tensor map whose box is 128 bytes x 128 rows, 128-byte swizzled.
+// 2-D K-major tensor map whose box is 128 bytes x box_rows rows, 128-byte swizzled.
 int make_tmap(const DeviceState* ds, CUtensorMap* tm, bool bf16, const void* base, uint64_t inner_elems,
-              uint64_t rows, uint64_t pitch_bytes) {
+              uint64_t rows, uint64_t pitch_bytes, uint32_t box_rows = 128) {
   if ((reinterpret_cast<uintptr_t>(base) & 15u) || (pitch_bytes & 15u))
     return fail(Q4T_ERR_INVALID, "operand base and row pitch must be 16-byte aligned");
   cuuint64_t dims[2] = {inner_elems, rows};
   cuuint64_t strides[1] = {pitch_bytes};
-  cuuint32_t box[2] = {bf16 ? 64u : 128u, 128u};
+  cuuint32_t box[2] = {bf16 ? 64u : 128u, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = ds->encode(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                           const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -285,21 +287,27 @@ int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w,
                     int K, cudaStream_t st) {
   cudaError_t e;
   if (M <= 8) {
-    if (K % 8) return fail(Q4T_ERR_INVALID, "K must be a multiple of 8");
+    if (K % 8 || static_cast<size_t>(M) * K * 2 > 98304)
+      return fail(Q4T_ERR_INVALID, "K must be a multiple of 8 and M*K at most 49152");
     if ((e = q4t::launch_small_m_linear(x, w, y, M, N, K, st)) != cudaSuccess) return fail_cuda("linear launch", e);
     return Q4T_OK;
   }
   if (K % 16 || N % 16) return fail(Q4T_ERR_INVALID, "K and N must be multiples of 16");
+  // few wide tiles would leave most SMs idle: use 64-column tiles then
+  const int m_tiles = (M + 127) / 128;
+  const bool narrow = m_tiles * ((N + 255) / 256) < ds->num_sms / 2 && N % 64 == 0;
+  const int cols = narrow ? 64 : 256;
   CUtensorMap ta, tb;
   int rc;
   if ((rc = make_tmap(ds, &ta, true, x, K, M, static_cast<uint64_t>(K) * 2)) != Q4T_OK) return rc;
-  if ((rc = make_tmap(ds, &tb, true, w, K, N, static_cast<uint64_t>(K) * 2)) != Q4T_OK) return rc;
+  if ((rc = make_tmap(ds, &tb, true, w, K, N, static_cast<uint64_t>(K) * 2, cols / 2)) != Q4T_OK) return rc;
   q4t::GemmArgs g{};
   g.K = K;
-  g.n_tiles = (N + 255) / 256;
-  g.n_per_tile = 256;
+  g.tile_cols = cols;
+  g.n_tiles = (N + cols - 1) / cols;
+  g.n_per_tile = cols;
   g.b_rows_valid = N;
-  g.ntiles_host = (M + 127) / 128;
+  g.ntiles_host = m_tiles;
   g.total_rows = M;
   g.out = y;
   g.ldo = N;
@@ -547,17 +555,22 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
     if ((rc = run_bf16_linear(ds, x, extra->shared_gu, sgu, T, 2 * sis, hs, st)) != Q4T_OK) return rc;
     if ((e = q4t::launch_swiglu(sgu, sact, T, sis, st)) != cudaSuccess) return fail_cuda("swiglu launch", e);
   } else {
+    const int m_tiles = (T + 127) / 128;
+    const bool narrow = m_tiles * (sis / 128) < ds->num_sms / 2;
+    const int cols = narrow ? 64 : 256;
     CUtensorMap ta, tb;
     if ((rc = make_tmap(ds, &ta, true, x, hs, T, static_cast<uint64_t>(hs) * 2)) != Q4T_OK) return rc;
-    if ((rc = make_tmap(ds, &tb, true, extra->shared_gu, hs, 2 * sis, static_cast<uint64_t>(hs) * 2)) != Q4T_OK)
+    if ((rc = make_tmap(ds, &tb, true, extra->shared_gu, hs, 2 * sis, static_cast<uint64_t>(hs) * 2, cols / 2)) !=
+        Q4T_OK)
       return rc;
     q4t::GemmArgs g{};
     g.K = hs;
-    g.n_tiles = sis / 128;
-    g.n_per_tile = 128;
+    g.tile_cols = cols;
+    g.n_tiles = sis / (cols / 2);
+    g.n_per_tile = cols / 2;
     g.up_row_offset = sis;
     g.b_rows_valid = sis;
-    g.ntiles_host = (T + 127) / 128;
+    g.ntiles_host = m_tiles;
     g.total_rows = T;
     g.out = sact;
     g.ldo = sis;

@@ -40,6 +40,7 @@ struct PlanTables {
   int32_t* flat_of_row;  // [R]
   int32_t* row_tile;     // [R]
 };
+cudaError_t routing_set_attributes();
 cudaError_t launch_small_m_linear(const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
                                   int K, cudaStream_t stream);
 cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw,
@@ -66,7 +67,8 @@ struct GemmArgs {
   // problem
   int K;                 // reduction length (elements)
   int n_tiles;           // column tiles per row tile
-  int n_per_tile;        // output columns produced per tile (256, or 128 for the SwiGLU epilogues)
+  int n_per_tile;        // output columns produced per tile (tile_cols, or half of it for the SwiGLU epilogues)
+  int tile_cols;         // accumulator columns per tile: 256 (0 means 256), or 64 for BF16 narrow tiles
   int up_row_offset;     // SwiGLU: row distance between a gate row and its up row in B
   int b_rows_per_group;  // rows of B belonging to one expert (0 for a dense GEMM)
   int b_rows_valid;      // output columns that exist (N); columns beyond are neither loaded as scales nor stored

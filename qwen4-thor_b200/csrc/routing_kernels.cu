@@ -17,6 +17,11 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const uint16_t* __r
                                                              const uint16_t* __restrict__ w,
                                                              uint16_t* __restrict__ y, int M, int N,
                                                              int K) {
+  extern __shared__ __align__(16) uint16_t s_x[];  // [M, K], loaded once per block
+  const int k8 = K >> 3;
+  for (int i = threadIdx.x; i < M * k8; i += 256)
+    reinterpret_cast<uint4*>(s_x)[i] = __ldg(reinterpret_cast<const uint4*>(x) + i);
+  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 8 + warp;
   if (n >= N) return;
@@ -24,19 +29,29 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const uint16_t* __r
   float ax[MAXM], ay[MAXM];
 #pragma unroll
   for (int m = 0; m < MAXM; ++m) ax[m] = ay[m] = 0.0f;
-  const int k8 = K >> 3;
-  for (int i = lane; i < k8; i += 32) {
-    const uint4 wv = __ldg(wrow + i);
-    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+  // chunks lane, lane+32, ... in order; the weight loads of eight chunks are
+  // issued together so that their latencies overlap
+  for (int i0 = lane; i0 < k8; i0 += 32 * 8) {
+    uint4 wv[8];
 #pragma unroll
-    for (int m = 0; m < MAXM; ++m) {
-      if (m < M) {
-        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * K) + i);
-        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    for (int u = 0; u < 8; ++u)
+      if (i0 + 32 * u < k8) wv[u] = __ldg(wrow + i0 + 32 * u);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          ax[m] = fmaf(bf16x2_lo(xw[j]), bf16x2_lo(ww[j]), ax[m]);
-          ay[m] = fmaf(bf16x2_hi(xw[j]), bf16x2_hi(ww[j]), ay[m]);
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + 32 * u;
+      if (i < k8) {
+        const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+#pragma unroll
+        for (int m = 0; m < MAXM; ++m) {
+          if (m < M) {
+            const uint4 xv = reinterpret_cast<const uint4*>(s_x + static_cast<size_t>(m) * K)[i];
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              ax[m] = fmaf(bf16x2_lo(xw[j]), bf16x2_lo(ww[j]), ax[m]);
+              ay[m] = fmaf(bf16x2_hi(xw[j]), bf16x2_hi(ww[j]), ay[m]);
+            }
+          }
         }
       }
     }
@@ -222,6 +237,100 @@ __global__ void __launch_bounds__(256) plan_scatter_kernel(const int32_t* __rest
   }
 }
 
+// Whole permutation in one block for small batches (R <= kPlanSmallMax): the
+// 32 warps each own a contiguous segment of the (token,slot) entries.  Per-warp
+// expert counts, a per-expert scan over the warps, the block scan that yields
+// offsets and the row-tile list, then every warp places its own entries in
+// order using its private cursors, so the result is the stable order.
+constexpr int kPlanSmallMax = 4096;
+__global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* __restrict__ ids, int R, int E,
+                                                          int max_tiles, PlanTables p) {
+  extern __shared__ uint16_t s_cnt[];  // [32][E]: counts, later exclusive bases, then cursors
+  __shared__ int32_t s_rows[1024];
+  __shared__ int32_t s_tiles[1024];
+  const int e = threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * E; i += 1024) s_cnt[i] = 0;
+  __syncthreads();
+  const int seg = (R + 31) / 32;
+  const int f0 = warp * seg, f1 = min(R, f0 + seg);
+  uint16_t* mine = s_cnt + warp * E;
+  for (int fb = f0; fb < f1; fb += 32) {
+    const int f = fb + lane;
+    const int v = f < f1 ? ids[f] : -1;
+    const bool valid = v >= 0 && v < E;
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? v : -1 - lane);
+    if (valid && __popc(peers & ((1u << lane) - 1u)) == 0) mine[v] += static_cast<uint16_t>(__popc(peers));
+    __syncwarp();
+  }
+  __syncthreads();
+  int32_t c = 0;
+  if (e < E) {
+    for (int w = 0; w < 32; ++w) {
+      const int32_t v = s_cnt[w * E + e];
+      s_cnt[w * E + e] = static_cast<uint16_t>(c);
+      c += v;
+    }
+  }
+  const int32_t tiles = (c + kTileM - 1) / kTileM;
+  s_rows[e] = c;
+  s_tiles[e] = tiles;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    int32_t a = 0, b = 0;
+    if (e >= off) {
+      a = s_rows[e - off];
+      b = s_tiles[e - off];
+    }
+    __syncthreads();
+    s_rows[e] += a;
+    s_tiles[e] += b;
+    __syncthreads();
+  }
+  const int32_t row_base = s_rows[e] - c, tile_base = s_tiles[e] - tiles;
+  const int32_t total_rows = s_rows[1023], total_tiles = s_tiles[1023];
+  __syncthreads();
+  s_rows[e] = row_base;   // from here on: first grouped row / first row tile of expert e
+  s_tiles[e] = tile_base;
+  if (e < E) {
+    p.counts[e] = c;
+    p.offsets[e] = row_base;
+    p.tile_off[e] = tile_base;
+    for (int i = 0; i < tiles; ++i) {
+      const int t = tile_base + i;
+      if (t < max_tiles) {
+        p.tile_expert[t] = e;
+        p.tile_row0[t] = row_base + i * kTileM;
+        p.tile_nrows[t] = min(kTileM, c - i * kTileM);
+      }
+    }
+  }
+  if (e == 0) {
+    p.offsets[E] = total_rows;
+    p.tile_off[E] = total_tiles;
+    p.ntiles[0] = min(total_tiles, max_tiles);
+  }
+  __syncthreads();
+  for (int fb = f0; fb < f1; fb += 32) {
+    const int f = fb + lane;
+    const int v = f < f1 ? ids[f] : -1;
+    const bool valid = v >= 0 && v < E;
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? v : -1 - lane);
+    if (valid) {
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int in_expert = mine[v] + rank;
+      const int row = s_rows[v] + in_expert;
+      __syncwarp(peers);
+      if (rank == 0) mine[v] += static_cast<uint16_t>(__popc(peers));
+      p.row_of_flat[f] = row;
+      p.flat_of_row[row] = f;
+      p.row_tile[row] = s_tiles[v] + in_expert / kTileM;
+    } else if (f < f1) {
+      p.row_of_flat[f] = -1;
+    }
+    __syncwarp();
+  }
+}
+
 // y[t, c] += sum over slots, in slot order, of w * bf16 row value, accumulated
 // by fused multiply-add from 0 (CombineGroupedKernel, src/quant/moe_gemm.cu:
 // 273-288).  One thread per 8 columns.
@@ -329,12 +438,24 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
 
 }  // namespace
 
+cudaError_t routing_set_attributes() {
+  cudaError_t e;
+  if ((e = cudaFuncSetAttribute(plan_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536)) != cudaSuccess)
+    return e;
+  if ((e = cudaFuncSetAttribute(small_m_linear_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304)) != cudaSuccess)
+    return e;
+  if ((e = cudaFuncSetAttribute(small_m_linear_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304)) != cudaSuccess)
+    return e;
+  return cudaFuncSetAttribute(small_m_linear_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304);
+}
+
 cudaError_t launch_small_m_linear(const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
                                   int K, cudaStream_t stream) {
   const unsigned blocks = static_cast<unsigned>((N + 7) / 8);
-  if (M <= 1) small_m_linear_kernel<1><<<blocks, 256, 0, stream>>>(x, w, y, M, N, K);
-  else if (M <= 4) small_m_linear_kernel<4><<<blocks, 256, 0, stream>>>(x, w, y, M, N, K);
-  else small_m_linear_kernel<8><<<blocks, 256, 0, stream>>>(x, w, y, M, N, K);
+  const size_t smem = static_cast<size_t>(M) * K * sizeof(uint16_t);
+  if (M <= 1) small_m_linear_kernel<1><<<blocks, 256, smem, stream>>>(x, w, y, M, N, K);
+  else if (M <= 4) small_m_linear_kernel<4><<<blocks, 256, smem, stream>>>(x, w, y, M, N, K);
+  else small_m_linear_kernel<8><<<blocks, 256, smem, stream>>>(x, w, y, M, N, K);
   return cudaGetLastError();
 }
 
@@ -346,6 +467,10 @@ cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_
 
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
                         cudaStream_t stream) {
+  if (R <= kPlanSmallMax) {
+    plan_small_kernel<<<1, 1024, 32 * E * sizeof(uint16_t), stream>>>(ids, R, E, max_tiles, p);
+    return cudaGetLastError();
+  }
   const int nblk = (R + kPlanChunk - 1) / kPlanChunk;
   plan_hist_kernel<<<nblk, 256, E * sizeof(int32_t), stream>>>(ids, R, E, p.blk_counts);
   plan_scan_kernel<<<1, 1024, 0, stream>>>(nblk, E, max_tiles, p);

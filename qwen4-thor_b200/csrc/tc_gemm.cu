@@ -8,10 +8,11 @@
 //                 grouped over experts through a row-tile list.
 //   NVF4 = false: kind::f16 MMA on bf16 operands (router logits, shared expert).
 //
-// Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
-// owner, warps 4..7 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31, i.e.
-// one output row per thread).  Stages hand over through mbarriers; every wait
-// is bounded and raises a status word instead of spinning forever.
+// Warp roles (576 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2..17 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31, i.e.
+// one output row per thread; the four warps of a quadrant split the columns).
+// Stages hand over through mbarriers; every wait is bounded and raises a
+// status word instead of spinning forever.
 //
 // A tile's 256 accumulator columns are either 256 consecutive output columns
 // or, for the SwiGLU epilogues, 128 gate columns followed by the 128 matching
@@ -24,18 +25,20 @@ namespace q4t {
 namespace {
 
 constexpr int kStages = 4;
-constexpr int kThreads = 256;
-constexpr uint32_t kABytes = 128 * 128;       // 128 rows x 128 bytes
-constexpr uint32_t kBBytes = 256 * 128;       // 256 rows x 128 bytes
-constexpr uint32_t kSfaBytes = 4 * 512;       // 4 atoms (one per MMA of a k-block)
-constexpr uint32_t kSfbBytes = 8 * 512;       // 2 x 4 atoms
+constexpr int kEpiWarpsPerQuad = 4;                       // epilogue warps sharing one TMEM lane quadrant
+constexpr int kEpiWarps = 4 * kEpiWarpsPerQuad;
+constexpr int kFirstEpiWarp = 2;                          // warp 0: producer, warp 1: MMA issuer
+constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
+constexpr uint32_t kABytes = 128 * 128;                   // 128 rows x 128 bytes
+constexpr uint32_t kSfaBytes = 4 * 512;                   // 4 atoms (one per MMA of a k-block)
+constexpr uint32_t kSfbBytes = 8 * 512;                   // 2 x 4 atoms
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSfTmemBase = 256;         // scale columns start after the accumulator
-constexpr uint32_t kSfTmemPerStage = 48;      // 16 (A) + 32 (B)
+constexpr uint32_t kSfTmemBase = 256;                     // scale columns start after the accumulator
+constexpr uint32_t kSfTmemPerStage = 48;                  // 16 (A) + 32 (B)
 
-template <bool NVF4>
+template <bool NVF4, int BN>
 constexpr uint32_t stage_bytes() {
-  return kABytes + kBBytes + (NVF4 ? kSfaBytes + kSfbBytes : 0u);
+  return kABytes + BN * 128 + (NVF4 ? kSfaBytes + kSfbBytes : 0u);
 }
 
 struct Barriers {
@@ -49,15 +52,19 @@ struct Barriers {
 
 __device__ __forceinline__ float sigmoid_ref(float g) { return __frcp_rn(1.0f + __expf(-g)); }
 
-template <bool NVF4, Epilogue EPI>
+// BN = accumulator columns of one tile (256, or 64 for the narrow BF16 tiles
+// that spread small-T projections over more SMs).
+template <bool NVF4, Epilogue EPI, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const GemmArgs args) {
+  static_assert(!NVF4 || BN == 256, "block-scaled tiles are 256 columns wide");
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  constexpr uint32_t kStage = stage_bytes<NVF4>();
+  constexpr uint32_t kBBytes = BN * 128;
+  constexpr uint32_t kStage = stage_bytes<NVF4, BN>();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile uint32_t* abort_flag = &bars.abort_flag;
 
@@ -67,7 +74,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(smem_u32(&bars.empty[s]), 1);
     }
     mbar_init(smem_u32(&bars.acc_full), 1);
-    mbar_init(smem_u32(&bars.acc_empty), 4);
+    mbar_init(smem_u32(&bars.acc_empty), kEpiWarps);
     bars.abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
@@ -85,6 +92,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int m_tiles = args.ntiles_dev ? *args.ntiles_dev : args.ntiles_host;
   const int total_tiles = m_tiles * args.n_tiles;
   constexpr bool kSwiglu = (EPI == Epilogue::kSwigluBf16 || EPI == Epilogue::kSwigluQuant);
+  constexpr int kHalf = BN / 2;  // SwiGLU: gate columns [0, kHalf), up columns [kHalf, BN)
   // bytes of K covered by one row: NVF4 packs two elements per byte
   const uint32_t k_bytes = NVF4 ? static_cast<uint32_t>(args.K) >> 1 : static_cast<uint32_t>(args.K) << 1;
   const int nkb = static_cast<int>((k_bytes + 127u) >> 7);
@@ -96,41 +104,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint32_t bar_full0 = smem_u32(&bars.full[0]), bar_empty0 = smem_u32(&bars.empty[0]);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int mt = tile / args.n_tiles, nt = tile - mt * args.n_tiles;
         const int group = args.tile_expert ? args.tile_expert[mt] : 0;
         const int row0 = args.tile_expert ? args.tile_row0[mt] : mt * kTileM;
         const int brow0 = group * args.b_rows_per_group + nt * args.n_per_tile;
-        const int brow1 = brow0 + (kSwiglu ? args.up_row_offset : 128);
+        const int brow1 = brow0 + (kSwiglu ? args.up_row_offset : kHalf);
         // scale atoms of B: row blocks of 128 inside the group's buffer
         const uint32_t rb0 = static_cast<uint32_t>(nt * args.n_per_tile) >> 7;
         const uint32_t rb1 = rb0 + (kSwiglu ? static_cast<uint32_t>(args.up_row_offset) >> 7 : 1u);
         const bool second_half = kSwiglu || (nt * args.n_per_tile + 128 < args.b_rows_valid);
+        // per-tile bases; the k loop below only adds constants
+        const uint8_t* ga = NVF4 ? args.sfa_tiles + static_cast<size_t>(mt) * ntk * 512u : nullptr;
+        const uint8_t* gbase = NVF4 ? args.sfb + static_cast<size_t>(group) * args.sfb_group_stride : nullptr;
+        const uint8_t* gb0 = NVF4 ? gbase + static_cast<size_t>(rb0) * ntk * 512u : nullptr;
+        const uint8_t* gb1 = NVF4 ? gbase + static_cast<size_t>(rb1) * ntk * 512u : nullptr;
+        uint32_t k_left = k_bytes;
+        int kc = 0;
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(smem_u32(&bars.empty[stage]), phase ^ 1u, abort_flag)) {
+          const uint32_t full = bar_full0 + stage * 8u, empty = bar_empty0 + stage * 8u;
+          if (!mbar_try_wait(empty, phase ^ 1u) && !mbar_wait(empty, phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
-          const uint32_t nm = min(4u, (k_bytes - static_cast<uint32_t>(kb) * 128u) >> 5);
+          const uint32_t nm = k_left >= 128u ? 4u : k_left >> 5;
           const uint32_t sa = smem_base + stage * kStage, sb = sa + kABytes;
-          const uint32_t full = smem_u32(&bars.full[stage]);
           uint32_t tx = kABytes + kBBytes;
           if (NVF4) tx += nm * 512u * (second_half ? 3u : 2u);
           mbar_expect_tx(full, tx);
-          const int kc = kb * (NVF4 ? 128 : 64);  // inner coordinate in tensor-map elements
           tma_load_2d(sa, &tmap_a, kc, row0, full);
-          tma_load_2d(sb, &tmap_b, kc, brow0, full);
+          tma_load_2d(sb, &tmap_b, kc, brow0, full);            // box = kHalf rows
           tma_load_2d(sb + kBBytes / 2, &tmap_b, kc, brow1, full);
           if (NVF4) {
             const uint32_t ssfa = sb + kBBytes, ssfb = ssfa + kSfaBytes;
-            const uint8_t* ga = args.sfa_tiles + (static_cast<size_t>(mt) * ntk + kb * 4u) * 512u;
-            const uint8_t* gb = args.sfb + static_cast<size_t>(group) * args.sfb_group_stride;
             bulk_load(ssfa, ga, nm * 512u, full);
-            bulk_load(ssfb, gb + (static_cast<size_t>(rb0) * ntk + kb * 4u) * 512u, nm * 512u, full);
-            if (second_half)
-              bulk_load(ssfb + kSfbBytes / 2, gb + (static_cast<size_t>(rb1) * ntk + kb * 4u) * 512u,
-                        nm * 512u, full);
+            bulk_load(ssfb, gb0, nm * 512u, full);
+            if (second_half) bulk_load(ssfb + kSfbBytes / 2, gb1, nm * 512u, full);
+            ga += 2048;
+            gb0 += 2048;
+            gb1 += 2048;
           }
+          kc += NVF4 ? 128 : 64;  // inner coordinate in tensor-map elements
+          k_left -= 128u;
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -142,60 +158,100 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // instruction descriptors (M = 128, N = 256, both operands K-major)
-      constexpr uint32_t idesc_nvf4 = (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
-      constexpr uint32_t idesc_bf16 =
-          (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+      // instruction descriptors (M = 128, N = BN, both operands K-major)
+      constexpr uint32_t idesc_nvf4 =
+          (1u << 7) | (1u << 10) | ((static_cast<uint32_t>(BN) >> 3) << 17) | ((128u >> 4) << 24);
+      constexpr uint32_t idesc_bf16 = (1u << 4) | (1u << 7) | (1u << 10) |
+                                      ((static_cast<uint32_t>(BN) >> 3) << 17) | ((128u >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      // descriptors of stage 0; later stages differ by a constant in the
+      // 14-bit start-address field, so plain 64-bit adds never carry out of it
+      const uint64_t adesc0 = umma_desc_sw128(smem_base), bdesc0 = umma_desc_sw128(smem_base + kABytes);
+      const uint64_t sfa0 = umma_desc_sf(smem_base + kABytes + kBBytes);
+      const uint64_t sfb0 = umma_desc_sf(smem_base + kABytes + kBBytes + kSfaBytes);
+      const uint32_t bar_full0 = smem_u32(&bars.full[0]), bar_empty0 = smem_u32(&bars.empty[0]);
+      const uint32_t bar_acc_full = smem_u32(&bars.acc_full), bar_acc_empty = smem_u32(&bars.acc_empty);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(smem_u32(&bars.acc_empty), acc_phase ^ 1u, abort_flag)) {
+        if (!mbar_try_wait(bar_acc_empty, acc_phase ^ 1u) && !mbar_wait(bar_acc_empty, acc_phase ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        uint32_t k_left = k_bytes;
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(smem_u32(&bars.full[stage]), phase, abort_flag)) {
+          const uint32_t full = bar_full0 + stage * 8u;
+          if (!mbar_try_wait(full, phase) && !mbar_wait(full, phase, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t nm = min(4u, (k_bytes - static_cast<uint32_t>(kb) * 128u) >> 5);
-          const uint32_t sa = smem_base + stage * kStage, sb = sa + kABytes;
-          const uint64_t adesc = umma_desc_sw128(sa), bdesc = umma_desc_sw128(sb);
+          const uint64_t soff = static_cast<uint64_t>(stage * (kStage >> 4));
+          const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
+          const uint32_t first = kb != 0;
           if (NVF4) {
-            const uint32_t ssfa = sb + kBBytes, ssfb = ssfa + kSfaBytes;
+            const uint64_t sfa = sfa0 + soff, sfb = sfb0 + soff;
             const uint32_t tsf = tmem + kSfTmemBase + stage * kSfTmemPerStage;
-            for (uint32_t kk = 0; kk < nm; ++kk) {
-              tc_cp_sf(tsf + kk * 4u, umma_desc_sf(ssfa + kk * 512u));
-              tc_cp_sf(tsf + 16u + kk * 8u, umma_desc_sf(ssfb + kk * 512u));
-              tc_cp_sf(tsf + 16u + kk * 8u + 4u, umma_desc_sf(ssfb + kSfbBytes / 2 + kk * 512u));
+            if (k_left >= 128u) {
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4; ++kk) {
+                tc_cp_sf(tsf + kk * 4u, sfa + kk * 32u);
+                tc_cp_sf(tsf + 16u + kk * 8u, sfb + kk * 32u);
+                tc_cp_sf(tsf + 20u + kk * 8u, sfb + (kSfbBytes / 32) + kk * 32u);
+              }
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4; ++kk)
+                tc_mma_nvf4(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_nvf4, tsf + kk * 4u,
+                            tsf + 16u + kk * 8u, kk == 0 ? first : 1u);
+            } else {
+              const uint32_t nm = k_left >> 5;
+              for (uint32_t kk = 0; kk < nm; ++kk) {
+                tc_cp_sf(tsf + kk * 4u, sfa + kk * 32u);
+                tc_cp_sf(tsf + 16u + kk * 8u, sfb + kk * 32u);
+                tc_cp_sf(tsf + 20u + kk * 8u, sfb + (kSfbBytes / 32) + kk * 32u);
+              }
+              for (uint32_t kk = 0; kk < nm; ++kk)
+                tc_mma_nvf4(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_nvf4, tsf + kk * 4u,
+                            tsf + 16u + kk * 8u, kk == 0 ? first : 1u);
             }
-            for (uint32_t kk = 0; kk < nm; ++kk)
-              tc_mma_nvf4(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_nvf4, tsf + kk * 4u,
-                          tsf + 16u + kk * 8u, (kb | static_cast<int>(kk)) != 0);
           } else {
-            for (uint32_t kk = 0; kk < nm; ++kk)
-              tc_mma_f16(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_bf16,
-                         (kb | static_cast<int>(kk)) != 0);
+            if (k_left >= 128u) {
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4; ++kk)
+                tc_mma_f16(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_bf16, kk == 0 ? first : 1u);
+            } else {
+              const uint32_t nm = k_left >> 5;
+              for (uint32_t kk = 0; kk < nm; ++kk)
+                tc_mma_f16(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_bf16, kk == 0 ? first : 1u);
+            }
           }
-          tc_commit(smem_u32(&bars.empty[stage]));  // frees the stage once these MMAs have read it
+          tc_commit(bar_empty0 + stage * 8u);  // frees the stage once these MMAs have read it
+          k_left -= 128u;
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) tc_commit(smem_u32(&bars.acc_full));
+        if (ok) tc_commit(bar_acc_full);
         acc_phase ^= 1u;
       }
       if (!ok && args.status) atomicMax(args.status, 2);
     }
-  } else if (warp >= 4) {
+  } else if (warp >= kFirstEpiWarp) {
     // ------------------------------------------------------------ epilogue
+    // Four warps share each TMEM lane quadrant and split the tile's columns
+    // into units of 16 (store) or 16 gate + 16 up (SwiGLU).  A warp first
+    // drains its units into registers (rounded to bf16 where the result is
+    // bf16 anyway), hands the accumulator back, and only then does the math
+    // and the stores, so the next tile's MMAs overlap with this work.
     const int quad = warp & 3;
+    const int sub = (warp - kFirstEpiWarp) >> 2;  // 0..3 within the quadrant
     const int row = quad * 32 + lane;
     const uint32_t tacc = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+    constexpr int kUnitCols = 16;
+    constexpr int kUnits = kSwiglu ? kHalf / kUnitCols : BN / kUnitCols;
+    constexpr int kUnitsPerWarp = (kUnits + kEpiWarpsPerQuad - 1) / kEpiWarpsPerQuad;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -211,111 +267,122 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
       tc_fence_after();
       const bool valid = row < nrows;
+      const bool warp_has_rows = quad * 32 < nrows;  // warp-uniform
       const size_t grow = static_cast<size_t>(row0 + row);
-      if (quad * 32 < nrows) {  // warp-uniform: skip quadrants without rows
-        if constexpr (!kSwiglu) {
-          const int n0 = nt * 256;
-#pragma unroll 1
-          for (int c0 = 0; c0 < 256; c0 += 16) {
-            if (n0 + c0 >= args.b_rows_valid) break;  // uniform
-            uint32_t r[16];
-            tmem_ld16(tacc + c0, r);
-            tmem_ld_wait();
-            if (valid) {
-              if constexpr (EPI == Epilogue::kStoreBf16) {
-                uint32_t o[8];
+      const int n0 = nt * args.n_per_tile;            // first output column of this tile
+
+      // ---- drain this warp's units into registers, then hand the accumulator
+      // back to the MMA warp before doing any arithmetic on them
+      uint32_t ra[kUnitsPerWarp][16];                 // store: 16 columns; SwiGLU: 16 gate columns
+      uint32_t rb[kSwiglu ? kUnitsPerWarp : 1][16];   // SwiGLU: the 16 matching up columns
+      if (warp_has_rows) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  o[j] = f32x2_to_bf16x2(alpha * __uint_as_float(r[2 * j]),
-                                         alpha * __uint_as_float(r[2 * j + 1]));
-                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) +
-                                                      grow * args.ldo + n0 + c0);
-                dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-              } else {
-                float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.out) +
-                                                        grow * args.ldo + n0 + c0);
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  dst[j] = make_float4(alpha * __uint_as_float(r[4 * j]),
-                                       alpha * __uint_as_float(r[4 * j + 1]),
-                                       alpha * __uint_as_float(r[4 * j + 2]),
-                                       alpha * __uint_as_float(r[4 * j + 3]));
-              }
-            }
-          }
-        } else {
-          const int n0 = nt * 128;  // first intermediate column of this tile
-          float next_scale = 1.0f;
-          if constexpr (EPI == Epilogue::kSwigluQuant) next_scale = args.next_scale[group];
-          const uint32_t out_ntk = (static_cast<uint32_t>(args.up_row_offset) + 63u) >> 6;
-          uint32_t sf_word = 0;
-#pragma unroll 1
-          for (int c0 = 0; c0 < 128; c0 += 16) {
-            uint32_t rg[16], ru[16];
-            tmem_ld16(tacc + c0, rg);
-            tmem_ld16(tacc + 128 + c0, ru);
-            tmem_ld_wait();
-            // the reference rounds the projection output to bf16 before SwiGLU
-            uint32_t gb[8], ub[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              gb[j] = f32x2_to_bf16x2(alpha * __uint_as_float(rg[2 * j]),
-                                      alpha * __uint_as_float(rg[2 * j + 1]));
-              ub[j] = f32x2_to_bf16x2(alpha * __uint_as_float(ru[2 * j]),
-                                      alpha * __uint_as_float(ru[2 * j + 1]));
-            }
-            if (args.gu_dump && valid) {
-              uint4* dg = reinterpret_cast<uint4*>(args.gu_dump + grow * args.gu_dump_ld + n0 + c0);
-              dg[0] = make_uint4(gb[0], gb[1], gb[2], gb[3]);
-              dg[1] = make_uint4(gb[4], gb[5], gb[6], gb[7]);
-              uint4* du = reinterpret_cast<uint4*>(args.gu_dump + grow * args.gu_dump_ld +
-                                                   args.up_row_offset + n0 + c0);
-              du[0] = make_uint4(ub[0], ub[1], ub[2], ub[3]);
-              du[1] = make_uint4(ub[4], ub[5], ub[6], ub[7]);
-            }
-            float a[16];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float g0 = bf16x2_lo(gb[j]), g1 = bf16x2_hi(gb[j]);
-              const float u0 = bf16x2_lo(ub[j]), u1 = bf16x2_hi(ub[j]);
-              a[2 * j] = (g0 * sigmoid_ref(g0)) * u0;
-              a[2 * j + 1] = (g1 * sigmoid_ref(g1)) * u1;
-            }
-            if constexpr (EPI == Epilogue::kSwigluBf16) {
-              if (valid) {
-                uint32_t o[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = f32x2_to_bf16x2(a[2 * j], a[2 * j + 1]);
-                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) +
-                                                      grow * args.ldo + n0 + c0);
-                dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-              }
-            } else {
-              uint32_t lo, hi;
-              const uint32_t sf = quantize_group16(a, next_scale, lo, hi);
-              sf_word |= sf << (8 * ((c0 >> 4) & 3));
-              if (valid) {
-                *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + grow * args.ldo +
-                                          ((n0 + c0) >> 1)) = make_uint2(lo, hi);
-                if (((c0 >> 4) & 3) == 3) {
-                  uint8_t* dst = args.out_sf_tiles +
-                                 (static_cast<size_t>(mt) * out_ntk + ((n0 + c0) >> 6)) * 512u +
-                                 sf_in_atom(row, 0);
-                  *reinterpret_cast<uint32_t*>(dst) = sf_word;
-                }
-              }
-              if (((c0 >> 4) & 3) == 3) sf_word = 0;
-            }
+        for (int j = 0; j < kUnitsPerWarp; ++j) {
+          const int unit = sub * kUnitsPerWarp + j;
+          if (unit < kUnits) {
+            tmem_ld16(tacc + unit * kUnitCols, ra[j]);
+            if constexpr (kSwiglu) tmem_ld16(tacc + kHalf + unit * kUnitCols, rb[j]);
           }
         }
+        tmem_ld_wait();
       }
-      // hand the accumulator back to the MMA warp
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty));
       acc_phase ^= 1u;
+      if (!warp_has_rows) continue;
+
+      // bf16x2 words (g then u for SwiGLU).  Rows past the tile's row count carry
+      // stale accumulator bits: zero them so the arithmetic below never meets
+      // NaNs or denormals.
+      uint32_t packed[kUnitsPerWarp][kSwiglu ? 16 : 8];
+      float raw[(EPI == Epilogue::kStoreF32) ? kUnitsPerWarp : 1][16];
+#pragma unroll
+      for (int j = 0; j < kUnitsPerWarp; ++j) {
+        if constexpr (EPI == Epilogue::kStoreF32) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) raw[j][i] = valid ? alpha * __uint_as_float(ra[j][i]) : 0.0f;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float lo = valid ? alpha * __uint_as_float(ra[j][2 * i]) : 0.0f;
+            const float hi = valid ? alpha * __uint_as_float(ra[j][2 * i + 1]) : 0.0f;
+            packed[j][i] = f32x2_to_bf16x2(lo, hi);
+          }
+          if constexpr (kSwiglu) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float lo = valid ? alpha * __uint_as_float(rb[j][2 * i]) : 0.0f;
+              const float hi = valid ? alpha * __uint_as_float(rb[j][2 * i + 1]) : 0.0f;
+              packed[j][8 + i] = f32x2_to_bf16x2(lo, hi);
+            }
+          }
+        }
+      }
+
+      // ---- math and stores from registers
+#pragma unroll
+      for (int j = 0; j < kUnitsPerWarp; ++j) {
+        const int unit = sub * kUnitsPerWarp + j;
+        if (unit >= kUnits) continue;
+        const int c0 = unit * kUnitCols;
+        if constexpr (EPI == Epilogue::kStoreBf16) {
+          if (valid && n0 + c0 < args.b_rows_valid) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) + grow * args.ldo + n0 + c0);
+            dst[0] = make_uint4(packed[j][0], packed[j][1], packed[j][2], packed[j][3]);
+            dst[1] = make_uint4(packed[j][4], packed[j][5], packed[j][6], packed[j][7]);
+          }
+        } else if constexpr (EPI == Epilogue::kStoreF32) {
+          if (valid && n0 + c0 < args.b_rows_valid) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.out) + grow * args.ldo + n0 + c0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              dst[i] = make_float4(raw[j][4 * i], raw[j][4 * i + 1], raw[j][4 * i + 2], raw[j][4 * i + 3]);
+          }
+        } else {
+          const uint32_t* gb = &packed[j][0];
+          const uint32_t* ub = &packed[j][8];
+          if (args.gu_dump && valid) {
+            uint4* dg = reinterpret_cast<uint4*>(args.gu_dump + grow * args.gu_dump_ld + n0 + c0);
+            dg[0] = make_uint4(gb[0], gb[1], gb[2], gb[3]);
+            dg[1] = make_uint4(gb[4], gb[5], gb[6], gb[7]);
+            uint4* du = reinterpret_cast<uint4*>(args.gu_dump + grow * args.gu_dump_ld + args.up_row_offset + n0 + c0);
+            du[0] = make_uint4(ub[0], ub[1], ub[2], ub[3]);
+            du[1] = make_uint4(ub[4], ub[5], ub[6], ub[7]);
+          }
+          // SwiGLU on the bf16-rounded projections: (g * sigmoid(g)) * u
+          float a[16];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float g0 = bf16x2_lo(gb[i]), g1 = bf16x2_hi(gb[i]);
+            const float u0 = bf16x2_lo(ub[i]), u1 = bf16x2_hi(ub[i]);
+            a[2 * i] = (g0 * sigmoid_ref(g0)) * u0;
+            a[2 * i + 1] = (g1 * sigmoid_ref(g1)) * u1;
+          }
+          if constexpr (EPI == Epilogue::kSwigluBf16) {
+            if (valid) {
+              uint32_t o[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = f32x2_to_bf16x2(a[2 * i], a[2 * i + 1]);
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) + grow * args.ldo + n0 + c0);
+              dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+          } else {
+            const float next_scale = args.next_scale[group];
+            const uint32_t out_ntk = (static_cast<uint32_t>(args.up_row_offset) + 63u) >> 6;
+            uint32_t lo, hi;
+            const uint32_t sf = quantize_group16(a, next_scale, lo, hi);
+            if (valid) {
+              *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + grow * args.ldo + ((n0 + c0) >> 1)) =
+                  make_uint2(lo, hi);
+              const uint32_t g = static_cast<uint32_t>(n0 + c0) >> 4;  // scale group along the intermediate
+              args.out_sf_tiles[(static_cast<size_t>(mt) * out_ntk + (g >> 2)) * 512u + sf_in_atom(row, g)] =
+                  static_cast<uint8_t>(sf);
+            }
+          }
+        }
+      }
     }
     if (!ok && args.status && lane == 0) atomicMax(args.status, 3);
   }
@@ -328,55 +395,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
-template <bool NVF4>
+template <bool NVF4, int BN>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, Epilogue epi,
                    int num_sms, cudaStream_t stream) {
-  const size_t smem = kStages * stage_bytes<NVF4>() + 1024;
-  const int m_tiles_bound = a.ntiles_dev ? num_sms : a.ntiles_host;
-  int grid = a.ntiles_dev ? num_sms : min(num_sms, m_tiles_bound * a.n_tiles);
+  const size_t smem = kStages * stage_bytes<NVF4, BN>() + 1024;
+  const int grid = a.ntiles_dev ? num_sms : min(num_sms, a.ntiles_host * a.n_tiles);
   if (grid <= 0) return cudaSuccess;
-#define Q4T_LAUNCH(E)                                                                          \
-  gemm_kernel<NVF4, E><<<grid, kThreads, smem, stream>>>(ta, tb, a);                           \
-  break
   switch (epi) {
-    case Epilogue::kStoreBf16: Q4T_LAUNCH(Epilogue::kStoreBf16);
-    case Epilogue::kStoreF32: Q4T_LAUNCH(Epilogue::kStoreF32);
-    case Epilogue::kSwigluBf16: Q4T_LAUNCH(Epilogue::kSwigluBf16);
-    case Epilogue::kSwigluQuant: Q4T_LAUNCH(Epilogue::kSwigluQuant);
+    case Epilogue::kStoreBf16:
+      gemm_kernel<NVF4, Epilogue::kStoreBf16, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
+      break;
+    case Epilogue::kStoreF32:
+      gemm_kernel<NVF4, Epilogue::kStoreF32, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
+      break;
+    case Epilogue::kSwigluBf16:
+      gemm_kernel<NVF4, Epilogue::kSwigluBf16, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
+      break;
+    case Epilogue::kSwigluQuant:
+      if constexpr (NVF4) {
+        gemm_kernel<NVF4, Epilogue::kSwigluQuant, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
+        break;
+      } else {
+        return cudaErrorInvalidValue;
+      }
   }
-#undef Q4T_LAUNCH
   return cudaGetLastError();
 }
 
-template <bool NVF4, Epilogue E>
+template <bool NVF4, Epilogue E, int BN>
 cudaError_t set_attr() {
-  return cudaFuncSetAttribute(gemm_kernel<NVF4, E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(kStages * stage_bytes<NVF4>() + 1024));
+  return cudaFuncSetAttribute(gemm_kernel<NVF4, E, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(kStages * stage_bytes<NVF4, BN>() + 1024));
 }
 
 }  // namespace
 
 cudaError_t gemm_set_attributes() {
   cudaError_t e;
-  if ((e = set_attr<true, Epilogue::kStoreBf16>()) != cudaSuccess) return e;
-  if ((e = set_attr<true, Epilogue::kStoreF32>()) != cudaSuccess) return e;
-  if ((e = set_attr<true, Epilogue::kSwigluBf16>()) != cudaSuccess) return e;
-  if ((e = set_attr<true, Epilogue::kSwigluQuant>()) != cudaSuccess) return e;
-  if ((e = set_attr<false, Epilogue::kStoreBf16>()) != cudaSuccess) return e;
-  if ((e = set_attr<false, Epilogue::kStoreF32>()) != cudaSuccess) return e;
-  if ((e = set_attr<false, Epilogue::kSwigluBf16>()) != cudaSuccess) return e;
+  if ((e = set_attr<true, Epilogue::kStoreBf16, 256>()) != cudaSuccess) return e;
+  if ((e = set_attr<true, Epilogue::kStoreF32, 256>()) != cudaSuccess) return e;
+  if ((e = set_attr<true, Epilogue::kSwigluBf16, 256>()) != cudaSuccess) return e;
+  if ((e = set_attr<true, Epilogue::kSwigluQuant, 256>()) != cudaSuccess) return e;
+  if ((e = set_attr<false, Epilogue::kStoreBf16, 256>()) != cudaSuccess) return e;
+  if ((e = set_attr<false, Epilogue::kStoreF32, 256>()) != cudaSuccess) return e;
+  if ((e = set_attr<false, Epilogue::kSwigluBf16, 256>()) != cudaSuccess) return e;
+  if ((e = set_attr<false, Epilogue::kStoreBf16, 64>()) != cudaSuccess) return e;
+  if ((e = set_attr<false, Epilogue::kStoreF32, 64>()) != cudaSuccess) return e;
+  if ((e = set_attr<false, Epilogue::kSwigluBf16, 64>()) != cudaSuccess) return e;
   return cudaSuccess;
 }
 
 cudaError_t launch_gemm_nvf4(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a,
                              Epilogue epi, int num_sms, cudaStream_t stream) {
-  return launch<true>(ta, tb, a, epi, num_sms, stream);
+  return launch<true, 256>(ta, tb, a, epi, num_sms, stream);
 }
 
 cudaError_t launch_gemm_bf16(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a,
                              Epilogue epi, int num_sms, cudaStream_t stream) {
-  if (epi == Epilogue::kSwigluQuant) return cudaErrorInvalidValue;
-  return launch<false>(ta, tb, a, epi, num_sms, stream);
+  if (a.tile_cols == 64) return launch<false, 64>(ta, tb, a, epi, num_sms, stream);
+  return launch<false, 256>(ta, tb, a, epi, num_sms, stream);
 }
 
 }  // namespace q4t
