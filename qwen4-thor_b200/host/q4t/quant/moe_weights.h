@@ -1,0 +1,121 @@
+// MoEWeightLayout and the expert loader with the reference's shape
+// (include/q4t/quant/moe_weights.h:43-123, src/quant/moe_weights.cpp:43-321).
+// The loader is generic over the tensor source: `read(name, dst, bytes)` copies
+// the checkpoint tensor `name` into host memory and returns false on failure,
+// which is what io::WeightLoader::ReadTensor does in the engine.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "q4t/quant/swizzle.h"
+#include "q4t/status.h"
+#include "q4t_moe_b200.h"
+
+namespace q4t::quant {
+
+struct MoEWeightLayout {
+  int E = 0, hs = 0, moe_is = 0;
+  bool slot_mode = false;
+  uint8_t* gu_packed = nullptr;
+  uint8_t* gu_sf = nullptr;
+  uint8_t* dn_packed = nullptr;
+  uint8_t* dn_sf = nullptr;
+  float* gu_w_scale2 = nullptr;
+  float* gu_input_scale = nullptr;
+  float* dn_w_scale2 = nullptr;
+  float* dn_input_scale = nullptr;
+  std::vector<float> gu_w_scale2_h, gu_input_scale_h, dn_w_scale2_h, dn_input_scale_h;
+
+  size_t gu_sf_block() const { return SfBufferSize(2 * moe_is, hs); }
+  size_t dn_sf_block() const { return SfBufferSize(hs, moe_is); }
+  uint8_t* gu_packed_expert(int e) const { return gu_packed + static_cast<size_t>(e) * moe_is * hs; }
+  uint8_t* gu_sf_expert(int e) const { return gu_sf + static_cast<size_t>(e) * gu_sf_block(); }
+  uint8_t* dn_packed_expert(int e) const { return dn_packed + static_cast<size_t>(e) * hs * (moe_is / 2); }
+  uint8_t* dn_sf_expert(int e) const { return dn_sf + static_cast<size_t>(e) * dn_sf_block(); }
+  size_t TotalBytes() const {
+    return static_cast<size_t>(2 * E * moe_is) * (hs / 2) + static_cast<size_t>(E) * gu_sf_block() +
+           static_cast<size_t>(E * hs) * (moe_is / 2) + static_cast<size_t>(E) * dn_sf_block() +
+           4 * static_cast<size_t>(E) * sizeof(float);
+  }
+  // POD image handed to the C ABI.
+  q4t_routed_weights Abi() const {
+    return q4t_routed_weights{E, hs, moe_is, slot_mode ? 1 : 0, gu_packed, gu_sf, dn_packed, dn_sf,
+                              gu_w_scale2, gu_input_scale, dn_w_scale2, dn_input_scale};
+  }
+};
+
+inline std::string MoEExpertTensorName(int layer, int e, const char* proj, const char* suffix) {
+  return "model.language_model.layers." + std::to_string(layer) + ".mlp.experts." + std::to_string(e) + "." + proj +
+         "." + suffix;
+}
+
+// Loads one layer's experts through `read`; on success the caller owns the eight
+// device buffers of `out` (cudaFree).  Gate and up share gate's two scalars.
+template <class ReadTensor>
+Status LoadMoEWeights(ReadTensor&& read, int layer_id, int E, int hs, int moe_is, MoEWeightLayout* out,
+                      cudaStream_t stream) {
+  if (E <= 0 || hs <= 0 || moe_is <= 0) return Status::Fail("invalid MoE dims");
+  if ((hs % 32) != 0 || (moe_is % 32) != 0) return Status::Fail("hs and moe_is must be multiples of 32 (FP4 GEMM)");
+  if ((2 * moe_is) % 128 != 0 || (hs % 128) != 0)
+    return Status::Fail("2*moe_is and hs must be multiples of 128 (per-expert SF blocks)");
+  out->E = E;
+  out->hs = hs;
+  out->moe_is = moe_is;
+  const size_t gu_blk = out->gu_sf_block(), dn_blk = out->dn_sf_block();
+  const size_t gu_w = static_cast<size_t>(moe_is) * (hs / 2), dn_w = static_cast<size_t>(hs) * (moe_is / 2);
+  const size_t gu_s = static_cast<size_t>(moe_is) * (hs / 16), dn_s = static_cast<size_t>(hs) * (moe_is / 16);
+  auto alloc = [](void* p, size_t bytes) { return cudaMalloc(reinterpret_cast<void**>(p), bytes) == cudaSuccess; };
+  if (!alloc(&out->gu_packed, 2 * gu_w * E) || !alloc(&out->gu_sf, gu_blk * E) || !alloc(&out->dn_packed, dn_w * E) ||
+      !alloc(&out->dn_sf, dn_blk * E) || !alloc(&out->gu_w_scale2, sizeof(float) * E) ||
+      !alloc(&out->gu_input_scale, sizeof(float) * E) || !alloc(&out->dn_w_scale2, sizeof(float) * E) ||
+      !alloc(&out->dn_input_scale, sizeof(float) * E))
+    return Status::Fail("cudaMalloc failed");
+  out->gu_w_scale2_h.resize(E);
+  out->gu_input_scale_h.resize(E);
+  out->dn_w_scale2_h.resize(E);
+  out->dn_input_scale_h.resize(E);
+  std::vector<uint8_t> gate_w(gu_w), up_w(gu_w), down_w(dn_w), gate_s(gu_s), up_s(gu_s), down_s(dn_s);
+  std::vector<uint8_t> gu_p(2 * gu_w), gu_sf(gu_blk), dn_p(dn_w), dn_sf(dn_blk);
+  for (int e = 0; e < E; ++e) {
+    auto name = [&](const char* proj, const char* suffix) { return MoEExpertTensorName(layer_id, e, proj, suffix); };
+    float sc[4];
+    if (!read(name("gate_proj", "weight"), gate_w.data(), gate_w.size()) ||
+        !read(name("up_proj", "weight"), up_w.data(), up_w.size()) ||
+        !read(name("down_proj", "weight"), down_w.data(), down_w.size()) ||
+        !read(name("gate_proj", "weight_scale"), gate_s.data(), gate_s.size()) ||
+        !read(name("up_proj", "weight_scale"), up_s.data(), up_s.size()) ||
+        !read(name("down_proj", "weight_scale"), down_s.data(), down_s.size()) ||
+        !read(name("gate_proj", "weight_scale_2"), &sc[0], sizeof(float)) ||
+        !read(name("gate_proj", "input_scale"), &sc[1], sizeof(float)) ||
+        !read(name("down_proj", "weight_scale_2"), &sc[2], sizeof(float)) ||
+        !read(name("down_proj", "input_scale"), &sc[3], sizeof(float)))
+      return Status::Fail("MoE expert load failed (layer " + std::to_string(layer_id) + ")");
+    if (q4t_pack_expert_host(gate_w.data(), up_w.data(), down_w.data(), gate_s.data(), up_s.data(), down_s.data(), hs,
+                             moe_is, gu_p.data(), gu_sf.data(), dn_p.data(), dn_sf.data()) != Q4T_OK)
+      return Status::Fail(q4t_last_error());
+    out->gu_w_scale2_h[e] = sc[0];
+    out->gu_input_scale_h[e] = sc[1];
+    out->dn_w_scale2_h[e] = sc[2];
+    out->dn_input_scale_h[e] = sc[3];
+    bool ok = cudaMemcpyAsync(out->gu_packed_expert(e), gu_p.data(), gu_p.size(), cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    ok = ok && cudaMemcpyAsync(out->gu_sf_expert(e), gu_sf.data(), gu_blk, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    ok = ok && cudaMemcpyAsync(out->dn_packed_expert(e), dn_p.data(), dn_p.size(), cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    ok = ok && cudaMemcpyAsync(out->dn_sf_expert(e), dn_sf.data(), dn_blk, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    // the staging vectors are reused by the next expert: finish these copies first
+    ok = ok && cudaStreamSynchronize(stream) == cudaSuccess;
+    if (!ok) return Status::Fail("expert upload failed");
+  }
+  const size_t sb = sizeof(float) * E;
+  if (cudaMemcpyAsync(out->gu_w_scale2, out->gu_w_scale2_h.data(), sb, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaMemcpyAsync(out->gu_input_scale, out->gu_input_scale_h.data(), sb, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaMemcpyAsync(out->dn_w_scale2, out->dn_w_scale2_h.data(), sb, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaMemcpyAsync(out->dn_input_scale, out->dn_input_scale_h.data(), sb, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return Status::Fail("scale upload failed");
+  return Status();
+}
+
+}  // namespace q4t::quant
