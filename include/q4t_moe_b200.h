@@ -179,6 +179,36 @@ int32_t q4t_moe_routed_forward(const uint16_t* x, const int32_t* expert_ids,
                                int32_t M, int32_t k, uint32_t flags,
                                void* stream);
 
+/* ---- q4t_moe_routed_forward for callers that cannot allocate device memory.
+ * This entry point has no counterpart in the reference.  It is meant for hosts
+ * whose device-memory budget is sealed after start-up (every later cudaMalloc
+ * is refused by a quota, or allocation is not permitted from the calling
+ * context at all), so that no workspace can be created for the call.  The
+ * workspace is a fixed array of Q4T_NOALLOC_SCRATCH_BYTES inside the
+ * library's device image: every GPU that loads the library holds that much
+ * memory until the process exits.  Arguments and results are those of
+ * q4t_moe_routed_forward (y fp32 [M,hs], zeroed by the caller, accumulated
+ * into).  Limits and rules:
+ *   - the batch must satisfy q4t_moe_routed_workspace_bytes(M, k, hs, moe_is,
+ *     E) <= Q4T_NOALLOC_SCRATCH_BYTES (8 tokens x top-10 at hs 2048 / is 512
+ *     and at hs 2560 / is 640 fit); larger batches fail with
+ *     Q4T_ERR_WORKSPACE and a message that states both sizes;
+ *   - the call itself performs no cudaMalloc / cudaFree and uses no allocating
+ *     library routine; the first call on each device resolves the array's
+ *     device address (cudaGetSymbolAddress) and sets kernel attributes, so
+ *     make that first call during set-up, before any stream capture;
+ *   - all calls on one device share the one array: two calls whose kernels
+ *     can overlap on the GPU (different streams, no ordering between them)
+ *     race on it.  Issue them on one stream or order them with events.  The
+ *     array keeps the previous call's tables; the status words are cleared at
+ *     the start of each call and everything else is rewritten before use.    */
+#define Q4T_NOALLOC_SCRATCH_BYTES (3u << 20)
+int32_t q4t_moe_routed_forward_noalloc(const uint16_t* x, const int32_t* expert_ids,
+                                       const float* router_w, float* y,
+                                       const q4t_routed_weights* weights,
+                                       int32_t M, int32_t k, uint32_t flags,
+                                       void* stream);
+
 /* ---- MoEForwardWorkspaceBytes (include/q4t/model/moe.h:72-76,
  * src/model/moe.cu:403-417).                                                  */
 size_t q4t_moe_forward_workspace_bytes(int32_t T, int32_t k, int32_t hs,

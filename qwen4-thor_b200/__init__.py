@@ -53,7 +53,9 @@ EXPORTS = [
     "q4t_moe_routed_workspace_layout", "q4t_moe_routed_forward", "q4t_moe_forward_workspace_bytes",
     "q4t_moe_forward_workspace_layout", "q4t_moe_forward", "q4t_moe_workspace_status",
     "q4t_selftest_encoders", "q4t_stage_timing_enable", "q4t_stage_timing_read",
+    "q4t_moe_routed_forward_noalloc",
 ]
+NOALLOC_SCRATCH_BYTES = 3 << 20
 
 _lib = None
 
@@ -88,6 +90,7 @@ def load():
     L.q4t_bf16_linear.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     L.q4t_moe_routed_workspace_layout.argtypes = [i32] * 5 + [C.POINTER(RoutedWsLayout)]
     L.q4t_moe_routed_forward.argtypes = [vp, vp, vp, vp, C.POINTER(RoutedWeights), vp, sz, i32, i32, u32, vp]
+    L.q4t_moe_routed_forward_noalloc.argtypes = [vp, vp, vp, vp, C.POINTER(RoutedWeights), i32, i32, u32, vp]
     L.q4t_moe_forward_workspace_layout.argtypes = [i32] * 6 + [C.POINTER(ForwardWsLayout)]
     L.q4t_moe_forward.argtypes = [vp, C.POINTER(RoutedWeights), C.POINTER(ExtraWeights), vp, i32, i32,
                                   vp, sz, vp, u32, vp]
@@ -243,6 +246,15 @@ class RoutedForward:
         torch.cuda.synchronize()
         check(load().q4t_moe_workspace_status(_ptr(self.ws), self.M, self.k, self.layer.hs,
                                               self.layer.moe_is, self.layer.E))
+
+
+def routed_forward_noalloc(layer: DeviceLayer, x, ids, rw, y, flags=0, stream=None):
+    """MoERoutedForward on the library's built-in scratch: no workspace, no
+    device allocation.  Small batches only (see NOALLOC_SCRATCH_BYTES)."""
+    M, k = ids.shape
+    check(load().q4t_moe_routed_forward_noalloc(_ptr(x), _ptr(ids), _ptr(rw), _ptr(y), C.byref(layer.routed),
+                                                M, k, flags, _stream_ptr(stream)))
+    return y
 
 
 class MoEForward:

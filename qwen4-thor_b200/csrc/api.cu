@@ -28,6 +28,13 @@ int fail_cuda(const char* what, cudaError_t e) {
   return Q4T_ERR_CUDA;
 }
 
+}  // namespace
+
+// Lets the library's other translation units record an error for the calling thread.
+int q4t_internal_fail(int code, const char* msg) { return fail(code, msg ? msg : ""); }
+
+namespace {
+
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,

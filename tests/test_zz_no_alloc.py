@@ -1,0 +1,52 @@
+"""GPU test of the no-allocation routed forward (q4t_moe_routed_forward_noalloc).
+
+The entry point serves hosts that cannot create a workspace because their
+device memory is sealed after start-up; it runs the routed experts on a fixed
+scratch array inside the library.  Checked here, through the C ABI: its output
+is bit-identical to q4t_moe_routed_forward with a caller-owned workspace, on
+two calls in a row with different inputs (the second call meets the first
+call's leftovers in the shared scratch), and batches beyond the scratch limit
+are refused with a clear message.  Collected last on purpose."""
+import numpy as np
+import pytest
+import torch
+
+import synth
+from gpu_util import dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def test_noalloc_matches_workspace_variant_twice(q4t, gpu_lib):
+    E, hs, is_, k = 64, 1024, 256, 6
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=128, seed=321, per_expert_input_scale=True)
+    dl = q4t.DeviceLayer.from_host(L)
+    for call, T in enumerate((8, 5)):          # second call: different batch size and data
+        x = dev(synth.make_x(T, hs, seed=900 + call))
+        ids_h, rw_h = synth.random_routing(T, k, E, seed=700 + call)
+        ids, rw = dev(ids_h), dev(rw_h)
+        ref = q4t.RoutedForward(dl, T, k)
+        y_ref = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
+        ref(x, ids, rw, y_ref)
+        ref.status()
+        y = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
+        q4t.routed_forward_noalloc(dl, x, ids, rw, y)
+        torch.cuda.synchronize()
+        assert torch.isfinite(y).all()
+        assert float(y.abs().max()) > 0
+        # same kernels, same arithmetic: the tolerance the routed tests allow is
+        # 2e-3 of the output scale; in fact the two must agree bit for bit
+        assert torch.equal(y, y_ref), f"call {call}: max diff {float((y - y_ref).abs().max())}"
+
+
+def test_noalloc_rejects_large_batches(q4t, gpu_lib):
+    L = synth.make_layer(E=16, hs=2048, moe_is=512, shared_is=128, seed=5)
+    dl = q4t.DeviceLayer.from_host(L)
+    T, k = 256, 8
+    assert q4t.load().q4t_moe_routed_workspace_bytes(T, k, 2048, 512, 16) > q4t.NOALLOC_SCRATCH_BYTES
+    x = dev(synth.make_x(T, 2048))
+    ids_h, rw_h = synth.random_routing(T, k, 16)
+    y = torch.zeros((T, 2048), dtype=torch.float32, device="cuda")
+    with pytest.raises(q4t.Q4TError, match="built-in scratch"):
+        q4t.routed_forward_noalloc(dl, x, dev(ids_h), dev(rw_h), y)
+    assert float(y.abs().max()) == 0.0
