@@ -237,6 +237,43 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
                         int32_t k, void* workspace, size_t workspace_bytes,
                         const int32_t* fixed_ids, uint32_t flags, void* stream);
 
+/* ---- expert parallelism.  The reference engine is single-GPU (it has no
+ * NCCL/MPI code), so these three entry points have no counterpart there; they
+ * cut q4t_moe_forward at the two points where rows cross GPUs.  Experts are
+ * split into n_ranks contiguous blocks of E/n_ranks; the caller moves the
+ * buffers between ranks (all-to-all with the counts as split sizes).
+ *
+ * q4t_ep_dispatch: sorts the (token,slot) entries of this rank's T tokens by
+ * the rank that owns their expert (stable) and gathers the bf16 token rows in
+ * that order.  send_rows [T*k, hs], send_local_expert [T*k] (expert index on
+ * its owner), send_counts [n_ranks] (rows per destination), row_of_flat [T*k]
+ * (position of (token,slot) in send order, -1 for ids outside [0,E)).        */
+size_t q4t_ep_dispatch_workspace_bytes(int32_t T, int32_t k, int32_t n_ranks);
+int32_t q4t_ep_dispatch(const uint16_t* x, const int32_t* expert_ids, int32_t T,
+                        int32_t k, int32_t E, int32_t hs, int32_t n_ranks,
+                        uint16_t* send_rows, int32_t* send_local_expert,
+                        int32_t* send_counts, int32_t* row_of_flat,
+                        void* workspace, size_t workspace_bytes, void* stream);
+/* q4t_moe_expert_rows: the routed-expert FFN on `rows` received rows, each
+ * with one local expert: out_rows[r] = bf16 down-projection of row r through
+ * expert local_expert[r], un-weighted, in the order received (bit-identical
+ * to the dn_out rows of q4t_moe_routed_forward).  `weights` describes this
+ * rank's expert block (E = experts on this rank).  workspace >=
+ * q4t_moe_routed_workspace_bytes(rows, 1, hs, moe_is, E).                     */
+int32_t q4t_moe_expert_rows(const uint16_t* x_rows, const int32_t* local_expert,
+                            uint16_t* out_rows, const q4t_routed_weights* weights,
+                            void* workspace, size_t workspace_bytes,
+                            int32_t rows, uint32_t flags, void* stream);
+/* q4t_moe_finish: on the rank that owns the tokens, the shared expert and the
+ * gated combine (src/model/moe.cu:291-321, 955-971) with the routed rows taken
+ * from expert_rows [T*k, hs] (send order) through row_of_flat.                */
+size_t q4t_moe_finish_workspace_bytes(int32_t T, int32_t hs, int32_t shared_is);
+int32_t q4t_moe_finish(const uint16_t* x, const uint16_t* expert_rows,
+                       const int32_t* row_of_flat, const float* router_w,
+                       const q4t_extra_weights* extra, uint16_t* y, int32_t T,
+                       int32_t k, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
 /* Reads the kernel status words of a workspace after the stream has been
  * synchronised by the caller: 0 = clean, otherwise a bounded device-side wait
  * ran out (the output is then undefined).  Copies with cudaMemcpy.            */

@@ -260,6 +260,17 @@ def routed_forward(x, ids, rw, layer: Layer, mode: int, want_taps: bool = False,
     return (y, taps) if want_taps else y
 
 
+def combine_rows(rows, row_of_flat, rw, T, k):
+    rows = np.ascontiguousarray(rows, np.uint16)
+    rof = np.ascontiguousarray(row_of_flat, np.int32)
+    rw = np.ascontiguousarray(rw, np.float32)
+    hs = rows.shape[1]
+    y = np.zeros((T, hs), np.float32)
+    lib().q4o_combine_rows(_p(rows, C.c_uint16), _p(rof, C.c_int32), _p(rw, C.c_float), C.c_int(T), C.c_int(k),
+                           C.c_int(hs), _p(y, C.c_float))
+    return y
+
+
 def shared_combine(x, routed, layer: Layer, linear_mode: int):
     x = np.ascontiguousarray(x, np.uint16)
     routed = np.ascontiguousarray(routed, np.float32)

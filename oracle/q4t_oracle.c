@@ -628,6 +628,22 @@ int q4o_routed_forward(const uint16_t* x, const int32_t* ids, const float* rw,
   return 0;
 }
 
+/* Slot-order combine of bf16 rows addressed through row_of_flat
+ * (CombineGroupedKernel, src/quant/moe_gemm.cu:273-288): y += fma chain from 0. */
+void q4o_combine_rows(const uint16_t* rows, const int32_t* row_of_flat, const float* rw,
+                      int T, int k, int hs, float* y) {
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < T; ++t)
+    for (int c = 0; c < hs; ++c) {
+      float acc = 0.0f;
+      for (int s = 0; s < k; ++s) {
+        const int r = row_of_flat[t * k + s];
+        if (r >= 0) acc = fmaf(rw[t * k + s], q4o_bf16_to_float(rows[(size_t)r * hs + c]), acc);
+      }
+      y[(size_t)t * hs + c] += acc;
+    }
+}
+
 /* ------------------------------------------------------------------------ */
 /* shared expert + gated combine                                              */
 /* ------------------------------------------------------------------------ */

@@ -138,6 +138,12 @@ int q4o_routed_forward(const uint16_t* x, const int32_t* ids, const float* rw,
                        float* y, const q4o_layer* L, int T, int k, int mode,
                        q4o_taps* taps);
 
+/* y[T,hs] (fp32) += slot-order fused multiply-add of bf16 rows [*, hs] taken
+ * through row_of_flat [T*k] (-1 = skipped), weights rw [T*k]
+ * (src/quant/moe_gemm.cu:273-288).                                            */
+void q4o_combine_rows(const uint16_t* rows, const int32_t* row_of_flat, const float* rw,
+                      int T, int k, int hs, float* y);
+
 /* Shared expert + gated combine (src/model/moe.cu:276-321, 955-971):
  * y_bf16 = bf16(routed + sigmoid(x . gate_scalar) * shared_down).
  * linear_mode is passed to q4o_bf16_linear; mode 1 also reproduces the

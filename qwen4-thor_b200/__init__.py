@@ -53,7 +53,8 @@ EXPORTS = [
     "q4t_moe_routed_workspace_layout", "q4t_moe_routed_forward", "q4t_moe_forward_workspace_bytes",
     "q4t_moe_forward_workspace_layout", "q4t_moe_forward", "q4t_moe_workspace_status",
     "q4t_selftest_encoders", "q4t_stage_timing_enable", "q4t_stage_timing_read",
-    "q4t_moe_routed_forward_noalloc",
+    "q4t_moe_routed_forward_noalloc", "q4t_ep_dispatch_workspace_bytes", "q4t_ep_dispatch",
+    "q4t_moe_expert_rows", "q4t_moe_finish_workspace_bytes", "q4t_moe_finish",
 ]
 NOALLOC_SCRATCH_BYTES = 3 << 20
 
@@ -91,6 +92,13 @@ def load():
     L.q4t_moe_routed_workspace_layout.argtypes = [i32] * 5 + [C.POINTER(RoutedWsLayout)]
     L.q4t_moe_routed_forward.argtypes = [vp, vp, vp, vp, C.POINTER(RoutedWeights), vp, sz, i32, i32, u32, vp]
     L.q4t_moe_routed_forward_noalloc.argtypes = [vp, vp, vp, vp, C.POINTER(RoutedWeights), i32, i32, u32, vp]
+    L.q4t_ep_dispatch_workspace_bytes.restype = C.c_size_t
+    L.q4t_ep_dispatch_workspace_bytes.argtypes = [i32, i32, i32]
+    L.q4t_ep_dispatch.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, sz, vp]
+    L.q4t_moe_expert_rows.argtypes = [vp, vp, vp, C.POINTER(RoutedWeights), vp, sz, i32, u32, vp]
+    L.q4t_moe_finish_workspace_bytes.restype = C.c_size_t
+    L.q4t_moe_finish_workspace_bytes.argtypes = [i32, i32, i32]
+    L.q4t_moe_finish.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, sz, vp]
     L.q4t_moe_forward_workspace_layout.argtypes = [i32] * 6 + [C.POINTER(ForwardWsLayout)]
     L.q4t_moe_forward.argtypes = [vp, C.POINTER(RoutedWeights), C.POINTER(ExtraWeights), vp, i32, i32,
                                   vp, sz, vp, u32, vp]

@@ -324,6 +324,45 @@ int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w,
   return Q4T_OK;
 }
 
+// Shared expert: act = bf16((g*sigmoid(g))*u) of bf16(x.Wgu^T), down = bf16(act.Wd^T)
+// (src/model/moe.cu:955-969).  T <= 8 uses the reference-order GEMV, larger T the tensor cores.
+int run_shared_expert(const DeviceState* ds, const uint16_t* x, const q4t_extra_weights* extra, uint16_t* sgu,
+                      uint16_t* sact, uint16_t* sdown, int T, uint32_t flags, cudaStream_t st) {
+  const int hs = extra->hs, sis = extra->shared_is;
+  cudaError_t e;
+  int rc;
+  if (T <= 8) {
+    if ((rc = run_bf16_linear(ds, x, extra->shared_gu, sgu, T, 2 * sis, hs, st)) != Q4T_OK) return rc;
+    if ((e = q4t::launch_swiglu(sgu, sact, T, sis, st)) != cudaSuccess) return fail_cuda("swiglu launch", e);
+  } else {
+    const int m_tiles = (T + 127) / 128;
+    const bool narrow = m_tiles * (sis / 128) < ds->num_sms / 2;
+    const int cols = narrow ? 64 : 256;
+    CUtensorMap ta, tb;
+    if ((rc = make_tmap(ds, &ta, true, x, hs, T, static_cast<uint64_t>(hs) * 2)) != Q4T_OK) return rc;
+    if ((rc = make_tmap(ds, &tb, true, extra->shared_gu, hs, 2 * sis, static_cast<uint64_t>(hs) * 2, cols / 2)) !=
+        Q4T_OK)
+      return rc;
+    q4t::GemmArgs g{};
+    g.K = hs;
+    g.tile_cols = cols;
+    g.n_tiles = sis / (cols / 2);
+    g.n_per_tile = cols / 2;
+    g.up_row_offset = sis;
+    g.b_rows_valid = sis;
+    g.ntiles_host = m_tiles;
+    g.total_rows = T;
+    g.out = sact;
+    g.ldo = sis;
+    g.alpha_const = 1.0f;
+    g.gu_dump = (flags & 1u) ? sgu : nullptr;
+    g.gu_dump_ld = 2 * sis;
+    if ((e = q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kSwigluBf16, ds->num_sms, st)) != cudaSuccess)
+      return fail_cuda("shared gate/up GEMM launch", e);
+  }
+  return run_bf16_linear(ds, sact, extra->shared_down, sdown, T, hs, sis, st);
+}
+
 }  // namespace
 
 extern "C" {
@@ -558,36 +597,7 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
   if ((rc = run_routed_core(ds, x, ids, routed, P, T, k, flags, st)) != Q4T_OK) return rc;
 
   // 4-6. shared expert
-  if (T <= 8) {
-    if ((rc = run_bf16_linear(ds, x, extra->shared_gu, sgu, T, 2 * sis, hs, st)) != Q4T_OK) return rc;
-    if ((e = q4t::launch_swiglu(sgu, sact, T, sis, st)) != cudaSuccess) return fail_cuda("swiglu launch", e);
-  } else {
-    const int m_tiles = (T + 127) / 128;
-    const bool narrow = m_tiles * (sis / 128) < ds->num_sms / 2;
-    const int cols = narrow ? 64 : 256;
-    CUtensorMap ta, tb;
-    if ((rc = make_tmap(ds, &ta, true, x, hs, T, static_cast<uint64_t>(hs) * 2)) != Q4T_OK) return rc;
-    if ((rc = make_tmap(ds, &tb, true, extra->shared_gu, hs, 2 * sis, static_cast<uint64_t>(hs) * 2, cols / 2)) !=
-        Q4T_OK)
-      return rc;
-    q4t::GemmArgs g{};
-    g.K = hs;
-    g.tile_cols = cols;
-    g.n_tiles = sis / (cols / 2);
-    g.n_per_tile = cols / 2;
-    g.up_row_offset = sis;
-    g.b_rows_valid = sis;
-    g.ntiles_host = m_tiles;
-    g.total_rows = T;
-    g.out = sact;
-    g.ldo = sis;
-    g.alpha_const = 1.0f;
-    g.gu_dump = (flags & 1u) ? sgu : nullptr;
-    g.gu_dump_ld = 2 * sis;
-    if ((e = q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kSwigluBf16, ds->num_sms, st)) != cudaSuccess)
-      return fail_cuda("shared gate/up GEMM launch", e);
-  }
-  if ((rc = run_bf16_linear(ds, sact, extra->shared_down, sdown, T, hs, sis, st)) != Q4T_OK) return rc;
+  if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, st)) != Q4T_OK) return rc;
   stage_end(6, st);
 
   // 7. routed sum + sigmoid-gated shared expert
@@ -596,6 +606,164 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
     return fail_cuda("combine launch", e);
   stage_end(7, st);
   return Q4T_OK;
+}
+
+// ---------------------------------------------------------------- expert parallelism
+namespace {
+struct EpDispatchLayout {
+  size_t dest, local, offsets, flat_of_row, row_tile, ntiles, tile_expert, tile_row0, tile_nrows, tile_off,
+      blk_counts, total;
+  size_t max_tiles;
+};
+void ep_dispatch_layout(int T, int k, int n_ranks, EpDispatchLayout* L) {
+  const size_t R = static_cast<size_t>(T) * k;
+  const size_t nblk = (R + q4t::kPlanChunk - 1) / q4t::kPlanChunk;
+  L->max_tiles = R / 128 + n_ranks + 1;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    off = align_up(off, 256);
+    const size_t at = off;
+    off += bytes;
+    return at;
+  };
+  L->dest = take(R * 4);
+  L->local = take(R * 4);
+  L->offsets = take(static_cast<size_t>(n_ranks + 1) * 4);
+  L->flat_of_row = take(R * 4);
+  L->row_tile = take(R * 4);
+  L->ntiles = take(256);
+  L->tile_expert = take(L->max_tiles * 4);
+  L->tile_row0 = take(L->max_tiles * 4);
+  L->tile_nrows = take(L->max_tiles * 4);
+  L->tile_off = take(static_cast<size_t>(n_ranks + 1) * 4);
+  L->blk_counts = take(nblk * static_cast<size_t>(n_ranks) * 4);
+  L->total = align_up(off, 256);
+}
+struct FinishLayout {
+  size_t routed, shared_gu, shared_act, shared_down, total;
+};
+void finish_layout(int T, int hs, int sis, FinishLayout* F) {
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    off = align_up(off, 256);
+    const size_t at = off;
+    off += bytes;
+    return at;
+  };
+  F->routed = take(static_cast<size_t>(T) * hs * 4);
+  F->shared_gu = take(static_cast<size_t>(T) * 2 * sis * 2);
+  F->shared_act = take(static_cast<size_t>(T) * sis * 2);
+  F->shared_down = take(static_cast<size_t>(T) * hs * 2);
+  F->total = align_up(off, 256);
+}
+}  // namespace
+
+size_t q4t_ep_dispatch_workspace_bytes(int32_t T, int32_t k, int32_t n_ranks) {
+  if (T <= 0 || k <= 0 || n_ranks <= 0) return 0;
+  EpDispatchLayout L;
+  ep_dispatch_layout(T, k, n_ranks, &L);
+  return L.total;
+}
+
+int32_t q4t_ep_dispatch(const uint16_t* x, const int32_t* expert_ids, int32_t T, int32_t k, int32_t E, int32_t hs,
+                        int32_t n_ranks, uint16_t* send_rows, int32_t* send_local_expert, int32_t* send_counts,
+                        int32_t* row_of_flat, void* workspace, size_t workspace_bytes, void* stream) {
+  if (T <= 0 || k <= 0 || E <= 0 || hs <= 0 || hs % 8 || n_ranks <= 0 || n_ranks > 1024 || E % n_ranks)
+    return fail(Q4T_ERR_INVALID, "invalid dispatch dims (E must be a multiple of n_ranks, hs of 8)");
+  if (!x || !expert_ids || !send_rows || !send_local_expert || !send_counts || !row_of_flat || !workspace)
+    return fail(Q4T_ERR_INVALID, "null pointer");
+  EpDispatchLayout L;
+  ep_dispatch_layout(T, k, n_ranks, &L);
+  if (workspace_bytes < L.total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  auto at = [&](size_t off) { return reinterpret_cast<int32_t*>(base + off); };
+  const int R = T * k;
+  cudaError_t e;
+  if ((e = q4t::launch_ep_split_ids(expert_ids, R, E, E / n_ranks, at(L.dest), at(L.local), st)) != cudaSuccess)
+    return fail_cuda("split ids launch", e);
+  q4t::PlanTables pt;
+  pt.blk_counts = at(L.blk_counts);
+  pt.counts = send_counts;
+  pt.offsets = at(L.offsets);
+  pt.tile_off = at(L.tile_off);
+  pt.tile_expert = at(L.tile_expert);
+  pt.tile_row0 = at(L.tile_row0);
+  pt.tile_nrows = at(L.tile_nrows);
+  pt.ntiles = at(L.ntiles);
+  pt.row_of_flat = row_of_flat;
+  pt.flat_of_row = at(L.flat_of_row);
+  pt.row_tile = at(L.row_tile);
+  if ((e = q4t::launch_plan(at(L.dest), R, n_ranks, static_cast<int>(L.max_tiles), pt, st)) != cudaSuccess)
+    return fail_cuda("dispatch plan launch", e);
+  // rows in destination order: source token = flat / k; the expert's index on its owner rides along
+  if ((e = q4t::launch_gather_rows(x, pt.flat_of_row, k, pt.offsets + n_ranks, R, hs, send_rows, at(L.local),
+                                   send_local_expert, st)) != cudaSuccess)
+    return fail_cuda("dispatch gather launch", e);
+  return Q4T_OK;
+}
+
+int32_t q4t_moe_expert_rows(const uint16_t* x_rows, const int32_t* local_expert, uint16_t* out_rows,
+                            const q4t_routed_weights* w, void* workspace, size_t workspace_bytes, int32_t rows,
+                            uint32_t flags, void* stream) {
+  if (rows == 0) return Q4T_OK;
+  if (!w) return fail(Q4T_ERR_INVALID, "null weights");
+  if (rows < 0 || w->E <= 0 || w->hs <= 0 || w->moe_is <= 0) return fail(Q4T_ERR_INVALID, "invalid MoE forward dims");
+  if (!routed_dims_ok(w->E, w->hs, w->moe_is))
+    return fail(Q4T_ERR_INVALID, "hs and moe_is must be multiples of 128 and E <= 1024");
+  if (!x_rows || !local_expert || !out_rows || !workspace) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(Q4T_ERR_INVALID, "workspace must be 256-byte aligned");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  RoutedPtrs P;
+  routed_layout(rows, 1, w->hs, w->moe_is, w->E, &P.L);
+  if (workspace_bytes < P.L.total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");
+  P.base = static_cast<uint8_t*>(workspace);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  stage_begin(st);
+  stage_end(1, st);
+  if ((rc = run_routed_core(ds, x_rows, local_expert, w, P, rows, 1, flags, st)) != Q4T_OK) return rc;
+  // back to the order the rows arrived in
+  cudaError_t e = q4t::launch_gather_rows(P.at<uint16_t>(P.L.dn_out), P.at<int32_t>(P.L.row_of_flat), 1, nullptr, rows,
+                                          w->hs, out_rows, nullptr, nullptr, st);
+  stage_end(7, st);
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("row gather launch", e);
+}
+
+size_t q4t_moe_finish_workspace_bytes(int32_t T, int32_t hs, int32_t shared_is) {
+  if (T <= 0 || hs <= 0 || shared_is <= 0) return 0;
+  FinishLayout F;
+  finish_layout(T, hs, shared_is, &F);
+  return F.total;
+}
+
+int32_t q4t_moe_finish(const uint16_t* x, const uint16_t* expert_rows, const int32_t* row_of_flat,
+                       const float* router_w, const q4t_extra_weights* extra, uint16_t* y, int32_t T, int32_t k,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  if (T <= 0) return Q4T_OK;
+  if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");
+  if (!extra || extra->hs <= 0 || extra->hs % 128 || extra->shared_is <= 0 || extra->shared_is % 128)
+    return fail(Q4T_ERR_INVALID, "unsupported dims (hs, shared_is multiples of 128)");
+  if (!x || !expert_rows || !row_of_flat || !router_w || !y || !workspace) return fail(Q4T_ERR_INVALID, "null pointer");
+  FinishLayout F;
+  finish_layout(T, extra->hs, extra->shared_is, &F);
+  if (workspace_bytes < F.total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  uint16_t* sgu = reinterpret_cast<uint16_t*>(base + F.shared_gu);
+  uint16_t* sact = reinterpret_cast<uint16_t*>(base + F.shared_act);
+  uint16_t* sdown = reinterpret_cast<uint16_t*>(base + F.shared_down);
+  if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, 0, st)) != Q4T_OK) return rc;
+  cudaError_t e = q4t::launch_final_combine(expert_rows, row_of_flat, router_w, sdown, x, extra->shared_gate_scalar,
+                                            reinterpret_cast<float*>(base + F.routed), y, T, k, extra->hs, st);
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("combine launch", e);
 }
 
 int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k, int32_t hs, int32_t moe_is,

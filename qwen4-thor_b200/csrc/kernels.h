@@ -47,6 +47,11 @@ cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_
                         int T, int E, int k, cudaStream_t stream);
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
                         cudaStream_t stream);
+cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_per_rank, int32_t* dest,
+                                int32_t* local, cudaStream_t stream);
+cudaError_t launch_gather_rows(const uint16_t* src, const int32_t* index, int div, const int32_t* rows_dev,
+                               int rows, int width, uint16_t* out, const int32_t* aux, int32_t* aux_out,
+                               cudaStream_t stream);
 cudaError_t launch_routed_combine(const uint16_t* dn_out, const int32_t* row_of_flat,
                                   const float* rw, float* y, int T, int k, int hs,
                                   cudaStream_t stream);

@@ -331,6 +331,41 @@ __global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* __restr
   }
 }
 
+// ---- expert-parallel helpers
+// dest[f] = owner rank of expert ids[f] (experts are split into contiguous
+// blocks of experts_per_rank); local[f] = index of that expert on its owner.
+// Ids outside [0, E) map to -1 and are skipped by the planner.
+__global__ void __launch_bounds__(256) ep_split_ids_kernel(const int32_t* __restrict__ ids, int R, int E,
+                                                           int experts_per_rank, int32_t* __restrict__ dest,
+                                                           int32_t* __restrict__ local) {
+  const int f = blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= R) return;
+  const int e = ids[f];
+  const bool ok = e >= 0 && e < E;
+  dest[f] = ok ? e / experts_per_rank : -1;
+  local[f] = ok ? e % experts_per_rank : -1;
+}
+
+// out[r, :] = src[index[r] / div, :] for r < *rows_dev (rows of `width` bf16
+// values, 16-byte vector copies); optionally aux_out[r] = aux[index[r]].
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint16_t* __restrict__ src,
+                                                          const int32_t* __restrict__ index, int div,
+                                                          const int32_t* __restrict__ rows_dev, int rows,
+                                                          int width, uint16_t* __restrict__ out,
+                                                          const int32_t* __restrict__ aux,
+                                                          int32_t* __restrict__ aux_out) {
+  const int per_row = width >> 3;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (rows_dev) rows = min(rows, *rows_dev);
+  if (idx >= static_cast<int64_t>(rows) * per_row) return;
+  const int r = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row);
+  const int i = index[r];
+  if (i < 0) return;
+  reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * width)[c] =
+      __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(i / div) * width) + c);
+  if (aux_out && c == 0) aux_out[r] = aux[i];
+}
+
 // y[t, c] += sum over slots, in slot order, of w * bf16 row value, accumulated
 // by fused multiply-add from 0 (CombineGroupedKernel, src/quant/moe_gemm.cu:
 // 273-288).  One thread per 8 columns.
@@ -475,6 +510,23 @@ cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const P
   plan_hist_kernel<<<nblk, 256, E * sizeof(int32_t), stream>>>(ids, R, E, p.blk_counts);
   plan_scan_kernel<<<1, 1024, 0, stream>>>(nblk, E, max_tiles, p);
   plan_scatter_kernel<<<nblk, 256, E * sizeof(int32_t), stream>>>(ids, R, E, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_per_rank, int32_t* dest,
+                                int32_t* local, cudaStream_t stream) {
+  if (R == 0) return cudaSuccess;
+  ep_split_ids_kernel<<<(R + 255) / 256, 256, 0, stream>>>(ids, R, E, experts_per_rank, dest, local);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const uint16_t* src, const int32_t* index, int div, const int32_t* rows_dev,
+                               int rows, int width, uint16_t* out, const int32_t* aux, int32_t* aux_out,
+                               cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(rows) * (width / 8);
+  if (total == 0) return cudaSuccess;
+  gather_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(src, index, div, rows_dev, rows,
+                                                                                     width, out, aux, aux_out);
   return cudaGetLastError();
 }
 

@@ -1,0 +1,121 @@
+"""Expert-parallel MoE layer over torch.distributed (one process per GPU).
+
+Experts are split into world_size contiguous blocks; the router and the shared
+expert are replicated and run where the token lives; tokens are sharded by
+rank.  One step is
+
+    router -> dispatch (sort (token,slot) by owner rank, gather rows)
+           -> all-to-all of the per-rank row counts, then of the rows
+           -> routed-expert FFN on the received rows (owner of the expert)
+           -> all-to-all of the bf16 result rows back
+           -> shared expert + slot-order combine (owner of the token)
+
+which yields, bit for bit, the output of the single-GPU layer on the same
+tokens: rows are quantised and multiplied per row, and the combine order is the
+slot order in both cases.  torch.distributed (NCCL on GPUs, gloo in the CPU
+tests) is plumbing only; every arithmetic step is an `ops` call.
+"""
+from __future__ import annotations
+
+
+class LibraryOps:
+    """The five steps on the GPU through the C ABI of libq4t_moe_b200."""
+
+    def __init__(self, q4t, layer_local, E_total, hs, k, world, T_local, cap_rows, device="cuda"):
+        import ctypes as C
+        import torch
+        self.q4t, self.C, self.torch = q4t, C, torch
+        self.L, self.E, self.hs, self.k, self.world, self.T = layer_local, E_total, hs, k, world, T_local
+        self.lib = q4t.load()
+        R = T_local * k
+        dev = device
+        self.logits = torch.empty((T_local, E_total), dtype=torch.bfloat16, device=dev)
+        self.ids = torch.empty((T_local, k), dtype=torch.int32, device=dev)
+        self.rw = torch.empty((T_local, k), dtype=torch.float32, device=dev)
+        self.send_rows = torch.empty((R, hs), dtype=torch.bfloat16, device=dev)
+        self.send_local = torch.empty((R,), dtype=torch.int32, device=dev)
+        self.send_counts = torch.empty((world,), dtype=torch.int32, device=dev)
+        self.row_of_flat = torch.empty((R,), dtype=torch.int32, device=dev)
+        self.dispatch_ws = torch.empty(self.lib.q4t_ep_dispatch_workspace_bytes(T_local, k, world), dtype=torch.uint8, device=dev)
+        self.cap = cap_rows
+        self.expert_ws_bytes = self.lib.q4t_moe_routed_workspace_bytes(cap_rows, 1, hs, layer_local.moe_is, layer_local.E)
+        self.expert_ws = torch.empty(self.expert_ws_bytes, dtype=torch.uint8, device=dev)
+        self.finish_ws_bytes = self.lib.q4t_moe_finish_workspace_bytes(T_local, hs, layer_local.shared_is)
+        self.finish_ws = torch.empty(self.finish_ws_bytes, dtype=torch.uint8, device=dev)
+
+    def _s(self):
+        return self.C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    def router(self, x):
+        q = self.q4t
+        q.check(self.lib.q4t_bf16_linear(x.data_ptr(), self.L.extra.gate, self.logits.data_ptr(), self.T, self.E, self.hs, self._s()))
+        q.check(self.lib.q4t_router_topk(self.logits.data_ptr(), self.ids.data_ptr(), self.rw.data_ptr(), self.T, self.E, self.k, self._s()))
+        return self.ids, self.rw
+
+    def dispatch(self, x, ids):
+        self.q4t.check(self.lib.q4t_ep_dispatch(x.data_ptr(), ids.data_ptr(), self.T, self.k, self.E, self.hs, self.world,
+                                                self.send_rows.data_ptr(), self.send_local.data_ptr(),
+                                                self.send_counts.data_ptr(), self.row_of_flat.data_ptr(),
+                                                self.dispatch_ws.data_ptr(), self.dispatch_ws.numel(), self._s()))
+        return self.send_rows, self.send_local, self.send_counts, self.row_of_flat
+
+    def expert_rows(self, rows, local, out, n):
+        self.q4t.check(self.lib.q4t_moe_expert_rows(rows.data_ptr(), local.data_ptr(), out.data_ptr(),
+                                                    self.C.byref(self.L.routed), self.expert_ws.data_ptr(),
+                                                    self.expert_ws_bytes, n, 0, self._s()))
+        return out
+
+    def finish(self, x, ret_rows, row_of_flat, rw, y):
+        self.q4t.check(self.lib.q4t_moe_finish(x.data_ptr(), ret_rows.data_ptr(), row_of_flat.data_ptr(), rw.data_ptr(),
+                                               self.C.byref(self.L.extra), y.data_ptr(), self.T, self.k,
+                                               self.finish_ws.data_ptr(), self.finish_ws_bytes, self._s()))
+        return y
+
+    def empty_rows(self, n):
+        return self.torch.empty((n, self.hs), dtype=self.torch.bfloat16, device=self.send_rows.device)
+
+
+class ExpertParallelMoE:
+    """Drives one expert-parallel layer step; `ops` supplies the arithmetic
+    (LibraryOps on GPUs; the CPU tests plug in an oracle-backed twin)."""
+
+    def __init__(self, ops, world: int, rank: int, group=None):
+        import torch.distributed as dist
+        self.ops, self.world, self.rank, self.group, self.dist = ops, world, rank, group, dist
+        self.last = {}
+
+    def exchange_counts(self, send_counts):
+        """Row counts per destination -> row counts per source (host lists)."""
+        import torch
+        recv = torch.empty_like(send_counts)
+        if self.world > 1:
+            self.dist.all_to_all_single(recv, send_counts, group=self.group)
+        else:
+            recv.copy_(send_counts)
+        return [int(v) for v in send_counts.tolist()], [int(v) for v in recv.tolist()]
+
+    def all_to_all_rows(self, out, inp, out_splits, in_splits):
+        if self.world > 1:
+            self.dist.all_to_all_single(out, inp, output_split_sizes=out_splits, input_split_sizes=in_splits,
+                                        group=self.group)
+        else:
+            out.copy_(inp)
+        return out
+
+    def forward(self, x, y):
+        ops = self.ops
+        ids, rw = ops.router(x)
+        send_rows, send_local, send_counts, row_of_flat = ops.dispatch(x, ids)
+        s_counts, r_counts = self.exchange_counts(send_counts)      # host sync: split sizes
+        n_send, n_recv = sum(s_counts), sum(r_counts)
+        recv_rows = ops.empty_rows(n_recv)
+        recv_local = send_local.new_empty((n_recv,))
+        self.all_to_all_rows(recv_rows, send_rows[:n_send], r_counts, s_counts)
+        self.all_to_all_rows(recv_local, send_local[:n_send], r_counts, s_counts)
+        out_rows = ops.empty_rows(n_recv)
+        ops.expert_rows(recv_rows, recv_local, out_rows, n_recv)
+        ret_rows = ops.empty_rows(max(n_send, 1))
+        self.all_to_all_rows(ret_rows[:n_send], out_rows, s_counts, r_counts)
+        ops.finish(x, ret_rows, row_of_flat, rw, y)
+        self.last = dict(rows_sent=n_send, rows_received=n_recv, send_counts=s_counts, recv_counts=r_counts)
+        return y
