@@ -44,6 +44,11 @@ struct DeviceState {
   bool ready = false;
   int num_sms = 0;
   EncodeFn encode = nullptr;
+  // The shared expert depends only on x, so q4t_moe_forward runs it on this
+  // library-owned stream beside the router / permutation / quantise chain and
+  // joins before the combine (fork and join by events, no host involvement).
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t fork_event = nullptr, join_event = nullptr;
 };
 constexpr int kMaxDevices = 16;
 DeviceState g_dev[kMaxDevices];
@@ -71,6 +76,10 @@ int device_state(const DeviceState** out) {
       return fail(Q4T_ERR_DEVICE, "cuTensorMapEncodeTiled entry point unavailable");
     if ((e = q4t::gemm_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = q4t::routing_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+    if ((e = cudaStreamCreateWithFlags(&s.side_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&s.fork_event, cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&s.join_event, cudaEventDisableTiming)) != cudaSuccess)
+      return fail_cuda("side stream set-up", e);
     s.encode = reinterpret_cast<EncodeFn>(fn);
     s.num_sms = prop.multiProcessorCount;
     s.ready = true;
@@ -194,15 +203,8 @@ struct RoutedPtrs {
 
 // Steps shared by the routed entry point and the full layer: permutation,
 // gather-quantise, gate/up GEMM with fused SwiGLU + requantisation, down GEMM.
-int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids,
-                    const q4t_routed_weights* w, const RoutedPtrs& P, int M, int k, uint32_t flags,
-                    cudaStream_t st) {
-  const int E = w->E, hs = w->hs, is = w->moe_is;
-  const int R = M * k;
+q4t::PlanTables plan_tables(const RoutedPtrs& P, int E) {
   const q4t_routed_ws_layout& L = P.L;
-  cudaError_t e;
-  if ((e = cudaMemsetAsync(P.at<int32_t>(L.status), 0, 16, st)) != cudaSuccess) return fail_cuda("memset status", e);
-
   q4t::PlanTables pt;
   pt.counts = P.at<int32_t>(L.counts);
   pt.offsets = P.at<int32_t>(L.offsets);
@@ -215,8 +217,23 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   pt.tile_nrows = P.at<int32_t>(L.tile_nrows);
   pt.tile_off = P.at<int32_t>(align_up(L.status + 256, 256));
   pt.blk_counts = P.at<int32_t>(align_up(align_up(L.status + 256, 256) + static_cast<size_t>(E + 1) * 4, 256));
-  if ((e = q4t::launch_plan(ids, R, E, static_cast<int>(L.max_tiles), pt, st)) != cudaSuccess)
-    return fail_cuda("plan launch", e);
+  pt.status = P.at<int32_t>(L.status);
+  return pt;
+}
+
+// plan_done: the permutation tables of P were already produced (fused with the router).
+int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids,
+                    const q4t_routed_weights* w, const RoutedPtrs& P, int M, int k, uint32_t flags,
+                    cudaStream_t st, bool plan_done = false) {
+  const int E = w->E, hs = w->hs, is = w->moe_is;
+  const int R = M * k;
+  const q4t_routed_ws_layout& L = P.L;
+  cudaError_t e;
+  const q4t::PlanTables pt = plan_tables(P, E);  // the planner also clears the status words
+  if (!plan_done) {
+    if ((e = q4t::launch_plan(ids, R, E, static_cast<int>(L.max_tiles), pt, st)) != cudaSuccess)
+      return fail_cuda("plan launch", e);
+  }
   stage_end(2, st);
 
   uint8_t* a_packed = P.at<uint8_t>(L.a_packed);
@@ -583,21 +600,43 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
   uint16_t* sdown = reinterpret_cast<uint16_t*>(base + F.shared_down);
   cudaError_t e;
 
+  // The shared expert runs beside the routed chain unless the stage timer is on
+  // (its marks assume one stream) or the batch is large enough to fill the GPU.
+  const bool fork = !g_timer.enabled && T <= 1024;
+  if (fork) {
+    if ((e = cudaEventRecord(ds->fork_event, st)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(ds->side_stream, ds->fork_event, 0)) != cudaSuccess)
+      return fail_cuda("fork", e);
+    if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, ds->side_stream)) != Q4T_OK) return rc;
+    if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return fail_cuda("join record", e);
+  }
+
   // 1-2. router logits and top-k
   stage_begin(st);
   if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, E, hs, st)) != Q4T_OK) return rc;
   stage_end(0, st);
-  if ((e = q4t::launch_topk(logits, fixed_ids, ids, rw, T, E, k, st)) != cudaSuccess) return fail_cuda("topk launch", e);
-  stage_end(1, st);
-
-  // 3. routed experts
   RoutedPtrs P;
   routed_layout(T, k, hs, is, E, &P.L);
   P.base = base + F.routed_ws;
-  if ((rc = run_routed_core(ds, x, ids, routed, P, T, k, flags, st)) != Q4T_OK) return rc;
+  const bool fused_route = q4t::route_and_plan_fits(T, k);
+  if (fused_route) {  // small batch: top-k and the permutation tables in one launch
+    if ((e = q4t::launch_route_and_plan(logits, fixed_ids, ids, rw, T, E, k, static_cast<int>(P.L.max_tiles),
+                                        plan_tables(P, E), st)) != cudaSuccess)
+      return fail_cuda("route+plan launch", e);
+  } else {
+    if ((e = q4t::launch_topk(logits, fixed_ids, ids, rw, T, E, k, st)) != cudaSuccess) return fail_cuda("topk launch", e);
+  }
+  stage_end(1, st);
+
+  // 3. routed experts
+  if ((rc = run_routed_core(ds, x, ids, routed, P, T, k, flags, st, fused_route)) != Q4T_OK) return rc;
 
   // 4-6. shared expert
-  if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, st)) != Q4T_OK) return rc;
+  if (fork) {
+    if ((e = cudaStreamWaitEvent(st, ds->join_event, 0)) != cudaSuccess) return fail_cuda("join", e);
+  } else {
+    if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, st)) != Q4T_OK) return rc;
+  }
   stage_end(6, st);
 
   // 7. routed sum + sigmoid-gated shared expert
@@ -697,6 +736,7 @@ int32_t q4t_ep_dispatch(const uint16_t* x, const int32_t* expert_ids, int32_t T,
   pt.row_of_flat = row_of_flat;
   pt.flat_of_row = at(L.flat_of_row);
   pt.row_tile = at(L.row_tile);
+  pt.status = nullptr;
   if ((e = q4t::launch_plan(at(L.dest), R, n_ranks, static_cast<int>(L.max_tiles), pt, st)) != cudaSuccess)
     return fail_cuda("dispatch plan launch", e);
   // rows in destination order: source token = flat / k; the expert's index on its owner rides along

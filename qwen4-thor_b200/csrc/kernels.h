@@ -39,12 +39,17 @@ struct PlanTables {
   int32_t* row_of_flat;  // [R]
   int32_t* flat_of_row;  // [R]
   int32_t* row_tile;     // [R]
+  int32_t* status;       // [4] kernel status words, cleared by the planner (may be null)
 };
 cudaError_t routing_set_attributes();
 cudaError_t launch_small_m_linear(const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
                                   int K, cudaStream_t stream);
 cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw,
                         int T, int E, int k, cudaStream_t stream);
+// Small batches: top-k and the permutation tables in one single-block launch.
+bool route_and_plan_fits(int T, int k);
+cudaError_t launch_route_and_plan(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw, int T,
+                                  int E, int k, int max_tiles, const PlanTables& p, cudaStream_t stream);
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
                         cudaStream_t stream);
 cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_per_rank, int32_t* dest,

@@ -71,19 +71,13 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const uint16_t* __r
 // (RouterTopkKernel, src/model/moe.cu:134-212): k rounds of arg-max by
 // (value desc, id asc) with the winner masked to -1e30; then, in selection
 // order, e_i = __expf(v_i - max), sum, w_i = e_i * (1/sum).
-__global__ void __launch_bounds__(256) topk_kernel(const uint16_t* __restrict__ logits,
-                                                   const int32_t* __restrict__ fixed_ids,
-                                                   int32_t* __restrict__ ids, float* __restrict__ rw,
-                                                   int T, int E, int k) {
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (t >= T) return;
-  const uint16_t* row = logits + static_cast<size_t>(t) * E;
+__device__ __forceinline__ void topk_token(const uint16_t* __restrict__ row, const int32_t* __restrict__ fixed,
+                                           int32_t* ids_out, float* rw_out, int E, int k, int lane) {
   float sel_v = 0.0f;  // lane i < k keeps the i-th selected value
   int sel_i = 0;
-  if (fixed_ids != nullptr) {
+  if (fixed != nullptr) {
     if (lane < k) {
-      sel_i = fixed_ids[static_cast<size_t>(t) * k + lane];
+      sel_i = fixed[lane];
       sel_v = bf16_to_f32(row[sel_i]);
     }
   } else {
@@ -132,9 +126,20 @@ __global__ void __launch_bounds__(256) topk_kernel(const uint16_t* __restrict__ 
   for (int i = 0; i < k; ++i) sum += __shfl_sync(0xffffffffu, ev, i);
   const float inv = __frcp_rn(sum);  // == 1.0f / sum under IEEE division
   if (lane < k) {
-    ids[static_cast<size_t>(t) * k + lane] = sel_i;
-    rw[static_cast<size_t>(t) * k + lane] = ev * inv;
+    ids_out[lane] = sel_i;
+    rw_out[lane] = ev * inv;
   }
+}
+
+__global__ void __launch_bounds__(256) topk_kernel(const uint16_t* __restrict__ logits,
+                                                   const int32_t* __restrict__ fixed_ids,
+                                                   int32_t* __restrict__ ids, float* __restrict__ rw,
+                                                   int T, int E, int k) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  topk_token(logits + static_cast<size_t>(t) * E, fixed_ids ? fixed_ids + static_cast<size_t>(t) * k : nullptr,
+             ids + static_cast<size_t>(t) * k, rw + static_cast<size_t>(t) * k, E, k, lane);
 }
 
 // ---- permutation: stable counting sort of the (token,slot) entries by expert.
@@ -203,6 +208,7 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int ma
     p.tile_off[E] = s_tiles[e];
     p.ntiles[0] = min(s_tiles[e], max_tiles);
   }
+  if (e < 4 && p.status) p.status[e] = 0;
 }
 
 __global__ void __launch_bounds__(256) plan_scatter_kernel(const int32_t* __restrict__ ids, int R, int E,
@@ -243,12 +249,25 @@ __global__ void __launch_bounds__(256) plan_scatter_kernel(const int32_t* __rest
 // offsets and the row-tile list, then every warp places its own entries in
 // order using its private cursors, so the result is the stable order.
 constexpr int kPlanSmallMax = 4096;
-__global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* __restrict__ ids, int R, int E,
-                                                          int max_tiles, PlanTables p) {
+// With ROUTE the same block first selects the experts of every token (top-k and
+// softmax, one warp per token) and then plans from the ids it just wrote.
+template <bool ROUTE>
+__global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* ids, int R, int E, int max_tiles,
+                                                          PlanTables p, const uint16_t* __restrict__ logits,
+                                                          const int32_t* __restrict__ fixed_ids, int32_t* ids_out,
+                                                          float* rw_out, int T, int k, int E_logits) {
   extern __shared__ uint16_t s_cnt[];  // [32][E]: counts, later exclusive bases, then cursors
   __shared__ int32_t s_rows[1024];
   __shared__ int32_t s_tiles[1024];
   const int e = threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if constexpr (ROUTE) {
+    for (int t = warp; t < T; t += 32)
+      topk_token(logits + static_cast<size_t>(t) * E_logits,
+                 fixed_ids ? fixed_ids + static_cast<size_t>(t) * k : nullptr,
+                 ids_out + static_cast<size_t>(t) * k, rw_out + static_cast<size_t>(t) * k, E_logits, k, lane);
+    __threadfence_block();  // the ids are read back below by other warps
+    ids = ids_out;
+  }
   for (int i = threadIdx.x; i < 32 * E; i += 1024) s_cnt[i] = 0;
   __syncthreads();
   const int seg = (R + 31) / 32;
@@ -309,6 +328,7 @@ __global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* __restr
     p.tile_off[E] = total_tiles;
     p.ntiles[0] = min(total_tiles, max_tiles);
   }
+  if (e < 4 && p.status) p.status[e] = 0;
   __syncthreads();
   for (int fb = f0; fb < f1; fb += 32) {
     const int f = fb + lane;
@@ -475,7 +495,9 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
 
 cudaError_t routing_set_attributes() {
   cudaError_t e;
-  if ((e = cudaFuncSetAttribute(plan_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536)) != cudaSuccess)
+  if ((e = cudaFuncSetAttribute(plan_small_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536)) != cudaSuccess)
+    return e;
+  if ((e = cudaFuncSetAttribute(plan_small_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536)) != cudaSuccess)
     return e;
   if ((e = cudaFuncSetAttribute(small_m_linear_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304)) != cudaSuccess)
     return e;
@@ -500,10 +522,20 @@ cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_
   return cudaGetLastError();
 }
 
+bool route_and_plan_fits(int T, int k) { return T * k <= kPlanSmallMax && T <= 16; }
+
+cudaError_t launch_route_and_plan(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw, int T,
+                                  int E, int k, int max_tiles, const PlanTables& p, cudaStream_t stream) {
+  plan_small_kernel<true><<<1, 1024, 32 * E * sizeof(uint16_t), stream>>>(nullptr, T * k, E, max_tiles, p, logits,
+                                                                          fixed_ids, ids, rw, T, k, E);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
                         cudaStream_t stream) {
   if (R <= kPlanSmallMax) {
-    plan_small_kernel<<<1, 1024, 32 * E * sizeof(uint16_t), stream>>>(ids, R, E, max_tiles, p);
+    plan_small_kernel<false><<<1, 1024, 32 * E * sizeof(uint16_t), stream>>>(ids, R, E, max_tiles, p, nullptr, nullptr,
+                                                                             nullptr, nullptr, 0, 0, 0);
     return cudaGetLastError();
   }
   const int nblk = (R + kPlanChunk - 1) / kPlanChunk;
