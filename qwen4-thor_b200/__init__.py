@@ -11,7 +11,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libq4t_moe_b200.so")
+LIB_PATH = os.environ.get("Q4T_LIB_PATH", os.path.join(_HERE, "libq4t_moe_b200.so"))
 
 
 class Q4TError(RuntimeError):

@@ -81,40 +81,42 @@ __device__ __forceinline__ void topk_token(const uint16_t* __restrict__ row, con
       sel_v = bf16_to_f32(row[sel_i]);
     }
   } else {
-    float v[16];
+    // Order-preserving 32-bit keys: high half = the bf16 logit mapped to an
+    // unsigned order (-0.0 folded into +0.0, which compare equal as floats),
+    // low half = 0xFFFF - expert id, so that the maximum key is the largest
+    // value and, among equal values, the lowest id.  A selected entry's key
+    // becomes 0.  One warp-wide integer max (redux) per round.
+    uint32_t key[16];
+    uint32_t lmax = 0;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int e = lane + 32 * i;
-      v[i] = e < E ? bf16_to_f32(row[e]) : -INFINITY;  // never beats the -1e30 start value
+      uint32_t kv = 0;
+      if (e < E) {
+        uint32_t b = row[e];
+        if (b == 0x8000u) b = 0;
+        const uint32_t ord = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+        kv = (ord << 16) | (0xffffu - static_cast<uint32_t>(e));
+      }
+      key[i] = kv;
+      lmax = max(lmax, kv);
     }
     for (int r = 0; r < k; ++r) {
-      float m = -1e30f;
-      int mid = 0;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int e = lane + 32 * i;
-        if (v[i] > m || (v[i] == m && e < mid)) {
-          m = v[i];
-          mid = e;
-        }
-      }
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        const float om = __shfl_xor_sync(0xffffffffu, m, off);
-        const int oid = __shfl_xor_sync(0xffffffffu, mid, off);
-        if (om > m || (om == m && oid < mid)) {
-          m = om;
-          mid = oid;
-        }
-      }
+      const uint32_t best = __reduce_max_sync(0xffffffffu, lmax);
+      const int mid = static_cast<int>(0xffffu - (best & 0xffffu));
       if (lane == r) {
-        sel_v = m;
+        const uint32_t ord = best >> 16;
+        const uint32_t b = (ord & 0x8000u) ? (ord & 0x7fffu) : (~ord & 0xffffu);
+        sel_v = bf16_to_f32(static_cast<uint16_t>(b));
         sel_i = mid;
       }
-      if ((mid & 31) == lane) {
+      if ((mid & 31) == lane) {  // the owner drops the winner and refreshes its local maximum
+        lmax = 0;
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (i == (mid >> 5)) v[i] = -1e30f;
+        for (int i = 0; i < 16; ++i) {
+          if (i == (mid >> 5)) key[i] = 0;
+          lmax = max(lmax, key[i]);
+        }
       }
     }
   }

@@ -24,7 +24,13 @@ namespace q4t {
 
 namespace {
 
-constexpr int kStages = 4;
+constexpr int kMaxStages = 4;
+// Shared-memory ring depth.  Three 54 KB stages measured faster than four for the
+// block-scaled tiles (decode gate/up 101 vs 108 us); the BF16 tiles keep four.
+template <bool NVF4>
+constexpr int num_stages() {
+  return NVF4 ? 3 : 4;
+}
 constexpr int kEpiWarpsPerQuad = 4;                       // epilogue warps sharing one TMEM lane quadrant
 constexpr int kEpiWarps = 4 * kEpiWarpsPerQuad;
 constexpr int kFirstEpiWarp = 2;                          // warp 0: producer, warp 1: MMA issuer
@@ -42,8 +48,8 @@ constexpr uint32_t stage_bytes() {
 }
 
 struct Barriers {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full;
   uint64_t acc_empty;
   uint32_t tmem_base;
@@ -65,6 +71,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   constexpr uint32_t kBBytes = BN * 128;
   constexpr uint32_t kStage = stage_bytes<NVF4, BN>();
+  constexpr int kStages = num_stages<NVF4>();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile uint32_t* abort_flag = &bars.abort_flag;
 
@@ -292,93 +299,82 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       acc_phase ^= 1u;
       if (!warp_has_rows) continue;
 
-      // bf16x2 words (g then u for SwiGLU).  Rows past the tile's row count carry
-      // stale accumulator bits: zero them so the arithmetic below never meets
-      // NaNs or denormals.
-      uint32_t packed[kUnitsPerWarp][kSwiglu ? 16 : 8];
-      float raw[(EPI == Epilogue::kStoreF32) ? kUnitsPerWarp : 1][16];
-#pragma unroll
-      for (int j = 0; j < kUnitsPerWarp; ++j) {
-        if constexpr (EPI == Epilogue::kStoreF32) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) raw[j][i] = valid ? alpha * __uint_as_float(ra[j][i]) : 0.0f;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float lo = valid ? alpha * __uint_as_float(ra[j][2 * i]) : 0.0f;
-            const float hi = valid ? alpha * __uint_as_float(ra[j][2 * i + 1]) : 0.0f;
-            packed[j][i] = f32x2_to_bf16x2(lo, hi);
-          }
-          if constexpr (kSwiglu) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float lo = valid ? alpha * __uint_as_float(rb[j][2 * i]) : 0.0f;
-              const float hi = valid ? alpha * __uint_as_float(rb[j][2 * i + 1]) : 0.0f;
-              packed[j][8 + i] = f32x2_to_bf16x2(lo, hi);
-            }
-          }
-        }
-      }
-
-      // ---- math and stores from registers
+      // ---- per unit: convert, compute, store (unit by unit keeps few registers live).
+      // Rows past the tile's row count carry stale accumulator bits: they are
+      // zeroed so the arithmetic below never meets NaNs or denormals.
 #pragma unroll
       for (int j = 0; j < kUnitsPerWarp; ++j) {
         const int unit = sub * kUnitsPerWarp + j;
         if (unit >= kUnits) continue;
         const int c0 = unit * kUnitCols;
-        if constexpr (EPI == Epilogue::kStoreBf16) {
-          if (valid && n0 + c0 < args.b_rows_valid) {
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) + grow * args.ldo + n0 + c0);
-            dst[0] = make_uint4(packed[j][0], packed[j][1], packed[j][2], packed[j][3]);
-            dst[1] = make_uint4(packed[j][4], packed[j][5], packed[j][6], packed[j][7]);
-          }
-        } else if constexpr (EPI == Epilogue::kStoreF32) {
+        if constexpr (EPI == Epilogue::kStoreF32) {
           if (valid && n0 + c0 < args.b_rows_valid) {
             float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.out) + grow * args.ldo + n0 + c0);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              dst[i] = make_float4(raw[j][4 * i], raw[j][4 * i + 1], raw[j][4 * i + 2], raw[j][4 * i + 3]);
+              dst[i] = make_float4(alpha * __uint_as_float(ra[j][4 * i]), alpha * __uint_as_float(ra[j][4 * i + 1]),
+                                   alpha * __uint_as_float(ra[j][4 * i + 2]), alpha * __uint_as_float(ra[j][4 * i + 3]));
           }
         } else {
-          const uint32_t* gb = &packed[j][0];
-          const uint32_t* ub = &packed[j][8];
-          if (args.gu_dump && valid) {
-            uint4* dg = reinterpret_cast<uint4*>(args.gu_dump + grow * args.gu_dump_ld + n0 + c0);
-            dg[0] = make_uint4(gb[0], gb[1], gb[2], gb[3]);
-            dg[1] = make_uint4(gb[4], gb[5], gb[6], gb[7]);
-            uint4* du = reinterpret_cast<uint4*>(args.gu_dump + grow * args.gu_dump_ld + args.up_row_offset + n0 + c0);
-            du[0] = make_uint4(ub[0], ub[1], ub[2], ub[3]);
-            du[1] = make_uint4(ub[4], ub[5], ub[6], ub[7]);
-          }
-          // SwiGLU on the bf16-rounded projections: (g * sigmoid(g)) * u
-          float a[16];
+          uint32_t gb[8];  // bf16x2 words of the 16 (gate) columns
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float g0 = bf16x2_lo(gb[i]), g1 = bf16x2_hi(gb[i]);
-            const float u0 = bf16x2_lo(ub[i]), u1 = bf16x2_hi(ub[i]);
-            a[2 * i] = (g0 * sigmoid_ref(g0)) * u0;
-            a[2 * i + 1] = (g1 * sigmoid_ref(g1)) * u1;
+            const float lo = valid ? alpha * __uint_as_float(ra[j][2 * i]) : 0.0f;
+            const float hi = valid ? alpha * __uint_as_float(ra[j][2 * i + 1]) : 0.0f;
+            gb[i] = f32x2_to_bf16x2(lo, hi);
           }
-          if constexpr (EPI == Epilogue::kSwigluBf16) {
-            if (valid) {
-              uint32_t o[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = f32x2_to_bf16x2(a[2 * i], a[2 * i + 1]);
+          if constexpr (EPI == Epilogue::kStoreBf16) {
+            if (valid && n0 + c0 < args.b_rows_valid) {
               uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) + grow * args.ldo + n0 + c0);
-              dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-              dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+              dst[0] = make_uint4(gb[0], gb[1], gb[2], gb[3]);
+              dst[1] = make_uint4(gb[4], gb[5], gb[6], gb[7]);
             }
           } else {
-            const float next_scale = args.next_scale[group];
-            const uint32_t out_ntk = (static_cast<uint32_t>(args.up_row_offset) + 63u) >> 6;
-            uint32_t lo, hi;
-            const uint32_t sf = quantize_group16(a, next_scale, lo, hi);
-            if (valid) {
-              *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + grow * args.ldo + ((n0 + c0) >> 1)) =
-                  make_uint2(lo, hi);
-              const uint32_t g = static_cast<uint32_t>(n0 + c0) >> 4;  // scale group along the intermediate
-              args.out_sf_tiles[(static_cast<size_t>(mt) * out_ntk + (g >> 2)) * 512u + sf_in_atom(row, g)] =
-                  static_cast<uint8_t>(sf);
+            uint32_t ub[8];  // the 16 matching up columns
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float lo = valid ? alpha * __uint_as_float(rb[j][2 * i]) : 0.0f;
+              const float hi = valid ? alpha * __uint_as_float(rb[j][2 * i + 1]) : 0.0f;
+              ub[i] = f32x2_to_bf16x2(lo, hi);
+            }
+            if (args.gu_dump && valid) {
+              uint4* dg = reinterpret_cast<uint4*>(args.gu_dump + grow * args.gu_dump_ld + n0 + c0);
+              dg[0] = make_uint4(gb[0], gb[1], gb[2], gb[3]);
+              dg[1] = make_uint4(gb[4], gb[5], gb[6], gb[7]);
+              uint4* du = reinterpret_cast<uint4*>(args.gu_dump + grow * args.gu_dump_ld + args.up_row_offset + n0 + c0);
+              du[0] = make_uint4(ub[0], ub[1], ub[2], ub[3]);
+              du[1] = make_uint4(ub[4], ub[5], ub[6], ub[7]);
+            }
+            // SwiGLU on the bf16-rounded projections: (g * sigmoid(g)) * u
+            float a[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float g0 = bf16x2_lo(gb[i]), g1 = bf16x2_hi(gb[i]);
+              const float u0 = bf16x2_lo(ub[i]), u1 = bf16x2_hi(ub[i]);
+              a[2 * i] = (g0 * sigmoid_ref(g0)) * u0;
+              a[2 * i + 1] = (g1 * sigmoid_ref(g1)) * u1;
+            }
+            if constexpr (EPI == Epilogue::kSwigluBf16) {
+              if (valid) {
+                uint32_t o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = f32x2_to_bf16x2(a[2 * i], a[2 * i + 1]);
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) + grow * args.ldo + n0 + c0);
+                dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+              }
+            } else {
+              const float next_scale = args.next_scale[group];
+              const uint32_t out_ntk = (static_cast<uint32_t>(args.up_row_offset) + 63u) >> 6;
+              uint32_t lo, hi;
+              const uint32_t sf = quantize_group16(a, next_scale, lo, hi);
+              if (valid) {
+                *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + grow * args.ldo + ((n0 + c0) >> 1)) =
+                    make_uint2(lo, hi);
+                const uint32_t g = static_cast<uint32_t>(n0 + c0) >> 4;  // scale group along the intermediate
+                args.out_sf_tiles[(static_cast<size_t>(mt) * out_ntk + (g >> 2)) * 512u + sf_in_atom(row, g)] =
+                    static_cast<uint8_t>(sf);
+              }
             }
           }
         }
@@ -398,7 +394,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 template <bool NVF4, int BN>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, Epilogue epi,
                    int num_sms, cudaStream_t stream) {
-  const size_t smem = kStages * stage_bytes<NVF4, BN>() + 1024;
+  const size_t smem = num_stages<NVF4>() * stage_bytes<NVF4, BN>() + 1024;
   const int grid = a.ntiles_dev ? num_sms : min(num_sms, a.ntiles_host * a.n_tiles);
   if (grid <= 0) return cudaSuccess;
   switch (epi) {
@@ -425,7 +421,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs&
 template <bool NVF4, Epilogue E, int BN>
 cudaError_t set_attr() {
   return cudaFuncSetAttribute(gemm_kernel<NVF4, E, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(kStages * stage_bytes<NVF4, BN>() + 1024));
+                              static_cast<int>(num_stages<NVF4>() * stage_bytes<NVF4, BN>() + 1024));
 }
 
 }  // namespace
