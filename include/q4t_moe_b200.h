@@ -62,6 +62,12 @@ typedef struct {
   const float* gu_input_scale;   /* [E] device */
   const float* dn_w_scale2;      /* [E] device */
   const float* dn_input_scale;   /* [E] device */
+  /* > 0: every expert's gate/up input scale equals this value (the caller
+   * checked its host copies).  Lets large batches quantise each token once and
+   * copy the codes to its top-k rows instead of quantising every (token,slot)
+   * row; the bytes produced are the same.  0: no such promise.               */
+  float gu_input_scale_uniform;
+  int32_t reserved;
 } q4t_routed_weights;
 
 /* Router and shared-expert BF16 weights on the device: the POD image of
@@ -155,6 +161,7 @@ typedef struct {
   size_t ntiles;                           /* int32 [1]   number of row tiles  */
   size_t tile_expert, tile_row0, tile_nrows; /* int32 [max_tiles]              */
   size_t a_sf_tiles;                       /* input scales, tile-local atoms   */
+  size_t xq_packed, xq_sf;                 /* per-token codes / scales (uniform input scale path) */
   size_t inter_packed;                     /* [M*k, moe_is/2] intermediate codes */
   size_t inter_sf_tiles;                   /* intermediate scales, tile-local  */
   size_t status;                           /* int32 [4] kernel status words    */

@@ -23,7 +23,8 @@ class RoutedWeights(C.Structure):
     _fields_ = [("E", C.c_int32), ("hs", C.c_int32), ("moe_is", C.c_int32), ("slot_mode", C.c_int32),
                 ("gu_packed", C.c_void_p), ("gu_sf", C.c_void_p), ("dn_packed", C.c_void_p),
                 ("dn_sf", C.c_void_p), ("gu_w_scale2", C.c_void_p), ("gu_input_scale", C.c_void_p),
-                ("dn_w_scale2", C.c_void_p), ("dn_input_scale", C.c_void_p)]
+                ("dn_w_scale2", C.c_void_p), ("dn_input_scale", C.c_void_p),
+                ("gu_input_scale_uniform", C.c_float), ("reserved", C.c_int32)]
 
 
 class ExtraWeights(C.Structure):
@@ -36,7 +37,7 @@ class ExtraWeights(C.Structure):
 class RoutedWsLayout(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in (
         "a_packed", "a_sf", "gu_out", "dn_out", "counts", "offsets", "row_of_flat", "flat_of_row",
-        "row_tile", "ntiles", "tile_expert", "tile_row0", "tile_nrows", "a_sf_tiles", "inter_packed",
+        "row_tile", "ntiles", "tile_expert", "tile_row0", "tile_nrows", "a_sf_tiles", "xq_packed", "xq_sf", "inter_packed",
         "inter_sf_tiles", "status", "max_tiles", "total")]
 
 
@@ -151,7 +152,12 @@ class DeviceLayer:
     def __init__(self, E, hs, moe_is, shared_is, tensors: dict):
         self.E, self.hs, self.moe_is, self.shared_is = E, hs, moe_is, shared_is
         self.t = tensors  # keeps the device buffers alive
-        self.routed = RoutedWeights(E, hs, moe_is, 0, *[self._p(n) for n in self.ROUTED])
+        gis = tensors.get("gu_input_scale")
+        uniform = 0.0
+        if gis is not None and gis.numel() > 0:   # one host read at construction time
+            lo, hi = float(gis.min()), float(gis.max())
+            uniform = lo if lo == hi and lo > 0 else 0.0
+        self.routed = RoutedWeights(E, hs, moe_is, 0, *[self._p(n) for n in self.ROUTED], uniform, 0)
         self.extra = ExtraWeights(E, hs, shared_is, *[self._p(n) for n in self.EXTRA])
 
     def _p(self, name):

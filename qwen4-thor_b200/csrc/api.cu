@@ -156,6 +156,8 @@ void routed_layout(int M, int k, int hs, int is, int E, q4t_routed_ws_layout* L)
   L->tile_row0 = take(max_tiles * 4);
   L->tile_nrows = take(max_tiles * 4);
   L->a_sf_tiles = take(max_tiles * static_cast<size_t>((hs + 63) / 64) * 512);
+  L->xq_packed = take(static_cast<size_t>(M) * (hs / 2));
+  L->xq_sf = take(sf_buffer_size(M, hs));
   L->inter_packed = take(R * (is / 2));
   L->inter_sf_tiles = take(max_tiles * static_cast<size_t>((is + 63) / 64) * 512);
   L->status = take(256);
@@ -238,9 +240,21 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
 
   uint8_t* a_packed = P.at<uint8_t>(L.a_packed);
   uint8_t* a_sf_tiles = P.at<uint8_t>(L.a_sf_tiles);
-  if ((e = q4t::launch_gather_quantize(x, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, ids,
-                                       w->gu_input_scale, pt.row_tile, pt.tile_row0, pt.offsets + E, k, E, st)) != cudaSuccess)
+  // With one input scale for all experts and a large batch, quantise each token
+  // once and copy its codes to its k rows; otherwise quantise every grouped row.
+  if (w->gu_input_scale_uniform > 0.0f && k > 1 && R >= 8192) {
+    uint8_t* xq = P.at<uint8_t>(L.xq_packed);
+    uint8_t* xq_sf = P.at<uint8_t>(L.xq_sf);
+    if ((e = q4t::launch_quantize(x, xq, xq_sf, M, hs, w->gu_input_scale_uniform, st)) != cudaSuccess)
+      return fail_cuda("token quantise launch", e);
+    if ((e = q4t::launch_gather_codes(xq, xq_sf, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, pt.row_tile,
+                                      pt.tile_row0, pt.offsets + E, k, st)) != cudaSuccess)
+      return fail_cuda("code gather launch", e);
+  } else if ((e = q4t::launch_gather_quantize(x, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, ids,
+                                              w->gu_input_scale, pt.row_tile, pt.tile_row0, pt.offsets + E, k, E,
+                                              st)) != cudaSuccess) {
     return fail_cuda("gather-quantise launch", e);
+  }
   stage_end(3, st);
 
   CUtensorMap tm_a, tm_b;

@@ -19,6 +19,9 @@ cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* 
                                    const float* input_scale, const int32_t* row_tile,
                                    const int32_t* tile_row0, const int32_t* rows_dev, int k, int E,
                                    cudaStream_t stream);
+cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed, uint8_t* sf_tiles,
+                                int R, int K, const int32_t* flat_of_row, const int32_t* row_tile,
+                                const int32_t* tile_row0, const int32_t* rows_dev, int k, cudaStream_t stream);
 cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,
                            float inv_global, int N, int K, cudaStream_t stream);
 cudaError_t launch_encoder_selftest(int which, uint64_t first, uint64_t count,

@@ -46,6 +46,10 @@ template <bool NVF4, int BN>
 constexpr uint32_t stage_bytes() {
   return kABytes + BN * 128 + (NVF4 ? kSfaBytes + kSfbBytes : 0u);
 }
+// Per-warp staging for the bf16 row stores: 32 rows x 64 bytes, through which a
+// warp turns "one row per lane" into "four lanes per row" so that each store
+// instruction writes whole 64-byte row segments.
+constexpr uint32_t kStoreStageBytes = 32 * 64;
 
 struct Barriers {
   uint64_t full[kMaxStages];
@@ -324,10 +328,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             gb[i] = f32x2_to_bf16x2(lo, hi);
           }
           if constexpr (EPI == Epilogue::kStoreBf16) {
-            if (valid && n0 + c0 < args.b_rows_valid) {
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) + grow * args.ldo + n0 + c0);
-              dst[0] = make_uint4(gb[0], gb[1], gb[2], gb[3]);
-              dst[1] = make_uint4(gb[4], gb[5], gb[6], gb[7]);
+            // Two units (32 columns = 64 bytes per row) go through the warp's staging
+            // block: written one row per lane (16-byte chunks, XOR-swizzled against bank
+            // conflicts), read back four lanes per row, stored as 64-byte row segments.
+            const uint32_t stg = smem_base + kStages * kStage + static_cast<uint32_t>(warp - kFirstEpiWarp) * kStoreStageBytes;
+            const uint32_t sw = (static_cast<uint32_t>(lane) >> 1) & 3u;
+            const uint32_t half = static_cast<uint32_t>(j & 1) * 2u;  // chunk pair of this unit inside the 64 bytes
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(stg + lane * 64u + ((half ^ sw) << 4)), "r"(gb[0]),
+                         "r"(gb[1]), "r"(gb[2]), "r"(gb[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(stg + lane * 64u + (((half + 1u) ^ sw) << 4)),
+                         "r"(gb[4]), "r"(gb[5]), "r"(gb[6]), "r"(gb[7]) : "memory");
+            if ((j & 1) == 1 || j == kUnitsPerWarp - 1) {
+              __syncwarp();
+              const bool pair = (j & 1) == 1;                        // a lone last unit stages 16 columns
+              const int cbase = (pair ? unit - 1 : unit) * kUnitCols;  // first column of what is staged
+              const uint32_t chunk = static_cast<uint32_t>(lane) & 3u;
+              const int ncols = (pair ? 2 : 1) * kUnitCols;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rr = (lane >> 2) + 8 * i;                  // row of the warp's 32
+                const uint32_t rsw = (static_cast<uint32_t>(rr) >> 1) & 3u;
+                uint32_t v0, v1, v2, v3;
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                             : "r"(stg + rr * 64u + ((chunk ^ rsw) << 4)) : "memory");
+                const int col = n0 + cbase + static_cast<int>(chunk) * 8;
+                if (quad * 32 + rr < nrows && static_cast<int>(chunk) * 8 < ncols && col < args.b_rows_valid)
+                  *reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) +
+                                            static_cast<size_t>(row0 + quad * 32 + rr) * args.ldo + col) =
+                      make_uint4(v0, v1, v2, v3);
+              }
+              __syncwarp();
             }
           } else {
             uint32_t ub[8];  // the 16 matching up columns
@@ -394,7 +424,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 template <bool NVF4, int BN>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, Epilogue epi,
                    int num_sms, cudaStream_t stream) {
-  const size_t smem = num_stages<NVF4>() * stage_bytes<NVF4, BN>() + 1024;
+  const size_t smem = num_stages<NVF4>() * stage_bytes<NVF4, BN>() + kEpiWarps * kStoreStageBytes + 1024;
   const int grid = a.ntiles_dev ? num_sms : min(num_sms, a.ntiles_host * a.n_tiles);
   if (grid <= 0) return cudaSuccess;
   switch (epi) {
@@ -421,7 +451,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs&
 template <bool NVF4, Epilogue E, int BN>
 cudaError_t set_attr() {
   return cudaFuncSetAttribute(gemm_kernel<NVF4, E, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(num_stages<NVF4>() * stage_bytes<NVF4, BN>() + 1024));
+                              static_cast<int>(num_stages<NVF4>() * stage_bytes<NVF4, BN>() + kEpiWarps * kStoreStageBytes + 1024));
 }
 
 }  // namespace

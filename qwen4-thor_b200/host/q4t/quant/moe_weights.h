@@ -42,8 +42,12 @@ struct MoEWeightLayout {
   }
   // POD image handed to the C ABI.
   q4t_routed_weights Abi() const {
+    float uniform = gu_input_scale_h.empty() ? 0.0f : gu_input_scale_h[0];
+    for (float v : gu_input_scale_h)
+      if (v != uniform) uniform = 0.0f;
     return q4t_routed_weights{E, hs, moe_is, slot_mode ? 1 : 0, gu_packed, gu_sf, dn_packed, dn_sf,
-                              gu_w_scale2, gu_input_scale, dn_w_scale2, dn_input_scale};
+                              gu_w_scale2, gu_input_scale, dn_w_scale2, dn_input_scale,
+                              uniform > 0.0f ? uniform : 0.0f, 0};
   }
 };
 

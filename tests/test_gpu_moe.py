@@ -89,6 +89,32 @@ def test_routed_accumulates_and_is_deterministic(q4t, gpu_lib):
     assert torch.equal(y1, y0 + 0.25)
 
 
+def test_uniform_input_scale_path_is_bit_identical(q4t, gpu_lib):
+    """Large batches with one gate/up input scale for all experts quantise each
+    token once and copy the codes; the result must equal the per-row path."""
+    E, hs, is_, T, k = 16, 256, 128, 1024, 8          # R = 8192 rows: the fast path's threshold
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=128, seed=88)
+    fast, slow = q4t.DeviceLayer.from_host(L), q4t.DeviceLayer.from_host(L)
+    assert fast.routed.gu_input_scale_uniform > 0
+    slow.routed.gu_input_scale_uniform = 0.0
+    x = dev(synth.make_x(T, hs, seed=4))
+    ids_h, rw_h = synth.random_routing(T, k, E, seed=6)
+    ids, rw = dev(ids_h), dev(rw_h)
+    outs = []
+    for dl in (fast, slow):
+        rf = q4t.RoutedForward(dl, T, k)
+        y = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
+        rf(x, ids, rw, y)
+        rf.status()
+        outs.append((y, rf.region("a_packed", torch.uint8, T * k * hs // 2).clone(),
+                     rf.region("dn_out", torch.int16, T * k * hs).clone()))
+    assert torch.equal(outs[0][1], outs[1][1])
+    assert torch.equal(outs[0][2], outs[1][2])
+    assert torch.equal(outs[0][0], outs[1][0])
+    want = O.routed_forward(host(x), ids_h, rw_h, L, 1)
+    assert np.abs(host(outs[0][0]) - want).max() <= 2e-3 * np.abs(want).max()
+
+
 @pytest.mark.parametrize("T", [2, 16, 130])
 def test_moe_forward_vs_oracle(q4t, gpu_lib, T):
     """T = 2 takes the exact-order GEMV projections, T >= 16 the tensor cores."""
