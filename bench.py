@@ -238,6 +238,9 @@ def main_single(args):
     q4t.load()
     torch.cuda.set_device(0)
     peaks = load_peaks()
+    if args.prefill_tokens > 0:
+        print(json.dumps(dict(prefill=run_prefill_point(torch, q4t, args.prefill_tokens, args.steps, args.warmup))))
+        return
     n_layers = 1 if args.impl == "reference" else args.layers
     layers = [syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=20260921 + 1000 + i) for i in range(n_layers)]
 
@@ -317,6 +320,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline point only (no sweep, no prefill)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=4, help="independent layer weight sets rotated per step")
+    ap.add_argument("--prefill-tokens", type=int, default=0,
+                    help="run only the Zipf-skewed prefill layer at this many tokens and print its result")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     world = int(os.environ.get("WORLD_SIZE", "1"))

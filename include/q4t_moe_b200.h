@@ -303,7 +303,8 @@ int32_t q4t_stage_timing_read(float* ms_out);
  * sweep float bit patterns [first, first+count) through the kernels' hardware
  * encoders and through a compare-chain restatement of format.h and return the
  * number of disagreements in *mismatches (host pointer).  which: 0 = e2m1,
- * 1 = ue4m3 (non-negative inputs only).  Synchronises the stream.             */
+ * 1 = ue4m3 (non-negative inputs only), 2 = the epilogue's branch-free
+ * reciprocal against IEEE 1/x on [1, 2^126).  Synchronises the stream.        */
 int32_t q4t_selftest_encoders(int32_t which, uint64_t first, uint64_t count,
                               uint64_t* mismatches, uint32_t* first_bad,
                               void* stream);

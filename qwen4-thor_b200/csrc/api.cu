@@ -487,6 +487,9 @@ int32_t q4t_fp4_gemm(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t
   g.out = out;
   g.ldo = N;
   g.alpha_const = inv_w_global * inv_a_global;  // include/q4t/quant/fp4_gemm.h:205
+#ifdef Q4T_TRACE
+  if (const char* t = std::getenv("Q4T_TRACE_PTR")) g.trace = reinterpret_cast<long long*>(std::strtoull(t, nullptr, 0));
+#endif
   cudaError_t e = q4t::launch_gemm_nvf4(ta, tb, g, out_is_bf16 ? q4t::Epilogue::kStoreBf16 : q4t::Epilogue::kStoreF32,
                                         ds->num_sms, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? Q4T_OK : fail_cuda("NVFP4 GEMM launch", e);

@@ -107,6 +107,7 @@ struct GemmArgs {
   uint16_t* gu_dump;           // optional bf16 [rows, 2*inner] copy of the rounded gate|up values
   int gu_dump_ld;
   int32_t* status;             // device status word (non-zero = a bounded wait ran out)
+  long long* trace;            // timestamps of CTA 0 (only read by builds with Q4T_TRACE; null otherwise)
 };
 // tmap_a: [rows, K] operand A; tmap_b: [all groups' rows, K] operand B (K-major, 128-byte boxes).
 cudaError_t launch_gemm_nvf4(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmArgs& a,

@@ -150,9 +150,12 @@ __global__ void encoder_selftest_kernel(int which, uint64_t first, uint64_t coun
       const uint32_t hw = e2m1x2_encode_hw(f, -f);
       const uint32_t sw = e2m1_encode_sw(f) | (e2m1_encode_sw(-f) << 4);
       differ = hw != sw;
-    } else {
+    } else if (which == 1) {
       if (f < 0.0f || bits == 0x80000000u) continue;
       differ = e4m3_encode_hw(f) != e4m3_encode_sw(f);
+    } else {  // branch-free reciprocal against the IEEE routine on [1, 2^126)
+      if (!(f >= 1.0f && f < Q4T_RCP_FAST_MAX)) continue;
+      differ = __float_as_uint(rcp_rn_ge1(f)) != __float_as_uint(__frcp_rn(f));
     }
     if (differ) {
       ++bad;

@@ -60,7 +60,15 @@ struct Barriers {
   uint32_t abort_flag;
 };
 
-__device__ __forceinline__ float sigmoid_ref(float g) { return __frcp_rn(1.0f + __expf(-g)); }
+#ifdef Q4T_TRACE
+// Timestamp slots per tile of CTA 0: [role][tile][slot]; role 0 producer, 1 MMA, 2 epilogue warp of quadrant 0.
+#define Q4T_STAMP(role, tile_idx, slot)                                                            \
+  do {                                                                                             \
+    if (args.trace && blockIdx.x == 0 && (tile_idx) < 64) args.trace[((role) * 64 + (tile_idx)) * 8 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define Q4T_STAMP(role, tile_idx, slot) do {} while (0)
+#endif
 
 // BN = accumulator columns of one tile (256, or 64 for the narrow BF16 tiles
 // that spread small-T projections over more SMs).
@@ -184,12 +192,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint64_t sfb0 = umma_desc_sf(smem_base + kABytes + kBBytes + kSfaBytes);
       const uint32_t bar_full0 = smem_u32(&bars.full[0]), bar_empty0 = smem_u32(&bars.empty[0]);
       const uint32_t bar_acc_full = smem_u32(&bars.acc_full), bar_acc_empty = smem_u32(&bars.acc_empty);
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int tcount = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+        Q4T_STAMP(1, tcount, 0);
         if (!mbar_try_wait(bar_acc_empty, acc_phase ^ 1u) && !mbar_wait(bar_acc_empty, acc_phase ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        Q4T_STAMP(1, tcount, 1);
         uint32_t k_left = k_bytes;
         for (int kb = 0; kb < nkb; ++kb) {
           const uint32_t full = bar_full0 + stage * 8u;
@@ -198,6 +209,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             break;
           }
           tc_fence_after();
+          if (kb < 4) Q4T_STAMP(1, tcount, 3 + kb);
           const uint64_t soff = static_cast<uint64_t>(stage * (kStage >> 4));
           const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
           const uint32_t first = kb != 0;
@@ -245,6 +257,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
         if (ok) tc_commit(bar_acc_full);
+        Q4T_STAMP(1, tcount, 2);
         acc_phase ^= 1u;
       }
       if (!ok && args.status) atomicMax(args.status, 2);
@@ -265,10 +278,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     constexpr int kUnitsPerWarp = (kUnits + kEpiWarpsPerQuad - 1) / kEpiWarpsPerQuad;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    int tcount = 0;
+    const bool stamp = warp == kFirstEpiWarp + 2 && lane == 0;  // quadrant 0, first of its four warps
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
       const int mt = tile / args.n_tiles, nt = tile - mt * args.n_tiles;
       const int group = args.tile_expert ? args.tile_expert[mt] : 0;
       const int row0 = args.tile_expert ? args.tile_row0[mt] : mt * kTileM;
+      if (stamp) Q4T_STAMP(2, tcount, 0);
       const int nrows = args.tile_expert ? args.tile_nrows[mt] : min(kTileM, args.total_rows - row0);
       const float alpha =
           args.alpha_w ? args.alpha_w[group] * args.alpha_a[group] : args.alpha_const;
@@ -277,6 +293,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         break;
       }
       tc_fence_after();
+      if (stamp) Q4T_STAMP(2, tcount, 1);
       const bool valid = row < nrows;
       const bool warp_has_rows = quad * 32 < nrows;  // warp-uniform
       const size_t grow = static_cast<size_t>(row0 + row);
@@ -284,15 +301,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
       // ---- drain this warp's units into registers, then hand the accumulator
       // back to the MMA warp before doing any arithmetic on them
-      uint32_t ra[kUnitsPerWarp][16];                 // store: 16 columns; SwiGLU: 16 gate columns
-      uint32_t rb[kSwiglu ? kUnitsPerWarp : 1][16];   // SwiGLU: the 16 matching up columns
+      // this warp's columns are consecutive: units [sub*kUnitsPerWarp, +kUnitsPerWarp)
+      uint32_t ra[kUnitsPerWarp * 16];                 // store: the columns; SwiGLU: the gate columns
+      uint32_t rb[kSwiglu ? kUnitsPerWarp * 16 : 16];  // SwiGLU: the matching up columns
       if (warp_has_rows) {
+        const uint32_t c_first = static_cast<uint32_t>(sub * kUnitsPerWarp * kUnitCols);
+        if constexpr (kUnitsPerWarp == 4) {
+          tmem_ld64(tacc + c_first, ra);
+        } else if constexpr (kUnitsPerWarp == 2) {
+          tmem_ld32(tacc + c_first, ra);
+          if constexpr (kSwiglu) tmem_ld32(tacc + kHalf + c_first, rb);
+        } else {
 #pragma unroll
-        for (int j = 0; j < kUnitsPerWarp; ++j) {
-          const int unit = sub * kUnitsPerWarp + j;
-          if (unit < kUnits) {
-            tmem_ld16(tacc + unit * kUnitCols, ra[j]);
-            if constexpr (kSwiglu) tmem_ld16(tacc + kHalf + unit * kUnitCols, rb[j]);
+          for (int j = 0; j < kUnitsPerWarp; ++j) {
+            const int unit = sub * kUnitsPerWarp + j;
+            if (unit < kUnits) {
+              tmem_ld16(tacc + unit * kUnitCols, *reinterpret_cast<uint32_t (*)[16]>(&ra[j * 16]));
+              if constexpr (kSwiglu)
+                tmem_ld16(tacc + kHalf + unit * kUnitCols, *reinterpret_cast<uint32_t (*)[16]>(&rb[j * 16]));
+            }
           }
         }
         tmem_ld_wait();
@@ -300,6 +327,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty));
+      if (stamp) Q4T_STAMP(2, tcount, 2);
       acc_phase ^= 1u;
       if (!warp_has_rows) continue;
 
@@ -316,15 +344,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             float4* dst = reinterpret_cast<float4*>(static_cast<float*>(args.out) + grow * args.ldo + n0 + c0);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-              dst[i] = make_float4(alpha * __uint_as_float(ra[j][4 * i]), alpha * __uint_as_float(ra[j][4 * i + 1]),
-                                   alpha * __uint_as_float(ra[j][4 * i + 2]), alpha * __uint_as_float(ra[j][4 * i + 3]));
+              dst[i] = make_float4(alpha * __uint_as_float(ra[j * 16 + 4 * i]), alpha * __uint_as_float(ra[j * 16 + 4 * i + 1]),
+                                   alpha * __uint_as_float(ra[j * 16 + 4 * i + 2]), alpha * __uint_as_float(ra[j * 16 + 4 * i + 3]));
           }
         } else {
           uint32_t gb[8];  // bf16x2 words of the 16 (gate) columns
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float lo = valid ? alpha * __uint_as_float(ra[j][2 * i]) : 0.0f;
-            const float hi = valid ? alpha * __uint_as_float(ra[j][2 * i + 1]) : 0.0f;
+            const float lo = valid ? alpha * __uint_as_float(ra[j * 16 + 2 * i]) : 0.0f;
+            const float hi = valid ? alpha * __uint_as_float(ra[j * 16 + 2 * i + 1]) : 0.0f;
             gb[i] = f32x2_to_bf16x2(lo, hi);
           }
           if constexpr (EPI == Epilogue::kStoreBf16) {
@@ -363,8 +391,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t ub[8];  // the 16 matching up columns
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float lo = valid ? alpha * __uint_as_float(rb[j][2 * i]) : 0.0f;
-              const float hi = valid ? alpha * __uint_as_float(rb[j][2 * i + 1]) : 0.0f;
+              const float lo = valid ? alpha * __uint_as_float(rb[j * 16 + 2 * i]) : 0.0f;
+              const float hi = valid ? alpha * __uint_as_float(rb[j * 16 + 2 * i + 1]) : 0.0f;
               ub[i] = f32x2_to_bf16x2(lo, hi);
             }
             if (args.gu_dump && valid) {
@@ -376,13 +404,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               du[1] = make_uint4(ub[4], ub[5], ub[6], ub[7]);
             }
             // SwiGLU on the bf16-rounded projections: (g * sigmoid(g)) * u
-            float a[16];
+            // sigmoid(g) = 1 / (1 + __expf(-g)) with IEEE division, as the reference
+            // computes it.  The denominators are >= 1, so the branch-free reciprocal
+            // gives the same bits unless one of them reaches 2^126 (g below about -87),
+            // in which case the whole unit takes the IEEE routine.
+            float a[16];  // first the sigmoid denominators, then the SwiGLU values
+            bool big = false;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float g0 = bf16x2_lo(gb[i]), g1 = bf16x2_hi(gb[i]);
-              const float u0 = bf16x2_lo(ub[i]), u1 = bf16x2_hi(ub[i]);
-              a[2 * i] = (g0 * sigmoid_ref(g0)) * u0;
-              a[2 * i + 1] = (g1 * sigmoid_ref(g1)) * u1;
+              a[2 * i] = 1.0f + __expf(-bf16x2_lo(gb[i]));
+              a[2 * i + 1] = 1.0f + __expf(-bf16x2_hi(gb[i]));
+              big |= !(a[2 * i] < Q4T_RCP_FAST_MAX) | !(a[2 * i + 1] < Q4T_RCP_FAST_MAX);
+            }
+            const bool slow = __any_sync(0xffffffffu, big);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {  // two halves of eight keep the live set small
+#pragma unroll
+              for (int i = 4 * h; i < 4 * h + 4; ++i) {
+                const float s0 = slow ? __frcp_rn(a[2 * i]) : rcp_rn_ge1(a[2 * i]);
+                const float s1 = slow ? __frcp_rn(a[2 * i + 1]) : rcp_rn_ge1(a[2 * i + 1]);
+                a[2 * i] = (bf16x2_lo(gb[i]) * s0) * bf16x2_lo(ub[i]);
+                a[2 * i + 1] = (bf16x2_hi(gb[i]) * s1) * bf16x2_hi(ub[i]);
+              }
             }
             if constexpr (EPI == Epilogue::kSwigluBf16) {
               if (valid) {
@@ -409,8 +452,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
       }
+      if (stamp) Q4T_STAMP(2, tcount, 3);
     }
     if (!ok && args.status && lane == 0) atomicMax(args.status, 3);
+    (void)stamp;
   }
 
   tc_fence_before();

@@ -17,6 +17,9 @@ def test_hw_encoders_equal_reference_encoders_exhaustively(q4t, gpu_lib):
     assert bad == 0, f"e2m1: {bad} mismatches, first at bits 0x{first:08x}"
     bad, first = q4t.selftest_encoders(1, 0, 1 << 31)
     assert bad == 0, f"ue4m3: {bad} mismatches, first at bits 0x{first:08x}"
+    # the SwiGLU epilogue's branch-free reciprocal equals IEEE 1/x on its whole domain
+    bad, first = q4t.selftest_encoders(2, 0x3F800000, 0x7E800000 - 0x3F800000)
+    assert bad == 0, f"reciprocal: {bad} mismatches, first at bits 0x{first:08x}"
 
 
 def test_act_quant_reference_golden(q4t, gpu_lib, golden):
