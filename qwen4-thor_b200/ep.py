@@ -83,6 +83,8 @@ class ExpertParallelMoE:
         import torch.distributed as dist
         self.ops, self.world, self.rank, self.group, self.dist = ops, world, rank, group, dist
         self.last = {}
+        self.profile = False       # when set, forward() records CUDA events between its phases
+        self.phase_ms = {}
 
     def exchange_counts(self, send_counts):
         """Row counts per destination -> row counts per source (host lists)."""
@@ -102,20 +104,39 @@ class ExpertParallelMoE:
             out.copy_(inp)
         return out
 
+    def _mark(self, marks, name):
+        if self.profile:
+            import torch
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append((name, ev))
+
     def forward(self, x, y):
         ops = self.ops
+        marks = []
+        self._mark(marks, "start")
         ids, rw = ops.router(x)
+        self._mark(marks, "router")
         send_rows, send_local, send_counts, row_of_flat = ops.dispatch(x, ids)
+        self._mark(marks, "dispatch_build")
         s_counts, r_counts = self.exchange_counts(send_counts)      # host sync: split sizes
+        self._mark(marks, "counts_exchange")
         n_send, n_recv = sum(s_counts), sum(r_counts)
         recv_rows = ops.empty_rows(n_recv)
         recv_local = send_local.new_empty((n_recv,))
         self.all_to_all_rows(recv_rows, send_rows[:n_send], r_counts, s_counts)
         self.all_to_all_rows(recv_local, send_local[:n_send], r_counts, s_counts)
+        self._mark(marks, "dispatch_all_to_all")
         out_rows = ops.empty_rows(n_recv)
         ops.expert_rows(recv_rows, recv_local, out_rows, n_recv)
+        self._mark(marks, "expert_rows")
         ret_rows = ops.empty_rows(max(n_send, 1))
         self.all_to_all_rows(ret_rows[:n_send], out_rows, s_counts, r_counts)
+        self._mark(marks, "return_all_to_all")
         ops.finish(x, ret_rows, row_of_flat, rw, y)
+        self._mark(marks, "finish")
+        if self.profile:
+            marks[-1][1].synchronize()
+            self.phase_ms = {b[0]: a[1].elapsed_time(b[1]) for a, b in zip(marks[:-1], marks[1:])}
         self.last = dict(rows_sent=n_send, rows_received=n_recv, send_counts=s_counts, recv_counts=r_counts)
         return y

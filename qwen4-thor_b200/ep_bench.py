@@ -87,6 +87,12 @@ def main_multi(args):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_e = float(t.item())
 
+    # phase breakdown of one more step on this rank (events between phases)
+    drv.profile = True
+    step(0)
+    phases = dict(drv.phase_ms)
+    drv.profile = False
+
     # per-rank load and link traffic of the last step
     rows_recv = torch.tensor([drv.last["rows_received"]], device="cuda", dtype=torch.float64)
     remote_out = sum(c for r, c in enumerate(drv.last["send_counts"]) if r != rank) + \
@@ -133,6 +139,6 @@ def main_multi(args):
                     cpu_baseline=None,
                     load=dict(rows_received_max=float(mx_rows.item()), rows_received_mean=T_TOTAL * K_TOP / world,
                               imbalance=float(mx_rows.item()) / (T_TOTAL * K_TOP / world)),
-                    single_gpu_same_workload=n1)
+                    phase_ms_rank0=phases, single_gpu_same_workload=n1)
         print(json.dumps(line))
     dist.destroy_process_group()
