@@ -317,6 +317,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "rows"],
+                    help="multi-GPU only: peer-memory pull/push (default) or NCCL all-to-all of rows")
     ap.add_argument("--quick", action="store_true", help="headline point only (no sweep, no prefill)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=4, help="independent layer weight sets rotated per step")

@@ -281,6 +281,59 @@ int32_t q4t_moe_finish(const uint16_t* x, const uint16_t* expert_rows,
                        int32_t k, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* ---- expert parallelism over peer memory (no reference counterpart either).
+ * Instead of exchanging rows through a collective, every rank PUBLISHES its
+ * tokens once, quantised (q4t_quantize_activation_fp4 with the layer's single
+ * gate/up input scale), in a buffer its peers can read, and owns a landing
+ * buffer dn_rows [tokens_per_rank*k, hs] its peers can write.  After the
+ * ranks' int32 [tokens_per_rank,k] expert ids have been all-gathered (rank
+ * order), q4t_moe_expert_peer on each rank
+ *   1. keeps the (token,slot) entries of ALL ranks whose expert lives here,
+ *   2. copies their codes and scales from the owners' published buffers
+ *      (plain loads over NVLink),
+ *   3. runs the gate/up and down GEMMs, the down GEMM's epilogue storing each
+ *      bf16 row directly at dn_rows[owner][(token*k + slot), :] (stores over
+ *      NVLink, overlapped with the tiles still being computed).
+ * The caller orders the steps across ranks with stream-ordered collectives:
+ * the id all-gather doubles as "published buffers are ready"; a barrier (any
+ * collective) after q4t_moe_expert_peer means "all rows have landed"; then
+ * q4t_moe_finish with row_of_flat from q4t_ep_flat_rows.  No kernel waits on
+ * another rank.  Results are bit-identical to q4t_moe_forward on one GPU.
+ * Needs weights->gu_input_scale_uniform > 0 (one input scale for all experts;
+ * otherwise use the row-exchange entry points above).
+ *
+ * q4t_peer_buffer_*: device buffers that another process on the same node can
+ * map: alloc/free on the owner, export -> 64-byte handle to send to the peers
+ * (any host channel), open/close on a peer.                                    */
+#define Q4T_EP_MAX_RANKS 8
+#define Q4T_PEER_HANDLE_BYTES 64
+typedef struct q4t_ep_peer_table {
+  int32_t world, rank;
+  int32_t tokens_per_rank;  /* rows every rank publishes (pad the last rank's) */
+  int32_t expert_map;       /* 0: expert e on rank e / (E/world), local e % (E/world);
+                               1: on rank e % world, local e / world           */
+  const uint8_t* xq_packed[Q4T_EP_MAX_RANKS]; /* [tokens_per_rank, hs/2] codes  */
+  const uint8_t* xq_sf[Q4T_EP_MAX_RANKS];     /* swizzled scales of those rows  */
+  uint16_t* dn_rows[Q4T_EP_MAX_RANKS];        /* [tokens_per_rank*k, hs] bf16   */
+} q4t_ep_peer_table;
+int32_t q4t_peer_buffer_alloc(size_t bytes, void** ptr);
+int32_t q4t_peer_buffer_free(void* ptr);
+int32_t q4t_peer_buffer_export(const void* ptr, uint8_t handle[Q4T_PEER_HANDLE_BYTES]);
+int32_t q4t_peer_buffer_open(const uint8_t handle[Q4T_PEER_HANDLE_BYTES], void** ptr);
+int32_t q4t_peer_buffer_close(void* ptr);
+/* ids_all: int32 [world*tokens_per_rank, k] global expert ids (entries outside
+ * [0, E_local*world) are skipped); weights: this rank's experts.              */
+size_t q4t_moe_expert_peer_workspace_bytes(int32_t tokens_all, int32_t k, int32_t hs,
+                                           int32_t moe_is, int32_t E_local);
+int32_t q4t_moe_expert_peer(const int32_t* ids_all, const q4t_ep_peer_table* peers,
+                            const q4t_routed_weights* weights, int32_t k,
+                            void* workspace, size_t workspace_bytes,
+                            uint32_t flags, void* stream);
+/* row_of_flat[f] = f where expert_ids[f] is in [0,E), else -1: the table
+ * q4t_moe_finish needs when the rows arrive in (token,slot) order.            */
+int32_t q4t_ep_flat_rows(const int32_t* expert_ids, int32_t rows, int32_t E,
+                         int32_t* row_of_flat, void* stream);
+
 /* Reads the kernel status words of a workspace after the stream has been
  * synchronised by the caller: 0 = clean, otherwise a bounded device-side wait
  * ran out (the output is then undefined).  Copies with cudaMemcpy.            */

@@ -41,6 +41,13 @@ class RoutedWsLayout(C.Structure):
         "inter_sf_tiles", "status", "max_tiles", "total")]
 
 
+class EpPeerTable(C.Structure):
+    """q4t_ep_peer_table: who publishes what, for the pull/push expert-parallel path."""
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("tokens_per_rank", C.c_int32),
+                ("expert_map", C.c_int32), ("xq_packed", C.c_void_p * 8), ("xq_sf", C.c_void_p * 8),
+                ("dn_rows", C.c_void_p * 8)]
+
+
 class ForwardWsLayout(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in (
         "routed_ws", "logits", "expert_ids", "router_w", "routed", "shared_gu", "shared_act",
@@ -56,7 +63,11 @@ EXPORTS = [
     "q4t_selftest_encoders", "q4t_stage_timing_enable", "q4t_stage_timing_read",
     "q4t_moe_routed_forward_noalloc", "q4t_ep_dispatch_workspace_bytes", "q4t_ep_dispatch",
     "q4t_moe_expert_rows", "q4t_moe_finish_workspace_bytes", "q4t_moe_finish",
+    "q4t_peer_buffer_alloc", "q4t_peer_buffer_free", "q4t_peer_buffer_export", "q4t_peer_buffer_open",
+    "q4t_peer_buffer_close", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
 ]
+EP_MAX_RANKS = 8
+PEER_HANDLE_BYTES = 64
 NOALLOC_SCRATCH_BYTES = 3 << 20
 
 _lib = None
@@ -100,6 +111,15 @@ def load():
     L.q4t_moe_finish_workspace_bytes.restype = C.c_size_t
     L.q4t_moe_finish_workspace_bytes.argtypes = [i32, i32, i32]
     L.q4t_moe_finish.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, sz, vp]
+    L.q4t_peer_buffer_alloc.argtypes = [sz, C.POINTER(C.c_void_p)]
+    L.q4t_peer_buffer_free.argtypes = [vp]
+    L.q4t_peer_buffer_export.argtypes = [vp, C.c_char_p]
+    L.q4t_peer_buffer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    L.q4t_peer_buffer_close.argtypes = [vp]
+    L.q4t_moe_expert_peer_workspace_bytes.restype = C.c_size_t
+    L.q4t_moe_expert_peer_workspace_bytes.argtypes = [i32] * 5
+    L.q4t_moe_expert_peer.argtypes = [vp, C.POINTER(EpPeerTable), C.POINTER(RoutedWeights), i32, vp, sz, u32, vp]
+    L.q4t_ep_flat_rows.argtypes = [vp, i32, i32, vp, vp]
     L.q4t_moe_forward_workspace_layout.argtypes = [i32] * 6 + [C.POINTER(ForwardWsLayout)]
     L.q4t_moe_forward.argtypes = [vp, C.POINTER(RoutedWeights), C.POINTER(ExtraWeights), vp, i32, i32,
                                   vp, sz, vp, u32, vp]

@@ -224,9 +224,16 @@ q4t::PlanTables plan_tables(const RoutedPtrs& P, int E) {
 }
 
 // plan_done: the permutation tables of P were already produced (fused with the router).
+// peer (optional): the token rows come quantised from the ranks' published buffers and
+// the down-projection rows go straight to their owners' landing buffers.
+struct PeerRoute {
+  q4t::PeerSources src;
+  uint16_t* dn_rows[q4t::kMaxPeers];
+  int rows_per_rank;  // tokens_per_rank * k
+};
 int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids,
                     const q4t_routed_weights* w, const RoutedPtrs& P, int M, int k, uint32_t flags,
-                    cudaStream_t st, bool plan_done = false) {
+                    cudaStream_t st, bool plan_done = false, const PeerRoute* peer = nullptr) {
   const int E = w->E, hs = w->hs, is = w->moe_is;
   const int R = M * k;
   const q4t_routed_ws_layout& L = P.L;
@@ -242,7 +249,11 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   uint8_t* a_sf_tiles = P.at<uint8_t>(L.a_sf_tiles);
   // With one input scale for all experts and a large batch, quantise each token
   // once and copy its codes to its k rows; otherwise quantise every grouped row.
-  if (w->gu_input_scale_uniform > 0.0f && k > 1 && R >= 8192) {
+  if (peer) {
+    if ((e = q4t::launch_gather_codes_peer(peer->src, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, pt.row_tile,
+                                           pt.tile_row0, pt.offsets + E, k, st)) != cudaSuccess)
+      return fail_cuda("peer code gather launch", e);
+  } else if (w->gu_input_scale_uniform > 0.0f && k > 1 && R >= 8192) {
     uint8_t* xq = P.at<uint8_t>(L.xq_packed);
     uint8_t* xq_sf = P.at<uint8_t>(L.xq_sf);
     if ((e = q4t::launch_quantize(x, xq, xq_sf, M, hs, w->gu_input_scale_uniform, st)) != cudaSuccess)
@@ -314,6 +325,11 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   d.alpha_w = w->dn_w_scale2;
   d.alpha_a = w->dn_input_scale;
   d.status = P.at<int32_t>(L.status);
+  if (peer) {
+    d.scatter_flat = pt.flat_of_row;
+    d.scatter_rows_per_rank = peer->rows_per_rank;
+    for (int i = 0; i < q4t::kMaxPeers; ++i) d.scatter_base[i] = peer->dn_rows[i];
+  }
   if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, d, q4t::Epilogue::kStoreBf16, ds->num_sms, st)) != cudaSuccess)
     return fail_cuda("down GEMM launch", e);
   stage_end(5, st);
@@ -821,6 +837,98 @@ int32_t q4t_moe_finish(const uint16_t* x, const uint16_t* expert_rows, const int
   cudaError_t e = q4t::launch_final_combine(expert_rows, row_of_flat, router_w, sdown, x, extra->shared_gate_scalar,
                                             reinterpret_cast<float*>(base + F.routed), y, T, k, extra->hs, st);
   return e == cudaSuccess ? Q4T_OK : fail_cuda("combine launch", e);
+}
+
+// ---- pull/push expert parallelism over peer memory
+int32_t q4t_peer_buffer_alloc(size_t bytes, void** ptr) {
+  if (!ptr || bytes == 0) return fail(Q4T_ERR_INVALID, "invalid arguments");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaError_t e = cudaMalloc(ptr, align_up(bytes, 256));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("peer buffer allocation", e);
+}
+int32_t q4t_peer_buffer_free(void* ptr) {
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("peer buffer free", e);
+}
+int32_t q4t_peer_buffer_export(const void* ptr, uint8_t handle[Q4T_PEER_HANDLE_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == Q4T_PEER_HANDLE_BYTES, "handle size");
+  if (!ptr || !handle) return fail(Q4T_ERR_INVALID, "null pointer");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(ptr));
+  if (e != cudaSuccess) return fail_cuda("peer buffer export", e);
+  std::memcpy(handle, &h, sizeof(h));
+  return Q4T_OK;
+}
+int32_t q4t_peer_buffer_open(const uint8_t handle[Q4T_PEER_HANDLE_BYTES], void** ptr) {
+  if (!ptr || !handle) return fail(Q4T_ERR_INVALID, "null pointer");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("peer buffer open", e);
+}
+int32_t q4t_peer_buffer_close(void* ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("peer buffer close", e);
+}
+
+size_t q4t_moe_expert_peer_workspace_bytes(int32_t tokens_all, int32_t k, int32_t hs, int32_t moe_is,
+                                           int32_t E_local) {
+  if (tokens_all <= 0 || k <= 0 || !routed_dims_ok(E_local, hs, moe_is)) return 0;
+  q4t_routed_ws_layout L;
+  routed_layout(tokens_all, k, hs, moe_is, E_local, &L);
+  return align_up(L.total, 256) + align_up(static_cast<size_t>(tokens_all) * k * 4, 256);
+}
+
+int32_t q4t_moe_expert_peer(const int32_t* ids_all, const q4t_ep_peer_table* peers, const q4t_routed_weights* w,
+                            int32_t k, void* workspace, size_t workspace_bytes, uint32_t flags, void* stream) {
+  if (!peers || !w || !ids_all || !workspace) return fail(Q4T_ERR_INVALID, "null pointer");
+  const int world = peers->world, rank = peers->rank, tpr = peers->tokens_per_rank;
+  if (world <= 0 || world > Q4T_EP_MAX_RANKS || rank < 0 || rank >= world || tpr <= 0)
+    return fail(Q4T_ERR_INVALID, "invalid peer table (world in [1,8], rank < world, tokens_per_rank > 0)");
+  if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");
+  if (!routed_dims_ok(w->E, w->hs, w->moe_is))
+    return fail(Q4T_ERR_INVALID, "hs and moe_is must be multiples of 128 and E <= 1024");
+  if (!(w->gu_input_scale_uniform > 0.0f))
+    return fail(Q4T_ERR_INVALID, "the peer path needs one gate/up input scale for all experts");
+  if (static_cast<int64_t>(world) * tpr * k > (1ll << 30)) return fail(Q4T_ERR_INVALID, "too many rows");
+  for (int i = 0; i < world; ++i)
+    if (!peers->xq_packed[i] || !peers->xq_sf[i] || !peers->dn_rows[i])
+      return fail(Q4T_ERR_INVALID, "peer table has a null buffer");
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(Q4T_ERR_INVALID, "workspace must be 256-byte aligned");
+  const int T_all = world * tpr, R = T_all * k;
+  if (workspace_bytes < q4t_moe_expert_peer_workspace_bytes(T_all, k, w->hs, w->moe_is, w->E))
+    return fail(Q4T_ERR_WORKSPACE, "workspace too small");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  RoutedPtrs P;
+  routed_layout(T_all, k, w->hs, w->moe_is, w->E, &P.L);
+  P.base = static_cast<uint8_t*>(workspace);
+  int32_t* local_ids = reinterpret_cast<int32_t*>(P.base + align_up(P.L.total, 256));
+  cudaError_t e = q4t::launch_ep_localise_ids(ids_all, R, w->E * world, world, rank, peers->expert_map == 1, local_ids, st);
+  if (e != cudaSuccess) return fail_cuda("id localise launch", e);
+  PeerRoute route{};
+  route.src.tokens_per_rank = tpr;
+  route.rows_per_rank = tpr * k;
+  for (int i = 0; i < q4t::kMaxPeers; ++i) {
+    const int j = i < world ? i : 0;
+    route.src.xq_packed[i] = peers->xq_packed[j];
+    route.src.xq_sf[i] = peers->xq_sf[j];
+    route.dn_rows[i] = peers->dn_rows[j];
+  }
+  stage_begin(st);
+  stage_end(1, st);
+  return run_routed_core(ds, nullptr, local_ids, w, P, T_all, k, flags, st, false, &route);
+}
+
+int32_t q4t_ep_flat_rows(const int32_t* expert_ids, int32_t rows, int32_t E, int32_t* row_of_flat, void* stream) {
+  if (rows <= 0) return Q4T_OK;
+  if (!expert_ids || !row_of_flat || E <= 0) return fail(Q4T_ERR_INVALID, "invalid arguments");
+  cudaError_t e = q4t::launch_ep_flat_rows(expert_ids, rows, E, row_of_flat, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("flat rows launch", e);
 }
 
 int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k, int32_t hs, int32_t moe_is,

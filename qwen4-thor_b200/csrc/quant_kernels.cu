@@ -107,6 +107,30 @@ __global__ void __launch_bounds__(256) gather_codes_kernel(
   }
 }
 
+// The same copy with the token rows spread over the ranks' buffers (plain loads:
+// the sources may be peer GPUs' memory).
+__global__ void __launch_bounds__(256) gather_codes_peer_kernel(
+    const __grid_constant__ PeerSources src, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_tiles,
+    int rows, int K, const int32_t* __restrict__ flat_of_row, const int32_t* __restrict__ row_tile,
+    const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ rows_dev, int k) {
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= min(rows, *rows_dev)) return;
+  const int token_all = flat_of_row[r] / k;
+  const int owner = token_all / src.tokens_per_rank;
+  const int token = token_all - owner * src.tokens_per_rank;
+  const int t = row_tile[r];
+  const uint32_t in_tile = static_cast<uint32_t>(r - tile_row0[t]);
+  const int row_bytes = K >> 1, ntk = K >> 6;
+  const uint4* from = reinterpret_cast<const uint4*>(src.xq_packed[owner] + static_cast<size_t>(token) * row_bytes);
+  const uint8_t* from_sf = src.xq_sf[owner];
+  uint4* dst = reinterpret_cast<uint4*>(packed + static_cast<size_t>(r) * row_bytes);
+  for (int c = lane; c < (row_bytes >> 4); c += 32) dst[c] = from[c];
+  for (int a = lane; a < ntk; a += 32) {
+    const uint32_t v = *reinterpret_cast<const uint32_t*>(from_sf + sf_offset(static_cast<uint32_t>(token), 4u * a, ntk));
+    *reinterpret_cast<uint32_t*>(sf_tiles + (static_cast<size_t>(t) * ntk + a) * 512u + sf_in_atom(in_tile, 0)) = v;
+  }
+}
+
 __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ packed,
                                                       const uint8_t* __restrict__ group_scale,
                                                       uint16_t* __restrict__ out, float inv_global,
@@ -197,6 +221,16 @@ cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, 
   if (R == 0) return cudaSuccess;
   gather_codes_kernel<<<(R + 7) / 8, 256, 0, stream>>>(xq_packed, xq_sf, packed, sf_tiles, R, K, flat_of_row, row_tile,
                                                        tile_row0, rows_dev, k);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_codes_peer(const PeerSources& src, uint8_t* packed, uint8_t* sf_tiles, int R, int K,
+                                     const int32_t* flat_of_row, const int32_t* row_tile,
+                                     const int32_t* tile_row0, const int32_t* rows_dev, int k,
+                                     cudaStream_t stream) {
+  if (R == 0) return cudaSuccess;
+  gather_codes_peer_kernel<<<(R + 7) / 8, 256, 0, stream>>>(src, packed, sf_tiles, R, K, flat_of_row, row_tile,
+                                                            tile_row0, rows_dev, k);
   return cudaGetLastError();
 }
 

@@ -368,6 +368,29 @@ __global__ void __launch_bounds__(256) ep_split_ids_kernel(const int32_t* __rest
   local[f] = ok ? e % experts_per_rank : -1;
 }
 
+__global__ void __launch_bounds__(256) ep_localise_ids_kernel(const int32_t* __restrict__ ids, int R, int E,
+                                                              int world, int rank, int interleaved,
+                                                              int32_t* __restrict__ local) {
+  const int f = blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= R) return;
+  const int e = ids[f];
+  int out = -1;
+  if (e >= 0 && e < E) {
+    const int per = E / world;
+    const int owner = interleaved ? e % world : e / per;
+    if (owner == rank) out = interleaved ? e / world : e - owner * per;
+  }
+  local[f] = out;
+}
+
+__global__ void __launch_bounds__(256) ep_flat_rows_kernel(const int32_t* __restrict__ ids, int R, int E,
+                                                           int32_t* __restrict__ row_of_flat) {
+  const int f = blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= R) return;
+  const int e = ids[f];
+  row_of_flat[f] = (e >= 0 && e < E) ? f : -1;
+}
+
 // out[r, :] = src[index[r] / div, :] for r < *rows_dev (rows of `width` bf16
 // values, 16-byte vector copies); optionally aux_out[r] = aux[index[r]].
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint16_t* __restrict__ src,
@@ -551,6 +574,17 @@ cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_pe
                                 int32_t* local, cudaStream_t stream) {
   if (R == 0) return cudaSuccess;
   ep_split_ids_kernel<<<(R + 255) / 256, 256, 0, stream>>>(ids, R, E, experts_per_rank, dest, local);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_localise_ids(const int32_t* ids, int R, int E, int world, int rank, bool interleaved,
+                                   int32_t* local, cudaStream_t stream) {
+  ep_localise_ids_kernel<<<(R + 255) / 256, 256, 0, stream>>>(ids, R, E, world, rank, interleaved ? 1 : 0, local);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_flat_rows(const int32_t* ids, int R, int E, int32_t* row_of_flat, cudaStream_t stream) {
+  ep_flat_rows_kernel<<<(R + 255) / 256, 256, 0, stream>>>(ids, R, E, row_of_flat);
   return cudaGetLastError();
 }
 

@@ -75,7 +75,7 @@ struct Barriers {
 template <bool NVF4, Epilogue EPI, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const GemmArgs args) {
+            const __grid_constant__ GemmArgs args) {
   static_assert(!NVF4 || BN == 256, "block-scaled tiles are 256 columns wide");
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
@@ -380,10 +380,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
                              : "r"(stg + rr * 64u + ((chunk ^ rsw) << 4)) : "memory");
                 const int col = n0 + cbase + static_cast<int>(chunk) * 8;
-                if (quad * 32 + rr < nrows && static_cast<int>(chunk) * 8 < ncols && col < args.b_rows_valid)
-                  *reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) +
-                                            static_cast<size_t>(row0 + quad * 32 + rr) * args.ldo + col) =
-                      make_uint4(v0, v1, v2, v3);
+                if (quad * 32 + rr < nrows && static_cast<int>(chunk) * 8 < ncols && col < args.b_rows_valid) {
+                  // the row's place: in the tile's own rows, or (scatter) in its owner's buffer
+                  uint16_t* rowp;
+                  if (args.scatter_flat) {
+                    const int f = args.scatter_flat[row0 + quad * 32 + rr];
+                    const int owner = f / args.scatter_rows_per_rank;
+                    rowp = args.scatter_base[owner] +
+                           static_cast<size_t>(f - owner * args.scatter_rows_per_rank) * args.ldo;
+                  } else {
+                    rowp = static_cast<uint16_t*>(args.out) + static_cast<size_t>(row0 + quad * 32 + rr) * args.ldo;
+                  }
+                  *reinterpret_cast<uint4*>(rowp + col) = make_uint4(v0, v1, v2, v3);
+                }
               }
               __syncwarp();
             }

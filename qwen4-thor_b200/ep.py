@@ -140,3 +140,158 @@ class ExpertParallelMoE:
             self.phase_ms = {b[0]: a[1].elapsed_time(b[1]) for a, b in zip(marks[:-1], marks[1:])}
         self.last = dict(rows_sent=n_send, rows_received=n_recv, send_counts=s_counts, recv_counts=r_counts)
         return y
+
+
+# ------------------------------------------------------------------ peer-memory path
+class PeerBuffers:
+    """One rank's published buffers (quantised tokens, landing rows) and its view of the
+    peers' buffers.  Real ranks: allocated by the library and mapped across processes
+    through exported handles (`connect`).  A single-process test can instead fill the
+    table with plain device pointers (`from_pointers`)."""
+
+    def __init__(self, q4t, world, rank, T_local, k, hs, expert_map=1):
+        self.q4t, self.lib = q4t, q4t.load()
+        self.world, self.rank, self.T, self.k, self.hs = world, rank, T_local, k, hs
+        self.table = q4t.EpPeerTable()
+        self.table.world, self.table.rank = world, rank
+        self.table.tokens_per_rank, self.table.expert_map = T_local, expert_map
+        self.sizes = (T_local * (hs // 2), self.lib.q4t_sf_buffer_size(T_local, hs), T_local * k * hs * 2)
+        self.own = None
+        self.opened = []
+
+    def allocate(self):
+        import ctypes as C
+        own = []
+        for nbytes in self.sizes:
+            p = C.c_void_p()
+            self.q4t.check(self.lib.q4t_peer_buffer_alloc(nbytes, C.byref(p)))
+            own.append(p.value)
+        self.own = own
+        return self
+
+    def handles(self):
+        import ctypes as C
+        out = []
+        for p in self.own:
+            h = C.create_string_buffer(self.q4t.PEER_HANDLE_BYTES)
+            self.q4t.check(self.lib.q4t_peer_buffer_export(p, h))
+            out.append(h.raw)
+        return out
+
+    def connect(self, all_handles):
+        """all_handles[r] = rank r's three handles (e.g. from all_gather_object)."""
+        import ctypes as C
+        for r in range(self.world):
+            ptrs = []
+            for i in range(3):
+                if r == self.rank:
+                    ptrs.append(self.own[i])
+                else:
+                    p = C.c_void_p()
+                    self.q4t.check(self.lib.q4t_peer_buffer_open(all_handles[r][i], C.byref(p)))
+                    self.opened.append(p.value)
+                    ptrs.append(p.value)
+            self.table.xq_packed[r], self.table.xq_sf[r], self.table.dn_rows[r] = ptrs
+        return self
+
+    def from_pointers(self, ptrs_by_rank):
+        for r, ptrs in enumerate(ptrs_by_rank):
+            self.table.xq_packed[r], self.table.xq_sf[r], self.table.dn_rows[r] = ptrs
+        self.own = list(ptrs_by_rank[self.rank])
+        return self
+
+    def close(self):
+        for p in self.opened:
+            self.lib.q4t_peer_buffer_close(p)
+        self.opened = []
+
+
+class PeerExpertParallelMoE:
+    """Expert-parallel step without row collectives: each rank publishes its quantised
+    tokens, the owner of an expert pulls the rows it needs from the publishers' memory and
+    its down GEMM stores the result rows straight into the token owners' landing buffers.
+    Only the expert ids travel through a collective (all-gather), which also orders
+    "published" before "pulled"; one more tiny collective orders "pushed" before "combined".
+
+    layer_local holds this rank's experts (expert_map 1: experts rank, rank+world, ...;
+    0: a contiguous block) plus the replicated router and shared expert."""
+
+    def __init__(self, q4t, layer_local, E_total, hs, k, world, rank, T_local, buffers: PeerBuffers,
+                 group=None, device="cuda"):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        self.q4t, self.C, self.torch, self.dist = q4t, C, torch, dist
+        self.lib = q4t.load()
+        self.L, self.E, self.hs, self.k = layer_local, E_total, hs, k
+        self.world, self.rank, self.T, self.group, self.buf = world, rank, T_local, group, buffers
+        if not layer_local.routed.gu_input_scale_uniform > 0:
+            raise q4t.Q4TError("the peer path needs one gate/up input scale for all experts")
+        dev = device
+        self.logits = torch.empty((T_local, E_total), dtype=torch.bfloat16, device=dev)
+        self.ids = torch.empty((T_local, k), dtype=torch.int32, device=dev)
+        self.rw = torch.empty((T_local, k), dtype=torch.float32, device=dev)
+        self.ids_all = torch.empty((world * T_local, k), dtype=torch.int32, device=dev)
+        self.row_of_flat = torch.empty((T_local * k,), dtype=torch.int32, device=dev)
+        self.sync_word = torch.zeros((1,), dtype=torch.int32, device=dev)
+        self.ws_bytes = self.lib.q4t_moe_expert_peer_workspace_bytes(world * T_local, k, hs, layer_local.moe_is,
+                                                                     layer_local.E)
+        self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=dev)
+        self.finish_ws_bytes = self.lib.q4t_moe_finish_workspace_bytes(T_local, hs, layer_local.shared_is)
+        self.finish_ws = torch.empty(self.finish_ws_bytes, dtype=torch.uint8, device=dev)
+        self.profile = False
+        self.phase_ms = {}
+
+    def _s(self):
+        return self.C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    def _mark(self, marks, name):
+        if self.profile:
+            ev = self.torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append((name, ev))
+
+    # the three device phases, separately callable so that a single-process test can
+    # interleave several ranks (all publish, then all compute, then all finish)
+    def publish(self, x):
+        q, lib = self.q4t, self.lib
+        q.check(lib.q4t_bf16_linear(x.data_ptr(), self.L.extra.gate, self.logits.data_ptr(), self.T, self.E, self.hs, self._s()))
+        q.check(lib.q4t_router_topk(self.logits.data_ptr(), self.ids.data_ptr(), self.rw.data_ptr(), self.T, self.E, self.k, self._s()))
+        q.check(lib.q4t_quantize_activation_fp4(x.data_ptr(), self.buf.own[0], self.buf.own[1], self.T, self.hs,
+                                                float(self.L.routed.gu_input_scale_uniform), self._s()))
+        return self.ids
+
+    def experts(self, ids_all):
+        self.q4t.check(self.lib.q4t_moe_expert_peer(ids_all.data_ptr(), self.C.byref(self.buf.table),
+                                                    self.C.byref(self.L.routed), self.k, self.ws.data_ptr(),
+                                                    self.ws_bytes, 0, self._s()))
+
+    def finish(self, x, y):
+        q, lib = self.q4t, self.lib
+        q.check(lib.q4t_ep_flat_rows(self.ids.data_ptr(), self.T * self.k, self.E, self.row_of_flat.data_ptr(), self._s()))
+        q.check(lib.q4t_moe_finish(x.data_ptr(), self.buf.own[2], self.row_of_flat.data_ptr(), self.rw.data_ptr(),
+                                   self.C.byref(self.L.extra), y.data_ptr(), self.T, self.k,
+                                   self.finish_ws.data_ptr(), self.finish_ws_bytes, self._s()))
+        return y
+
+    def forward(self, x, y):
+        marks = []
+        self._mark(marks, "start")
+        self.publish(x)
+        self._mark(marks, "publish")
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.ids_all, self.ids, group=self.group)
+        else:
+            self.ids_all.copy_(self.ids)
+        self._mark(marks, "ids_all_gather")
+        self.experts(self.ids_all)
+        self._mark(marks, "experts_pull_push")
+        if self.world > 1:      # every rank's rows have landed once this returns on the stream
+            self.dist.all_reduce(self.sync_word, group=self.group)
+        self._mark(marks, "landed_barrier")
+        self.finish(x, y)
+        self._mark(marks, "finish")
+        if self.profile:
+            marks[-1][1].synchronize()
+            self.phase_ms = {b[0]: a[1].elapsed_time(b[1]) for a, b in zip(marks[:-1], marks[1:])}
+        return y

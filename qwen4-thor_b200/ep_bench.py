@@ -31,6 +31,20 @@ def _local_layer(q4t, full, lo, hi):
     return q4t.DeviceLayer(hi - lo, hs, is_, full.shared_is, t)
 
 
+def _local_layer_interleaved(q4t, full, rank, world):
+    """Experts rank, rank+world, rank+2*world, ... of a full device layer (copied)."""
+    is_, hs, E = full.moe_is, full.hs, full.E
+    t = dict(full.t)
+    pick = slice(rank, E, world)
+    t["gu_packed"] = full.t["gu_packed"].view(E, -1)[pick].contiguous().view(-1, hs // 2)
+    t["gu_sf"] = full.t["gu_sf"].view(E, -1)[pick].contiguous().view(-1)
+    t["dn_packed"] = full.t["dn_packed"].view(E, -1)[pick].contiguous().view(-1, is_ // 2)
+    t["dn_sf"] = full.t["dn_sf"].view(E, -1)[pick].contiguous().view(-1)
+    for n in ("gu_w_scale2", "gu_input_scale", "dn_w_scale2", "dn_input_scale"):
+        t[n] = full.t[n][pick].contiguous()
+    return q4t.DeviceLayer(E // world, hs, is_, full.shared_is, t)
+
+
 def main_multi(args):
     import torch
     import torch.distributed as dist
@@ -53,12 +67,36 @@ def main_multi(args):
 
     T_loc = T_TOTAL // world
     per = E // world
+    peer_mode = args.exchange == "peer"
     full = syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=20260921 + 4000, zipf_s=1.1)
-    local = _local_layer(q4t, full, rank * per, (rank + 1) * per)
     xs = [syn.make_x(T_loc, HS, seed=400 + 10 * i + rank, bias_column=True) for i in range(2)]
     y = torch.empty((T_loc, HS), dtype=torch.bfloat16, device="cuda")
+    # row-exchange path (NCCL all-to-all both ways), contiguous expert blocks
+    local = _local_layer(q4t, full, rank * per, (rank + 1) * per)
     ops = ep.LibraryOps(q4t, local, E, HS, K_TOP, world, T_loc, cap_rows=T_TOTAL * K_TOP)
-    drv = ep.ExpertParallelMoE(ops, world, rank)
+    drv_rows = ep.ExpertParallelMoE(ops, world, rank)
+    drv = drv_rows
+    if peer_mode:
+        # pull/push over peer memory, experts interleaved over the ranks (balances a skewed router)
+        local_i = _local_layer_interleaved(q4t, full, rank, world)
+        buf = ep.PeerBuffers(q4t, world, rank, T_loc, K_TOP, HS, expert_map=1).allocate()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, buf.handles())
+        buf.connect(gathered)
+        drv = ep.PeerExpertParallelMoE(q4t, local_i, E, HS, K_TOP, world, rank, T_loc, buf)
+        # both paths must give the same bits
+        y2 = torch.empty_like(y)
+        drv.forward(xs[0], y)
+        drv_rows.forward(xs[0], y2)
+        torch.cuda.synchronize()
+        same = torch.tensor([int(torch.equal(y.view(torch.int16), y2.view(torch.int16)))], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        if int(same.item()) != 1:
+            raise RuntimeError("peer path and row-exchange path disagree")
+        del y2
+        if args.quick:
+            del drv_rows, ops
+            torch.cuda.empty_cache()
 
     def step(i):
         drv.forward(xs[i % 2], y)
@@ -94,10 +132,20 @@ def main_multi(args):
     drv.profile = False
 
     # per-rank load and link traffic of the last step
-    rows_recv = torch.tensor([drv.last["rows_received"]], device="cuda", dtype=torch.float64)
-    remote_out = sum(c for r, c in enumerate(drv.last["send_counts"]) if r != rank) + \
-        sum(c for r, c in enumerate(drv.last["recv_counts"]) if r != rank)
-    out_bytes = torch.tensor([remote_out * HS * 2.0], device="cuda", dtype=torch.float64)
+    if peer_mode:
+        owner = drv.ids_all.remainder(world)
+        mine = owner == rank
+        rows_here = int(mine.sum().item())
+        src_rank = torch.arange(world * T_loc, device="cuda").div(T_loc, rounding_mode="floor")[:, None].expand_as(owner)
+        remote_rows = int((mine & (src_rank != rank)).sum().item())
+        rows_recv = torch.tensor([float(rows_here)], device="cuda", dtype=torch.float64)
+        # leaving this GPU: result rows pushed to other ranks; entering: codes + scales pulled
+        out_bytes = torch.tensor([remote_rows * HS * 2.0], device="cuda", dtype=torch.float64)
+    else:
+        rows_recv = torch.tensor([drv.last["rows_received"]], device="cuda", dtype=torch.float64)
+        remote_out = sum(c for r, c in enumerate(drv.last["send_counts"]) if r != rank) + \
+            sum(c for r, c in enumerate(drv.last["recv_counts"]) if r != rank)
+        out_bytes = torch.tensor([remote_out * HS * 2.0], device="cuda", dtype=torch.float64)
     mx_rows, mx_bytes = rows_recv.clone(), out_bytes.clone()
     dist.all_reduce(mx_rows, op=dist.ReduceOp.MAX)
     dist.all_reduce(mx_bytes, op=dist.ReduceOp.MAX)
@@ -124,14 +172,18 @@ def main_multi(args):
                     vs_baseline=None, dtype="nvfp4 (e2m1 x ue4m3, fp32 accumulate); bf16 router and shared expert",
                     data="synthetic",
                     config=dict(workload=f"expert-parallel prefill MoE layer, T={T_TOTAL} total, {per} experts per GPU",
+                                expert_map="interleaved (e % N)" if peer_mode else "contiguous blocks",
                                 hidden=HS, experts=E, top_k=K_TOP, moe_intermediate=MOE_IS, shared_intermediate=SHARED_IS,
                                 routing="zipf(s=1.1) bias on router column 0", parallelism=f"ep{world}",
                                 l2="2 inputs alternated; one step moves > 1 GB per GPU",
-                                exchange="bf16 rows both ways, NCCL all_to_all_single, one host sync per step for the split sizes"),
+                                exchange=("quantised rows pulled from and bf16 result rows pushed to peer memory by the "
+                                          "gather and down-GEMM kernels; NCCL only for the id all-gather and one barrier; "
+                                          "checked bit-identical to the row-exchange path") if peer_mode else
+                                "bf16 rows both ways, NCCL all_to_all_single, one host sync per step for the split sizes"),
                     clocks=clocks.summary(),
                     e2e=dict(value=T_TOTAL / (ms_e * 1e-3), unit="tokens/s", h2d_bytes_per_step=T_TOTAL * HS * 2,
                              d2h_bytes_per_step=T_TOTAL * HS * 2),
-                    gpu_launches=(2 + 5 + 8 + 4) * args.steps * world,
+                    gpu_launches=(14 if peer_mode else 19) * args.steps * world,
                     roofline=dict(bound="nvlink", achieved=float(mx_bytes.item()) / (ms * 1e-3) / 1e9, peak=770.0,
                                   unit="GB/s", frac=target / (ms * 1e-3), traffic=None,
                                   note="frac = max(link time at 770 GB/s per direction, routed flops at 4x measured bf16) / step time; "

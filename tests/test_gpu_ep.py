@@ -79,6 +79,67 @@ def test_ep_two_emulated_ranks_equal_forward(q4t, gpu_lib):
     assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
 
 
+@pytest.mark.parametrize("W,expert_map", [(2, 0), (2, 1), (4, 1)])
+def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
+    """The pull/push path with W ranks living in one process on one GPU: the "peer"
+    pointers are ordinary device pointers and the ranks' phases are run one after the
+    other (all publish, all compute, all finish), so no kernel waits on another."""
+    ep = importlib.import_module("qwen4-thor_b200.ep")
+    epb = importlib.import_module("qwen4-thor_b200.ep_bench")
+    E, hs, is_, sis, k, T = 16, 512, 128, 128, 3, 400
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=63)
+    full = q4t.DeviceLayer.from_host(L)
+    assert full.routed.gu_input_scale_uniform > 0
+    x = dev(synth.make_x(T, hs, seed=11)).view(torch.bfloat16)
+    y_ref = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    fwd = q4t.MoEForward(full, T, k)
+    fwd(x, y_ref)
+    fwd.status()
+    Tl, per = T // W, E // W
+    sf_bytes = q4t.load().q4t_sf_buffer_size(Tl, hs)
+    pub = [(torch.empty((Tl, hs // 2), dtype=torch.uint8, device="cuda"),
+            torch.zeros(sf_bytes, dtype=torch.uint8, device="cuda"),
+            torch.full((Tl * k, hs), -1, dtype=torch.int16, device="cuda")) for _ in range(W)]
+    ptrs = [tuple(t.data_ptr() for t in p) for p in pub]
+    drv = []
+    for r in range(W):
+        local = (epb._local_layer_interleaved(q4t, full, r, W) if expert_map == 1
+                 else _slice_layer(q4t, full, r * per, (r + 1) * per))
+        buf = ep.PeerBuffers(q4t, W, r, Tl, k, hs, expert_map=expert_map).from_pointers(ptrs)
+        drv.append(ep.PeerExpertParallelMoE(q4t, local, E, hs, k, W, r, Tl, buf))
+    xs = [x[r * Tl:(r + 1) * Tl].contiguous() for r in range(W)]
+    ids_all = torch.cat([d.publish(xr) for d, xr in zip(drv, xs)])
+    for d in drv:
+        d.experts(ids_all)
+    ys = [d.finish(xr, torch.empty((Tl, hs), dtype=torch.bfloat16, device="cuda")) for d, xr in zip(drv, xs)]
+    torch.cuda.synchronize()
+    for d in drv:
+        q4t.check(q4t.load().q4t_moe_workspace_status(d.ws.data_ptr(), W * Tl, k, hs, is_, per))
+    assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
+    # a second step over the same buffers (stale rows from step one must not leak)
+    x2 = dev(synth.make_x(T, hs, seed=12)).view(torch.bfloat16)
+    fwd(x2, y_ref)
+    xs = [x2[r * Tl:(r + 1) * Tl].contiguous() for r in range(W)]
+    ids_all = torch.cat([d.publish(xr) for d, xr in zip(drv, xs)])
+    for d in drv:
+        d.experts(ids_all)
+    ys = [d.finish(xr, torch.empty((Tl, hs), dtype=torch.bfloat16, device="cuda")) for d, xr in zip(drv, xs)]
+    torch.cuda.synchronize()
+    assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
+
+
+def test_peer_path_rejects_per_expert_input_scales(q4t, gpu_lib):
+    L = synth.make_layer(E=8, hs=256, moe_is=128, shared_is=128, seed=64, per_expert_input_scale=True)
+    dl = q4t.DeviceLayer.from_host(L)
+    table = q4t.EpPeerTable()
+    table.world, table.rank, table.tokens_per_rank = 1, 0, 8
+    ids = torch.zeros((8, 2), dtype=torch.int32, device="cuda")
+    ws = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
+    rc = q4t.load().q4t_moe_expert_peer(ids.data_ptr(), q4t.C.byref(table), q4t.C.byref(dl.routed), 2,
+                                        ws.data_ptr(), ws.numel(), 0, None)
+    assert rc != 0 and b"one gate/up input scale" in q4t.load().q4t_last_error()
+
+
 def test_ep_two_gpus_nccl(q4t, gpu_lib):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
