@@ -319,6 +319,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "rows"],
                     help="multi-GPU only: peer-memory pull/push (default) or NCCL all-to-all of rows")
+    ap.add_argument("--hot-experts", type=int, default=32,
+                    help="multi-GPU peer exchange: experts replicated on every GPU (0 = none, interleaved sharding)")
     ap.add_argument("--quick", action="store_true", help="headline point only (no sweep, no prefill)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=4, help="independent layer weight sets rotated per step")

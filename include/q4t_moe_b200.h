@@ -281,25 +281,40 @@ int32_t q4t_moe_finish(const uint16_t* x, const uint16_t* expert_rows,
                        int32_t k, void* workspace, size_t workspace_bytes,
                        void* stream);
 
+/* The two halves of q4t_moe_finish, for callers that run the shared expert
+ * beside the exchange (another stream): q4t_moe_shared_expert leaves the
+ * shared expert's down projection in the workspace, q4t_moe_combine reads it
+ * from there.  Same workspace for both (q4t_moe_finish_workspace_bytes).      */
+int32_t q4t_moe_shared_expert(const uint16_t* x, const q4t_extra_weights* extra,
+                              int32_t T, void* workspace, size_t workspace_bytes,
+                              void* stream);
+int32_t q4t_moe_combine(const uint16_t* x, const uint16_t* expert_rows,
+                        const int32_t* row_of_flat, const float* router_w,
+                        const q4t_extra_weights* extra, uint16_t* y, int32_t T,
+                        int32_t k, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
 /* ---- expert parallelism over peer memory (no reference counterpart either).
- * Instead of exchanging rows through a collective, every rank PUBLISHES its
- * tokens once, quantised (q4t_quantize_activation_fp4 with the layer's single
- * gate/up input scale), in a buffer its peers can read, and owns a landing
- * buffer dn_rows [tokens_per_rank*k, hs] its peers can write.  After the
- * ranks' int32 [tokens_per_rank,k] expert ids have been all-gathered (rank
- * order), q4t_moe_expert_peer on each rank
- *   1. keeps the (token,slot) entries of ALL ranks whose expert lives here,
- *   2. copies their codes and scales from the owners' published buffers
- *      (plain loads over NVLink),
- *   3. runs the gate/up and down GEMMs, the down GEMM's epilogue storing each
+ * Instead of exchanging rows through collectives, the kernels themselves write
+ * into the other GPUs' memory.  Every rank owns two buffers its peers can
+ * write: a GATHERED token buffer (codes [world*tokens_per_rank, hs/2] and
+ * world swizzled scale blocks of q4t_sf_buffer_size(tokens_per_rank, hs)
+ * bytes) and a LANDING buffer dn_rows [tokens_per_rank*k, hs].  One step:
+ *   1. q4t_ep_publish: quantises this rank's tokens once (the layer's single
+ *      gate/up input scale) and stores codes and scales into its block of
+ *      EVERY rank's gathered buffer (stores over NVLink from the quantiser).
+ *   2. the ranks' int32 [tokens_per_rank,k] expert ids are all-gathered in
+ *      rank order (any collective; it also orders step 1 before step 3).
+ *   3. q4t_moe_expert_peer: keeps the (token,slot) entries of ALL ranks whose
+ *      expert lives here, groups their codes from the local gathered buffer,
+ *      runs the gate/up and down GEMMs; the down GEMM's epilogue stores each
  *      bf16 row directly at dn_rows[owner][(token*k + slot), :] (stores over
  *      NVLink, overlapped with the tiles still being computed).
- * The caller orders the steps across ranks with stream-ordered collectives:
- * the id all-gather doubles as "published buffers are ready"; a barrier (any
- * collective) after q4t_moe_expert_peer means "all rows have landed"; then
- * q4t_moe_finish with row_of_flat from q4t_ep_flat_rows.  No kernel waits on
- * another rank.  Results are bit-identical to q4t_moe_forward on one GPU.
- * Needs weights->gu_input_scale_uniform > 0 (one input scale for all experts;
+ *   4. a barrier (any collective) = "all rows have landed"; then
+ *      q4t_moe_finish on the landing buffer, row_of_flat from q4t_ep_flat_rows.
+ * The caller issues the collectives stream-ordered; no kernel waits on another
+ * rank.  Results are bit-identical to q4t_moe_forward on one GPU.  Needs
+ * weights->gu_input_scale_uniform > 0 (one input scale for all experts;
  * otherwise use the row-exchange entry points above).
  *
  * q4t_peer_buffer_*: device buffers that another process on the same node can
@@ -311,16 +326,30 @@ typedef struct q4t_ep_peer_table {
   int32_t world, rank;
   int32_t tokens_per_rank;  /* rows every rank publishes (pad the last rank's) */
   int32_t expert_map;       /* 0: expert e on rank e / (E/world), local e % (E/world);
-                               1: on rank e % world, local e / world           */
-  const uint8_t* xq_packed[Q4T_EP_MAX_RANKS]; /* [tokens_per_rank, hs/2] codes  */
-  const uint8_t* xq_sf[Q4T_EP_MAX_RANKS];     /* swizzled scales of those rows  */
-  uint16_t* dn_rows[Q4T_EP_MAX_RANKS];        /* [tokens_per_rank*k, hs] bf16   */
+                               1: on rank e % world, local e / world;
+                               2: by `placement` (below)                       */
+  const uint8_t* xq_packed[Q4T_EP_MAX_RANKS]; /* rank r's gathered code buffer  */
+  const uint8_t* xq_sf[Q4T_EP_MAX_RANKS];     /* rank r's gathered scale blocks */
+  uint16_t* dn_rows[Q4T_EP_MAX_RANKS];        /* rank r's landing buffer        */
+  /* expert_map 2: THIS rank's device table int32 [experts_total]: -1 = the
+   * expert is served elsewhere; v >= 0 = served here as local expert v for
+   * tokens of every rank; v | Q4T_EP_REPLICATED = the expert is replicated on
+   * all ranks and served here, as local expert v, for this rank's own tokens
+   * only.  The ranks' tables must agree (every expert either has exactly one
+   * rank with v >= 0 or is replicated everywhere).                            */
+  const int32_t* placement;
+  int32_t experts_total;
+  int32_t reserved;
 } q4t_ep_peer_table;
+#define Q4T_EP_REPLICATED (1 << 30)
 int32_t q4t_peer_buffer_alloc(size_t bytes, void** ptr);
 int32_t q4t_peer_buffer_free(void* ptr);
 int32_t q4t_peer_buffer_export(const void* ptr, uint8_t handle[Q4T_PEER_HANDLE_BYTES]);
 int32_t q4t_peer_buffer_open(const uint8_t handle[Q4T_PEER_HANDLE_BYTES], void** ptr);
 int32_t q4t_peer_buffer_close(void* ptr);
+/* x: bf16 [tokens_per_rank, hs]; hs a multiple of 64.                         */
+int32_t q4t_ep_publish(const uint16_t* x, const q4t_ep_peer_table* peers, int32_t hs,
+                       float input_scale, void* stream);
 /* ids_all: int32 [world*tokens_per_rank, k] global expert ids (entries outside
  * [0, E_local*world) are skipped); weights: this rank's experts.              */
 size_t q4t_moe_expert_peer_workspace_bytes(int32_t tokens_all, int32_t k, int32_t hs,

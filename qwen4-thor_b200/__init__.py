@@ -45,7 +45,8 @@ class EpPeerTable(C.Structure):
     """q4t_ep_peer_table: who publishes what, for the pull/push expert-parallel path."""
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("tokens_per_rank", C.c_int32),
                 ("expert_map", C.c_int32), ("xq_packed", C.c_void_p * 8), ("xq_sf", C.c_void_p * 8),
-                ("dn_rows", C.c_void_p * 8)]
+                ("dn_rows", C.c_void_p * 8), ("placement", C.c_void_p), ("experts_total", C.c_int32),
+                ("reserved", C.c_int32)]
 
 
 class ForwardWsLayout(C.Structure):
@@ -63,11 +64,13 @@ EXPORTS = [
     "q4t_selftest_encoders", "q4t_stage_timing_enable", "q4t_stage_timing_read",
     "q4t_moe_routed_forward_noalloc", "q4t_ep_dispatch_workspace_bytes", "q4t_ep_dispatch",
     "q4t_moe_expert_rows", "q4t_moe_finish_workspace_bytes", "q4t_moe_finish",
+    "q4t_moe_shared_expert", "q4t_moe_combine",
     "q4t_peer_buffer_alloc", "q4t_peer_buffer_free", "q4t_peer_buffer_export", "q4t_peer_buffer_open",
-    "q4t_peer_buffer_close", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
+    "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
 ]
 EP_MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
+EP_REPLICATED = 1 << 30
 NOALLOC_SCRATCH_BYTES = 3 << 20
 
 _lib = None
@@ -116,6 +119,9 @@ def load():
     L.q4t_peer_buffer_export.argtypes = [vp, C.c_char_p]
     L.q4t_peer_buffer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
     L.q4t_peer_buffer_close.argtypes = [vp]
+    L.q4t_moe_shared_expert.argtypes = [vp, C.POINTER(ExtraWeights), i32, vp, sz, vp]
+    L.q4t_moe_combine.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, sz, vp]
+    L.q4t_ep_publish.argtypes = [vp, C.POINTER(EpPeerTable), i32, f32, vp]
     L.q4t_moe_expert_peer_workspace_bytes.restype = C.c_size_t
     L.q4t_moe_expert_peer_workspace_bytes.argtypes = [i32] * 5
     L.q4t_moe_expert_peer.argtypes = [vp, C.POINTER(EpPeerTable), C.POINTER(RoutedWeights), i32, vp, sz, u32, vp]

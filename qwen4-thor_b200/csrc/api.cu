@@ -224,10 +224,12 @@ q4t::PlanTables plan_tables(const RoutedPtrs& P, int E) {
 }
 
 // plan_done: the permutation tables of P were already produced (fused with the router).
-// peer (optional): the token rows come quantised from the ranks' published buffers and
+// peer (optional): the token rows come quantised from the gathered per-rank blocks and
 // the down-projection rows go straight to their owners' landing buffers.
 struct PeerRoute {
-  q4t::PeerSources src;
+  const uint8_t* xq_packed;  // [world*tokens_per_rank, hs/2]
+  const uint8_t* xq_sf;      // world swizzled blocks
+  int tokens_per_rank;
   uint16_t* dn_rows[q4t::kMaxPeers];
   int rows_per_rank;  // tokens_per_rank * k
 };
@@ -250,9 +252,10 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   // With one input scale for all experts and a large batch, quantise each token
   // once and copy its codes to its k rows; otherwise quantise every grouped row.
   if (peer) {
-    if ((e = q4t::launch_gather_codes_peer(peer->src, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, pt.row_tile,
-                                           pt.tile_row0, pt.offsets + E, k, st)) != cudaSuccess)
-      return fail_cuda("peer code gather launch", e);
+    if ((e = q4t::launch_gather_codes_blocks(peer->xq_packed, peer->xq_sf, peer->tokens_per_rank, a_packed,
+                                             a_sf_tiles, R, hs, pt.flat_of_row, pt.row_tile, pt.tile_row0,
+                                             pt.offsets + E, k, st)) != cudaSuccess)
+      return fail_cuda("block code gather launch", e);
   } else if (w->gu_input_scale_uniform > 0.0f && k > 1 && R >= 8192) {
     uint8_t* xq = P.at<uint8_t>(L.xq_packed);
     uint8_t* xq_sf = P.at<uint8_t>(L.xq_sf);
@@ -330,7 +333,8 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
     d.scatter_rows_per_rank = peer->rows_per_rank;
     for (int i = 0; i < q4t::kMaxPeers; ++i) d.scatter_base[i] = peer->dn_rows[i];
   }
-  if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, d, q4t::Epilogue::kStoreBf16, ds->num_sms, st)) != cudaSuccess)
+  if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, d, peer ? q4t::Epilogue::kStoreBf16Rows : q4t::Epilogue::kStoreBf16,
+                                 ds->num_sms, st)) != cudaSuccess)
     return fail_cuda("down GEMM launch", e);
   stage_end(5, st);
   return Q4T_OK;
@@ -814,29 +818,60 @@ size_t q4t_moe_finish_workspace_bytes(int32_t T, int32_t hs, int32_t shared_is) 
   return F.total;
 }
 
+namespace {
+int finish_args_ok(const q4t_extra_weights* extra, int T, int k, const void* workspace, size_t workspace_bytes,
+                   FinishLayout* F) {
+  if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");
+  if (!extra || extra->hs <= 0 || extra->hs % 128 || extra->shared_is <= 0 || extra->shared_is % 128)
+    return fail(Q4T_ERR_INVALID, "unsupported dims (hs, shared_is multiples of 128)");
+  if (!workspace) return fail(Q4T_ERR_INVALID, "null pointer");
+  finish_layout(T, extra->hs, extra->shared_is, F);
+  if (workspace_bytes < F->total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");
+  return Q4T_OK;
+}
+}  // namespace
+
+int32_t q4t_moe_shared_expert(const uint16_t* x, const q4t_extra_weights* extra, int32_t T, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  if (T <= 0) return Q4T_OK;
+  FinishLayout F;
+  int rc = finish_args_ok(extra, T, 1, workspace, workspace_bytes, &F);
+  if (rc != Q4T_OK) return rc;
+  if (!x) return fail(Q4T_ERR_INVALID, "null pointer");
+  const DeviceState* ds;
+  if ((rc = device_state(&ds)) != Q4T_OK) return rc;
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  return run_shared_expert(ds, x, extra, reinterpret_cast<uint16_t*>(base + F.shared_gu),
+                           reinterpret_cast<uint16_t*>(base + F.shared_act),
+                           reinterpret_cast<uint16_t*>(base + F.shared_down), T, 0, static_cast<cudaStream_t>(stream));
+}
+
+int32_t q4t_moe_combine(const uint16_t* x, const uint16_t* expert_rows, const int32_t* row_of_flat,
+                        const float* router_w, const q4t_extra_weights* extra, uint16_t* y, int32_t T, int32_t k,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (T <= 0) return Q4T_OK;
+  FinishLayout F;
+  int rc = finish_args_ok(extra, T, k, workspace, workspace_bytes, &F);
+  if (rc != Q4T_OK) return rc;
+  if (!x || !expert_rows || !row_of_flat || !router_w || !y) return fail(Q4T_ERR_INVALID, "null pointer");
+  const DeviceState* ds;
+  if ((rc = device_state(&ds)) != Q4T_OK) return rc;
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  cudaError_t e = q4t::launch_final_combine(expert_rows, row_of_flat, router_w,
+                                            reinterpret_cast<uint16_t*>(base + F.shared_down), x,
+                                            extra->shared_gate_scalar, reinterpret_cast<float*>(base + F.routed), y, T,
+                                            k, extra->hs, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("combine launch", e);
+}
+
 int32_t q4t_moe_finish(const uint16_t* x, const uint16_t* expert_rows, const int32_t* row_of_flat,
                        const float* router_w, const q4t_extra_weights* extra, uint16_t* y, int32_t T, int32_t k,
                        void* workspace, size_t workspace_bytes, void* stream) {
   if (T <= 0) return Q4T_OK;
   if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");
-  if (!extra || extra->hs <= 0 || extra->hs % 128 || extra->shared_is <= 0 || extra->shared_is % 128)
-    return fail(Q4T_ERR_INVALID, "unsupported dims (hs, shared_is multiples of 128)");
-  if (!x || !expert_rows || !row_of_flat || !router_w || !y || !workspace) return fail(Q4T_ERR_INVALID, "null pointer");
-  FinishLayout F;
-  finish_layout(T, extra->hs, extra->shared_is, &F);
-  if (workspace_bytes < F.total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");
-  const DeviceState* ds;
-  int rc = device_state(&ds);
+  int rc = q4t_moe_shared_expert(x, extra, T, workspace, workspace_bytes, stream);
   if (rc != Q4T_OK) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  uint8_t* base = static_cast<uint8_t*>(workspace);
-  uint16_t* sgu = reinterpret_cast<uint16_t*>(base + F.shared_gu);
-  uint16_t* sact = reinterpret_cast<uint16_t*>(base + F.shared_act);
-  uint16_t* sdown = reinterpret_cast<uint16_t*>(base + F.shared_down);
-  if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, 0, st)) != Q4T_OK) return rc;
-  cudaError_t e = q4t::launch_final_combine(expert_rows, row_of_flat, router_w, sdown, x, extra->shared_gate_scalar,
-                                            reinterpret_cast<float*>(base + F.routed), y, T, k, extra->hs, st);
-  return e == cudaSuccess ? Q4T_OK : fail_cuda("combine launch", e);
+  return q4t_moe_combine(x, expert_rows, row_of_flat, router_w, extra, y, T, k, workspace, workspace_bytes, stream);
 }
 
 // ---- pull/push expert parallelism over peer memory
@@ -871,6 +906,32 @@ int32_t q4t_peer_buffer_open(const uint8_t handle[Q4T_PEER_HANDLE_BYTES], void**
 int32_t q4t_peer_buffer_close(void* ptr) {
   cudaError_t e = cudaIpcCloseMemHandle(ptr);
   return e == cudaSuccess ? Q4T_OK : fail_cuda("peer buffer close", e);
+}
+
+int32_t q4t_ep_publish(const uint16_t* x, const q4t_ep_peer_table* peers, int32_t hs, float input_scale,
+                       void* stream) {
+  if (!x || !peers) return fail(Q4T_ERR_INVALID, "null pointer");
+  const int world = peers->world, rank = peers->rank, tpr = peers->tokens_per_rank;
+  if (world <= 0 || world > Q4T_EP_MAX_RANKS || rank < 0 || rank >= world || tpr <= 0)
+    return fail(Q4T_ERR_INVALID, "invalid peer table (world in [1,8], rank < world, tokens_per_rank > 0)");
+  if (hs <= 0 || hs % 64) return fail(Q4T_ERR_INVALID, "hs must be a multiple of 64");
+  if (!(input_scale > 0.0f)) return fail(Q4T_ERR_INVALID, "input scale must be positive");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  q4t::PublishTargets dst{};
+  dst.n = world;
+  const size_t code_block = static_cast<size_t>(tpr) * (hs / 2), sf_block = sf_buffer_size(tpr, hs);
+  for (int i = 0; i < world; ++i) {
+    // own copy first: the peers' copies follow in ring order so that the ranks do not all
+    // write to the same GPU at the same moment
+    const int p = (rank + i) % world;
+    if (!peers->xq_packed[p] || !peers->xq_sf[p]) return fail(Q4T_ERR_INVALID, "peer table has a null buffer");
+    dst.packed[i] = const_cast<uint8_t*>(peers->xq_packed[p]) + code_block * rank;
+    dst.sf[i] = const_cast<uint8_t*>(peers->xq_sf[p]) + sf_block * rank;
+  }
+  cudaError_t e = q4t::launch_publish_tokens(x, dst, tpr, hs, input_scale, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("publish launch", e);
 }
 
 size_t q4t_moe_expert_peer_workspace_bytes(int32_t tokens_all, int32_t k, int32_t hs, int32_t moe_is,
@@ -908,17 +969,20 @@ int32_t q4t_moe_expert_peer(const int32_t* ids_all, const q4t_ep_peer_table* pee
   routed_layout(T_all, k, w->hs, w->moe_is, w->E, &P.L);
   P.base = static_cast<uint8_t*>(workspace);
   int32_t* local_ids = reinterpret_cast<int32_t*>(P.base + align_up(P.L.total, 256));
-  cudaError_t e = q4t::launch_ep_localise_ids(ids_all, R, w->E * world, world, rank, peers->expert_map == 1, local_ids, st);
+  const int map = peers->expert_map;
+  if (map < 0 || map > 2) return fail(Q4T_ERR_INVALID, "expert_map must be 0, 1 or 2");
+  if (map == 2 && (!peers->placement || peers->experts_total <= 0))
+    return fail(Q4T_ERR_INVALID, "expert_map 2 needs a placement table");
+  const int E_total = map == 2 ? peers->experts_total : w->E * world;
+  cudaError_t e = q4t::launch_ep_localise_ids(ids_all, R, E_total, world, rank, map, peers->placement, tpr * k,
+                                              local_ids, st);
   if (e != cudaSuccess) return fail_cuda("id localise launch", e);
   PeerRoute route{};
-  route.src.tokens_per_rank = tpr;
+  route.xq_packed = peers->xq_packed[rank];
+  route.xq_sf = peers->xq_sf[rank];
+  route.tokens_per_rank = tpr;
   route.rows_per_rank = tpr * k;
-  for (int i = 0; i < q4t::kMaxPeers; ++i) {
-    const int j = i < world ? i : 0;
-    route.src.xq_packed[i] = peers->xq_packed[j];
-    route.src.xq_sf[i] = peers->xq_sf[j];
-    route.dn_rows[i] = peers->dn_rows[j];
-  }
+  for (int i = 0; i < q4t::kMaxPeers; ++i) route.dn_rows[i] = peers->dn_rows[i < world ? i : 0];
   stage_begin(st);
   stage_end(1, st);
   return run_routed_core(ds, nullptr, local_ids, w, P, T_all, k, flags, st, false, &route);

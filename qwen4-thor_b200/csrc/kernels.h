@@ -22,20 +22,23 @@ cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* 
 cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed, uint8_t* sf_tiles,
                                 int R, int K, const int32_t* flat_of_row, const int32_t* row_tile,
                                 const int32_t* tile_row0, const int32_t* rows_dev, int k, cudaStream_t stream);
-// Peer table of the pull/push expert-parallel path: every rank's quantised token rows
-// (read by the owner of each expert) and its landing buffer for down-projection rows.
+// Expert parallelism over peer memory: a rank quantises its tokens once and writes the
+// codes and scales into its block of every rank's gathered buffer (the targets may be
+// peer GPUs' memory; K a multiple of 64).
 constexpr int kMaxPeers = 8;
-struct PeerSources {
-  const uint8_t* xq_packed[kMaxPeers];  // [tokens_per_rank, K/2] codes
-  const uint8_t* xq_sf[kMaxPeers];      // swizzled scales of the same rows
-  int tokens_per_rank;
+struct PublishTargets {
+  uint8_t* packed[kMaxPeers];  // start of this rank's block in each gathered code buffer
+  uint8_t* sf[kMaxPeers];      // start of this rank's swizzled scale block in each
+  int n;
 };
-// As launch_gather_codes, with flat indices running over all ranks' tokens:
-// token = flat / k lives on rank token / tokens_per_rank.
-cudaError_t launch_gather_codes_peer(const PeerSources& src, uint8_t* packed, uint8_t* sf_tiles, int R, int K,
-                                     const int32_t* flat_of_row, const int32_t* row_tile,
-                                     const int32_t* tile_row0, const int32_t* rows_dev, int k,
-                                     cudaStream_t stream);
+cudaError_t launch_publish_tokens(const uint16_t* x, const PublishTargets& dst, int M, int K, float global_scale,
+                                  cudaStream_t stream);
+// As launch_gather_codes, reading the gathered buffers: xq_packed [world*tokens_per_rank, K/2],
+// xq_sf = world swizzled blocks of sf_buffer_size(tokens_per_rank, K) bytes each.
+cudaError_t launch_gather_codes_blocks(const uint8_t* xq_packed, const uint8_t* xq_sf, int tokens_per_rank,
+                                       uint8_t* packed, uint8_t* sf_tiles, int R, int K, const int32_t* flat_of_row,
+                                       const int32_t* row_tile, const int32_t* tile_row0, const int32_t* rows_dev,
+                                       int k, cudaStream_t stream);
 cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,
                            float inv_global, int N, int K, cudaStream_t stream);
 cudaError_t launch_encoder_selftest(int which, uint64_t first, uint64_t count,
@@ -71,11 +74,14 @@ cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const P
                         cudaStream_t stream);
 cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_per_rank, int32_t* dest,
                                 int32_t* local, cudaStream_t stream);
-// local[f] = index of expert ids[f] on `rank` (-1 when it lives elsewhere or is out of range).
-// interleaved: expert e lives on rank e % world as local e / world; else on rank
-// e / (E/world) as local e % (E/world).
-cudaError_t launch_ep_localise_ids(const int32_t* ids, int R, int E, int world, int rank, bool interleaved,
-                                   int32_t* local, cudaStream_t stream);
+// local[f] = index of expert ids[f] on `rank` (-1 when it is served elsewhere or out of range).
+// map 0: expert e lives on rank e / (E/world) as local e % (E/world); 1: on rank e % world as
+// local e / world; 2: placement[e] = -1, the local index, or (1<<30 | local index) for an expert
+// replicated on all ranks, which serves only the entries of this rank's own tokens
+// (f / flats_per_rank == rank).
+cudaError_t launch_ep_localise_ids(const int32_t* ids, int R, int E, int world, int rank, int map,
+                                   const int32_t* placement, int flats_per_rank, int32_t* local,
+                                   cudaStream_t stream);
 // row_of_flat[f] = f for ids[f] in [0,E), else -1 (rows delivered in flat order).
 cudaError_t launch_ep_flat_rows(const int32_t* ids, int R, int E, int32_t* row_of_flat, cudaStream_t stream);
 cudaError_t launch_gather_rows(const uint16_t* src, const int32_t* index, int div, const int32_t* rows_dev,
@@ -95,7 +101,9 @@ enum class Epilogue : int {
   kStoreBf16 = 0,     // out[row, n] = bf16(alpha * acc)
   kStoreF32 = 1,      // out[row, n] = alpha * acc
   kSwigluBf16 = 2,    // gate|up tile -> bf16((g*sig(g))*u), g/u rounded to bf16 first
-  kSwigluQuant = 3    // as above, then NVFP4 quantisation with the expert's down input scale
+  kSwigluQuant = 3,   // as above, then NVFP4 quantisation with the expert's down input scale
+  kStoreBf16Rows = 4  // kStoreBf16 written as whole 128-byte row segments, rows optionally scattered
+                      // (NVFP4 only; the form used when rows may go to peer GPUs)
 };
 struct GemmArgs {
   // problem
@@ -127,7 +135,7 @@ struct GemmArgs {
   uint8_t* out_sf_tiles;       // kSwigluQuant: tile-local scale atoms of the intermediate
   uint16_t* gu_dump;           // optional bf16 [rows, 2*inner] copy of the rounded gate|up values
   int gu_dump_ld;
-  // kStoreBf16 only: when scatter_flat is set, row r of the output goes to
+  // kStoreBf16Rows only: when scatter_flat is set, row r of the output goes to
   // scatter_base[f / scatter_rows_per_rank] + (f % scatter_rows_per_rank) * ldo with
   // f = scatter_flat[r] (the bases may be peer GPUs' memory) instead of out + r * ldo.
   const int32_t* scatter_flat;

@@ -84,6 +84,44 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(
   }
 }
 
+// The plain-row quantiser writing the same codes and scales to several buffers
+// (this GPU's and its peers' copies of a rank's token block); K a multiple of 64.
+__global__ void __launch_bounds__(256) publish_tokens_kernel(const uint16_t* __restrict__ x,
+                                                             const __grid_constant__ PublishTargets dst,
+                                                             int rows, int K, float global_scale) {
+  const int groups = K >> 4;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(rows) * groups;
+  const bool live = idx < total;
+  const int row = live ? static_cast<int>(idx / groups) : 0;
+  const int g = live ? static_cast<int>(idx % groups) : 0;
+  uint32_t sf = 0;
+  if (live) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * K + g * 16);
+    const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float a[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      a[2 * j] = bf16x2_lo(w[j]);
+      a[2 * j + 1] = bf16x2_hi(w[j]);
+    }
+    uint32_t lo, hi;
+    sf = quantize_group16(a, global_scale, lo, hi);
+    const size_t at = (static_cast<size_t>(row) * groups + g) * 8;
+    for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint2*>(dst.packed[d] + at) = make_uint2(lo, hi);
+  }
+  const uint32_t lane = threadIdx.x & 31u;
+  uint32_t word = sf;
+  word |= __shfl_down_sync(0xffffffffu, sf, 1) << 8;
+  word |= __shfl_down_sync(0xffffffffu, sf, 2) << 16;
+  word |= __shfl_down_sync(0xffffffffu, sf, 3) << 24;
+  if (live && (lane & 3u) == 0) {
+    const size_t off = sf_offset(static_cast<uint32_t>(row), g, groups >> 2);
+    for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint32_t*>(dst.sf[d] + off) = word;
+  }
+}
+
 // One warp per grouped row: copies the row's token codes (quantised once per
 // token) and moves its scale bytes from the per-token swizzled buffer into the
 // row tile's local atoms, four bytes (one K-tile of one row) at a time.
@@ -107,24 +145,25 @@ __global__ void __launch_bounds__(256) gather_codes_kernel(
   }
 }
 
-// The same copy with the token rows spread over the ranks' buffers (plain loads:
-// the sources may be peer GPUs' memory).
-__global__ void __launch_bounds__(256) gather_codes_peer_kernel(
-    const __grid_constant__ PeerSources src, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_tiles,
+// The same copy from the gathered per-rank token blocks: token = flat / k of
+// all ranks' tokens lives in block token / tokens_per_rank.
+__global__ void __launch_bounds__(256) gather_codes_blocks_kernel(
+    const uint8_t* __restrict__ xq_packed, const uint8_t* __restrict__ xq_sf, int tokens_per_rank,
+    size_t sf_block_bytes, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_tiles,
     int rows, int K, const int32_t* __restrict__ flat_of_row, const int32_t* __restrict__ row_tile,
     const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ rows_dev, int k) {
   const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= min(rows, *rows_dev)) return;
   const int token_all = flat_of_row[r] / k;
-  const int owner = token_all / src.tokens_per_rank;
-  const int token = token_all - owner * src.tokens_per_rank;
+  const int owner = token_all / tokens_per_rank;
+  const int token = token_all - owner * tokens_per_rank;
   const int t = row_tile[r];
   const uint32_t in_tile = static_cast<uint32_t>(r - tile_row0[t]);
   const int row_bytes = K >> 1, ntk = K >> 6;
-  const uint4* from = reinterpret_cast<const uint4*>(src.xq_packed[owner] + static_cast<size_t>(token) * row_bytes);
-  const uint8_t* from_sf = src.xq_sf[owner];
+  const uint4* from = reinterpret_cast<const uint4*>(xq_packed + static_cast<size_t>(token_all) * row_bytes);
+  const uint8_t* from_sf = xq_sf + static_cast<size_t>(owner) * sf_block_bytes;
   uint4* dst = reinterpret_cast<uint4*>(packed + static_cast<size_t>(r) * row_bytes);
-  for (int c = lane; c < (row_bytes >> 4); c += 32) dst[c] = from[c];
+  for (int c = lane; c < (row_bytes >> 4); c += 32) dst[c] = __ldg(from + c);
   for (int a = lane; a < ntk; a += 32) {
     const uint32_t v = *reinterpret_cast<const uint32_t*>(from_sf + sf_offset(static_cast<uint32_t>(token), 4u * a, ntk));
     *reinterpret_cast<uint32_t*>(sf_tiles + (static_cast<size_t>(t) * ntk + a) * 512u + sf_in_atom(in_tile, 0)) = v;
@@ -224,13 +263,22 @@ cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, 
   return cudaGetLastError();
 }
 
-cudaError_t launch_gather_codes_peer(const PeerSources& src, uint8_t* packed, uint8_t* sf_tiles, int R, int K,
-                                     const int32_t* flat_of_row, const int32_t* row_tile,
-                                     const int32_t* tile_row0, const int32_t* rows_dev, int k,
-                                     cudaStream_t stream) {
+cudaError_t launch_gather_codes_blocks(const uint8_t* xq_packed, const uint8_t* xq_sf, int tokens_per_rank,
+                                       uint8_t* packed, uint8_t* sf_tiles, int R, int K, const int32_t* flat_of_row,
+                                       const int32_t* row_tile, const int32_t* tile_row0, const int32_t* rows_dev,
+                                       int k, cudaStream_t stream) {
   if (R == 0) return cudaSuccess;
-  gather_codes_peer_kernel<<<(R + 7) / 8, 256, 0, stream>>>(src, packed, sf_tiles, R, K, flat_of_row, row_tile,
-                                                            tile_row0, rows_dev, k);
+  gather_codes_blocks_kernel<<<(R + 7) / 8, 256, 0, stream>>>(
+      xq_packed, xq_sf, tokens_per_rank, static_cast<size_t>((tokens_per_rank + 127) / 128) * 128 * (K / 16),
+      packed, sf_tiles, R, K, flat_of_row, row_tile, tile_row0, rows_dev, k);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_publish_tokens(const uint16_t* x, const PublishTargets& dst, int M, int K, float global_scale,
+                                  cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(M) * (K / 16);
+  if (total == 0 || dst.n == 0) return cudaSuccess;
+  publish_tokens_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(x, dst, M, K, global_scale);
   return cudaGetLastError();
 }
 

@@ -369,16 +369,26 @@ __global__ void __launch_bounds__(256) ep_split_ids_kernel(const int32_t* __rest
 }
 
 __global__ void __launch_bounds__(256) ep_localise_ids_kernel(const int32_t* __restrict__ ids, int R, int E,
-                                                              int world, int rank, int interleaved,
-                                                              int32_t* __restrict__ local) {
+                                                              int world, int rank, int map,
+                                                              const int32_t* __restrict__ placement,
+                                                              int flats_per_rank, int32_t* __restrict__ local) {
   const int f = blockIdx.x * blockDim.x + threadIdx.x;
   if (f >= R) return;
   const int e = ids[f];
   int out = -1;
   if (e >= 0 && e < E) {
-    const int per = E / world;
-    const int owner = interleaved ? e % world : e / per;
-    if (owner == rank) out = interleaved ? e / world : e - owner * per;
+    if (map == 2) {
+      const int v = placement[e];
+      if (v >= 0) {
+        const int idx = v & ~(1 << 30);
+        // a replicated expert serves only the tokens that live on this rank
+        out = (v & (1 << 30)) ? (f / flats_per_rank == rank ? idx : -1) : idx;
+      }
+    } else {
+      const int per = E / world;
+      const int owner = map == 1 ? e % world : e / per;
+      if (owner == rank) out = map == 1 ? e / world : e - owner * per;
+    }
   }
   local[f] = out;
 }
@@ -577,9 +587,11 @@ cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_pe
   return cudaGetLastError();
 }
 
-cudaError_t launch_ep_localise_ids(const int32_t* ids, int R, int E, int world, int rank, bool interleaved,
-                                   int32_t* local, cudaStream_t stream) {
-  ep_localise_ids_kernel<<<(R + 255) / 256, 256, 0, stream>>>(ids, R, E, world, rank, interleaved ? 1 : 0, local);
+cudaError_t launch_ep_localise_ids(const int32_t* ids, int R, int E, int world, int rank, int map,
+                                   const int32_t* placement, int flats_per_rank, int32_t* local,
+                                   cudaStream_t stream) {
+  ep_localise_ids_kernel<<<(R + 255) / 256, 256, 0, stream>>>(ids, R, E, world, rank, map, placement, flats_per_rank,
+                                                              local);
   return cudaGetLastError();
 }
 

@@ -288,6 +288,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int nrows = args.tile_expert ? args.tile_nrows[mt] : min(kTileM, args.total_rows - row0);
       const float alpha =
           args.alpha_w ? args.alpha_w[group] * args.alpha_a[group] : args.alpha_const;
+      // everything the epilogue reads from global memory is fetched before the wait
+      [[maybe_unused]] float next_scale = 0.0f;
+      if constexpr (EPI == Epilogue::kSwigluQuant) next_scale = args.next_scale[group];
+      // Row-segment stores: where this lane's own row goes (its place in the tile's rows,
+      // or, scattered, in its owner's buffer), looked up while the accumulator is still
+      // being produced; the storing lanes fetch it by shuffle.
+      [[maybe_unused]] unsigned long long my_row_ptr = 0;
+      if constexpr (EPI == Epilogue::kStoreBf16Rows) {
+        if (quad * 32 + lane < nrows) {
+          const int r = row0 + quad * 32 + lane;
+          if (args.scatter_flat) {
+            const int f = args.scatter_flat[r];
+            const int owner = f / args.scatter_rows_per_rank;
+            my_row_ptr = reinterpret_cast<unsigned long long>(
+                args.scatter_base[owner] + static_cast<size_t>(f - owner * args.scatter_rows_per_rank) * args.ldo);
+          } else {
+            my_row_ptr = reinterpret_cast<unsigned long long>(static_cast<uint16_t*>(args.out) +
+                                                              static_cast<size_t>(r) * args.ldo);
+          }
+        }
+      }
       if (!mbar_wait(smem_u32(&bars.acc_full), acc_phase, abort_flag)) {
         ok = false;
         break;
@@ -334,6 +355,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       // ---- per unit: convert, compute, store (unit by unit keeps few registers live).
       // Rows past the tile's row count carry stale accumulator bits: they are
       // zeroed so the arithmetic below never meets NaNs or denormals.
+      if constexpr (EPI == Epilogue::kStoreBf16Rows) {
+        static_assert(kUnitsPerWarp == 4, "row-segment stores cover 64 columns per warp");
+        // This warp's 64 columns are 128 bytes of each of its 32 rows.  Round to bf16 in
+        // place, then pass the rows through the warp's staging block sixteen at a time
+        // (one row per lane, 16-byte chunks XOR-swizzled against bank conflicts) and
+        // read them back eight lanes per row, so that every store instruction writes
+        // whole 128-byte row segments (full lines in L2, full packets to a peer GPU).
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float lo = valid ? alpha * __uint_as_float(ra[2 * i]) : 0.0f;
+          const float hi = valid ? alpha * __uint_as_float(ra[2 * i + 1]) : 0.0f;
+          ra[i] = f32x2_to_bf16x2(lo, hi);
+        }
+        const uint32_t stg = smem_base + kStages * kStage + static_cast<uint32_t>(warp - kFirstEpiWarp) * kStoreStageBytes;
+        const uint32_t r16 = static_cast<uint32_t>(lane) & 15u;
+        const uint32_t chunk = static_cast<uint32_t>(lane) & 7u;
+        const int col = n0 + sub * (kUnitsPerWarp * kUnitCols) + static_cast<int>(chunk) * 8;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          if ((lane >> 4) == half) {
+#pragma unroll
+            for (uint32_t c = 0; c < 8; ++c)
+              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(stg + r16 * 128u + ((c ^ (r16 & 7u)) << 4)),
+                           "r"(ra[4 * c]), "r"(ra[4 * c + 1]), "r"(ra[4 * c + 2]), "r"(ra[4 * c + 3]) : "memory");
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t rs = (static_cast<uint32_t>(lane) >> 3) + 4u * i;  // row of the sixteen staged
+            uint32_t v0, v1, v2, v3;
+            asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                         : "r"(stg + rs * 128u + ((chunk ^ (rs & 7u)) << 4)) : "memory");
+            // the lane that owns row rr of the quadrant holds its destination (0 past the tile's rows)
+            const unsigned long long dst =
+                __shfl_sync(0xffffffffu, my_row_ptr, half * 16 + static_cast<int>(rs));
+            if (dst != 0 && col < args.b_rows_valid)
+              *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dst) + col) = make_uint4(v0, v1, v2, v3);
+          }
+          __syncwarp();
+        }
+      } else {
 #pragma unroll
       for (int j = 0; j < kUnitsPerWarp; ++j) {
         const int unit = sub * kUnitsPerWarp + j;
@@ -380,19 +442,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
                              : "r"(stg + rr * 64u + ((chunk ^ rsw) << 4)) : "memory");
                 const int col = n0 + cbase + static_cast<int>(chunk) * 8;
-                if (quad * 32 + rr < nrows && static_cast<int>(chunk) * 8 < ncols && col < args.b_rows_valid) {
-                  // the row's place: in the tile's own rows, or (scatter) in its owner's buffer
-                  uint16_t* rowp;
-                  if (args.scatter_flat) {
-                    const int f = args.scatter_flat[row0 + quad * 32 + rr];
-                    const int owner = f / args.scatter_rows_per_rank;
-                    rowp = args.scatter_base[owner] +
-                           static_cast<size_t>(f - owner * args.scatter_rows_per_rank) * args.ldo;
-                  } else {
-                    rowp = static_cast<uint16_t*>(args.out) + static_cast<size_t>(row0 + quad * 32 + rr) * args.ldo;
-                  }
-                  *reinterpret_cast<uint4*>(rowp + col) = make_uint4(v0, v1, v2, v3);
-                }
+                if (quad * 32 + rr < nrows && static_cast<int>(chunk) * 8 < ncols && col < args.b_rows_valid)
+                  *reinterpret_cast<uint4*>(static_cast<uint16_t*>(args.out) +
+                                            static_cast<size_t>(row0 + quad * 32 + rr) * args.ldo + col) =
+                      make_uint4(v0, v1, v2, v3);
               }
               __syncwarp();
             }
@@ -446,7 +499,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
               }
             } else {
-              const float next_scale = args.next_scale[group];
               const uint32_t out_ntk = (static_cast<uint32_t>(args.up_row_offset) + 63u) >> 6;
               uint32_t lo, hi;
               const uint32_t sf = quantize_group16(a, next_scale, lo, hi);
@@ -461,6 +513,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
       }
+      }  // per-unit epilogues
       if (stamp) Q4T_STAMP(2, tcount, 3);
     }
     if (!ok && args.status && lane == 0) atomicMax(args.status, 3);
@@ -498,6 +551,13 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs&
       } else {
         return cudaErrorInvalidValue;
       }
+    case Epilogue::kStoreBf16Rows:
+      if constexpr (NVF4) {
+        gemm_kernel<NVF4, Epilogue::kStoreBf16Rows, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
+        break;
+      } else {
+        return cudaErrorInvalidValue;
+      }
   }
   return cudaGetLastError();
 }
@@ -516,6 +576,7 @@ cudaError_t gemm_set_attributes() {
   if ((e = set_attr<true, Epilogue::kStoreF32, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<true, Epilogue::kSwigluBf16, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<true, Epilogue::kSwigluQuant, 256>()) != cudaSuccess) return e;
+  if ((e = set_attr<true, Epilogue::kStoreBf16Rows, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<false, Epilogue::kStoreBf16, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<false, Epilogue::kStoreF32, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<false, Epilogue::kSwigluBf16, 256>()) != cudaSuccess) return e;

@@ -143,19 +143,74 @@ class ExpertParallelMoE:
 
 
 # ------------------------------------------------------------------ peer-memory path
+def plan_placement(counts, world: int, hot: int):
+    """Expert placement from per-expert row counts of a profiling batch.
+
+    The `hot` most used experts are replicated on every rank (their rows never leave the GPU
+    that owns the token, which also balances them perfectly); the others are dealt out one by
+    one, busiest first, to the rank with the least load so far.  Returns (experts, tables):
+    experts[r] = global ids served by rank r in local order, tables[r] = the int32 [E] table
+    q4t_ep_peer_table.placement expects on rank r."""
+    import numpy as np
+    counts = np.asarray(counts, dtype=np.int64)
+    E = counts.shape[0]
+    order = np.argsort(-counts, kind="stable")
+    hot_ids = sorted(int(e) for e in order[:hot])
+    experts = [[] for _ in range(world)]
+    load = [0] * world
+    for e in order[hot:]:
+        r = min(range(world), key=lambda i: (load[i], len(experts[i]), i))
+        experts[r].append(int(e))
+        load[r] += int(counts[e])
+    tables = []
+    for r in range(world):
+        # sharded experts first: their result rows are the ones that cross NVLink, and the
+        # down GEMM walks the experts in local order, so those stores start early and
+        # overlap with the replicated experts' tiles
+        experts[r] = experts[r] + hot_ids
+        t = np.full(E, -1, dtype=np.int32)
+        for idx, e in enumerate(experts[r]):
+            t[e] = idx | (1 << 30) if idx >= len(experts[r]) - len(hot_ids) else idx
+        tables.append(t)
+    return experts, tables
+
+
+def local_layer_from_list(q4t, full, experts):
+    """The experts `experts` (global ids, local order) of a full device layer, copied."""
+    import torch
+    is_, hs, E = full.moe_is, full.hs, full.E
+    pick = torch.as_tensor(experts, dtype=torch.long, device=full.t["gu_packed"].device)
+    t = dict(full.t)
+    t["gu_packed"] = full.t["gu_packed"].view(E, -1).index_select(0, pick).view(-1, hs // 2)
+    t["gu_sf"] = full.t["gu_sf"].view(E, -1).index_select(0, pick).view(-1)
+    t["dn_packed"] = full.t["dn_packed"].view(E, -1).index_select(0, pick).view(-1, is_ // 2)
+    t["dn_sf"] = full.t["dn_sf"].view(E, -1).index_select(0, pick).view(-1)
+    for n in ("gu_w_scale2", "gu_input_scale", "dn_w_scale2", "dn_input_scale"):
+        t[n] = full.t[n].index_select(0, pick)
+    return q4t.DeviceLayer(len(experts), hs, is_, full.shared_is, t)
+
+
 class PeerBuffers:
-    """One rank's published buffers (quantised tokens, landing rows) and its view of the
-    peers' buffers.  Real ranks: allocated by the library and mapped across processes
+    """One rank's peer-writable buffers (gathered quantised tokens of all ranks, landing rows
+    of its own tokens) and its view of the peers' buffers.  Real ranks: allocated by the library and mapped across processes
     through exported handles (`connect`).  A single-process test can instead fill the
     table with plain device pointers (`from_pointers`)."""
 
-    def __init__(self, q4t, world, rank, T_local, k, hs, expert_map=1):
+    def __init__(self, q4t, world, rank, T_local, k, hs, expert_map=1, placement=None):
+        """placement: this rank's device int32 [E] table (plan_placement) -> expert_map 2."""
         self.q4t, self.lib = q4t, q4t.load()
         self.world, self.rank, self.T, self.k, self.hs = world, rank, T_local, k, hs
         self.table = q4t.EpPeerTable()
         self.table.world, self.table.rank = world, rank
         self.table.tokens_per_rank, self.table.expert_map = T_local, expert_map
-        self.sizes = (T_local * (hs // 2), self.lib.q4t_sf_buffer_size(T_local, hs), T_local * k * hs * 2)
+        self.placement = placement          # keeps the device table alive
+        if placement is not None:
+            self.table.expert_map = 2
+            self.table.placement = placement.data_ptr()
+            self.table.experts_total = placement.numel()
+        # gathered codes, gathered scale blocks (all ranks' tokens), landing rows (own tokens)
+        self.sizes = (world * T_local * (hs // 2), world * self.lib.q4t_sf_buffer_size(T_local, hs),
+                      T_local * k * hs * 2)
         self.own = None
         self.opened = []
 
@@ -207,11 +262,11 @@ class PeerBuffers:
 
 
 class PeerExpertParallelMoE:
-    """Expert-parallel step without row collectives: each rank publishes its quantised
-    tokens, the owner of an expert pulls the rows it needs from the publishers' memory and
-    its down GEMM stores the result rows straight into the token owners' landing buffers.
-    Only the expert ids travel through a collective (all-gather), which also orders
-    "published" before "pulled"; one more tiny collective orders "pushed" before "combined".
+    """Expert-parallel step without row collectives: each rank's quantiser stores its tokens
+    into every rank's gathered buffer, and the down GEMM of an expert's owner stores the
+    result rows straight into the token owners' landing buffers.  Only the expert ids travel
+    through a collective (all-gather), which also orders "published" before "used"; one more
+    tiny collective orders "pushed" before "combined".
 
     layer_local holds this rank's experts (expert_map 1: experts rank, rank+world, ...;
     0: a contiguous block) plus the replicated router and shared expert."""
@@ -241,6 +296,7 @@ class PeerExpertParallelMoE:
         self.finish_ws = torch.empty(self.finish_ws_bytes, dtype=torch.uint8, device=dev)
         self.profile = False
         self.phase_ms = {}
+        self.side = None
 
     def _s(self):
         return self.C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
@@ -257,8 +313,8 @@ class PeerExpertParallelMoE:
         q, lib = self.q4t, self.lib
         q.check(lib.q4t_bf16_linear(x.data_ptr(), self.L.extra.gate, self.logits.data_ptr(), self.T, self.E, self.hs, self._s()))
         q.check(lib.q4t_router_topk(self.logits.data_ptr(), self.ids.data_ptr(), self.rw.data_ptr(), self.T, self.E, self.k, self._s()))
-        q.check(lib.q4t_quantize_activation_fp4(x.data_ptr(), self.buf.own[0], self.buf.own[1], self.T, self.hs,
-                                                float(self.L.routed.gu_input_scale_uniform), self._s()))
+        q.check(lib.q4t_ep_publish(x.data_ptr(), self.C.byref(self.buf.table), self.hs,
+                                   float(self.L.routed.gu_input_scale_uniform), self._s()))
         return self.ids
 
     def experts(self, ids_all):
@@ -266,17 +322,33 @@ class PeerExpertParallelMoE:
                                                     self.C.byref(self.L.routed), self.k, self.ws.data_ptr(),
                                                     self.ws_bytes, 0, self._s()))
 
-    def finish(self, x, y):
+    def shared(self, x):
+        """The shared expert (needs nothing from the other ranks)."""
+        self.q4t.check(self.lib.q4t_moe_shared_expert(x.data_ptr(), self.C.byref(self.L.extra), self.T,
+                                                      self.finish_ws.data_ptr(), self.finish_ws_bytes, self._s()))
+
+    def combine(self, x, y):
         q, lib = self.q4t, self.lib
         q.check(lib.q4t_ep_flat_rows(self.ids.data_ptr(), self.T * self.k, self.E, self.row_of_flat.data_ptr(), self._s()))
-        q.check(lib.q4t_moe_finish(x.data_ptr(), self.buf.own[2], self.row_of_flat.data_ptr(), self.rw.data_ptr(),
-                                   self.C.byref(self.L.extra), y.data_ptr(), self.T, self.k,
-                                   self.finish_ws.data_ptr(), self.finish_ws_bytes, self._s()))
+        q.check(lib.q4t_moe_combine(x.data_ptr(), self.buf.own[2], self.row_of_flat.data_ptr(), self.rw.data_ptr(),
+                                    self.C.byref(self.L.extra), y.data_ptr(), self.T, self.k,
+                                    self.finish_ws.data_ptr(), self.finish_ws_bytes, self._s()))
         return y
+
+    def finish(self, x, y):
+        self.shared(x)
+        return self.combine(x, y)
 
     def forward(self, x, y):
         marks = []
         self._mark(marks, "start")
+        torch = self.torch
+        main = torch.cuda.current_stream()
+        if self.side is None:
+            self.side = torch.cuda.Stream()
+        self.side.wait_stream(main)          # x is ready
+        with torch.cuda.stream(self.side):   # the shared expert runs beside the exchange
+            self.shared(x)
         self.publish(x)
         self._mark(marks, "publish")
         if self.world > 1:
@@ -289,8 +361,9 @@ class PeerExpertParallelMoE:
         if self.world > 1:      # every rank's rows have landed once this returns on the stream
             self.dist.all_reduce(self.sync_word, group=self.group)
         self._mark(marks, "landed_barrier")
-        self.finish(x, y)
-        self._mark(marks, "finish")
+        main.wait_stream(self.side)
+        self.combine(x, y)
+        self._mark(marks, "combine")
         if self.profile:
             marks[-1][1].synchronize()
             self.phase_ms = {b[0]: a[1].elapsed_time(b[1]) for a, b in zip(marks[:-1], marks[1:])}

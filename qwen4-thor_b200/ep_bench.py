@@ -11,6 +11,7 @@ from __future__ import annotations
 import importlib
 import json
 import os
+import sys
 
 HS, E, K_TOP, MOE_IS, SHARED_IS = 2048, 512, 10, 512, 512
 T_TOTAL = 32768
@@ -57,6 +58,11 @@ def main_multi(args):
         if rank == 0:
             bench.main_single(args)
         return
+    # NCCL's version banner goes to stdout, and the bench prints exactly one line there:
+    # until the result line, whatever is written to descriptor 1 lands on stderr instead
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     q4t = importlib.import_module("qwen4-thor_b200")
@@ -76,10 +82,20 @@ def main_multi(args):
     ops = ep.LibraryOps(q4t, local, E, HS, K_TOP, world, T_loc, cap_rows=T_TOTAL * K_TOP)
     drv_rows = ep.ExpertParallelMoE(ops, world, rank)
     drv = drv_rows
+    placement = None
     if peer_mode:
-        # pull/push over peer memory, experts interleaved over the ranks (balances a skewed router)
-        local_i = _local_layer_interleaved(q4t, full, rank, world)
-        buf = ep.PeerBuffers(q4t, world, rank, T_loc, K_TOP, HS, expert_map=1).allocate()
+        # Placement from a profiling batch: the most used experts are replicated on every rank,
+        # the others dealt out by load (hot_experts 0: plain interleaving e % N instead).
+        if args.hot_experts > 0:
+            ops.router(xs[0])
+            counts = torch.bincount(ops.ids.flatten().long(), minlength=E)
+            dist.all_reduce(counts)
+            experts, tables = ep.plan_placement(counts.cpu().numpy(), world, args.hot_experts)
+            local_i = ep.local_layer_from_list(q4t, full, experts[rank])
+            placement = torch.from_numpy(tables[rank]).cuda()
+        else:
+            local_i = _local_layer_interleaved(q4t, full, rank, world)
+        buf = ep.PeerBuffers(q4t, world, rank, T_loc, K_TOP, HS, expert_map=1, placement=placement).allocate()
         gathered = [None] * world
         dist.all_gather_object(gathered, buf.handles())
         buf.connect(gathered)
@@ -131,16 +147,32 @@ def main_multi(args):
     phases = dict(drv.phase_ms)
     drv.profile = False
 
+    # stage times inside the expert phase, every rank (the slowest rank sets the step time)
+    stage_all = None
+    if peer_mode:
+        q4t.stage_timing(True)
+        drv.experts(drv.ids_all)
+        st = q4t.stage_timing_read()
+        q4t.stage_timing(False)
+        mine = {n: round(v, 4) for n, v in st.items() if v > 0}
+        stage_all = [None] * world
+        dist.all_gather_object(stage_all, mine)
+        dist.barrier()
+
     # per-rank load and link traffic of the last step
     if peer_mode:
-        owner = drv.ids_all.remainder(world)
-        mine = owner == rank
+        src_rank = torch.arange(world * T_loc, device="cuda").div(T_loc, rounding_mode="floor")[:, None].expand_as(drv.ids_all)
+        if placement is not None:
+            v = placement[drv.ids_all.long()]
+            mine = (v >= 0) & (((v >> 30) & 1 == 0) | (src_rank == rank))
+        else:
+            mine = drv.ids_all.remainder(world) == rank
         rows_here = int(mine.sum().item())
-        src_rank = torch.arange(world * T_loc, device="cuda").div(T_loc, rounding_mode="floor")[:, None].expand_as(owner)
         remote_rows = int((mine & (src_rank != rank)).sum().item())
         rows_recv = torch.tensor([float(rows_here)], device="cuda", dtype=torch.float64)
-        # leaving this GPU: result rows pushed to other ranks; entering: codes + scales pulled
-        out_bytes = torch.tensor([remote_rows * HS * 2.0], device="cuda", dtype=torch.float64)
+        # leaving this GPU: result rows pushed to other ranks (plus its token block to every peer)
+        out_bytes = torch.tensor([remote_rows * HS * 2.0 + (world - 1) * T_loc * (HS // 2 + HS // 16)],
+                                 device="cuda", dtype=torch.float64)
     else:
         rows_recv = torch.tensor([drv.last["rows_received"]], device="cuda", dtype=torch.float64)
         remote_out = sum(c for r, c in enumerate(drv.last["send_counts"]) if r != rank) + \
@@ -172,12 +204,16 @@ def main_multi(args):
                     vs_baseline=None, dtype="nvfp4 (e2m1 x ue4m3, fp32 accumulate); bf16 router and shared expert",
                     data="synthetic",
                     config=dict(workload=f"expert-parallel prefill MoE layer, T={T_TOTAL} total, {per} experts per GPU",
-                                expert_map="interleaved (e % N)" if peer_mode else "contiguous blocks",
+                                expert_map=(f"{args.hot_experts} most used experts of a profiling batch replicated on every GPU, "
+                                            "the rest dealt out by load" if placement is not None else
+                                            "interleaved (e % N)" if peer_mode else "contiguous blocks"),
+                                experts_on_rank0=local_i.E if peer_mode else per,
                                 hidden=HS, experts=E, top_k=K_TOP, moe_intermediate=MOE_IS, shared_intermediate=SHARED_IS,
                                 routing="zipf(s=1.1) bias on router column 0", parallelism=f"ep{world}",
                                 l2="2 inputs alternated; one step moves > 1 GB per GPU",
-                                exchange=("quantised rows pulled from and bf16 result rows pushed to peer memory by the "
-                                          "gather and down-GEMM kernels; NCCL only for the id all-gather and one barrier; "
+                                exchange=("quantised tokens stored into every GPU's gathered buffer by the quantiser, bf16 result "
+                                          "rows stored into the token owner's buffer by the down GEMM's epilogue (peer memory "
+                                          "over NVLink); NCCL only for the id all-gather and one barrier; "
                                           "checked bit-identical to the row-exchange path") if peer_mode else
                                 "bf16 rows both ways, NCCL all_to_all_single, one host sync per step for the split sizes"),
                     clocks=clocks.summary(),
@@ -191,6 +227,9 @@ def main_multi(args):
                     cpu_baseline=None,
                     load=dict(rows_received_max=float(mx_rows.item()), rows_received_mean=T_TOTAL * K_TOP / world,
                               imbalance=float(mx_rows.item()) / (T_TOTAL * K_TOP / world)),
-                    phase_ms_rank0=phases, single_gpu_same_workload=n1)
-        print(json.dumps(line))
+                    phase_ms_rank0=phases, expert_stage_ms_by_rank=stage_all, single_gpu_same_workload=n1)
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     dist.destroy_process_group()

@@ -79,7 +79,7 @@ def test_ep_two_emulated_ranks_equal_forward(q4t, gpu_lib):
     assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
 
 
-@pytest.mark.parametrize("W,expert_map", [(2, 0), (2, 1), (4, 1)])
+@pytest.mark.parametrize("W,expert_map", [(2, 0), (2, 1), (4, 1), (2, 2), (4, 2)])
 def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
     """The pull/push path with W ranks living in one process on one GPU: the "peer"
     pointers are ordinary device pointers and the ranks' phases are run one after the
@@ -97,15 +97,25 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
     fwd.status()
     Tl, per = T // W, E // W
     sf_bytes = q4t.load().q4t_sf_buffer_size(Tl, hs)
-    pub = [(torch.empty((Tl, hs // 2), dtype=torch.uint8, device="cuda"),
-            torch.zeros(sf_bytes, dtype=torch.uint8, device="cuda"),
+    pub = [(torch.empty((W * Tl, hs // 2), dtype=torch.uint8, device="cuda"),
+            torch.zeros(W * sf_bytes, dtype=torch.uint8, device="cuda"),
             torch.full((Tl * k, hs), -1, dtype=torch.int16, device="cuda")) for _ in range(W)]
     ptrs = [tuple(t.data_ptr() for t in p) for p in pub]
     drv = []
+    if expert_map == 2:   # placement table: 3 experts replicated everywhere, the rest by load
+        ids_ref = fwd.region("expert_ids", torch.int32, T * k).cpu().numpy()
+        experts, tables = ep.plan_placement(np.bincount(ids_ref, minlength=E), W, hot=3)
+        assert sorted(e for lst in experts for e in lst[:-3]) == sorted(set(range(E)) - set(experts[0][-3:]))
     for r in range(W):
-        local = (epb._local_layer_interleaved(q4t, full, r, W) if expert_map == 1
-                 else _slice_layer(q4t, full, r * per, (r + 1) * per))
-        buf = ep.PeerBuffers(q4t, W, r, Tl, k, hs, expert_map=expert_map).from_pointers(ptrs)
+        placement = None
+        if expert_map == 2:
+            local = ep.local_layer_from_list(q4t, full, experts[r])
+            placement = torch.from_numpy(tables[r]).cuda()
+        elif expert_map == 1:
+            local = epb._local_layer_interleaved(q4t, full, r, W)
+        else:
+            local = _slice_layer(q4t, full, r * per, (r + 1) * per)
+        buf = ep.PeerBuffers(q4t, W, r, Tl, k, hs, expert_map=expert_map, placement=placement).from_pointers(ptrs)
         drv.append(ep.PeerExpertParallelMoE(q4t, local, E, hs, k, W, r, Tl, buf))
     xs = [x[r * Tl:(r + 1) * Tl].contiguous() for r in range(W)]
     ids_all = torch.cat([d.publish(xr) for d, xr in zip(drv, xs)])
@@ -114,7 +124,7 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
     ys = [d.finish(xr, torch.empty((Tl, hs), dtype=torch.bfloat16, device="cuda")) for d, xr in zip(drv, xs)]
     torch.cuda.synchronize()
     for d in drv:
-        q4t.check(q4t.load().q4t_moe_workspace_status(d.ws.data_ptr(), W * Tl, k, hs, is_, per))
+        q4t.check(q4t.load().q4t_moe_workspace_status(d.ws.data_ptr(), W * Tl, k, hs, is_, d.L.E))
     assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
     # a second step over the same buffers (stale rows from step one must not leak)
     x2 = dev(synth.make_x(T, hs, seed=12)).view(torch.bfloat16)
