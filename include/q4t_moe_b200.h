@@ -298,8 +298,8 @@ int32_t q4t_moe_combine(const uint16_t* x, const uint16_t* expert_rows,
  * Instead of exchanging rows through collectives, the kernels themselves write
  * into the other GPUs' memory.  Every rank owns two buffers its peers can
  * write: a GATHERED token buffer (codes [world*tokens_per_rank, hs/2] and
- * world swizzled scale blocks of q4t_sf_buffer_size(tokens_per_rank, hs)
- * bytes) and a LANDING buffer dn_rows [tokens_per_rank*k, hs].  One step:
+ * scale bytes [world*tokens_per_rank, hs/16], row-major, not swizzled) and a
+ * LANDING buffer dn_rows [tokens_per_rank*k, hs].  One step:
  *   1. q4t_ep_publish: quantises this rank's tokens once (the layer's single
  *      gate/up input scale) and stores codes and scales into its block of
  *      EVERY rank's gathered buffer (stores over NVLink from the quantiser).
@@ -329,7 +329,7 @@ typedef struct q4t_ep_peer_table {
                                1: on rank e % world, local e / world;
                                2: by `placement` (below)                       */
   const uint8_t* xq_packed[Q4T_EP_MAX_RANKS]; /* rank r's gathered code buffer  */
-  const uint8_t* xq_sf[Q4T_EP_MAX_RANKS];     /* rank r's gathered scale blocks */
+  const uint8_t* xq_sf[Q4T_EP_MAX_RANKS];     /* rank r's gathered scale bytes  */
   uint16_t* dn_rows[Q4T_EP_MAX_RANKS];        /* rank r's landing buffer        */
   /* expert_map 2: THIS rank's device table int32 [experts_total]: -1 = the
    * expert is served elsewhere; v >= 0 = served here as local expert v for

@@ -228,8 +228,7 @@ q4t::PlanTables plan_tables(const RoutedPtrs& P, int E) {
 // the down-projection rows go straight to their owners' landing buffers.
 struct PeerRoute {
   const uint8_t* xq_packed;  // [world*tokens_per_rank, hs/2]
-  const uint8_t* xq_sf;      // world swizzled blocks
-  int tokens_per_rank;
+  const uint8_t* xq_sf;      // [world*tokens_per_rank, hs/16] row-major scale bytes
   uint16_t* dn_rows[q4t::kMaxPeers];
   int rows_per_rank;  // tokens_per_rank * k
 };
@@ -252,9 +251,9 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   // With one input scale for all experts and a large batch, quantise each token
   // once and copy its codes to its k rows; otherwise quantise every grouped row.
   if (peer) {
-    if ((e = q4t::launch_gather_codes_blocks(peer->xq_packed, peer->xq_sf, peer->tokens_per_rank, a_packed,
-                                             a_sf_tiles, R, hs, pt.flat_of_row, pt.row_tile, pt.tile_row0,
-                                             pt.offsets + E, k, st)) != cudaSuccess)
+    if ((e = q4t::launch_gather_codes_rowsf(peer->xq_packed, peer->xq_sf, a_packed, a_sf_tiles, R, hs,
+                                            pt.flat_of_row, pt.row_tile, pt.tile_row0, pt.offsets + E, k, st)) !=
+        cudaSuccess)
       return fail_cuda("block code gather launch", e);
   } else if (w->gu_input_scale_uniform > 0.0f && k > 1 && R >= 8192) {
     uint8_t* xq = P.at<uint8_t>(L.xq_packed);
@@ -921,7 +920,7 @@ int32_t q4t_ep_publish(const uint16_t* x, const q4t_ep_peer_table* peers, int32_
   if (rc != Q4T_OK) return rc;
   q4t::PublishTargets dst{};
   dst.n = world;
-  const size_t code_block = static_cast<size_t>(tpr) * (hs / 2), sf_block = sf_buffer_size(tpr, hs);
+  const size_t code_block = static_cast<size_t>(tpr) * (hs / 2), sf_block = static_cast<size_t>(tpr) * (hs / 16);
   for (int i = 0; i < world; ++i) {
     // own copy first: the peers' copies follow in ring order so that the ranks do not all
     // write to the same GPU at the same moment
@@ -980,7 +979,6 @@ int32_t q4t_moe_expert_peer(const int32_t* ids_all, const q4t_ep_peer_table* pee
   PeerRoute route{};
   route.xq_packed = peers->xq_packed[rank];
   route.xq_sf = peers->xq_sf[rank];
-  route.tokens_per_rank = tpr;
   route.rows_per_rank = tpr * k;
   for (int i = 0; i < q4t::kMaxPeers; ++i) route.dn_rows[i] = peers->dn_rows[i < world ? i : 0];
   stage_begin(st);

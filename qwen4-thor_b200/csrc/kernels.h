@@ -23,22 +23,22 @@ cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, 
                                 int R, int K, const int32_t* flat_of_row, const int32_t* row_tile,
                                 const int32_t* tile_row0, const int32_t* rows_dev, int k, cudaStream_t stream);
 // Expert parallelism over peer memory: a rank quantises its tokens once and writes the
-// codes and scales into its block of every rank's gathered buffer (the targets may be
-// peer GPUs' memory; K a multiple of 64).
+// codes and the scale bytes (row-major [tokens, K/16], not swizzled) into its block of
+// every rank's gathered buffer (the targets may be peer GPUs' memory; K a multiple of 64).
 constexpr int kMaxPeers = 8;
 struct PublishTargets {
   uint8_t* packed[kMaxPeers];  // start of this rank's block in each gathered code buffer
-  uint8_t* sf[kMaxPeers];      // start of this rank's swizzled scale block in each
+  uint8_t* sf[kMaxPeers];      // start of this rank's block in each gathered scale buffer
   int n;
 };
 cudaError_t launch_publish_tokens(const uint16_t* x, const PublishTargets& dst, int M, int K, float global_scale,
                                   cudaStream_t stream);
-// As launch_gather_codes, reading the gathered buffers: xq_packed [world*tokens_per_rank, K/2],
-// xq_sf = world swizzled blocks of sf_buffer_size(tokens_per_rank, K) bytes each.
-cudaError_t launch_gather_codes_blocks(const uint8_t* xq_packed, const uint8_t* xq_sf, int tokens_per_rank,
-                                       uint8_t* packed, uint8_t* sf_tiles, int R, int K, const int32_t* flat_of_row,
-                                       const int32_t* row_tile, const int32_t* tile_row0, const int32_t* rows_dev,
-                                       int k, cudaStream_t stream);
+// As launch_gather_codes, reading the gathered buffers of all ranks' tokens:
+// xq_packed [tokens, K/2], xq_sf [tokens, K/16] row-major.
+cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed,
+                                      uint8_t* sf_tiles, int R, int K, const int32_t* flat_of_row,
+                                      const int32_t* row_tile, const int32_t* tile_row0, const int32_t* rows_dev,
+                                      int k, cudaStream_t stream);
 cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,
                            float inv_global, int N, int K, cudaStream_t stream);
 cudaError_t launch_encoder_selftest(int which, uint64_t first, uint64_t count,

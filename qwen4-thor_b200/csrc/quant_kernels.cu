@@ -84,41 +84,40 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(
   }
 }
 
-// The plain-row quantiser writing the same codes and scales to several buffers
-// (this GPU's and its peers' copies of a rank's token block); K a multiple of 64.
+// Quantises token rows once and writes codes and scale bytes to several buffers (this
+// GPU's and its peers' copies of a rank's token block).  One warp per row; a lane owns
+// four neighbouring groups (64 values), so each destination receives the row as 32-byte
+// code pieces and 4-byte scale pieces that the warp lays down contiguously: 1 KB of codes
+// and 128 scale bytes (row-major, NOT swizzled) per 2048 values.  K a multiple of 64.
 __global__ void __launch_bounds__(256) publish_tokens_kernel(const uint16_t* __restrict__ x,
                                                              const __grid_constant__ PublishTargets dst,
                                                              int rows, int K, float global_scale) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
   const int groups = K >> 4;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t total = static_cast<int64_t>(rows) * groups;
-  const bool live = idx < total;
-  const int row = live ? static_cast<int>(idx / groups) : 0;
-  const int g = live ? static_cast<int>(idx % groups) : 0;
-  uint32_t sf = 0;
-  if (live) {
-    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * K + g * 16);
-    const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
-    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    float a[16];
+  for (int g0 = lane * 4; g0 < groups; g0 += 128) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * K + g0 * 16);
+    uint32_t codes[8], sfw = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      a[2 * j] = bf16x2_lo(w[j]);
-      a[2 * j + 1] = bf16x2_hi(w[j]);
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v0 = __ldg(src + 2 * j), v1 = __ldg(src + 2 * j + 1);
+      const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+      float a[16];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        a[2 * i] = bf16x2_lo(w[i]);
+        a[2 * i + 1] = bf16x2_hi(w[i]);
+      }
+      sfw |= quantize_group16(a, global_scale, codes[2 * j], codes[2 * j + 1]) << (8 * j);
     }
-    uint32_t lo, hi;
-    sf = quantize_group16(a, global_scale, lo, hi);
-    const size_t at = (static_cast<size_t>(row) * groups + g) * 8;
-    for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint2*>(dst.packed[d] + at) = make_uint2(lo, hi);
-  }
-  const uint32_t lane = threadIdx.x & 31u;
-  uint32_t word = sf;
-  word |= __shfl_down_sync(0xffffffffu, sf, 1) << 8;
-  word |= __shfl_down_sync(0xffffffffu, sf, 2) << 16;
-  word |= __shfl_down_sync(0xffffffffu, sf, 3) << 24;
-  if (live && (lane & 3u) == 0) {
-    const size_t off = sf_offset(static_cast<uint32_t>(row), g, groups >> 2);
-    for (int d = 0; d < dst.n; ++d) *reinterpret_cast<uint32_t*>(dst.sf[d] + off) = word;
+    const size_t code_at = static_cast<size_t>(row) * (K >> 1) + static_cast<size_t>(g0) * 8;
+    const size_t sf_at = static_cast<size_t>(row) * groups + g0;
+    for (int d = 0; d < dst.n; ++d) {
+      uint4* c = reinterpret_cast<uint4*>(dst.packed[d] + code_at);
+      c[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      c[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+      *reinterpret_cast<uint32_t*>(dst.sf[d] + sf_at) = sfw;
+    }
   }
 }
 
@@ -145,29 +144,26 @@ __global__ void __launch_bounds__(256) gather_codes_kernel(
   }
 }
 
-// The same copy from the gathered per-rank token blocks: token = flat / k of
-// all ranks' tokens lives in block token / tokens_per_rank.
-__global__ void __launch_bounds__(256) gather_codes_blocks_kernel(
-    const uint8_t* __restrict__ xq_packed, const uint8_t* __restrict__ xq_sf, int tokens_per_rank,
-    size_t sf_block_bytes, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_tiles,
-    int rows, int K, const int32_t* __restrict__ flat_of_row, const int32_t* __restrict__ row_tile,
-    const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ rows_dev, int k) {
+// The same copy from the gathered token buffer of all ranks (token = flat / k over all
+// ranks' tokens), whose scale bytes are row-major [tokens, K/16].
+__global__ void __launch_bounds__(256) gather_codes_rowsf_kernel(
+    const uint8_t* __restrict__ xq_packed, const uint8_t* __restrict__ xq_sf, uint8_t* __restrict__ packed,
+    uint8_t* __restrict__ sf_tiles, int rows, int K, const int32_t* __restrict__ flat_of_row,
+    const int32_t* __restrict__ row_tile, const int32_t* __restrict__ tile_row0,
+    const int32_t* __restrict__ rows_dev, int k) {
   const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= min(rows, *rows_dev)) return;
-  const int token_all = flat_of_row[r] / k;
-  const int owner = token_all / tokens_per_rank;
-  const int token = token_all - owner * tokens_per_rank;
+  const int token = flat_of_row[r] / k;
   const int t = row_tile[r];
   const uint32_t in_tile = static_cast<uint32_t>(r - tile_row0[t]);
   const int row_bytes = K >> 1, ntk = K >> 6;
-  const uint4* from = reinterpret_cast<const uint4*>(xq_packed + static_cast<size_t>(token_all) * row_bytes);
-  const uint8_t* from_sf = xq_sf + static_cast<size_t>(owner) * sf_block_bytes;
+  const uint4* from = reinterpret_cast<const uint4*>(xq_packed + static_cast<size_t>(token) * row_bytes);
+  const uint32_t* from_sf = reinterpret_cast<const uint32_t*>(xq_sf + static_cast<size_t>(token) * (K >> 4));
   uint4* dst = reinterpret_cast<uint4*>(packed + static_cast<size_t>(r) * row_bytes);
   for (int c = lane; c < (row_bytes >> 4); c += 32) dst[c] = __ldg(from + c);
-  for (int a = lane; a < ntk; a += 32) {
-    const uint32_t v = *reinterpret_cast<const uint32_t*>(from_sf + sf_offset(static_cast<uint32_t>(token), 4u * a, ntk));
-    *reinterpret_cast<uint32_t*>(sf_tiles + (static_cast<size_t>(t) * ntk + a) * 512u + sf_in_atom(in_tile, 0)) = v;
-  }
+  for (int a = lane; a < ntk; a += 32)
+    *reinterpret_cast<uint32_t*>(sf_tiles + (static_cast<size_t>(t) * ntk + a) * 512u + sf_in_atom(in_tile, 0)) =
+        __ldg(from_sf + a);
 }
 
 __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ packed,
@@ -263,22 +259,20 @@ cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, 
   return cudaGetLastError();
 }
 
-cudaError_t launch_gather_codes_blocks(const uint8_t* xq_packed, const uint8_t* xq_sf, int tokens_per_rank,
-                                       uint8_t* packed, uint8_t* sf_tiles, int R, int K, const int32_t* flat_of_row,
-                                       const int32_t* row_tile, const int32_t* tile_row0, const int32_t* rows_dev,
-                                       int k, cudaStream_t stream) {
+cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed,
+                                      uint8_t* sf_tiles, int R, int K, const int32_t* flat_of_row,
+                                      const int32_t* row_tile, const int32_t* tile_row0, const int32_t* rows_dev,
+                                      int k, cudaStream_t stream) {
   if (R == 0) return cudaSuccess;
-  gather_codes_blocks_kernel<<<(R + 7) / 8, 256, 0, stream>>>(
-      xq_packed, xq_sf, tokens_per_rank, static_cast<size_t>((tokens_per_rank + 127) / 128) * 128 * (K / 16),
-      packed, sf_tiles, R, K, flat_of_row, row_tile, tile_row0, rows_dev, k);
+  gather_codes_rowsf_kernel<<<(R + 7) / 8, 256, 0, stream>>>(xq_packed, xq_sf, packed, sf_tiles, R, K, flat_of_row,
+                                                             row_tile, tile_row0, rows_dev, k);
   return cudaGetLastError();
 }
 
 cudaError_t launch_publish_tokens(const uint16_t* x, const PublishTargets& dst, int M, int K, float global_scale,
                                   cudaStream_t stream) {
-  const int64_t total = static_cast<int64_t>(M) * (K / 16);
-  if (total == 0 || dst.n == 0) return cudaSuccess;
-  publish_tokens_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(x, dst, M, K, global_scale);
+  if (M == 0 || dst.n == 0) return cudaSuccess;
+  publish_tokens_kernel<<<(M + 7) / 8, 256, 0, stream>>>(x, dst, M, K, global_scale);
   return cudaGetLastError();
 }
 

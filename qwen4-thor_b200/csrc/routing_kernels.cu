@@ -170,10 +170,18 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int ma
   const int e = threadIdx.x;
   int32_t c = 0;
   if (e < E) {
-    for (int b = 0; b < nblk; ++b) {
-      const int32_t v = p.blk_counts[static_cast<size_t>(b) * E + e];
-      p.blk_counts[static_cast<size_t>(b) * E + e] = c;
-      c += v;
+    // sixteen blocks at a time: the loads of a chunk are independent, so the chain is
+    // one memory round trip per chunk instead of one per block
+    int32_t* col = p.blk_counts + e;
+    for (int b0 = 0; b0 < nblk; b0 += 16) {
+      int32_t v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = b0 + i < nblk ? col[static_cast<size_t>(b0 + i) * E] : 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (b0 + i < nblk) col[static_cast<size_t>(b0 + i) * E] = c;
+        c += v[i];
+      }
     }
     p.counts[e] = c;
   }
@@ -193,55 +201,101 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int ma
     __syncthreads();
   }
   const int32_t row_base = s_rows[e] - c, tile_base = s_tiles[e] - tiles;
+  const int32_t total_rows = s_rows[1023], total_tiles = s_tiles[1023];
+  __syncthreads();
+  s_rows[e] = row_base;   // from here on: first grouped row / first row tile of expert e
+  s_tiles[e] = tile_base;
+  __syncthreads();
   if (e < E) {
     p.offsets[e] = row_base;
     p.tile_off[e] = tile_base;
-    for (int i = 0; i < tiles; ++i) {
-      const int t = tile_base + i;
-      if (t < max_tiles) {
-        p.tile_expert[t] = e;
-        p.tile_row0[t] = row_base + i * kTileM;
-        p.tile_nrows[t] = min(kTileM, c - i * kTileM);
-      }
-    }
   }
-  if (e == E - 1) {
-    p.offsets[E] = s_rows[e];
-    p.tile_off[E] = s_tiles[e];
-    p.ntiles[0] = min(s_tiles[e], max_tiles);
+  if (e == 0) {
+    p.offsets[E] = total_rows;
+    p.tile_off[E] = total_tiles;
+    p.ntiles[0] = min(total_tiles, max_tiles);
   }
   if (e < 4 && p.status) p.status[e] = 0;
+  // The tile list, all threads together (a popular expert owns hundreds of tiles): tile t
+  // belongs to the last expert whose first tile is <= t (experts without rows share their
+  // successor's first tile and come before it).
+  for (int t = e; t < min(total_tiles, max_tiles); t += 1024) {
+    int lo = 0, hi = E - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (s_tiles[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    const int i = t - s_tiles[lo];
+    const int32_t rows_e = (lo + 1 < E ? s_rows[lo + 1] : total_rows) - s_rows[lo];
+    p.tile_expert[t] = lo;
+    p.tile_row0[t] = s_rows[lo] + i * kTileM;
+    p.tile_nrows[t] = min(kTileM, rows_e - i * kTileM);
+  }
 }
 
 __global__ void __launch_bounds__(256) plan_scatter_kernel(const int32_t* __restrict__ ids, int R, int E,
                                                            PlanTables p) {
-  extern __shared__ int32_t cursor[];  // next grouped row of each expert for this block
-  for (int e = threadIdx.x; e < E; e += blockDim.x)
-    cursor[e] = p.offsets[e] + p.blk_counts[static_cast<size_t>(blockIdx.x) * E + e];
-  __syncthreads();
+  // Each of the 8 warps owns 256 consecutive entries of the block's chunk.  A first pass
+  // counts every warp's entries per expert, a scan over the warps turns the counts into
+  // each warp's first position, and a second pass places the entries; positions follow the
+  // flat order without the warps having to take turns.
+  extern __shared__ int32_t sm[];
+  int32_t* first_row = sm;             // [E] first grouped row of the expert
+  int32_t* first_tile = sm + E;        // [E] its first row tile
+  uint16_t* wcnt = reinterpret_cast<uint16_t*>(sm + 2 * E);  // [8][E] per-warp counts, then cursors
+  int32_t* wbase = sm + 2 * E + 4 * E;  // [E] block's first grouped row of the expert
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int base = blockIdx.x * kPlanChunk;
-  for (int round = 0; round < kPlanChunk / 256; ++round) {
-    const int f = base + round * 256 + threadIdx.x;
-    const int e = f < R ? ids[f] : -1;
-    const bool valid = e >= 0 && e < E;
-    for (int w = 0; w < 8; ++w) {  // warps take turns so that positions follow the flat order
-      if (warp == w) {
-        const uint32_t peers = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);
-        if (valid) {
-          const int rank = __popc(peers & ((1u << lane) - 1u));
-          const int row = cursor[e] + rank;
-          __syncwarp(peers);
-          if (rank == 0) cursor[e] += __popc(peers);
-          p.row_of_flat[f] = row;
-          p.flat_of_row[row] = f;
-          p.row_tile[row] = p.tile_off[e] + (row - p.offsets[e]) / kTileM;
-        } else if (f < R) {
-          p.row_of_flat[f] = -1;
-        }
-      }
-      __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int32_t o = p.offsets[e];
+    first_row[e] = o;
+    first_tile[e] = p.tile_off[e];
+    wbase[e] = o + p.blk_counts[static_cast<size_t>(blockIdx.x) * E + e];
+  }
+  for (int i = threadIdx.x; i < 8 * E; i += blockDim.x) wcnt[i] = 0;
+  __syncthreads();
+  constexpr int kSeg = kPlanChunk / 8;
+  const int f0 = blockIdx.x * kPlanChunk + warp * kSeg;
+  uint16_t* mine = wcnt + warp * E;
+  int vals[kSeg / 32];
+#pragma unroll
+  for (int it = 0; it < kSeg / 32; ++it) {
+    const int f = f0 + it * 32 + lane;
+    const int v = f < R ? ids[f] : -1;
+    vals[it] = v;
+    const bool valid = v >= 0 && v < E;
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? v : -1 - lane);
+    if (valid && __popc(peers & ((1u << lane) - 1u)) == 0) mine[v] += static_cast<uint16_t>(__popc(peers));
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {  // exclusive scan over the warps
+    uint32_t c = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const uint32_t v = wcnt[w * E + e];
+      wcnt[w * E + e] = static_cast<uint16_t>(c);
+      c += v;
     }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = 0; it < kSeg / 32; ++it) {
+    const int f = f0 + it * 32 + lane;
+    const int v = vals[it];
+    const bool valid = v >= 0 && v < E;
+    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? v : -1 - lane);
+    if (valid) {
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int row = wbase[v] + mine[v] + rank;
+      __syncwarp(peers);
+      if (rank == 0) mine[v] += static_cast<uint16_t>(__popc(peers));
+      p.row_of_flat[f] = row;
+      p.flat_of_row[row] = f;
+      p.row_tile[row] = first_tile[v] + (row - first_row[v]) / kTileM;
+    } else if (f < R) {
+      p.row_of_flat[f] = -1;
+    }
+    __syncwarp();
   }
 }
 
@@ -576,7 +630,7 @@ cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const P
   const int nblk = (R + kPlanChunk - 1) / kPlanChunk;
   plan_hist_kernel<<<nblk, 256, E * sizeof(int32_t), stream>>>(ids, R, E, p.blk_counts);
   plan_scan_kernel<<<1, 1024, 0, stream>>>(nblk, E, max_tiles, p);
-  plan_scatter_kernel<<<nblk, 256, E * sizeof(int32_t), stream>>>(ids, R, E, p);
+  plan_scatter_kernel<<<nblk, 256, 7 * E * sizeof(int32_t), stream>>>(ids, R, E, p);
   return cudaGetLastError();
 }
 

@@ -209,8 +209,7 @@ class PeerBuffers:
             self.table.placement = placement.data_ptr()
             self.table.experts_total = placement.numel()
         # gathered codes, gathered scale blocks (all ranks' tokens), landing rows (own tokens)
-        self.sizes = (world * T_local * (hs // 2), world * self.lib.q4t_sf_buffer_size(T_local, hs),
-                      T_local * k * hs * 2)
+        self.sizes = (world * T_local * (hs // 2), world * T_local * (hs // 16), T_local * k * hs * 2)
         self.own = None
         self.opened = []
 

@@ -96,7 +96,7 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
     fwd(x, y_ref)
     fwd.status()
     Tl, per = T // W, E // W
-    sf_bytes = q4t.load().q4t_sf_buffer_size(Tl, hs)
+    sf_bytes = Tl * (hs // 16)
     pub = [(torch.empty((W * Tl, hs // 2), dtype=torch.uint8, device="cuda"),
             torch.zeros(W * sf_bytes, dtype=torch.uint8, device="cuda"),
             torch.full((Tl * k, hs), -1, dtype=torch.int16, device="cuda")) for _ in range(W)]
