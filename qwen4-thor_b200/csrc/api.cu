@@ -57,6 +57,9 @@ std::mutex g_dev_mutex;
 // Per-device one-time set-up: architecture check, driver entry point for the
 // tensor-map encoder, shared-memory attribute of the GEMM kernels.
 int device_state(const DeviceState** out) {
+  // every compute entry point passes here first: its first kernel follows the caller's
+  // own stream work and is launched the ordinary way
+  q4t::chain_break();
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(Q4T_ERR_DEVICE, std::string("no CUDA device: ") + cudaGetErrorString(e));
@@ -643,8 +646,10 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
     if ((e = cudaEventRecord(ds->fork_event, st)) != cudaSuccess ||
         (e = cudaStreamWaitEvent(ds->side_stream, ds->fork_event, 0)) != cudaSuccess)
       return fail_cuda("fork", e);
+    q4t::chain_break();  // first kernel behind an event wait
     if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, ds->side_stream)) != Q4T_OK) return rc;
     if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return fail_cuda("join record", e);
+    q4t::chain_break();  // back on the caller's stream, behind the caller's own work
   }
 
   // 1-2. router logits and top-k
@@ -670,6 +675,7 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
   // 4-6. shared expert
   if (fork) {
     if ((e = cudaStreamWaitEvent(st, ds->join_event, 0)) != cudaSuccess) return fail_cuda("join", e);
+    q4t::chain_break();
   } else {
     if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, st)) != Q4T_OK) return rc;
   }

@@ -9,6 +9,37 @@
 namespace q4t {
 
 constexpr int kTileM = 128;        // rows of one GEMM tile (tokens of one expert)
+// Launches `kernel` with programmatic stream serialisation: it may become resident once
+// the previous kernel's blocks have exited, and calls chain_wait() before touching global
+// memory.  Worth about 6 % of a decode step (launch and prologue of each kernel overlap
+// with the tail of the one before).  Measured: a kernel launched this way directly after a
+// cudaStreamWaitEvent did not wait for the other stream's work, hence chain_break().
+// chaining_enabled() is false when the environment variable Q4T_NO_CHAIN is set (ordinary
+// launches, for comparison runs).
+bool chaining_enabled();
+// The next launch_chained() of this thread is an ordinary launch.  Called at the start of
+// every public entry point and after every cross-stream event wait: a kernel that follows
+// anything but a kernel of this library in its stream (a copy, an event wait, a caller's
+// kernel) must keep the full stream ordering.
+void chain_break();
+bool chain_break_pending();  // reads and clears the mark
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                           Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  const bool plain = chain_break_pending();
+  cfg.numAttrs = (chaining_enabled() && !plain) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 constexpr int kPlanChunk = 2048;   // (token,slot) entries handled by one planning block
 
 // ---- quantise / dequantise (quant_kernels.cu)

@@ -139,6 +139,17 @@ __device__ __host__ __forceinline__ size_t sf_offset(uint32_t row, uint32_t grou
 }
 
 // ---------------------------------------------------------------- PTX: sync
+// ---- programmatic dependent launch: a kernel launched with launch_chained() may become
+// resident as soon as the blocks of the kernel before it in the stream have exited, before
+// that kernel's memory is flushed and its completion is processed; it must execute
+// chain_wait() before its first access to global memory (the wait returns once the earlier
+// kernel has completed and its writes are visible).  No kernel here signals its dependents
+// early: with griddepcontrol.launch_dependents issued BEFORE the kernel's own wait, a chain
+// of three kernels produced wrong results on B200 (the third no longer waited for the first),
+// and issuing it after the wait measured no faster than not issuing it at all.
+// A no-op in a kernel launched the ordinary way.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

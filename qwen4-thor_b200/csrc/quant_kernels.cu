@@ -21,6 +21,7 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(
     const int32_t* __restrict__ flat_of_row, const int32_t* __restrict__ expert_ids,
     const float* __restrict__ input_scale, const int32_t* __restrict__ row_tile,
     const int32_t* __restrict__ tile_row0, const int32_t* __restrict__ rows_dev, int k, int E) {
+  chain_wait();
   const int groups = K >> 4;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   // grouped rows past the device-side count belong to skipped (token,slot) entries
@@ -129,6 +130,7 @@ __global__ void __launch_bounds__(256) gather_codes_kernel(
     uint8_t* __restrict__ sf_tiles, int rows, int K, const int32_t* __restrict__ flat_of_row,
     const int32_t* __restrict__ row_tile, const int32_t* __restrict__ tile_row0,
     const int32_t* __restrict__ rows_dev, int k) {
+  chain_wait();
   const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= min(rows, *rows_dev)) return;
   const int token = flat_of_row[r] / k;
@@ -231,9 +233,10 @@ cudaError_t launch_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf, int
   const int64_t total = static_cast<int64_t>(M) * (K / 16);
   if (total == 0) return cudaSuccess;
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
-  quantize_rows_kernel<false><<<blocks, 256, 0, stream>>>(x, packed, sf, M, K, global_scale, nullptr,
-                                                          nullptr, nullptr, nullptr, nullptr, nullptr, 1, 0);
-  return cudaGetLastError();
+  const int32_t* no_table = nullptr;
+  const float* no_scale = nullptr;
+  return launch_chained(quantize_rows_kernel<false>, dim3(blocks), dim3(256), 0, stream, x, packed, sf, M, K,
+                        global_scale, no_table, no_table, no_scale, no_table, no_table, no_table, 1, 0);
 }
 
 cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int R,
@@ -244,19 +247,16 @@ cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* 
   const int64_t total = static_cast<int64_t>(R) * (K / 16);
   if (total == 0) return cudaSuccess;
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
-  quantize_rows_kernel<true><<<blocks, 256, 0, stream>>>(x, packed, sf_tiles, R, K, 0.0f, flat_of_row,
-                                                         expert_ids, input_scale, row_tile, tile_row0,
-                                                         rows_dev, k, E);
-  return cudaGetLastError();
+  return launch_chained(quantize_rows_kernel<true>, dim3(blocks), dim3(256), 0, stream, x, packed, sf_tiles, R, K,
+                        0.0f, flat_of_row, expert_ids, input_scale, row_tile, tile_row0, rows_dev, k, E);
 }
 
 cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed, uint8_t* sf_tiles,
                                 int R, int K, const int32_t* flat_of_row, const int32_t* row_tile,
                                 const int32_t* tile_row0, const int32_t* rows_dev, int k, cudaStream_t stream) {
   if (R == 0) return cudaSuccess;
-  gather_codes_kernel<<<(R + 7) / 8, 256, 0, stream>>>(xq_packed, xq_sf, packed, sf_tiles, R, K, flat_of_row, row_tile,
-                                                       tile_row0, rows_dev, k);
-  return cudaGetLastError();
+  return launch_chained(gather_codes_kernel, dim3((R + 7) / 8), dim3(256), 0, stream, xq_packed, xq_sf, packed,
+                        sf_tiles, R, K, flat_of_row, row_tile, tile_row0, rows_dev, k);
 }
 
 cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed,

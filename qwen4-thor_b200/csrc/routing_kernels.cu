@@ -1,4 +1,6 @@
 // Router, token->expert permutation, SwiGLU and combine kernels.
+#include <cstdlib>
+
 #include "kernels.h"
 #include "q4t_device.cuh"
 
@@ -17,6 +19,7 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const uint16_t* __r
                                                              const uint16_t* __restrict__ w,
                                                              uint16_t* __restrict__ y, int M, int N,
                                                              int K) {
+  chain_wait();
   extern __shared__ __align__(16) uint16_t s_x[];  // [M, K], loaded once per block
   const int k8 = K >> 3;
   for (int i = threadIdx.x; i < M * k8; i += 256)
@@ -137,6 +140,7 @@ __global__ void __launch_bounds__(256) topk_kernel(const uint16_t* __restrict__ 
                                                    const int32_t* __restrict__ fixed_ids,
                                                    int32_t* __restrict__ ids, float* __restrict__ rw,
                                                    int T, int E, int k) {
+  chain_wait();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (t >= T) return;
@@ -147,6 +151,7 @@ __global__ void __launch_bounds__(256) topk_kernel(const uint16_t* __restrict__ 
 // ---- permutation: stable counting sort of the (token,slot) entries by expert.
 __global__ void __launch_bounds__(256) plan_hist_kernel(const int32_t* __restrict__ ids, int R, int E,
                                                         int32_t* __restrict__ blk_counts) {
+  chain_wait();
   extern __shared__ int32_t hist[];
   for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
   __syncthreads();
@@ -165,6 +170,7 @@ __global__ void __launch_bounds__(256) plan_hist_kernel(const int32_t* __restric
 // One block of 1024 threads, E <= 1024.  Turns the per-block counts into
 // per-block bases, builds offsets[E+1], the row-tile list and its count.
 __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int max_tiles, PlanTables p) {
+  chain_wait();
   __shared__ int32_t s_rows[1024];
   __shared__ int32_t s_tiles[1024];
   const int e = threadIdx.x;
@@ -235,6 +241,7 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int ma
 
 __global__ void __launch_bounds__(256) plan_scatter_kernel(const int32_t* __restrict__ ids, int R, int E,
                                                            PlanTables p) {
+  chain_wait();
   // Each of the 8 warps owns 256 consecutive entries of the block's chunk.  A first pass
   // counts every warp's entries per expert, a scan over the warps turns the counts into
   // each warp's first position, and a second pass places the entries; positions follow the
@@ -312,6 +319,7 @@ __global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* ids, in
                                                           PlanTables p, const uint16_t* __restrict__ logits,
                                                           const int32_t* __restrict__ fixed_ids, int32_t* ids_out,
                                                           float* rw_out, int T, int k, int E_logits) {
+  chain_wait();
   extern __shared__ uint16_t s_cnt[];  // [32][E]: counts, later exclusive bases, then cursors
   __shared__ int32_t s_rows[1024];
   __shared__ int32_t s_tiles[1024];
@@ -482,6 +490,7 @@ __global__ void __launch_bounds__(256) routed_combine_kernel(const uint16_t* __r
                                                              const int32_t* __restrict__ row_of_flat,
                                                              const float* __restrict__ rw,
                                                              float* __restrict__ y, int T, int k, int hs) {
+  chain_wait();
   const int per_row = hs >> 3;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<int64_t>(T) * per_row) return;
@@ -512,6 +521,7 @@ __global__ void __launch_bounds__(256) routed_combine_kernel(const uint16_t* __r
 // out[t, c] = bf16((g * sigmoid(g)) * u) (SwiGLUKernel, src/model/moe.cu:276-287).
 __global__ void __launch_bounds__(256) swiglu_kernel(const uint16_t* __restrict__ gu,
                                                      uint16_t* __restrict__ out, int T, int inner) {
+  chain_wait();
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<int64_t>(T) * inner) return;
   const int t = static_cast<int>(idx / inner), c = static_cast<int>(idx % inner);
@@ -525,11 +535,16 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const uint16_t* __restrict_
 // sigmoid(x . gate_scalar) with the reference's 256 strided fused partials and
 // halving tree, y = bf16(fma(gate, shared_down, routed)) (MoECombineKernel,
 // src/model/moe.cu:291-321).  Also leaves the fp32 routed sum in `routed`.
+// PRELOAD: request all of the token's rows before the first is used (k <= 16), so that the
+// slot-order sum costs one memory round trip instead of k: 3 us of a 13 us decode launch; at
+// 16 K tokens the extra registers cost more than the latency they hide (254 vs 175 us).
+template <bool PRELOAD>
 __global__ void __launch_bounds__(256) final_combine_kernel(
     const uint16_t* __restrict__ dn_out, const int32_t* __restrict__ row_of_flat,
     const float* __restrict__ rw, const uint16_t* __restrict__ shared_down,
     const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate_scalar,
     float* __restrict__ routed, uint16_t* __restrict__ y, int T, int k, int hs) {
+  chain_wait();
   __shared__ float part[256];
   __shared__ int s_row[16];
   __shared__ float s_w[16];
@@ -552,16 +567,36 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
     float a[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = 0.0f;
-    for (int s = 0; s < k; ++s) {
-      const int r = s_row[s];
-      if (r < 0) continue;
-      const float wgt = s_w[s];
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(r) * hs) + c8);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    if constexpr (PRELOAD) {
+      uint4 v[16];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        a[2 * j] = fmaf(wgt, bf16x2_lo(w[j]), a[2 * j]);
-        a[2 * j + 1] = fmaf(wgt, bf16x2_hi(w[j]), a[2 * j + 1]);
+      for (int s = 0; s < 16; ++s)
+        if (s < k && s_row[s] >= 0)
+          v[s] = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(s_row[s]) * hs) + c8);
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {
+        if (s < k && s_row[s] >= 0) {
+          const float wgt = s_w[s];
+          const uint32_t w[4] = {v[s].x, v[s].y, v[s].z, v[s].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            a[2 * j] = fmaf(wgt, bf16x2_lo(w[j]), a[2 * j]);
+            a[2 * j + 1] = fmaf(wgt, bf16x2_hi(w[j]), a[2 * j + 1]);
+          }
+        }
+      }
+    } else {
+      for (int s = 0; s < k; ++s) {
+        const int r = s_row[s];
+        if (r < 0) continue;
+        const float wgt = s_w[s];
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(r) * hs) + c8);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          a[2 * j] = fmaf(wgt, bf16x2_lo(w[j]), a[2 * j]);
+          a[2 * j + 1] = fmaf(wgt, bf16x2_hi(w[j]), a[2 * j + 1]);
+        }
       }
     }
 #pragma unroll
@@ -595,43 +630,58 @@ cudaError_t routing_set_attributes() {
   return cudaFuncSetAttribute(small_m_linear_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304);
 }
 
+bool chaining_enabled() {
+  static const bool on = getenv("Q4T_NO_CHAIN") == nullptr;
+  return on;
+}
+namespace {
+thread_local bool t_chain_break = true;  // a thread's first launch is an ordinary one
+}
+void chain_break() { t_chain_break = true; }
+bool chain_break_pending() {
+  const bool v = t_chain_break;
+  t_chain_break = false;
+  return v;
+}
+
 cudaError_t launch_small_m_linear(const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
                                   int K, cudaStream_t stream) {
-  const unsigned blocks = static_cast<unsigned>((N + 7) / 8);
+  const dim3 blocks(static_cast<unsigned>((N + 7) / 8)), threads(256);
   const size_t smem = static_cast<size_t>(M) * K * sizeof(uint16_t);
-  if (M <= 1) small_m_linear_kernel<1><<<blocks, 256, smem, stream>>>(x, w, y, M, N, K);
-  else if (M <= 4) small_m_linear_kernel<4><<<blocks, 256, smem, stream>>>(x, w, y, M, N, K);
-  else small_m_linear_kernel<8><<<blocks, 256, smem, stream>>>(x, w, y, M, N, K);
-  return cudaGetLastError();
+  if (M <= 1) return launch_chained(small_m_linear_kernel<1>, blocks, threads, smem, stream, x, w, y, M, N, K);
+  if (M <= 4) return launch_chained(small_m_linear_kernel<4>, blocks, threads, smem, stream, x, w, y, M, N, K);
+  return launch_chained(small_m_linear_kernel<8>, blocks, threads, smem, stream, x, w, y, M, N, K);
 }
 
 cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw,
                         int T, int E, int k, cudaStream_t stream) {
-  topk_kernel<<<static_cast<unsigned>((T + 7) / 8), 256, 0, stream>>>(logits, fixed_ids, ids, rw, T, E, k);
-  return cudaGetLastError();
+  return launch_chained(topk_kernel, dim3(static_cast<unsigned>((T + 7) / 8)), dim3(256), 0, stream, logits, fixed_ids,
+                        ids, rw, T, E, k);
 }
 
 bool route_and_plan_fits(int T, int k) { return T * k <= kPlanSmallMax && T <= 16; }
 
 cudaError_t launch_route_and_plan(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw, int T,
                                   int E, int k, int max_tiles, const PlanTables& p, cudaStream_t stream) {
-  plan_small_kernel<true><<<1, 1024, 32 * E * sizeof(uint16_t), stream>>>(nullptr, T * k, E, max_tiles, p, logits,
-                                                                          fixed_ids, ids, rw, T, k, E);
-  return cudaGetLastError();
+  return launch_chained(plan_small_kernel<true>, dim3(1), dim3(1024), 32 * E * sizeof(uint16_t), stream,
+                        static_cast<const int32_t*>(nullptr), T * k, E, max_tiles, p, logits, fixed_ids, ids, rw, T, k,
+                        E);
 }
 
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
                         cudaStream_t stream) {
-  if (R <= kPlanSmallMax) {
-    plan_small_kernel<false><<<1, 1024, 32 * E * sizeof(uint16_t), stream>>>(ids, R, E, max_tiles, p, nullptr, nullptr,
-                                                                             nullptr, nullptr, 0, 0, 0);
-    return cudaGetLastError();
-  }
+  if (R <= kPlanSmallMax)
+    return launch_chained(plan_small_kernel<false>, dim3(1), dim3(1024), 32 * E * sizeof(uint16_t), stream, ids, R, E,
+                          max_tiles, p, static_cast<const uint16_t*>(nullptr), static_cast<const int32_t*>(nullptr),
+                          static_cast<int32_t*>(nullptr), static_cast<float*>(nullptr), 0, 0, 0);
   const int nblk = (R + kPlanChunk - 1) / kPlanChunk;
-  plan_hist_kernel<<<nblk, 256, E * sizeof(int32_t), stream>>>(ids, R, E, p.blk_counts);
-  plan_scan_kernel<<<1, 1024, 0, stream>>>(nblk, E, max_tiles, p);
-  plan_scatter_kernel<<<nblk, 256, 7 * E * sizeof(int32_t), stream>>>(ids, R, E, p);
-  return cudaGetLastError();
+  cudaError_t e;
+  if ((e = launch_chained(plan_hist_kernel, dim3(nblk), dim3(256), E * sizeof(int32_t), stream, ids, R, E,
+                          p.blk_counts)) != cudaSuccess)
+    return e;
+  if ((e = launch_chained(plan_scan_kernel, dim3(1), dim3(1024), 0, stream, nblk, E, max_tiles, p)) != cudaSuccess)
+    return e;
+  return launch_chained(plan_scatter_kernel, dim3(nblk), dim3(256), 7 * E * sizeof(int32_t), stream, ids, R, E, p);
 }
 
 cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_per_rank, int32_t* dest,
@@ -668,24 +718,25 @@ cudaError_t launch_routed_combine(const uint16_t* dn_out, const int32_t* row_of_
                                   const float* rw, float* y, int T, int k, int hs,
                                   cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(T) * (hs / 8);
-  routed_combine_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
-      dn_out, row_of_flat, rw, y, T, k, hs);
-  return cudaGetLastError();
+  return launch_chained(routed_combine_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream,
+                        dn_out, row_of_flat, rw, y, T, k, hs);
 }
 
 cudaError_t launch_swiglu(const uint16_t* gu, uint16_t* out, int T, int inner, cudaStream_t stream) {
   const int64_t total = static_cast<int64_t>(T) * inner;
-  swiglu_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(gu, out, T, inner);
-  return cudaGetLastError();
+  return launch_chained(swiglu_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, gu, out,
+                        T, inner);
 }
 
 cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,
                                  const uint16_t* shared_down, const uint16_t* x,
                                  const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
                                  int k, int hs, cudaStream_t stream) {
-  final_combine_kernel<<<T, 256, 0, stream>>>(dn_out, row_of_flat, rw, shared_down, x, gate_scalar,
-                                              routed, y, T, k, hs);
-  return cudaGetLastError();
+  if (T <= 1024)
+    return launch_chained(final_combine_kernel<true>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
+                          shared_down, x, gate_scalar, routed, y, T, k, hs);
+  return launch_chained(final_combine_kernel<false>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
+                        shared_down, x, gate_scalar, routed, y, T, k, hs);
 }
 
 }  // namespace q4t

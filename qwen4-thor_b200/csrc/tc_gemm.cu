@@ -107,6 +107,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
+  // Barriers, tensor memory and descriptors are set up (possibly while the previous kernel
+  // of the stream was still draining); from here on the kernel reads what that kernel wrote.
+  chain_wait();
 
   const int m_tiles = args.ntiles_dev ? *args.ntiles_dev : args.ntiles_host;
   const int total_tiles = m_tiles * args.n_tiles;
@@ -536,25 +539,20 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs&
   if (grid <= 0) return cudaSuccess;
   switch (epi) {
     case Epilogue::kStoreBf16:
-      gemm_kernel<NVF4, Epilogue::kStoreBf16, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
-      break;
+      return launch_chained(gemm_kernel<NVF4, Epilogue::kStoreBf16, BN>, dim3(grid), dim3(kThreads), smem, stream, ta, tb, a);
     case Epilogue::kStoreF32:
-      gemm_kernel<NVF4, Epilogue::kStoreF32, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
-      break;
+      return launch_chained(gemm_kernel<NVF4, Epilogue::kStoreF32, BN>, dim3(grid), dim3(kThreads), smem, stream, ta, tb, a);
     case Epilogue::kSwigluBf16:
-      gemm_kernel<NVF4, Epilogue::kSwigluBf16, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
-      break;
+      return launch_chained(gemm_kernel<NVF4, Epilogue::kSwigluBf16, BN>, dim3(grid), dim3(kThreads), smem, stream, ta, tb, a);
     case Epilogue::kSwigluQuant:
       if constexpr (NVF4) {
-        gemm_kernel<NVF4, Epilogue::kSwigluQuant, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
-        break;
+        return launch_chained(gemm_kernel<NVF4, Epilogue::kSwigluQuant, BN>, dim3(grid), dim3(kThreads), smem, stream, ta, tb, a);
       } else {
         return cudaErrorInvalidValue;
       }
     case Epilogue::kStoreBf16Rows:
       if constexpr (NVF4) {
-        gemm_kernel<NVF4, Epilogue::kStoreBf16Rows, BN><<<grid, kThreads, smem, stream>>>(ta, tb, a);
-        break;
+        return launch_chained(gemm_kernel<NVF4, Epilogue::kStoreBf16Rows, BN>, dim3(grid), dim3(kThreads), smem, stream, ta, tb, a);
       } else {
         return cudaErrorInvalidValue;
       }
