@@ -62,18 +62,22 @@ class ClockSampler:
         self.index, self.rows, self.proc, self.period = index, [], None, period_s
         self.stop = threading.Event()
         self.thread = None
+        self.nvml = None
 
-    def _nvml_loop(self, nv, h):
+    def _nvml_sample(self):
+        nv, h = self.nvml
         bits = (nv.nvmlClocksThrottleReasonHwSlowdown, nv.nvmlClocksThrottleReasonHwThermalSlowdown,
                 nv.nvmlClocksThrottleReasonSwThermalSlowdown, nv.nvmlClocksThrottleReasonSwPowerCap)
-        mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        try:
+            sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+            mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+            self.rows.append([str(sm), str(self.max_mhz)] + ["Active" if mask & b else "Not Active" for b in bits])
+        except Exception:   # a failed query is a missing sample, nothing more
+            pass
+
+    def _nvml_loop(self):
         while not self.stop.is_set():
-            try:
-                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
-                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                self.rows.append([str(sm), str(mx)] + ["Active" if mask & b else "Not Active" for b in bits])
-            except Exception:   # a failed query is a missing sample, nothing more
-                pass
+            self._nvml_sample()
             self.stop.wait(self.period)
 
     def __enter__(self):
@@ -81,7 +85,9 @@ class ClockSampler:
             import pynvml as nv
             nv.nvmlInit()
             h = nv.nvmlDeviceGetHandleByIndex(self.index)
-            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.nvml = (nv, h)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
             self.thread.start()
             return self
         except Exception:
@@ -101,6 +107,8 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def __exit__(self, *a):
+        if self.nvml is not None:
+            self._nvml_sample()   # the region has just ended: the GPU is still at its load clocks
         self.stop.set()
         if self.proc is not None:
             self.proc.terminate()

@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "q4t/quant/moe_gemm.h"
+#include "q4t/io/weight_loader.h"
 #include "q4t/quant/moe_weights.h"
 #include "q4t/status.h"
 #include "q4t_moe_b200.h"
@@ -31,6 +32,43 @@ struct MoEExtraWeights {
   }
   q4t_extra_weights Abi() const { return q4t_extra_weights{E, hs, shared_is, gate, shared_gu, shared_down, shared_gate_scalar}; }
 };
+
+// Router and shared-expert BF16 weights of one layer from the checkpoint (reference
+// src/model/moe.cu:344-398): `prefix`.gate.weight [E,hs], .shared_expert.{gate,up,down}_proj
+// .weight (gate rows first, then up rows, in shared_gu), .shared_expert_gate.weight [1,hs].
+// A tensor of another byte size is refused.  No FP8 shadows.
+inline Status LoadMoEExtra(const io::WeightLoader& loader, const std::string& prefix, int E, int hs, int shared_is,
+                           MoEExtraWeights* out, cudaStream_t stream) {
+  if (E <= 0 || hs <= 0 || shared_is <= 0) return Status::Fail("bad dims");
+  out->E = E;
+  out->hs = hs;
+  out->shared_is = shared_is;
+  const size_t gate_b = static_cast<size_t>(E) * hs * 2, proj_b = static_cast<size_t>(shared_is) * hs * 2;
+  const size_t scalar_b = static_cast<size_t>(hs) * 2;
+  if (cudaMalloc(reinterpret_cast<void**>(&out->gate), gate_b) != cudaSuccess ||
+      cudaMalloc(reinterpret_cast<void**>(&out->shared_gu), 2 * proj_b) != cudaSuccess ||
+      cudaMalloc(reinterpret_cast<void**>(&out->shared_down), proj_b) != cudaSuccess ||
+      cudaMalloc(reinterpret_cast<void**>(&out->shared_gate_scalar), scalar_b) != cudaSuccess)
+    return Status::Fail("cudaMalloc failed");
+  std::vector<uint8_t> host;
+  auto load = [&](const std::string& name, uint16_t* dst, size_t bytes) {
+    host.resize(bytes);
+    Status s = loader.ReadTensor(name, host.data(), bytes);
+    if (!s.ok()) return s;
+    // the staging buffer is reused by the next tensor: finish the copy first
+    if (cudaMemcpyAsync(dst, host.data(), bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess)
+      return Status::Fail("upload failed: " + name);
+    return Status();
+  };
+  Status s;
+  if (!(s = load(prefix + ".gate.weight", out->gate, gate_b)).ok()) return s;
+  if (!(s = load(prefix + ".shared_expert.gate_proj.weight", out->shared_gu, proj_b)).ok()) return s;
+  if (!(s = load(prefix + ".shared_expert.up_proj.weight", out->shared_gu + static_cast<size_t>(shared_is) * hs, proj_b)).ok())
+    return s;
+  if (!(s = load(prefix + ".shared_expert.down_proj.weight", out->shared_down, proj_b)).ok()) return s;
+  return load(prefix + ".shared_expert_gate.weight", out->shared_gate_scalar, scalar_b);
+}
 
 struct MoEForwardDiagnostics {
   bool partition_requested = false, partition_applied = false, partition_fallback = false;

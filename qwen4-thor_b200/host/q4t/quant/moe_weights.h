@@ -8,8 +8,10 @@
 
 #include <cstdint>
 #include <string>
+#include <type_traits>
 #include <vector>
 
+#include "q4t/io/weight_loader.h"
 #include "q4t/quant/swizzle.h"
 #include "q4t/status.h"
 #include "q4t_moe_b200.h"
@@ -58,7 +60,8 @@ inline std::string MoEExpertTensorName(int layer, int e, const char* proj, const
 
 // Loads one layer's experts through `read`; on success the caller owns the eight
 // device buffers of `out` (cudaFree).  Gate and up share gate's two scalars.
-template <class ReadTensor>
+template <class ReadTensor,
+          std::enable_if_t<std::is_invocable_r_v<bool, ReadTensor&, const std::string&, void*, size_t>, int> = 0>
 Status LoadMoEWeights(ReadTensor&& read, int layer_id, int E, int hs, int moe_is, MoEWeightLayout* out,
                       cudaStream_t stream) {
   if (E <= 0 || hs <= 0 || moe_is <= 0) return Status::Fail("invalid MoE dims");
@@ -120,6 +123,49 @@ Status LoadMoEWeights(ReadTensor&& read, int layer_id, int E, int hs, int moe_is
       cudaStreamSynchronize(stream) != cudaSuccess)
     return Status::Fail("scale upload failed");
   return Status();
+}
+
+// The consumer's NVFP4 layout, checked on the checkpoint's metadata before anything is
+// allocated or read (reference include/q4t/quant/moe_tensor_contract.h:11-48): per expert
+// and projection a U8 weight [rows, cols/2], an F8_E4M3 weight_scale [rows, cols/16] and
+// two FP32 scalars (rank 0 or a one-element vector).
+inline Status ValidateMoEExpert(const io::WeightLoader& loader, int layer, int expert, int hs, int moe_is) {
+  for (const char* proj : {"down_proj", "gate_proj", "up_proj"}) {
+    const bool down = proj[0] == 'd';
+    const int64_t rows = down ? hs : moe_is, cols = down ? moe_is : hs;
+    for (const char* suffix : {"weight", "weight_scale", "weight_scale_2", "input_scale"}) {
+      const std::string name = MoEExpertTensorName(layer, expert, proj, suffix);
+      const io::TensorInfo* t = loader.FindTensor(name);
+      if (!t) return Status::Fail("missing MoE tensor: " + name);
+      const std::string kind(suffix);
+      if (kind == "weight" || kind == "weight_scale") {
+        const int64_t width = cols / (kind == "weight" ? 2 : 16);
+        const io::Dtype want = kind == "weight" ? io::Dtype::kU8 : io::Dtype::kF8E4M3;
+        if (t->dtype != want || t->shape.size() != 2 || t->shape[0] != rows || t->shape[1] != width ||
+            t->byte_size() != static_cast<uint64_t>(rows * width))
+          return Status::Fail("MoE tensor dtype/shape/size mismatch: " + name);
+      } else {
+        const bool scalar = t->shape.empty() || (t->shape.size() == 1 && t->shape[0] == 1);
+        if (t->dtype != io::Dtype::kF32 || !scalar || t->byte_size() != sizeof(float))
+          return Status::Fail("MoE scalar dtype/shape/size mismatch: " + name);
+      }
+    }
+  }
+  return Status();
+}
+
+// The engine's own signature (reference include/q4t/quant/moe_weights.h:121-123): every
+// expert's metadata is validated first, then the tensors are read through the loader.
+inline Status LoadMoEWeights(const io::WeightLoader& loader, int layer_id, int E, int hs, int moe_is,
+                             MoEWeightLayout* out, cudaStream_t stream) {
+  if (E <= 0 || hs <= 0 || moe_is <= 0) return Status::Fail("invalid MoE dims");
+  for (int e = 0; e < E; ++e) {
+    Status s = ValidateMoEExpert(loader, layer_id, e, hs, moe_is);
+    if (!s.ok()) return s;
+  }
+  return LoadMoEWeights(
+      [&](const std::string& name, void* dst, size_t bytes) { return loader.ReadTensor(name, dst, bytes).ok(); },
+      layer_id, E, hs, moe_is, out, stream);
 }
 
 }  // namespace q4t::quant
