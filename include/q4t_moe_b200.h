@@ -363,6 +363,15 @@ int32_t q4t_moe_expert_peer(const int32_t* ids_all, const q4t_ep_peer_table* pee
 int32_t q4t_ep_flat_rows(const int32_t* expert_ids, int32_t rows, int32_t E,
                          int32_t* row_of_flat, void* stream);
 
+/* ---- the step between two layers of a decode stack (the 48-layer harness):
+ * x <- bf16(x + y) in place (fp32 add, one rounding; y may be NULL), then
+ * h <- x * rsqrt(mean(x^2) + eps) in bf16, no learned weight.  Summation order
+ * of GroupedRmsNormKernel (src/model/hyperconnection.cu:55-110) with the
+ * correctly rounded reciprocal square root in place of rsqrtf.  x, y, h: bf16
+ * [T, hs], 16-byte aligned; hs a multiple of 8.                                */
+int32_t q4t_residual_rmsnorm_bf16(uint16_t* x, const uint16_t* y, uint16_t* h,
+                                  int32_t T, int32_t hs, float eps, void* stream);
+
 /* Reads the kernel status words of a workspace after the stream has been
  * synchronised by the caller: 0 = clean, otherwise a bounded device-side wait
  * ran out (the output is then undefined).  Copies with cudaMemcpy.            */

@@ -309,5 +309,17 @@ def rmsnorm_bf16(x, eps: float = 1e-6):
     return out
 
 
+def residual_rmsnorm_bf16(x, y, eps: float = 1e-6):
+    """Returns (bf16(x + y), RMSNorm of that); y may be None (norm only).  Follows
+    q4o_residual_rmsnorm_bf16."""
+    x = np.array(x, np.uint16, copy=True, order="C")
+    T, hs = x.shape
+    h = np.empty_like(x)
+    yp = None if y is None else _p(np.ascontiguousarray(y, np.uint16), C.c_uint16)
+    lib().q4o_residual_rmsnorm_bf16(_p(x, C.c_uint16), yp, C.c_int(T), C.c_int(hs), C.c_float(eps),
+                                    _p(h, C.c_uint16))
+    return x, h
+
+
 def num_threads() -> int:
     return int(lib().q4o_num_threads())

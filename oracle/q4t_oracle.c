@@ -722,18 +722,51 @@ int q4o_moe_forward(const uint16_t* x, const q4o_layer* L, int T, int k,
   return rc;
 }
 
+/* RMSNorm of bf16 rows without a learned weight, in the summation order of the reference's
+ * GroupedRmsNormKernel (src/model/hyperconnection.cu:55-110): one warp per row, lane l sums
+ * the squares of elements [8i, 8i+8) for i = l, l+32, ... (eight fused multiply-adds per
+ * group, then one add into the lane's partial), the 32 partials are combined by the xor
+ * butterfly 16, 8, 4, 2, 1, and the row is scaled by 1/sqrt(mean + eps).  The device code of
+ * the reference uses rsqrtf (approximate, not reproducible on a host); the correctly rounded
+ * reciprocal square root stands in for it here and in the CUDA path (at most 2 ulp apart). */
 void q4o_rmsnorm_bf16(const uint16_t* x, int T, int hs, float eps, uint16_t* out) {
+  const int n8 = hs / 8;
   for (int t = 0; t < T; ++t) {
-    float ss = 0.0f;
-    for (int c = 0; c < hs; ++c) {
-      const float v = q4o_bf16_to_float(x[(size_t)t * hs + c]);
-      ss += v * v;
+    const uint16_t* row = x + (size_t)t * hs;
+    float part[32];
+    for (int l = 0; l < 32; ++l) {
+      float acc = 0.0f;
+      for (int i = l; i < n8; i += 32) {
+        float s = 0.0f;
+        for (int j = 0; j < 8; ++j) {
+          const float v = q4o_bf16_to_float(row[8 * i + j]);
+          s = fmaf(v, v, s);
+        }
+        acc += s;
+      }
+      for (int i = n8 * 8 + l; i < hs; i += 32) {
+        const float v = q4o_bf16_to_float(row[i]);
+        acc = fmaf(v, v, acc);
+      }
+      part[l] = acc;
     }
-    const float r = 1.0f / sqrtf(ss / (float)hs + eps);
-    for (int c = 0; c < hs; ++c)
-      out[(size_t)t * hs + c] =
-          q4o_float_to_bf16(q4o_bf16_to_float(x[(size_t)t * hs + c]) * r);
+    for (int off = 16; off > 0; off >>= 1) {
+      float next[32];
+      for (int l = 0; l < 32; ++l) next[l] = part[l] + part[l ^ off];
+      memcpy(part, next, sizeof(part));
+    }
+    const float r = 1.0f / sqrtf(part[0] / (float)hs + eps);
+    for (int c = 0; c < hs; ++c) out[(size_t)t * hs + c] = q4o_float_to_bf16(q4o_bf16_to_float(row[c]) * r);
   }
+}
+
+/* x <- bf16(x + y) (fp32 add, one rounding), then h <- RMSNorm(x): the step between two
+ * layers of the decode stack.  y may be NULL (first layer: only the norm). */
+void q4o_residual_rmsnorm_bf16(uint16_t* x, const uint16_t* y, int T, int hs, float eps, uint16_t* h) {
+  if (y)
+    for (size_t i = 0; i < (size_t)T * hs; ++i)
+      x[i] = q4o_float_to_bf16(q4o_bf16_to_float(x[i]) + q4o_bf16_to_float(y[i]));
+  q4o_rmsnorm_bf16(x, T, hs, eps, h);
 }
 
 int q4o_num_threads(void) {

@@ -164,6 +164,7 @@ int q4o_moe_forward(const uint16_t* x, const q4o_layer* L, int T, int k,
  * (src/model/hyperconnection.cu:55-110): bf16(x * rsqrt(mean(x^2)+eps)).     */
 void q4o_rmsnorm_bf16(const uint16_t* x, int T, int hs, float eps,
                       uint16_t* out);
+void q4o_residual_rmsnorm_bf16(uint16_t* x, const uint16_t* y, int T, int hs, float eps, uint16_t* h);
 
 int q4o_num_threads(void);
 

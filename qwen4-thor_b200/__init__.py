@@ -64,7 +64,7 @@ EXPORTS = [
     "q4t_selftest_encoders", "q4t_stage_timing_enable", "q4t_stage_timing_read",
     "q4t_moe_routed_forward_noalloc", "q4t_ep_dispatch_workspace_bytes", "q4t_ep_dispatch",
     "q4t_moe_expert_rows", "q4t_moe_finish_workspace_bytes", "q4t_moe_finish",
-    "q4t_moe_shared_expert", "q4t_moe_combine",
+    "q4t_moe_shared_expert", "q4t_moe_combine", "q4t_residual_rmsnorm_bf16",
     "q4t_peer_buffer_alloc", "q4t_peer_buffer_free", "q4t_peer_buffer_export", "q4t_peer_buffer_open",
     "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
 ]
@@ -121,6 +121,7 @@ def load():
     L.q4t_peer_buffer_close.argtypes = [vp]
     L.q4t_moe_shared_expert.argtypes = [vp, C.POINTER(ExtraWeights), i32, vp, sz, vp]
     L.q4t_moe_combine.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, sz, vp]
+    L.q4t_residual_rmsnorm_bf16.argtypes = [vp, vp, vp, i32, i32, f32, vp]
     L.q4t_ep_publish.argtypes = [vp, C.POINTER(EpPeerTable), i32, f32, vp]
     L.q4t_moe_expert_peer_workspace_bytes.restype = C.c_size_t
     L.q4t_moe_expert_peer_workspace_bytes.argtypes = [i32] * 5
@@ -335,6 +336,42 @@ class MoEForward:
 
 STAGES = ("router_logits", "topk", "permutation", "gather_quantise", "gate_up_gemm", "down_gemm",
           "shared_expert", "combine")
+
+
+def residual_rmsnorm(x, y, h, eps: float = 1e-6, stream=None):
+    """x <- bf16(x + y) in place (y may be None), h <- RMSNorm(x): the step between two
+    layers of a decode stack.  x, y, h: CUDA bf16 [T, hs]."""
+    T, hs = x.shape
+    check(load().q4t_residual_rmsnorm_bf16(_ptr(x), _ptr(y), _ptr(h), T, hs, float(eps), _stream_ptr(stream)))
+    return h
+
+
+class DecodeStack:
+    """L MoE layers applied as x <- bf16(x + MoE_l(RMSNorm(x))), the decode-stack harness
+    (eps 1e-6, no norm weight).  One workspace is shared by all layers."""
+
+    def __init__(self, layers, T: int, k: int, eps: float = 1e-6, device="cuda"):
+        import torch
+        self.layers, self.T, self.k, self.eps = layers, T, k, eps
+        self.fwd = MoEForward(layers[0], T, k, device)
+        hs = layers[0].hs
+        self.h = torch.empty((T, hs), dtype=torch.bfloat16, device=device)
+        self.y = torch.empty((T, hs), dtype=torch.bfloat16, device=device)
+
+    def __call__(self, x, stream=None):
+        """Runs the stack in place on x (bf16 [T, hs]); returns x."""
+        L = load()
+        sp = _stream_ptr(stream)
+        fw = self.fwd
+        for i, layer in enumerate(self.layers):
+            check(L.q4t_residual_rmsnorm_bf16(_ptr(x), _ptr(self.y) if i else None, _ptr(self.h), self.T,
+                                              layer.hs, float(self.eps), sp))
+            check(L.q4t_moe_forward(_ptr(self.h), C.byref(layer.routed), C.byref(layer.extra), _ptr(self.y), self.T,
+                                    self.k, _ptr(fw.ws), fw.ws.numel(), None, 0, sp))
+        # the last layer's output joins the residual stream
+        check(L.q4t_residual_rmsnorm_bf16(_ptr(x), _ptr(self.y), _ptr(self.h), self.T, self.layers[0].hs,
+                                          float(self.eps), sp))
+        return x
 
 
 def stage_timing(enable: bool) -> None:

@@ -999,6 +999,20 @@ int32_t q4t_ep_flat_rows(const int32_t* expert_ids, int32_t rows, int32_t E, int
   return e == cudaSuccess ? Q4T_OK : fail_cuda("flat rows launch", e);
 }
 
+int32_t q4t_residual_rmsnorm_bf16(uint16_t* x, const uint16_t* y, uint16_t* h, int32_t T, int32_t hs, float eps,
+                                  void* stream) {
+  if (T <= 0) return Q4T_OK;
+  if (!x || !h) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (hs <= 0 || hs % 8) return fail(Q4T_ERR_INVALID, "hs must be a multiple of 8");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(h)) & 15u)
+    return fail(Q4T_ERR_INVALID, "rows must be 16-byte aligned");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  cudaError_t e = q4t::launch_residual_rmsnorm(x, y, h, T, hs, eps, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("rmsnorm launch", e);
+}
+
 int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k, int32_t hs, int32_t moe_is,
                                  int32_t E) {
   if (!workspace || M <= 0 || k <= 0) return fail(Q4T_ERR_INVALID, "invalid arguments");

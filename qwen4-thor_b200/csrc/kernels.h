@@ -122,6 +122,9 @@ cudaError_t launch_routed_combine(const uint16_t* dn_out, const int32_t* row_of_
                                   const float* rw, float* y, int T, int k, int hs,
                                   cudaStream_t stream);
 cudaError_t launch_swiglu(const uint16_t* gu, uint16_t* out, int T, int inner, cudaStream_t stream);
+// x <- bf16(x + y) (y may be null), h <- RMSNorm(x) without a weight; hs % 8 == 0.
+cudaError_t launch_residual_rmsnorm(uint16_t* x, const uint16_t* y, uint16_t* h, int T, int hs, float eps,
+                                    cudaStream_t stream);
 cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,
                                  const uint16_t* shared_down, const uint16_t* x,
                                  const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,

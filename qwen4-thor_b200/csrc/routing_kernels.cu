@@ -531,6 +531,57 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const uint16_t* __restrict_
   out[idx] = f32_to_bf16((g * sig) * u);
 }
 
+// The step between two layers of a decode stack: x <- bf16(x + y) (y may be null), then
+// h <- x * rsqrt(mean(x^2) + eps) in bf16.  One warp per row, the summation order of
+// GroupedRmsNormKernel (src/model/hyperconnection.cu:55-110): lane l sums the squares of the
+// 8-element groups l, l+32, ... (eight fused multiply-adds per group, one add per group),
+// xor butterfly over the lanes; the reciprocal square root is the correctly rounded one
+// (the reference's rsqrtf is within 2 ulp of it).  hs a multiple of 8.
+__global__ void __launch_bounds__(256) residual_rmsnorm_kernel(uint16_t* __restrict__ x,
+                                                               const uint16_t* __restrict__ y,
+                                                               uint16_t* __restrict__ h, int T, int hs, float eps) {
+  chain_wait();
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const int n8 = hs >> 3;
+  uint4* xr = reinterpret_cast<uint4*>(x + static_cast<size_t>(t) * hs);
+  const uint4* yr = y ? reinterpret_cast<const uint4*>(y + static_cast<size_t>(t) * hs) : nullptr;
+  uint4* hr = reinterpret_cast<uint4*>(h + static_cast<size_t>(t) * hs);
+  float acc = 0.0f;
+  for (int i = lane; i < n8; i += 32) {
+    uint4 v = xr[i];
+    if (yr) {
+      const uint4 w = yr[i];
+      const uint32_t a[4] = {v.x, v.y, v.z, v.w}, b[4] = {w.x, w.y, w.z, w.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = f32x2_to_bf16x2(bf16x2_lo(a[j]) + bf16x2_lo(b[j]), bf16x2_hi(a[j]) + bf16x2_hi(b[j]));
+      v = make_uint4(o[0], o[1], o[2], o[3]);
+      xr[i] = v;
+    }
+    const uint32_t a[4] = {v.x, v.y, v.z, v.w};
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      s = fmaf(bf16x2_lo(a[j]), bf16x2_lo(a[j]), s);
+      s = fmaf(bf16x2_hi(a[j]), bf16x2_hi(a[j]), s);
+    }
+    acc += s;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  const float r = __frsqrt_rn(__fdiv_rn(acc, static_cast<float>(hs)) + eps);
+  for (int i = lane; i < n8; i += 32) {  // each lane reads back the groups it has just written
+    const uint4 v = xr[i];
+    const uint32_t a[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = f32x2_to_bf16x2(bf16x2_lo(a[j]) * r, bf16x2_hi(a[j]) * r);
+    hr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // One block of 256 threads per token: routed sum (slot order), gate =
 // sigmoid(x . gate_scalar) with the reference's 256 strided fused partials and
 // halving tree, y = bf16(fma(gate, shared_down, routed)) (MoECombineKernel,
@@ -726,6 +777,11 @@ cudaError_t launch_swiglu(const uint16_t* gu, uint16_t* out, int T, int inner, c
   const int64_t total = static_cast<int64_t>(T) * inner;
   return launch_chained(swiglu_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream, gu, out,
                         T, inner);
+}
+
+cudaError_t launch_residual_rmsnorm(uint16_t* x, const uint16_t* y, uint16_t* h, int T, int hs, float eps,
+                                    cudaStream_t stream) {
+  return launch_chained(residual_rmsnorm_kernel, dim3((T + 7) / 8), dim3(256), 0, stream, x, y, h, T, hs, eps);
 }
 
 cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,

@@ -1,0 +1,64 @@
+"""The decode-stack harness: x <- bf16(x + MoE_l(RMSNorm(x))) over several layers.
+The residual + RMSNorm step is bit-exact against the oracle; the stack equals the
+layer-by-layer composition of the same entry points bit for bit and follows the oracle's
+stack within the layer tolerance."""
+import numpy as np
+import pytest
+import torch
+
+import synth
+from gpu_util import dev, host
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("T,hs", [(1, 256), (5, 2048), (130, 2560), (9, 8192)])
+def test_residual_rmsnorm_bit_exact(q4t, gpu_lib, T, hs):
+    rng = np.random.default_rng(T + hs)
+    x = O.f32_to_bf16(rng.standard_normal((T, hs), dtype=np.float32) * np.float32(2.0))
+    y = O.f32_to_bf16(rng.standard_normal((T, hs), dtype=np.float32))
+    for with_y in (True, False):
+        xd, yd = dev(x), dev(y)
+        hd = torch.empty_like(xd)
+        q4t.residual_rmsnorm(xd, yd if with_y else None, hd)
+        torch.cuda.synchronize()
+        x_ref, h_ref = O.residual_rmsnorm_bf16(x, y if with_y else None)
+        assert np.array_equal(host(xd).view(np.uint16), x_ref)
+        assert np.array_equal(host(hd).view(np.uint16), h_ref)
+
+
+def test_residual_rmsnorm_rejects_bad_dims(q4t, gpu_lib):
+    x = torch.zeros((2, 100), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(q4t.Q4TError, match="multiple of 8"):
+        q4t.residual_rmsnorm(x, None, torch.empty_like(x))
+
+
+def test_stack_equals_composition_and_oracle(q4t, gpu_lib):
+    E, hs, is_, sis, k, T, nl = 32, 512, 256, 128, 4, 24, 3
+    layers = [synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=70 + i) for i in range(nl)]
+    dls = [q4t.DeviceLayer.from_host(L) for L in layers]
+    x0 = synth.make_x(T, hs, seed=8)
+    # the stack in one go
+    xs = dev(x0).view(torch.bfloat16).clone()
+    q4t.DecodeStack(dls, T, k)(xs)
+    # the same entry points, layer by layer
+    xc = dev(x0).view(torch.bfloat16).clone()
+    h = torch.empty_like(xc)
+    y = torch.empty_like(xc)
+    for i, dl in enumerate(dls):
+        q4t.residual_rmsnorm(xc, y if i else None, h)
+        q4t.MoEForward(dl, T, k)(h, y)
+    q4t.residual_rmsnorm(xc, y, h)
+    torch.cuda.synchronize()
+    assert torch.equal(xs.view(torch.int16), xc.view(torch.int16))
+    # the oracle's stack (device-order arithmetic; fp32 logits order differs from the tensor cores',
+    # so a near-tie in one router can move one token: compare in the layer tolerance)
+    xo = x0.copy()
+    yo = None
+    for L in layers:
+        xo, ho = O.residual_rmsnorm_bf16(xo, yo)
+        yo = O.moe_forward(ho, L, k)["y"]
+    xo, _ = O.residual_rmsnorm_bf16(xo, yo)
+    got, ref = O.bf16_to_f32(host(xs).view(np.uint16)), O.bf16_to_f32(xo)
+    assert np.max(np.abs(got - ref)) <= 2e-3 * np.max(np.abs(ref)) + 2.0 ** -8 * np.max(np.abs(ref))

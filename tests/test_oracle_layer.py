@@ -156,3 +156,21 @@ def test_exact_gemm_against_float64_numpy():
     alpha = np.float64(np.float32(iw * ia))
     want = ((ad @ wd.T) * alpha).astype(np.float32)
     assert np.array_equal(got, want)
+
+
+def test_rmsnorm_matches_float64_and_residual_step():
+    """RMSNorm restated in the reference's summation order agrees with a float64
+    evaluation to bf16 rounding, and the residual step is exactly bf16(x + y)."""
+    rng = np.random.default_rng(5)
+    for hs in (256, 2048, 2560):
+        x = O.f32_to_bf16(rng.standard_normal((7, hs), dtype=np.float32) * np.float32(3.0))
+        y = O.f32_to_bf16(rng.standard_normal((7, hs), dtype=np.float32))
+        h = O.bf16_to_f32(O.rmsnorm_bf16(x))
+        xf = O.bf16_to_f32(x).astype(np.float64)
+        ref = xf / np.sqrt((xf * xf).mean(axis=1, keepdims=True) + 1e-6)
+        assert np.max(np.abs(h - ref) / np.maximum(np.abs(ref), 1e-3)) < 2.0 ** -7.5
+        x2, h2 = O.residual_rmsnorm_bf16(x, y)
+        assert np.array_equal(x2, O.f32_to_bf16(O.bf16_to_f32(x) + O.bf16_to_f32(y)))
+        assert np.array_equal(h2, O.rmsnorm_bf16(x2))
+        x3, h3 = O.residual_rmsnorm_bf16(x, None)
+        assert np.array_equal(x3, x) and np.array_equal(h3, O.rmsnorm_bf16(x))
