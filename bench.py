@@ -269,6 +269,45 @@ def pick_cpu_tokens(layer_host, budget_s=4.0):
     return T
 
 
+def run_stack_point(torch, q4t, syn, layers, n_layers, T, passes, layer_bytes):
+    """Config 3: n_layers layers with independent weights, x <- bf16(x + MoE(RMSNorm(x))), T tokens.
+    One pass = the whole stack; timed eagerly and, when capture works, as one CUDA graph."""
+    t_build = time.time()
+    while len(layers) < n_layers:
+        layers.append(syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=20260921 + 1000 + len(layers)))
+    build_s = time.time() - t_build
+    stack = q4t.DecodeStack(layers[:n_layers], T, K_TOP)
+    x0 = syn.make_x(T, HS, seed=4242)
+    x = x0.clone()
+
+    def one_pass(_i=0):
+        x.copy_(x0)
+        stack(x)
+
+    ms = time_steps(torch, one_pass, passes, 2)
+    out = dict(layers=n_layers, tokens=T, build_s=build_s, ms_per_pass=ms, us_per_layer=ms * 1e3 / n_layers,
+               layer_tokens_per_s=T * n_layers / (ms * 1e-3),
+               hbm_frac_of_measured=layer_bytes * n_layers / (ms * 1e-3) / 1e9 / load_peaks()["hbm_gbs"],
+               weights_gb=n_layers * 0.906, graph=None)
+    try:   # the same pass as one CUDA graph (side-stream fork/join and chained launches are captured with it)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            one_pass()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                one_pass()
+        torch.cuda.current_stream().wait_stream(side)
+        x_ref = x.clone()
+        ms_g = time_steps(torch, lambda i: graph.replay(), passes, 2)
+        same = bool(torch.equal(x.view(torch.int16), x_ref.view(torch.int16)))
+        out["graph"] = dict(ms_per_pass=ms_g, us_per_layer=ms_g * 1e3 / n_layers, replay_equals_eager=same,
+                            hbm_frac_of_measured=layer_bytes * n_layers / (ms_g * 1e-3) / 1e9 / load_peaks()["hbm_gbs"])
+    except Exception as exc:   # capture is optional: report why it was not measured
+        out["graph"] = dict(error=str(exc).splitlines()[0][:200])
+    return out
+
+
 def main_single(args):
     import torch
     q4t = importlib.import_module("qwen4-thor_b200")
@@ -334,6 +373,9 @@ def main_single(args):
         cpu = dict(value=tps, unit="tokens/s", cores=threads, kind="port",
                    sample=f"2 layer forwards of {Tc} tokens (oracle restatement of the reference's host-side MoE)")
 
+    if not args.quick and args.stack_layers > 0:   # last: the graph capture attempt must not disturb the rest
+        also["stack"] = run_stack_point(torch, q4t, syn, layers, args.stack_layers, T, 5, main["layer_bytes"])
+
     launches_per_step = 3 + 3 + 1 + 1 + 1 + 1 + 1 + 1   # logits, topk, plan x3, quant, gu, dn, shared x2, combine
     line = dict(metric="moe_layer_tokens_per_s", value=main["tokens_per_s"], unit="tokens/s", n_gpus=1,
                 steps=args.steps, warmup=args.warmup, ms_per_step=main["ms_per_step"], higher_is_better=True,
@@ -362,6 +404,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline point only (no sweep, no prefill)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=4, help="independent layer weight sets rotated per step")
+    ap.add_argument("--stack-layers", type=int, default=48,
+                    help="layers of the decode-stack point (x <- x + MoE(RMSNorm(x)), T=128); 0 skips it")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="run only the Zipf-skewed prefill layer at this many tokens and print its result")
     args = ap.parse_args()
