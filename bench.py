@@ -269,6 +269,11 @@ def pick_cpu_tokens(layer_host, budget_s=4.0):
     return T
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate/up GEMM launch at T = 128 divided by
+# the experts that launch touched (ncu --set full capture, summarised under profiles/)
+GU_DRAM_BYTES_PER_EXPERT = 567.25e6 / 467.5
+
+
 def run_stack_point(torch, q4t, syn, layers, n_layers, T, passes, layer_bytes):
     """Config 3: n_layers layers with independent weights, x <- bf16(x + MoE(RMSNorm(x))), T tokens.
     One pass = the whole stack; timed eagerly and, when capture works, as one CUDA graph."""
@@ -360,7 +365,9 @@ def main_single(args):
     gu_gbs = gu_bytes / (st["gate_up_gemm"] * 1e-3) / 1e9
     roofline = dict(bound="hbm", kernel="gate_up_gemm (tcgen05 NVFP4 grouped GEMM + SwiGLU + requantise)",
                     achieved=gu_gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gu_gbs / peaks["hbm_gbs"],
-                    peak_source=peaks["source"], traffic=None, algorithmic_bytes=gu_bytes,
+                    peak_source=peaks["source"], traffic=GU_DRAM_BYTES_PER_EXPERT * main["unique_experts"],
+                    traffic_source="ncu capture of one launch (567.25 MB at 467.5 experts), scaled by the experts touched",
+                    algorithmic_bytes=gu_bytes,
                     kernel_ms=st["gate_up_gemm"],
                     layer=dict(achieved=main["layer_gbs"], frac=main["layer_gbs"] / peaks["hbm_gbs"],
                                frac_of_8tbs=main["layer_gbs"] / 8000.0, bytes=main["layer_bytes"]))
