@@ -127,10 +127,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       const uint32_t bar_full0 = smem_u32(&bars.full[0]), bar_empty0 = smem_u32(&bars.empty[0]);
+      // The expert and first row of a tile are fetched one tile ahead: with short tiles (two
+      // k-blocks in the down GEMM) a table lookup in front of every tile's first load would
+      // leave the ring short of requests for the length of an L2 round trip.
+      int next_group = 0, next_row0 = 0;
+      if (static_cast<int>(blockIdx.x) < total_tiles) {
+        const int mt0 = blockIdx.x / args.n_tiles;
+        next_group = args.tile_expert ? args.tile_expert[mt0] : 0;
+        next_row0 = args.tile_expert ? args.tile_row0[mt0] : mt0 * kTileM;
+      }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int mt = tile / args.n_tiles, nt = tile - mt * args.n_tiles;
-        const int group = args.tile_expert ? args.tile_expert[mt] : 0;
-        const int row0 = args.tile_expert ? args.tile_row0[mt] : mt * kTileM;
+        const int group = next_group, row0 = next_row0;
+        if (tile + static_cast<int>(gridDim.x) < total_tiles) {
+          const int nmt = (tile + static_cast<int>(gridDim.x)) / args.n_tiles;
+          next_group = args.tile_expert ? args.tile_expert[nmt] : 0;
+          next_row0 = args.tile_expert ? args.tile_row0[nmt] : nmt * kTileM;
+        }
         const int brow0 = group * args.b_rows_per_group + nt * args.n_per_tile;
         const int brow1 = brow0 + (kSwiglu ? args.up_row_offset : kHalf);
         // scale atoms of B: row blocks of 128 inside the group's buffer
