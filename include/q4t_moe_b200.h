@@ -350,6 +350,23 @@ int32_t q4t_peer_buffer_close(void* ptr);
 /* x: bf16 [tokens_per_rank, hs]; hs a multiple of 64.                         */
 int32_t q4t_ep_publish(const uint16_t* x, const q4t_ep_peer_table* peers, int32_t hs,
                        float input_scale, void* stream);
+/* Steps 1 and 4 as single calls, for drivers that count host overhead:
+ * q4t_ep_route_publish = router logits (scratch bf16 [tokens_per_rank, E]) + top-k
+ * (expert_ids, router_w) + q4t_ep_publish, and it starts the shared expert on
+ * the library's side stream (result left in finish_workspace);
+ * q4t_ep_combine = wait for that shared expert + q4t_ep_flat_rows (row_of_flat:
+ * int32 [T*k] scratch) + q4t_moe_combine on the landing buffer.                */
+int32_t q4t_ep_route_publish(const uint16_t* x, const q4t_extra_weights* extra,
+                             const q4t_ep_peer_table* peers, int32_t k,
+                             float input_scale, uint16_t* logits,
+                             int32_t* expert_ids, float* router_w,
+                             void* finish_workspace, size_t finish_workspace_bytes,
+                             void* stream);
+int32_t q4t_ep_combine(const uint16_t* x, const uint16_t* landed_rows,
+                       const int32_t* expert_ids, const float* router_w,
+                       const q4t_extra_weights* extra, uint16_t* y, int32_t T,
+                       int32_t k, int32_t* row_of_flat, void* finish_workspace,
+                       size_t finish_workspace_bytes, void* stream);
 /* ids_all: int32 [world*tokens_per_rank, k] global expert ids (entries outside
  * [0, E_local*world) are skipped); weights: this rank's experts.              */
 size_t q4t_moe_expert_peer_workspace_bytes(int32_t tokens_all, int32_t k, int32_t hs,

@@ -66,7 +66,7 @@ EXPORTS = [
     "q4t_moe_expert_rows", "q4t_moe_finish_workspace_bytes", "q4t_moe_finish",
     "q4t_moe_shared_expert", "q4t_moe_combine", "q4t_residual_rmsnorm_bf16",
     "q4t_peer_buffer_alloc", "q4t_peer_buffer_free", "q4t_peer_buffer_export", "q4t_peer_buffer_open",
-    "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
+    "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_ep_route_publish", "q4t_ep_combine", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
 ]
 EP_MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
@@ -122,6 +122,9 @@ def load():
     L.q4t_moe_shared_expert.argtypes = [vp, C.POINTER(ExtraWeights), i32, vp, sz, vp]
     L.q4t_moe_combine.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, sz, vp]
     L.q4t_residual_rmsnorm_bf16.argtypes = [vp, vp, vp, i32, i32, f32, vp]
+    L.q4t_ep_route_publish.argtypes = [vp, C.POINTER(ExtraWeights), C.POINTER(EpPeerTable), i32, f32, vp, vp, vp, vp,
+                                       sz, vp]
+    L.q4t_ep_combine.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, vp, sz, vp]
     L.q4t_ep_publish.argtypes = [vp, C.POINTER(EpPeerTable), i32, f32, vp]
     L.q4t_moe_expert_peer_workspace_bytes.restype = C.c_size_t
     L.q4t_moe_expert_peer_workspace_bytes.argtypes = [i32] * 5
@@ -176,8 +179,11 @@ class DeviceLayer:
               "dn_w_scale2", "dn_input_scale")
     EXTRA = ("gate", "shared_gu", "shared_down", "shared_gate_scalar")
 
-    def __init__(self, E, hs, moe_is, shared_is, tensors: dict):
+    def __init__(self, E, hs, moe_is, shared_is, tensors: dict, E_router=None):
+        """E_router: experts the router chooses among when this object holds only some of
+        them (one rank of an expert-parallel layer); defaults to E."""
         self.E, self.hs, self.moe_is, self.shared_is = E, hs, moe_is, shared_is
+        self.E_router = E if E_router is None else E_router
         self.t = tensors  # keeps the device buffers alive
         gis = tensors.get("gu_input_scale")
         uniform = 0.0
@@ -185,7 +191,7 @@ class DeviceLayer:
             lo, hi = float(gis.min()), float(gis.max())
             uniform = lo if lo == hi and lo > 0 else 0.0
         self.routed = RoutedWeights(E, hs, moe_is, 0, *[self._p(n) for n in self.ROUTED], uniform, 0)
-        self.extra = ExtraWeights(E, hs, shared_is, *[self._p(n) for n in self.EXTRA])
+        self.extra = ExtraWeights(self.E_router, hs, shared_is, *[self._p(n) for n in self.EXTRA])
 
     def _p(self, name):
         t = self.t.get(name)

@@ -939,6 +939,62 @@ int32_t q4t_ep_publish(const uint16_t* x, const q4t_ep_peer_table* peers, int32_
   return e == cudaSuccess ? Q4T_OK : fail_cuda("publish launch", e);
 }
 
+int32_t q4t_ep_route_publish(const uint16_t* x, const q4t_extra_weights* extra, const q4t_ep_peer_table* peers,
+                             int32_t k, float input_scale, uint16_t* logits, int32_t* expert_ids, float* router_w,
+                             void* finish_workspace, size_t finish_workspace_bytes, void* stream) {
+  if (!x || !extra || !peers || !logits || !expert_ids || !router_w) return fail(Q4T_ERR_INVALID, "null pointer");
+  const int T = peers->tokens_per_rank;
+  if (T <= 0) return fail(Q4T_ERR_INVALID, "invalid peer table (tokens_per_rank > 0)");
+  if (k <= 0 || k > 16 || k > extra->E) return fail(Q4T_ERR_INVALID, "k out of range");
+  FinishLayout F;
+  int rc = finish_args_ok(extra, T, k, finish_workspace, finish_workspace_bytes, &F);
+  if (rc != Q4T_OK) return rc;
+  const DeviceState* ds;
+  if ((rc = device_state(&ds)) != Q4T_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* base = static_cast<uint8_t*>(finish_workspace);
+  cudaError_t e;
+  // the shared expert needs nothing from the other ranks: it runs beside everything up to the combine
+  if ((e = cudaEventRecord(ds->fork_event, st)) != cudaSuccess ||
+      (e = cudaStreamWaitEvent(ds->side_stream, ds->fork_event, 0)) != cudaSuccess)
+    return fail_cuda("fork", e);
+  q4t::chain_break();
+  if ((rc = run_shared_expert(ds, x, extra, reinterpret_cast<uint16_t*>(base + F.shared_gu),
+                              reinterpret_cast<uint16_t*>(base + F.shared_act),
+                              reinterpret_cast<uint16_t*>(base + F.shared_down), T, 0, ds->side_stream)) != Q4T_OK)
+    return rc;
+  if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return fail_cuda("join record", e);
+  q4t::chain_break();
+  if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, extra->E, extra->hs, st)) != Q4T_OK) return rc;
+  if ((e = q4t::launch_topk(logits, nullptr, expert_ids, router_w, T, extra->E, k, st)) != cudaSuccess)
+    return fail_cuda("topk launch", e);
+  return q4t_ep_publish(x, peers, extra->hs, input_scale, stream);
+}
+
+int32_t q4t_ep_combine(const uint16_t* x, const uint16_t* landed_rows, const int32_t* expert_ids,
+                       const float* router_w, const q4t_extra_weights* extra, uint16_t* y, int32_t T, int32_t k,
+                       int32_t* row_of_flat, void* finish_workspace, size_t finish_workspace_bytes, void* stream) {
+  if (T <= 0) return Q4T_OK;
+  FinishLayout F;
+  int rc = finish_args_ok(extra, T, k, finish_workspace, finish_workspace_bytes, &F);
+  if (rc != Q4T_OK) return rc;
+  if (!x || !landed_rows || !expert_ids || !router_w || !y || !row_of_flat) return fail(Q4T_ERR_INVALID, "null pointer");
+  const DeviceState* ds;
+  if ((rc = device_state(&ds)) != Q4T_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  // the shared expert started by q4t_ep_route_publish (a no-op wait when there was none)
+  if ((e = cudaStreamWaitEvent(st, ds->join_event, 0)) != cudaSuccess) return fail_cuda("join", e);
+  q4t::chain_break();
+  if ((e = q4t::launch_ep_flat_rows(expert_ids, T * k, extra->E, row_of_flat, st)) != cudaSuccess)
+    return fail_cuda("flat rows launch", e);
+  uint8_t* base = static_cast<uint8_t*>(finish_workspace);
+  e = q4t::launch_final_combine(landed_rows, row_of_flat, router_w, reinterpret_cast<uint16_t*>(base + F.shared_down), x,
+                                extra->shared_gate_scalar, reinterpret_cast<float*>(base + F.routed), y, T, k,
+                                extra->hs, st);
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("combine launch", e);
+}
+
 size_t q4t_moe_expert_peer_workspace_bytes(int32_t tokens_all, int32_t k, int32_t hs, int32_t moe_is,
                                            int32_t E_local) {
   if (tokens_all <= 0 || k <= 0 || !routed_dims_ok(E_local, hs, moe_is)) return 0;

@@ -187,7 +187,7 @@ def local_layer_from_list(q4t, full, experts):
     t["dn_sf"] = full.t["dn_sf"].view(E, -1).index_select(0, pick).view(-1)
     for n in ("gu_w_scale2", "gu_input_scale", "dn_w_scale2", "dn_input_scale"):
         t[n] = full.t[n].index_select(0, pick)
-    return q4t.DeviceLayer(len(experts), hs, is_, full.shared_is, t)
+    return q4t.DeviceLayer(len(experts), hs, is_, full.shared_is, t, E_router=full.E_router)
 
 
 class PeerBuffers:
@@ -295,7 +295,11 @@ class PeerExpertParallelMoE:
         self.finish_ws = torch.empty(self.finish_ws_bytes, dtype=torch.uint8, device=dev)
         self.profile = False
         self.phase_ms = {}
-        self.side = None
+        # argument values that never change, converted once
+        self._extra, self._table = C.byref(layer_local.extra), C.byref(buffers.table)
+        self._scale = float(layer_local.routed.gu_input_scale_uniform)
+        self._p_logits, self._p_ids, self._p_rw = self.logits.data_ptr(), self.ids.data_ptr(), self.rw.data_ptr()
+        self._p_fws, self._p_rof = self.finish_ws.data_ptr(), self.row_of_flat.data_ptr()
 
     def _s(self):
         return self.C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
@@ -338,17 +342,26 @@ class PeerExpertParallelMoE:
         self.shared(x)
         return self.combine(x, y)
 
+    def route_publish(self, x):
+        """publish() as one library call that also starts the shared expert on the library's
+        side stream; pairs with combine_landed()."""
+        self.q4t.check(self.lib.q4t_ep_route_publish(x.data_ptr(), self._extra, self._table, self.k, self._scale,
+                                                     self._p_logits, self._p_ids, self._p_rw, self._p_fws,
+                                                     self.finish_ws_bytes, self._s()))
+        return self.ids
+
+    def combine_landed(self, x, y):
+        self.q4t.check(self.lib.q4t_ep_combine(x.data_ptr(), self.buf.own[2], self._p_ids, self._p_rw, self._extra,
+                                               y.data_ptr(), self.T, self.k, self._p_rof, self._p_fws,
+                                               self.finish_ws_bytes, self._s()))
+        return y
+
     def forward(self, x, y):
+        """One step: three library calls and two collectives (host time per step matters once
+        the per-rank GPU work drops to a few hundred microseconds)."""
         marks = []
         self._mark(marks, "start")
-        torch = self.torch
-        main = torch.cuda.current_stream()
-        if self.side is None:
-            self.side = torch.cuda.Stream()
-        self.side.wait_stream(main)          # x is ready
-        with torch.cuda.stream(self.side):   # the shared expert runs beside the exchange
-            self.shared(x)
-        self.publish(x)
+        self.route_publish(x)
         self._mark(marks, "publish")
         if self.world > 1:
             self.dist.all_gather_into_tensor(self.ids_all, self.ids, group=self.group)
@@ -360,8 +373,7 @@ class PeerExpertParallelMoE:
         if self.world > 1:      # every rank's rows have landed once this returns on the stream
             self.dist.all_reduce(self.sync_word, group=self.group)
         self._mark(marks, "landed_barrier")
-        main.wait_stream(self.side)
-        self.combine(x, y)
+        self.combine_landed(x, y)
         self._mark(marks, "combine")
         if self.profile:
             marks[-1][1].synchronize()

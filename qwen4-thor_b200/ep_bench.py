@@ -29,7 +29,7 @@ def _local_layer(q4t, full, lo, hi):
     t["dn_sf"] = full.t["dn_sf"][lo * db:hi * db]
     for n in ("gu_w_scale2", "gu_input_scale", "dn_w_scale2", "dn_input_scale"):
         t[n] = full.t[n][lo:hi]
-    return q4t.DeviceLayer(hi - lo, hs, is_, full.shared_is, t)
+    return q4t.DeviceLayer(hi - lo, hs, is_, full.shared_is, t, E_router=full.E_router)
 
 
 def _local_layer_interleaved(q4t, full, rank, world):
@@ -43,7 +43,7 @@ def _local_layer_interleaved(q4t, full, rank, world):
     t["dn_sf"] = full.t["dn_sf"].view(E, -1)[pick].contiguous().view(-1)
     for n in ("gu_w_scale2", "gu_input_scale", "dn_w_scale2", "dn_input_scale"):
         t[n] = full.t[n][pick].contiguous()
-    return q4t.DeviceLayer(E // world, hs, is_, full.shared_is, t)
+    return q4t.DeviceLayer(E // world, hs, is_, full.shared_is, t, E_router=full.E_router)
 
 
 def main_multi(args):

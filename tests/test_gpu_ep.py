@@ -118,6 +118,7 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
         buf = ep.PeerBuffers(q4t, W, r, Tl, k, hs, expert_map=expert_map, placement=placement).from_pointers(ptrs)
         drv.append(ep.PeerExpertParallelMoE(q4t, local, E, hs, k, W, r, Tl, buf))
     xs = [x[r * Tl:(r + 1) * Tl].contiguous() for r in range(W)]
+    # first step: the separate entry points; second step below: the two single-call entries
     ids_all = torch.cat([d.publish(xr) for d, xr in zip(drv, xs)])
     for d in drv:
         d.experts(ids_all)
@@ -130,12 +131,35 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
     x2 = dev(synth.make_x(T, hs, seed=12)).view(torch.bfloat16)
     fwd(x2, y_ref)
     xs = [x2[r * Tl:(r + 1) * Tl].contiguous() for r in range(W)]
-    ids_all = torch.cat([d.publish(xr) for d, xr in zip(drv, xs)])
+    ids_all = torch.cat([d.route_publish(xr) for d, xr in zip(drv, xs)])
     for d in drv:
         d.experts(ids_all)
-    ys = [d.finish(xr, torch.empty((Tl, hs), dtype=torch.bfloat16, device="cuda")) for d, xr in zip(drv, xs)]
+    ys = [d.combine_landed(xr, torch.empty((Tl, hs), dtype=torch.bfloat16, device="cuda")) for d, xr in zip(drv, xs)]
     torch.cuda.synchronize()
     assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
+
+
+def test_peer_path_forward_one_rank(q4t, gpu_lib):
+    """The driver's own step (route+publish and combine as single library calls, shared expert
+    on the library's side stream) on one rank, twice, against MoEForward."""
+    ep = importlib.import_module("qwen4-thor_b200.ep")
+    E, hs, is_, sis, k, T = 32, 1024, 256, 256, 5, 130
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=65)
+    full = q4t.DeviceLayer.from_host(L)
+    pub = (torch.empty((T, hs // 2), dtype=torch.uint8, device="cuda"),
+           torch.zeros(T * (hs // 16), dtype=torch.uint8, device="cuda"),
+           torch.full((T * k, hs), -1, dtype=torch.int16, device="cuda"))
+    buf = ep.PeerBuffers(q4t, 1, 0, T, k, hs, expert_map=0).from_pointers([tuple(t.data_ptr() for t in pub)])
+    drv = ep.PeerExpertParallelMoE(q4t, full, E, hs, k, 1, 0, T, buf)
+    fwd = q4t.MoEForward(full, T, k)
+    for seed in (21, 22):
+        x = dev(synth.make_x(T, hs, seed=seed)).view(torch.bfloat16)
+        y_ref = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+        y = torch.empty_like(y_ref)
+        fwd(x, y_ref)
+        drv.forward(x, y)
+        torch.cuda.synchronize()
+        assert torch.equal(y.view(torch.int16), y_ref.view(torch.int16))
 
 
 def test_peer_path_rejects_per_expert_input_scales(q4t, gpu_lib):
