@@ -964,11 +964,14 @@ int32_t q4t_ep_route_publish(const uint16_t* x, const q4t_extra_weights* extra, 
                               reinterpret_cast<uint16_t*>(base + F.shared_down), T, 0, ds->side_stream)) != Q4T_OK)
     return rc;
   if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return fail_cuda("join record", e);
+  // The publish kernel first: it is bound by the links, not by the SMs, so it overlaps with
+  // the shared expert's GEMMs that have just started on the side stream; the router follows.
+  if ((rc = q4t_ep_publish(x, peers, extra->hs, input_scale, stream)) != Q4T_OK) return rc;
   q4t::chain_break();
   if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, extra->E, extra->hs, st)) != Q4T_OK) return rc;
   if ((e = q4t::launch_topk(logits, nullptr, expert_ids, router_w, T, extra->E, k, st)) != cudaSuccess)
     return fail_cuda("topk launch", e);
-  return q4t_ep_publish(x, peers, extra->hs, input_scale, stream);
+  return Q4T_OK;
 }
 
 int32_t q4t_ep_combine(const uint16_t* x, const uint16_t* landed_rows, const int32_t* expert_ids,
