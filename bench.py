@@ -135,7 +135,7 @@ class ClockSampler:
                     samples=len(sm))
 
 
-def time_steps(torch, fn, steps, warmup, barrier=None):
+def time_steps(torch, fn, steps, warmup, barrier=None, finish=None):
     """W untimed steps, then exactly K timed steps between CUDA events on the
     current stream, with a synchronise (and barrier) on both sides."""
     for i in range(warmup):
@@ -147,6 +147,8 @@ def time_steps(torch, fn, steps, warmup, barrier=None):
     t0.record()
     for i in range(steps):
         fn(warmup + i)
+    if finish:      # e.g. make the timing stream wait for copies still running on other streams
+        finish()
     t1.record()
     torch.cuda.synchronize()
     if barrier:
@@ -195,16 +197,41 @@ def run_decode_point(torch, q4t, layers, T, steps, warmup, n_inputs=8, with_e2e=
         q4t.stage_timing(False)
         out["stage_ms"] = {kname: v / n for kname, v in acc.items()}
     if with_e2e:
+        # Every step copies its input from pinned host memory and its result back.  The copies
+        # run on their own streams with two buffers each way, so the input of step i+1 and the
+        # result of step i-1 move while step i computes; the timed region ends only when the
+        # last result has reached the host.
         hx = [x.cpu().pin_memory() for x in xs]
-        hy = torch.empty((T, HS), dtype=torch.bfloat16).pin_memory()
-        dx = torch.empty((T, HS), dtype=torch.bfloat16, device="cuda")
+        hy = [torch.empty((T, HS), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        dx = [torch.empty((T, HS), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        dy = [torch.empty((T, HS), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        main, s_in, s_out = torch.cuda.current_stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_done = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
+        for e in ev_done + ev_out:
+            e.record(main)
 
         def step_e2e(i):
-            dx.copy_(hx[i % n_inputs], non_blocking=True)
-            fwds[i % len(fwds)](dx, y)
-            hy.copy_(y, non_blocking=True)
+            b = i & 1
+            s_in.wait_event(ev_done[b])            # the forward that last read dx[b] is over
+            with torch.cuda.stream(s_in):
+                dx[b].copy_(hx[i % n_inputs], non_blocking=True)
+                ev_in[b].record(s_in)
+            main.wait_event(ev_in[b])
+            main.wait_event(ev_out[b])             # dy[b] has been copied out
+            fwds[i % len(fwds)](dx[b], dy[b])
+            ev_done[b].record(main)
+            s_out.wait_event(ev_done[b])
+            with torch.cuda.stream(s_out):
+                hy[b].copy_(dy[b], non_blocking=True)
+                ev_out[b].record(s_out)
 
-        ms_e = time_steps(torch, step_e2e, steps, warmup)
+        def drain():
+            main.wait_event(ev_out[0])
+            main.wait_event(ev_out[1])
+
+        ms_e = time_steps(torch, step_e2e, steps, warmup, finish=drain)
         out["e2e"] = dict(value=T / (ms_e * 1e-3), unit="tokens/s", ms_per_step=ms_e,
                           h2d_bytes_per_step=T * HS * 2, d2h_bytes_per_step=T * HS * 2)
     del fwds

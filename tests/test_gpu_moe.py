@@ -202,3 +202,36 @@ def test_batch_independence_at_scale(q4t, gpu_lib):
     diff = (a != b).float().mean().item()
     print(f"rows differing between T=4096 and T=64 batches: {diff:.3e}")
     assert diff == 0.0
+
+
+def test_config0_full_size_layer_vs_oracle(q4t, gpu_lib):
+    """The reference-runnable configuration at full size: T = 16, hidden 2048, 512 experts,
+    top-10, intermediate 512, shared 512.  The layer is built on the device (seeded), copied to
+    the host for the oracle, and every stage is compared as in the small-layer test."""
+    import importlib
+    syn = importlib.import_module("qwen4-thor_b200.synthetic")
+    E, hs, is_, sis, k, T = 512, 2048, 512, 512, 10, 16
+    dl = syn.device_layer(q4t, E, hs, is_, sis, seed=20260921)
+    arrs = {n: (t.view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy())
+            for n, t in dl.t.items()}
+    L = O.Layer(E, hs, is_, sis, **arrs)
+    x = synth.make_x(T, hs, seed=16)
+    fwd = q4t.MoEForward(dl, T, k)
+    y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    fwd(dev(x), y, flags=1)
+    fwd.status()
+    logits = host(fwd.region("logits", torch.int16, T * E)).reshape(T, E)
+    ids = host(fwd.region("expert_ids", torch.int32, T * k)).reshape(T, k)
+    rw = host(fwd.region("router_w", torch.float32, T * k)).reshape(T, k)
+    want_ids, want_rw = O.router_topk(logits, k)
+    assert np.array_equal(ids, want_ids)
+    assert np.abs(rw - want_rw).max() <= 2e-6
+    routed = O.routed_forward(x, ids, rw, L, 1)
+    got_routed = host(fwd.region("routed", torch.float32, T * hs)).reshape(T, hs)
+    assert np.abs(got_routed - routed).max() <= 2e-3 * np.abs(routed).max()
+    want_y = O.bf16_to_f32(O.shared_combine(x, routed, L, 1))
+    got_y = O.bf16_to_f32(host(y))
+    err = np.abs(got_y - want_y).max() / np.abs(want_y).max()
+    print(f"config 0 layer output: max |diff| / max |ref| = {err:.3e}; routed equal bits: "
+          f"{np.array_equal(got_routed, routed)}")
+    assert err <= 2e-3 + 2.0 ** -8
