@@ -259,13 +259,9 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
         cudaSuccess)
       return fail_cuda("block code gather launch", e);
   } else if (w->gu_input_scale_uniform > 0.0f && k > 1 && R >= 8192) {
-    uint8_t* xq = P.at<uint8_t>(L.xq_packed);
-    uint8_t* xq_sf = P.at<uint8_t>(L.xq_sf);
-    if ((e = q4t::launch_quantize(x, xq, xq_sf, M, hs, w->gu_input_scale_uniform, st)) != cudaSuccess)
-      return fail_cuda("token quantise launch", e);
-    if ((e = q4t::launch_gather_codes(xq, xq_sf, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, pt.row_tile,
-                                      pt.tile_row0, pt.offsets + E, k, st)) != cudaSuccess)
-      return fail_cuda("code gather launch", e);
+    if ((e = q4t::launch_quantize_scatter(x, a_packed, a_sf_tiles, M, hs, w->gu_input_scale_uniform, pt.row_of_flat,
+                                          pt.row_tile, pt.tile_row0, k, st)) != cudaSuccess)
+      return fail_cuda("quantise-scatter launch", e);
   } else if ((e = q4t::launch_gather_quantize(x, a_packed, a_sf_tiles, R, hs, pt.flat_of_row, ids,
                                               w->gu_input_scale, pt.row_tile, pt.tile_row0, pt.offsets + E, k, E,
                                               st)) != cudaSuccess) {

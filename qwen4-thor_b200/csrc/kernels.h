@@ -50,9 +50,11 @@ cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* 
                                    const float* input_scale, const int32_t* row_tile,
                                    const int32_t* tile_row0, const int32_t* rows_dev, int k, int E,
                                    cudaStream_t stream);
-cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed, uint8_t* sf_tiles,
-                                int R, int K, const int32_t* flat_of_row, const int32_t* row_tile,
-                                const int32_t* tile_row0, const int32_t* rows_dev, int k, cudaStream_t stream);
+// One input scale for all experts: quantise each of the T tokens once and write codes and
+// scales to its k grouped rows (row_of_flat[t*k+s], -1 = skipped); K % 64 == 0, k <= 32.
+cudaError_t launch_quantize_scatter(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int T, int K,
+                                    float global_scale, const int32_t* row_of_flat, const int32_t* row_tile,
+                                    const int32_t* tile_row0, int k, cudaStream_t stream);
 // Expert parallelism over peer memory: a rank quantises its tokens once and writes the
 // codes and the scale bytes (row-major [tokens, K/16], not swizzled) into its block of
 // every rank's gathered buffer (the targets may be peer GPUs' memory; K a multiple of 64).
@@ -64,7 +66,7 @@ struct PublishTargets {
 };
 cudaError_t launch_publish_tokens(const uint16_t* x, const PublishTargets& dst, int M, int K, float global_scale,
                                   cudaStream_t stream);
-// As launch_gather_codes, reading the gathered buffers of all ranks' tokens:
+// Copies each grouped row's codes and scales out of the gathered buffers of all ranks' tokens:
 // xq_packed [tokens, K/2], xq_sf [tokens, K/16] row-major.
 cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed,
                                       uint8_t* sf_tiles, int R, int K, const int32_t* flat_of_row,

@@ -122,32 +122,65 @@ __global__ void __launch_bounds__(256) publish_tokens_kernel(const uint16_t* __r
   }
 }
 
-// One warp per grouped row: copies the row's token codes (quantised once per
-// token) and moves its scale bytes from the per-token swizzled buffer into the
-// row tile's local atoms, four bytes (one K-tile of one row) at a time.
-__global__ void __launch_bounds__(256) gather_codes_kernel(
-    const uint8_t* __restrict__ xq_packed, const uint8_t* __restrict__ xq_sf, uint8_t* __restrict__ packed,
-    uint8_t* __restrict__ sf_tiles, int rows, int K, const int32_t* __restrict__ flat_of_row,
-    const int32_t* __restrict__ row_tile, const int32_t* __restrict__ tile_row0,
-    const int32_t* __restrict__ rows_dev, int k) {
+// Quantises every token once (one input scale for all experts) and writes the codes and
+// scale bytes straight to the token's k grouped rows: one warp per token, a lane owns four
+// neighbouring groups (64 values), so every destination row receives 1 KB-contiguous code
+// runs and one 4-byte scale word per K-tile in its tile-local atom.  Replaces "quantise the
+// tokens, then copy each row k times" (half the memory traffic).  K a multiple of 64.
+__global__ void __launch_bounds__(256) quantize_scatter_kernel(
+    const uint16_t* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_tiles, int T, int K,
+    float global_scale, const int32_t* __restrict__ row_of_flat, const int32_t* __restrict__ row_tile,
+    const int32_t* __restrict__ tile_row0, int k) {
   chain_wait();
-  const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (r >= min(rows, *rows_dev)) return;
-  const int token = flat_of_row[r] / k;
-  const int t = row_tile[r];
-  const uint32_t in_tile = static_cast<uint32_t>(r - tile_row0[t]);
-  const int row_bytes = K >> 1, ntk = K >> 6;
-  const uint4* src = reinterpret_cast<const uint4*>(xq_packed + static_cast<size_t>(token) * row_bytes);
-  uint4* dst = reinterpret_cast<uint4*>(packed + static_cast<size_t>(r) * row_bytes);
-  for (int c = lane; c < (row_bytes >> 4); c += 32) dst[c] = __ldg(src + c);
-  for (int a = lane; a < ntk; a += 32) {
-    const uint32_t v = *reinterpret_cast<const uint32_t*>(xq_sf + sf_offset(static_cast<uint32_t>(token), 4u * a, ntk));
-    *reinterpret_cast<uint32_t*>(sf_tiles + (static_cast<size_t>(t) * ntk + a) * 512u + sf_in_atom(in_tile, 0)) = v;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const int groups = K >> 4, ntk = K >> 6;
+  // where the token's k rows go (lane s < k holds slot s; fetched once, shared by shuffle)
+  int my_row = -1, my_tile = 0, my_in_tile = 0;
+  if (lane < k) {
+    my_row = row_of_flat[t * k + lane];
+    if (my_row >= 0) {
+      my_tile = row_tile[my_row];
+      my_in_tile = my_row - tile_row0[my_tile];
+    }
+  }
+  for (int base = 0; base < groups; base += 128) {  // warp-uniform trip count: the shuffles below need every lane
+    const int g0 = base + lane * 4;
+    const bool active = g0 < groups;
+    uint32_t codes[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sfw = 0;
+    if (active) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * K + g0 * 16);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v0 = __ldg(src + 2 * j), v1 = __ldg(src + 2 * j + 1);
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        float a[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          a[2 * i] = bf16x2_lo(w[i]);
+          a[2 * i + 1] = bf16x2_hi(w[i]);
+        }
+        sfw |= quantize_group16(a, global_scale, codes[2 * j], codes[2 * j + 1]) << (8 * j);
+      }
+    }
+    for (int s = 0; s < k; ++s) {
+      const int r = __shfl_sync(0xffffffffu, my_row, s);
+      const int tile = __shfl_sync(0xffffffffu, my_tile, s);
+      const int in_tile = __shfl_sync(0xffffffffu, my_in_tile, s);
+      if (r < 0 || !active) continue;
+      uint4* c = reinterpret_cast<uint4*>(packed + static_cast<size_t>(r) * (K >> 1) + static_cast<size_t>(g0) * 8);
+      c[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      c[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+      *reinterpret_cast<uint32_t*>(sf_tiles + (static_cast<size_t>(tile) * ntk + (g0 >> 2)) * 512u +
+                                   sf_in_atom(static_cast<uint32_t>(in_tile), 0)) = sfw;
+    }
   }
 }
 
-// The same copy from the gathered token buffer of all ranks (token = flat / k over all
-// ranks' tokens), whose scale bytes are row-major [tokens, K/16].
+// One warp per grouped row: copies the row's token codes (quantised once per token by
+// its owner rank) from the gathered token buffer of all ranks (token = flat / k over all
+// ranks' tokens; scale bytes row-major [tokens, K/16]) and moves the scale bytes into the
+// row tile's local atoms, four bytes (one K-tile of one row) at a time.
 __global__ void __launch_bounds__(256) gather_codes_rowsf_kernel(
     const uint8_t* __restrict__ xq_packed, const uint8_t* __restrict__ xq_sf, uint8_t* __restrict__ packed,
     uint8_t* __restrict__ sf_tiles, int rows, int K, const int32_t* __restrict__ flat_of_row,
@@ -251,12 +284,12 @@ cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* 
                         0.0f, flat_of_row, expert_ids, input_scale, row_tile, tile_row0, rows_dev, k, E);
 }
 
-cudaError_t launch_gather_codes(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed, uint8_t* sf_tiles,
-                                int R, int K, const int32_t* flat_of_row, const int32_t* row_tile,
-                                const int32_t* tile_row0, const int32_t* rows_dev, int k, cudaStream_t stream) {
-  if (R == 0) return cudaSuccess;
-  return launch_chained(gather_codes_kernel, dim3((R + 7) / 8), dim3(256), 0, stream, xq_packed, xq_sf, packed,
-                        sf_tiles, R, K, flat_of_row, row_tile, tile_row0, rows_dev, k);
+cudaError_t launch_quantize_scatter(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int T, int K,
+                                    float global_scale, const int32_t* row_of_flat, const int32_t* row_tile,
+                                    const int32_t* tile_row0, int k, cudaStream_t stream) {
+  if (T == 0) return cudaSuccess;
+  return launch_chained(quantize_scatter_kernel, dim3((T + 7) / 8), dim3(256), 0, stream, x, packed, sf_tiles, T, K,
+                        global_scale, row_of_flat, row_tile, tile_row0, k);
 }
 
 cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed,

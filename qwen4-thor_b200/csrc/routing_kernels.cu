@@ -89,20 +89,33 @@ __device__ __forceinline__ void topk_token(const uint16_t* __restrict__ row, con
     // low half = 0xFFFF - expert id, so that the maximum key is the largest
     // value and, among equal values, the lowest id.  A selected entry's key
     // becomes 0.  One warp-wide integer max (redux) per round.
+    // Register slot i of lane l holds expert (i / 8) * 256 + 8 * l + i % 8: two 16-byte
+    // loads per lane when the row is 16-byte aligned (E a multiple of 8), the ids travel
+    // inside the keys, so the placement does not matter for the result.
     uint32_t key[16];
     uint32_t lmax = 0;
+    const bool vec = (E & 7) == 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int e = lane + 32 * i;
-      uint32_t kv = 0;
-      if (e < E) {
-        uint32_t b = row[e];
-        if (b == 0x8000u) b = 0;
-        const uint32_t ord = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
-        kv = (ord << 16) | (0xffffu - static_cast<uint32_t>(e));
+    for (int h = 0; h < 2; ++h) {
+      const int e0 = h * 256 + 8 * lane;
+      uint32_t w[4] = {0, 0, 0, 0};
+      if (vec && e0 < E) {
+        const uint4 v = *reinterpret_cast<const uint4*>(row + e0);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
       }
-      key[i] = kv;
-      lmax = max(lmax, kv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = e0 + j;
+        uint32_t kv = 0;
+        if (e < E) {
+          uint32_t b = vec ? ((w[j >> 1] >> (16 * (j & 1))) & 0xffffu) : row[e];
+          if (b == 0x8000u) b = 0;
+          const uint32_t ord = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+          kv = (ord << 16) | (0xffffu - static_cast<uint32_t>(e));
+        }
+        key[h * 8 + j] = kv;
+        lmax = max(lmax, kv);
+      }
     }
     for (int r = 0; r < k; ++r) {
       const uint32_t best = __reduce_max_sync(0xffffffffu, lmax);
@@ -113,11 +126,12 @@ __device__ __forceinline__ void topk_token(const uint16_t* __restrict__ row, con
         sel_v = bf16_to_f32(static_cast<uint16_t>(b));
         sel_i = mid;
       }
-      if ((mid & 31) == lane) {  // the owner drops the winner and refreshes its local maximum
+      if (((mid & 255) >> 3) == lane) {  // the owner drops the winner and refreshes its local maximum
+        const int slot = ((mid >> 8) << 3) | (mid & 7);
         lmax = 0;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          if (i == (mid >> 5)) key[i] = 0;
+          if (i == slot) key[i] = 0;
           lmax = max(lmax, key[i]);
         }
       }
