@@ -238,7 +238,11 @@ int32_t q4t_moe_forward_workspace_layout(int32_t T, int32_t k, int32_t hs,
  * be in [1,16] ("k out of range"); a short workspace fails with "workspace
  * too small".  fixed_ids (may be NULL) replaces the selected experts by a
  * caller-supplied int32 [T,k] table while the weights are still the softmax of
- * the current logits at those ids (the replay hook, moe.cu:214-237).          */
+ * the current logits at those ids (the replay hook, moe.cu:214-237).
+ * flags: bit 0 = materialise the bf16 gate|up projections (gu_out and the
+ * shared expert's), bit 1 = materialise the fp32 routed sum in the workspace's
+ * `routed` region; both are what the reference always writes and only its
+ * diagnostics read, so they are off unless asked for.                         */
 int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
                         const q4t_extra_weights* extra, uint16_t* y, int32_t T,
                         int32_t k, void* workspace, size_t workspace_bytes,

@@ -629,7 +629,8 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
   uint16_t* logits = reinterpret_cast<uint16_t*>(base + F.logits);
   int32_t* ids = reinterpret_cast<int32_t*>(base + F.expert_ids);
   float* rw = reinterpret_cast<float*>(base + F.router_w);
-  float* routed_f32 = reinterpret_cast<float*>(base + F.routed);
+  // the fp32 routed sum is a diagnostic region: written only on request (flags bit 1)
+  float* routed_f32 = (flags & 2u) ? reinterpret_cast<float*>(base + F.routed) : nullptr;
   uint16_t* sgu = reinterpret_cast<uint16_t*>(base + F.shared_gu);
   uint16_t* sact = reinterpret_cast<uint16_t*>(base + F.shared_act);
   uint16_t* sdown = reinterpret_cast<uint16_t*>(base + F.shared_down);

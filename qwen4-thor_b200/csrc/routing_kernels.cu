@@ -599,7 +599,7 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(uint16_t* __restr
 // One block of 256 threads per token: routed sum (slot order), gate =
 // sigmoid(x . gate_scalar) with the reference's 256 strided fused partials and
 // halving tree, y = bf16(fma(gate, shared_down, routed)) (MoECombineKernel,
-// src/model/moe.cu:291-321).  Also leaves the fp32 routed sum in `routed`.
+// src/model/moe.cu:291-321).  Also leaves the fp32 routed sum in `routed` when that is not null.
 // PRELOAD: request all of the token's rows before the first is used (k <= 16), so that the
 // slot-order sum costs one memory round trip instead of k: 3 us of a 13 us decode launch; at
 // 16 K tokens the extra registers cost more than the latency they hide (254 vs 175 us).
@@ -666,9 +666,11 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = 0.0f + a[j];  // the reference adds into a zeroed buffer
-    float4* rdst = reinterpret_cast<float4*>(routed + static_cast<size_t>(t) * hs) + c8 * 2;
-    rdst[0] = make_float4(a[0], a[1], a[2], a[3]);
-    rdst[1] = make_float4(a[4], a[5], a[6], a[7]);
+    if (routed) {  // optional fp32 copy of the routed sum
+      float4* rdst = reinterpret_cast<float4*>(routed + static_cast<size_t>(t) * hs) + c8 * 2;
+      rdst[0] = make_float4(a[0], a[1], a[2], a[3]);
+      rdst[1] = make_float4(a[4], a[5], a[6], a[7]);
+    }
     const uint4 sv = __ldg(reinterpret_cast<const uint4*>(shared_down + static_cast<size_t>(t) * hs) + c8);
     const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
     uint32_t o[4];

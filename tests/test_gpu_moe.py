@@ -124,7 +124,7 @@ def test_moe_forward_vs_oracle(q4t, gpu_lib, T):
     x = synth.make_x(T, hs, seed=T)
     fwd = q4t.MoEForward(dl, T, k)
     y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
-    fwd(dev(x), y, flags=1)
+    fwd(dev(x), y, flags=3)
     fwd.status()
     logits = host(fwd.region("logits", torch.int16, T * E)).reshape(T, E)
     ids = host(fwd.region("expert_ids", torch.int32, T * k)).reshape(T, k)
@@ -218,7 +218,7 @@ def test_config0_full_size_layer_vs_oracle(q4t, gpu_lib):
     x = synth.make_x(T, hs, seed=16)
     fwd = q4t.MoEForward(dl, T, k)
     y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
-    fwd(dev(x), y, flags=1)
+    fwd(dev(x), y, flags=3)
     fwd.status()
     logits = host(fwd.region("logits", torch.int16, T * E)).reshape(T, E)
     ids = host(fwd.region("expert_ids", torch.int32, T * k)).reshape(T, k)
