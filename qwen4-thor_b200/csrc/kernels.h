@@ -51,7 +51,7 @@ cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* 
                                    const int32_t* tile_row0, const int32_t* rows_dev, int k, int E,
                                    cudaStream_t stream);
 // One input scale for all experts: quantise each of the T tokens once and write codes and
-// scales to its k grouped rows (row_of_flat[t*k+s], -1 = skipped); K % 64 == 0, k <= 32.
+// scales to its k grouped rows (row_of_flat[t*k+s], -1 = skipped); K % 64 == 0, K >= 128, k <= 16.
 cudaError_t launch_quantize_scatter(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int T, int K,
                                     float global_scale, const int32_t* row_of_flat, const int32_t* row_tile,
                                     const int32_t* tile_row0, int k, cudaStream_t stream);

@@ -123,57 +123,65 @@ __global__ void __launch_bounds__(256) publish_tokens_kernel(const uint16_t* __r
 }
 
 // Quantises every token once (one input scale for all experts) and writes the codes and
-// scale bytes straight to the token's k grouped rows: one warp per token, a lane owns four
-// neighbouring groups (64 values), so every destination row receives 1 KB-contiguous code
-// runs and one 4-byte scale word per K-tile in its tile-local atom.  Replaces "quantise the
-// tokens, then copy each row k times" (half the memory traffic).  K a multiple of 64.
+// scale bytes straight to the token's k grouped rows.  One thread per group of 16 values, as
+// in the plain quantiser (neighbouring lanes read and write neighbouring 32 / 8 bytes; four
+// lanes merge their scale bytes into one word of the destination row's tile-local atom); the
+// k destinations of the block's tokens are looked up once into shared memory.  Replaces
+// "quantise the tokens, then copy each row k times" (half the memory traffic).
+// K a multiple of 64 and at least 128, k <= 16.
+constexpr int kScatterMaxTokens = 34;  // tokens one block of 256 groups can touch when K >= 128
 __global__ void __launch_bounds__(256) quantize_scatter_kernel(
     const uint16_t* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_tiles, int T, int K,
     float global_scale, const int32_t* __restrict__ row_of_flat, const int32_t* __restrict__ row_tile,
     const int32_t* __restrict__ tile_row0, int k) {
   chain_wait();
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (t >= T) return;
+  __shared__ int32_t s_row[kScatterMaxTokens * 16], s_tile[kScatterMaxTokens * 16], s_in[kScatterMaxTokens * 16];
   const int groups = K >> 4, ntk = K >> 6;
-  // where the token's k rows go (lane s < k holds slot s; fetched once, shared by shuffle)
-  int my_row = -1, my_tile = 0, my_in_tile = 0;
-  if (lane < k) {
-    my_row = row_of_flat[t * k + lane];
-    if (my_row >= 0) {
-      my_tile = row_tile[my_row];
-      my_in_tile = my_row - tile_row0[my_tile];
+  const int64_t idx0 = static_cast<int64_t>(blockIdx.x) * 256, total = static_cast<int64_t>(T) * groups;
+  const int tok0 = static_cast<int>(idx0 / groups);
+  const int tok1 = static_cast<int>(min(total - 1, idx0 + 255) / groups);
+  for (int j = threadIdx.x; j < (tok1 - tok0 + 1) * k; j += 256) {
+    const int r = row_of_flat[(tok0 + j / k) * k + j % k];
+    s_row[j] = r;
+    if (r >= 0) {
+      const int tile = row_tile[r];
+      s_tile[j] = tile;
+      s_in[j] = r - tile_row0[tile];
     }
   }
-  for (int base = 0; base < groups; base += 128) {  // warp-uniform trip count: the shuffles below need every lane
-    const int g0 = base + lane * 4;
-    const bool active = g0 < groups;
-    uint32_t codes[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sfw = 0;
-    if (active) {
-      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * K + g0 * 16);
+  __syncthreads();
+  const int64_t idx = idx0 + threadIdx.x;
+  const bool live = idx < total;
+  const int token = live ? static_cast<int>(idx / groups) : tok0;
+  const int g = live ? static_cast<int>(idx % groups) : 0;
+  uint32_t lo = 0, hi = 0, sf = 0;
+  if (live) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(token) * K + g * 16);
+    const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float a[16];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 v0 = __ldg(src + 2 * j), v1 = __ldg(src + 2 * j + 1);
-        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        float a[16];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          a[2 * i] = bf16x2_lo(w[i]);
-          a[2 * i + 1] = bf16x2_hi(w[i]);
-        }
-        sfw |= quantize_group16(a, global_scale, codes[2 * j], codes[2 * j + 1]) << (8 * j);
-      }
+    for (int j = 0; j < 8; ++j) {
+      a[2 * j] = bf16x2_lo(w[j]);
+      a[2 * j + 1] = bf16x2_hi(w[j]);
     }
-    for (int s = 0; s < k; ++s) {
-      const int r = __shfl_sync(0xffffffffu, my_row, s);
-      const int tile = __shfl_sync(0xffffffffu, my_tile, s);
-      const int in_tile = __shfl_sync(0xffffffffu, my_in_tile, s);
-      if (r < 0 || !active) continue;
-      uint4* c = reinterpret_cast<uint4*>(packed + static_cast<size_t>(r) * (K >> 1) + static_cast<size_t>(g0) * 8);
-      c[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-      c[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
-      *reinterpret_cast<uint32_t*>(sf_tiles + (static_cast<size_t>(tile) * ntk + (g0 >> 2)) * 512u +
-                                   sf_in_atom(static_cast<uint32_t>(in_tile), 0)) = sfw;
-    }
+    sf = quantize_group16(a, global_scale, lo, hi);
+  }
+  // groups is a multiple of 4, so the four lanes of a quad hold groups g..g+3 of one token
+  uint32_t word = sf;
+  word |= __shfl_down_sync(0xffffffffu, sf, 1) << 8;
+  word |= __shfl_down_sync(0xffffffffu, sf, 2) << 16;
+  word |= __shfl_down_sync(0xffffffffu, sf, 3) << 24;
+  if (!live) return;
+  const bool leader = (threadIdx.x & 3) == 0;
+  const int base = (token - tok0) * k;
+  for (int s = 0; s < k; ++s) {
+    const int r = s_row[base + s];
+    if (r < 0) continue;
+    *reinterpret_cast<uint2*>(packed + static_cast<size_t>(r) * (K >> 1) + static_cast<size_t>(g) * 8) = make_uint2(lo, hi);
+    if (leader)
+      *reinterpret_cast<uint32_t*>(sf_tiles + (static_cast<size_t>(s_tile[base + s]) * ntk + (g >> 2)) * 512u +
+                                   sf_in_atom(static_cast<uint32_t>(s_in[base + s]), 0)) = word;
   }
 }
 
@@ -287,9 +295,11 @@ cudaError_t launch_gather_quantize(const uint16_t* x, uint8_t* packed, uint8_t* 
 cudaError_t launch_quantize_scatter(const uint16_t* x, uint8_t* packed, uint8_t* sf_tiles, int T, int K,
                                     float global_scale, const int32_t* row_of_flat, const int32_t* row_tile,
                                     const int32_t* tile_row0, int k, cudaStream_t stream) {
-  if (T == 0) return cudaSuccess;
-  return launch_chained(quantize_scatter_kernel, dim3((T + 7) / 8), dim3(256), 0, stream, x, packed, sf_tiles, T, K,
-                        global_scale, row_of_flat, row_tile, tile_row0, k);
+  const int64_t total = static_cast<int64_t>(T) * (K / 16);
+  if (total == 0) return cudaSuccess;
+  if (K < 128 || K % 64 || k > 16) return cudaErrorInvalidValue;
+  return launch_chained(quantize_scatter_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, stream,
+                        x, packed, sf_tiles, T, K, global_scale, row_of_flat, row_tile, tile_row0, k);
 }
 
 cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed,
