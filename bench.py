@@ -8,12 +8,16 @@ experts, top-10, intermediate 512, shared expert 512, T = 128 tokens per step,
 uniform-random routing, NVFP4 weights ~ N(0, 0.02).  Each step runs one layer
 forward; successive steps rotate over several independent layer weight sets
 and inputs so that no step finds its weights in L2.  The line also carries the
-sweep over T in {1, 8, 32, 64} and the 16384-token Zipf-skewed prefill layer
-under "also".
+sweep over T in {1, 8, 32, 64}, the 16384-token Zipf-skewed prefill layer and
+the 48-layer decode stack (x <- x + MoE(RMSNorm(x)), eager and as one CUDA
+graph) under "also".  "e2e" is the same step fed from pinned host memory with
+the result copied back, copies on their own streams.
 
 N > 1 (launched by torchrun, one rank per GPU): the expert-parallel prefill
-layer, T = 32768 tokens per step sharded by rank, 512/N experts per GPU,
-all-to-all dispatch and return over NCCL.
+layer, T = 32768 tokens per step sharded by rank (strong scaling).  Default
+exchange: kernels store into peer memory over NVLink (NCCL carries only the
+expert ids and one barrier), the most used experts replicated on every GPU;
+--exchange rows is the all-to-all of rows over NCCL with 512/N experts per GPU.
 
 --impl reference times the reference's CPU formulation of the layer (the CPU
 oracle's restatement of the reference's host-side MoE) on the host cores.
