@@ -248,6 +248,37 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
                         int32_t k, void* workspace, size_t workspace_bytes,
                         const int32_t* fixed_ids, uint32_t flags, void* stream);
 
+/* ---- BF16 routed experts: the MTP draft layer's MoE (include/q4t/mtp/moe_bf16.h:
+ * 36-123, src/mtp/moe_bf16.cu).  Same orchestration as the NVFP4 layer with
+ * plain BF16 expert GEMMs: h = bf16(x.W_gu[e]^T), inter = bf16((g*sigmoid(g))*u),
+ * out = bf16(inter.W_dn[e]^T), y[t] += r[t,e]*out.  Weights as in the
+ * checkpoint: gu [E, 2*moe_is, hs] (gate rows then up rows per expert), down
+ * [E, hs, moe_is], bf16 row-major.  The routed sum is formed in slot order
+ * (the reference adds with atomicAdd in no particular order), the router is
+ * the one of q4t_moe_forward (same selected set and weights as the MTP path's
+ * own top-k kernel, ids in value order).  y of the routed call: fp32 [M,hs],
+ * accumulated into (zero it first), as in MoeBf16RoutedForward.              */
+typedef struct q4t_bf16_expert_weights {
+  int32_t E, hs, moe_is, reserved;
+  const uint16_t* gu;
+  const uint16_t* down;
+} q4t_bf16_expert_weights;
+size_t q4t_moe_bf16_workspace_bytes(int32_t M, int32_t k, int32_t hs,
+                                    int32_t moe_is, int32_t E);
+int32_t q4t_moe_bf16_routed_forward(const uint16_t* x, const int32_t* expert_ids,
+                                    const float* router_w, float* y,
+                                    const q4t_bf16_expert_weights* weights,
+                                    void* workspace, size_t workspace_bytes,
+                                    int32_t M, int32_t k, void* stream);
+size_t q4t_moe_bf16_forward_workspace_bytes(int32_t T, int32_t k, int32_t hs,
+                                            int32_t moe_is, int32_t shared_is,
+                                            int32_t E);
+int32_t q4t_moe_bf16_forward(const uint16_t* x,
+                             const q4t_bf16_expert_weights* routed,
+                             const q4t_extra_weights* extra, uint16_t* y,
+                             int32_t T, int32_t k, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 /* ---- expert parallelism.  The reference engine is single-GPU (it has no
  * NCCL/MPI code), so these three entry points have no counterpart there; they
  * cut q4t_moe_forward at the two points where rows cross GPUs.  Experts are

@@ -321,5 +321,23 @@ def residual_rmsnorm_bf16(x, y, eps: float = 1e-6):
     return x, h
 
 
+def moe_bf16_routed_forward(x, ids, rw, gu, down, y0=None):
+    """The MTP draft layer's BF16 routed experts (q4o_moe_bf16_routed_forward): gu [E, 2*is, hs],
+    down [E, hs, is] bf16 bit patterns; returns fp32 [T, hs] (added to y0 when given)."""
+    x = np.ascontiguousarray(x, np.uint16)
+    ids = np.ascontiguousarray(ids, np.int32)
+    rw = np.ascontiguousarray(rw, np.float32)
+    gu = np.ascontiguousarray(gu, np.uint16)
+    down = np.ascontiguousarray(down, np.uint16)
+    T, hs = x.shape
+    k = ids.shape[1]
+    E, two_is, _ = gu.shape
+    y = np.zeros((T, hs), np.float32) if y0 is None else np.array(y0, np.float32, copy=True, order="C")
+    lib().q4o_moe_bf16_routed_forward(_p(x, C.c_uint16), _p(ids, C.c_int32), _p(rw, C.c_float), _p(gu, C.c_uint16),
+                                      _p(down, C.c_uint16), C.c_int(T), C.c_int(k), C.c_int(E), C.c_int(hs),
+                                      C.c_int(two_is // 2), _p(y, C.c_float))
+    return y
+
+
 def num_threads() -> int:
     return int(lib().q4o_num_threads())

@@ -769,6 +769,47 @@ void q4o_residual_rmsnorm_bf16(uint16_t* x, const uint16_t* y, int T, int hs, fl
   q4o_rmsnorm_bf16(x, T, hs, eps, h);
 }
 
+/* The MTP draft layer's BF16 routed experts (src/mtp/moe_bf16.cu:93-131, 340-420): per
+ * (token, slot) h = bf16(x . W_gu[e]^T) with fp32 accumulation (sequential here; the
+ * reference's library GEMM leaves the order open), inter = bf16((g * (1/(1+expf(-g)))) * u),
+ * out = bf16(inter . W_dn[e]^T), y[t] += r * out.  The reference adds with atomicAdd in
+ * no fixed order; here the slots are added in order with a fused multiply-add, as the
+ * NVFP4 layer does.  gu [E, 2*is, hs], down [E, hs, is] bf16; y fp32 [T, hs] accumulated into. */
+void q4o_moe_bf16_routed_forward(const uint16_t* x, const int32_t* ids, const float* rw, const uint16_t* gu,
+                                 const uint16_t* down, int T, int k, int E, int hs, int is, float* y) {
+#pragma omp parallel for schedule(dynamic)
+  for (int t = 0; t < T; ++t) {
+    float* h = (float*)malloc(sizeof(float) * (size_t)(2 * is + is + hs));
+    float* inter = h + 2 * is;
+    float* xf = inter + is;
+    for (int c = 0; c < hs; ++c) xf[c] = q4o_bf16_to_float(x[(size_t)t * hs + c]);
+    for (int s = 0; s < k; ++s) {
+      const int e = ids[t * k + s];
+      if (e < 0 || e >= E) continue;
+      const uint16_t* wg = gu + (size_t)e * 2 * is * hs;
+      for (int n = 0; n < 2 * is; ++n) {
+        float acc = 0.0f;
+        for (int c = 0; c < hs; ++c) acc += xf[c] * q4o_bf16_to_float(wg[(size_t)n * hs + c]);
+        h[n] = q4o_bf16_to_float(q4o_float_to_bf16(acc));
+      }
+      for (int n = 0; n < is; ++n) {
+        const float g = h[n], u = h[is + n];
+        const float sg = 1.0f / (1.0f + expf(-g));
+        inter[n] = q4o_bf16_to_float(q4o_float_to_bf16((g * sg) * u));
+      }
+      const uint16_t* wd = down + (size_t)e * hs * is;
+      const float w = rw[t * k + s];
+      for (int c = 0; c < hs; ++c) {
+        float acc = 0.0f;
+        for (int n = 0; n < is; ++n) acc += inter[n] * q4o_bf16_to_float(wd[(size_t)c * is + n]);
+        const float o = q4o_bf16_to_float(q4o_float_to_bf16(acc));
+        y[(size_t)t * hs + c] = fmaf(w, o, y[(size_t)t * hs + c]);
+      }
+    }
+    free(h);
+  }
+}
+
 int q4o_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -41,6 +41,12 @@ class RoutedWsLayout(C.Structure):
         "inter_sf_tiles", "status", "max_tiles", "total")]
 
 
+class Bf16ExpertWeights(C.Structure):
+    """q4t_bf16_expert_weights: the MTP draft layer's BF16 routed experts."""
+    _fields_ = [("E", C.c_int32), ("hs", C.c_int32), ("moe_is", C.c_int32), ("reserved", C.c_int32),
+                ("gu", C.c_void_p), ("down", C.c_void_p)]
+
+
 class EpPeerTable(C.Structure):
     """q4t_ep_peer_table: who publishes what, for the pull/push expert-parallel path."""
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("tokens_per_rank", C.c_int32),
@@ -65,6 +71,8 @@ EXPORTS = [
     "q4t_moe_routed_forward_noalloc", "q4t_ep_dispatch_workspace_bytes", "q4t_ep_dispatch",
     "q4t_moe_expert_rows", "q4t_moe_finish_workspace_bytes", "q4t_moe_finish",
     "q4t_moe_shared_expert", "q4t_moe_combine", "q4t_residual_rmsnorm_bf16",
+    "q4t_moe_bf16_workspace_bytes", "q4t_moe_bf16_routed_forward", "q4t_moe_bf16_forward_workspace_bytes",
+    "q4t_moe_bf16_forward",
     "q4t_peer_buffer_alloc", "q4t_peer_buffer_free", "q4t_peer_buffer_export", "q4t_peer_buffer_open",
     "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_ep_route_publish", "q4t_ep_combine", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
 ]
@@ -121,6 +129,13 @@ def load():
     L.q4t_peer_buffer_close.argtypes = [vp]
     L.q4t_moe_shared_expert.argtypes = [vp, C.POINTER(ExtraWeights), i32, vp, sz, vp]
     L.q4t_moe_combine.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, sz, vp]
+    L.q4t_moe_bf16_workspace_bytes.restype = C.c_size_t
+    L.q4t_moe_bf16_workspace_bytes.argtypes = [i32] * 5
+    L.q4t_moe_bf16_forward_workspace_bytes.restype = C.c_size_t
+    L.q4t_moe_bf16_forward_workspace_bytes.argtypes = [i32] * 6
+    L.q4t_moe_bf16_routed_forward.argtypes = [vp, vp, vp, vp, C.POINTER(Bf16ExpertWeights), vp, sz, i32, i32, vp]
+    L.q4t_moe_bf16_forward.argtypes = [vp, C.POINTER(Bf16ExpertWeights), C.POINTER(ExtraWeights), vp, i32, i32, vp, sz,
+                                       vp]
     L.q4t_residual_rmsnorm_bf16.argtypes = [vp, vp, vp, i32, i32, f32, vp]
     L.q4t_ep_route_publish.argtypes = [vp, C.POINTER(ExtraWeights), C.POINTER(EpPeerTable), i32, f32, vp, vp, vp, vp,
                                        sz, vp]
@@ -342,6 +357,34 @@ class MoEForward:
 
 STAGES = ("router_logits", "topk", "permutation", "gather_quantise", "gate_up_gemm", "down_gemm",
           "shared_expert", "combine")
+
+
+class Bf16MoE:
+    """The MTP draft layer's MoE: BF16 routed experts (gu [E, 2*moe_is, hs], down [E, hs, moe_is],
+    CUDA bf16 tensors) with the router and shared expert of `extra_layer` (a DeviceLayer whose
+    EXTRA tensors are set)."""
+
+    def __init__(self, gu, down, extra_layer, T: int, k: int, device="cuda"):
+        import torch
+        E, two_is, hs = gu.shape
+        self.gu, self.down, self.extra_layer, self.T, self.k = gu, down, extra_layer, T, k
+        self.E, self.hs, self.moe_is = E, hs, two_is // 2
+        self.w = Bf16ExpertWeights(E, hs, self.moe_is, 0, gu.data_ptr(), down.data_ptr())
+        lib = load()
+        self.routed_bytes = lib.q4t_moe_bf16_workspace_bytes(T, k, hs, self.moe_is, E)
+        sis = extra_layer.shared_is if extra_layer is not None else 128
+        self.forward_bytes = lib.q4t_moe_bf16_forward_workspace_bytes(T, k, hs, self.moe_is, sis, E)
+        self.ws = torch.empty(max(self.routed_bytes, self.forward_bytes), dtype=torch.uint8, device=device)
+
+    def routed(self, x, ids, rw, y, stream=None):
+        check(load().q4t_moe_bf16_routed_forward(_ptr(x), _ptr(ids), _ptr(rw), _ptr(y), C.byref(self.w), _ptr(self.ws),
+                                                 self.ws.numel(), self.T, self.k, _stream_ptr(stream)))
+        return y
+
+    def forward(self, x, y, stream=None):
+        check(load().q4t_moe_bf16_forward(_ptr(x), C.byref(self.w), C.byref(self.extra_layer.extra), _ptr(y), self.T,
+                                          self.k, _ptr(self.ws), self.ws.numel(), _stream_ptr(stream)))
+        return y
 
 
 def residual_rmsnorm(x, y, h, eps: float = 1e-6, stream=None):

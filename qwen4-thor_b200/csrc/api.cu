@@ -338,6 +338,78 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   return Q4T_OK;
 }
 
+// The routed experts with BF16 weights (the MTP draft layer's MoE, src/mtp/moe_bf16.cu:
+// 300-420): gather the token rows in expert order, gate/up GEMM with the SwiGLU epilogue
+// (bf16 projections, bf16((g*sigmoid(g))*u)), down GEMM to bf16 rows.  `compact` is the
+// [M*k, hs] bf16 row buffer; the intermediate reuses the gu_out region, the result dn_out.
+int run_routed_core_bf16(const DeviceState* ds, const uint16_t* x, const int32_t* ids,
+                         const q4t_bf16_expert_weights* w, const RoutedPtrs& P, uint16_t* compact, int M, int k,
+                         cudaStream_t st, bool plan_done) {
+  const int E = w->E, hs = w->hs, is = w->moe_is;
+  const int R = M * k;
+  const q4t_routed_ws_layout& L = P.L;
+  cudaError_t e;
+  const q4t::PlanTables pt = plan_tables(P, E);
+  if (!plan_done && (e = q4t::launch_plan(ids, R, E, static_cast<int>(L.max_tiles), pt, st)) != cudaSuccess)
+    return fail_cuda("plan launch", e);
+  stage_end(2, st);
+  if ((e = q4t::launch_gather_rows(x, pt.flat_of_row, k, pt.offsets + E, R, hs, compact, nullptr, nullptr, st)) !=
+      cudaSuccess)
+    return fail_cuda("row gather launch", e);
+  stage_end(3, st);
+  uint16_t* inter = P.at<uint16_t>(L.gu_out);
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if ((rc = make_tmap(ds, &tm_a, true, compact, hs, R, static_cast<uint64_t>(hs) * 2)) != Q4T_OK) return rc;
+  if ((rc = make_tmap(ds, &tm_b, true, w->gu, hs, static_cast<uint64_t>(E) * 2 * is, static_cast<uint64_t>(hs) * 2)) !=
+      Q4T_OK)
+    return rc;
+  q4t::GemmArgs g{};
+  g.K = hs;
+  g.tile_cols = 256;
+  g.n_tiles = is / 128;
+  g.n_per_tile = 128;
+  g.up_row_offset = is;
+  g.b_rows_per_group = 2 * is;
+  g.b_rows_valid = is;
+  g.ntiles_dev = pt.ntiles;
+  g.tile_expert = pt.tile_expert;
+  g.tile_row0 = pt.tile_row0;
+  g.tile_nrows = pt.tile_nrows;
+  g.total_rows = R;
+  g.out = inter;
+  g.ldo = is;
+  g.alpha_const = 1.0f;
+  g.status = P.at<int32_t>(L.status);
+  if ((e = q4t::launch_gemm_bf16(tm_a, tm_b, g, q4t::Epilogue::kSwigluBf16, ds->num_sms, st)) != cudaSuccess)
+    return fail_cuda("bf16 gate/up GEMM launch", e);
+  stage_end(4, st);
+  if ((rc = make_tmap(ds, &tm_a, true, inter, is, R, static_cast<uint64_t>(is) * 2)) != Q4T_OK) return rc;
+  if ((rc = make_tmap(ds, &tm_b, true, w->down, is, static_cast<uint64_t>(E) * hs, static_cast<uint64_t>(is) * 2)) !=
+      Q4T_OK)
+    return rc;
+  q4t::GemmArgs d{};
+  d.K = is;
+  d.tile_cols = 256;
+  d.n_tiles = (hs + 255) / 256;
+  d.n_per_tile = 256;
+  d.b_rows_per_group = hs;
+  d.b_rows_valid = hs;
+  d.ntiles_dev = pt.ntiles;
+  d.tile_expert = pt.tile_expert;
+  d.tile_row0 = pt.tile_row0;
+  d.tile_nrows = pt.tile_nrows;
+  d.total_rows = R;
+  d.out = P.at<uint16_t>(L.dn_out);
+  d.ldo = hs;
+  d.alpha_const = 1.0f;
+  d.status = P.at<int32_t>(L.status);
+  if ((e = q4t::launch_gemm_bf16(tm_a, tm_b, d, q4t::Epilogue::kStoreBf16, ds->num_sms, st)) != cudaSuccess)
+    return fail_cuda("bf16 down GEMM launch", e);
+  stage_end(5, st);
+  return Q4T_OK;
+}
+
 // y[M,N] = bf16(x . w^T): exact-order warp GEMV for M <= 8, tensor cores above.
 int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
                     int K, cudaStream_t st) {
@@ -606,18 +678,27 @@ int32_t q4t_moe_forward_workspace_layout(int32_t T, int32_t k, int32_t hs, int32
   return Q4T_OK;
 }
 
-int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, const q4t_extra_weights* extra,
-                        uint16_t* y, int32_t T, int32_t k, void* workspace, size_t workspace_bytes,
-                        const int32_t* fixed_ids, uint32_t flags, void* stream) {
+}  // extern "C"
+
+namespace {
+// The whole layer for either kind of routed experts (exactly one of routed / routed_bf16 is set).
+int moe_forward_impl(const uint16_t* x, const q4t_routed_weights* routed, const q4t_bf16_expert_weights* routed_bf16,
+                     const q4t_extra_weights* extra, uint16_t* y, int32_t T, int32_t k, void* workspace,
+                     size_t workspace_bytes, const int32_t* fixed_ids, uint32_t flags, void* stream) {
   if (T <= 0) return Q4T_OK;                                           // src/model/moe.cu:442
   if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");  // moe.cu:443
-  if (!routed || !extra) return fail(Q4T_ERR_INVALID, "null weights");
-  const int E = extra->E, hs = extra->hs, sis = extra->shared_is, is = routed->moe_is;
-  if (routed->E != E || routed->hs != hs) return fail(Q4T_ERR_INVALID, "routed and extra weights disagree on E/hs");
+  if ((!routed && !routed_bf16) || !extra) return fail(Q4T_ERR_INVALID, "null weights");
+  const int E = extra->E, hs = extra->hs, sis = extra->shared_is;
+  const int is = routed ? routed->moe_is : routed_bf16->moe_is;
+  if ((routed ? routed->E : routed_bf16->E) != E || (routed ? routed->hs : routed_bf16->hs) != hs)
+    return fail(Q4T_ERR_INVALID, "routed and extra weights disagree on E/hs");
   if (!routed_dims_ok(E, hs, is) || E > 512 || k > E || sis <= 0 || sis % 128)
     return fail(Q4T_ERR_INVALID, "unsupported dims (hs, moe_is, shared_is multiples of 128; E <= 512)");
   q4t_forward_ws_layout F;
   forward_layout(T, k, hs, is, sis, E, &F);
+  // BF16 experts: the gathered bf16 rows [T*k, hs] follow the regions of the NVFP4 layout
+  const size_t compact_at = F.total;
+  if (routed_bf16) F.total = align_up(compact_at + static_cast<size_t>(T) * k * hs * 2, 256);
   if (workspace_bytes < F.total) return fail(Q4T_ERR_WORKSPACE, "workspace too small");  // moe.cu:444-447
   if (!x || !y || !workspace) return fail(Q4T_ERR_INVALID, "null pointer");
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(Q4T_ERR_INVALID, "workspace must be 256-byte aligned");
@@ -667,7 +748,12 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
   stage_end(1, st);
 
   // 3. routed experts
-  if ((rc = run_routed_core(ds, x, ids, routed, P, T, k, flags, st, fused_route)) != Q4T_OK) return rc;
+  if (routed) {
+    if ((rc = run_routed_core(ds, x, ids, routed, P, T, k, flags, st, fused_route)) != Q4T_OK) return rc;
+  } else if ((rc = run_routed_core_bf16(ds, x, ids, routed_bf16, P, reinterpret_cast<uint16_t*>(base + compact_at), T, k,
+                                        st, fused_route)) != Q4T_OK) {
+    return rc;
+  }
 
   // 4-6. shared expert
   if (fork) {
@@ -684,6 +770,67 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
     return fail_cuda("combine launch", e);
   stage_end(7, st);
   return Q4T_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, const q4t_extra_weights* extra,
+                        uint16_t* y, int32_t T, int32_t k, void* workspace, size_t workspace_bytes,
+                        const int32_t* fixed_ids, uint32_t flags, void* stream) {
+  if (T > 0 && k > 0 && k <= 16 && !routed) return fail(Q4T_ERR_INVALID, "null weights");
+  return moe_forward_impl(x, routed, nullptr, extra, y, T, k, workspace, workspace_bytes, fixed_ids, flags, stream);
+}
+
+// ---- BF16 routed experts (the MTP draft layer)
+size_t q4t_moe_bf16_workspace_bytes(int32_t M, int32_t k, int32_t hs, int32_t moe_is, int32_t E) {
+  if (M <= 0 || k <= 0 || !routed_dims_ok(E, hs, moe_is)) return 0;
+  q4t_routed_ws_layout L;
+  routed_layout(M, k, hs, moe_is, E, &L);
+  return align_up(L.total, 256) + align_up(static_cast<size_t>(M) * k * hs * 2, 256);
+}
+
+int32_t q4t_moe_bf16_routed_forward(const uint16_t* x, const int32_t* expert_ids, const float* router_w, float* y,
+                                    const q4t_bf16_expert_weights* w, void* workspace, size_t workspace_bytes,
+                                    int32_t M, int32_t k, void* stream) {
+  if (!w) return fail(Q4T_ERR_INVALID, "null weights");
+  if (M <= 0 || k <= 0 || w->E <= 0 || w->hs <= 0 || w->moe_is <= 0) return fail(Q4T_ERR_INVALID, "invalid MoE forward dims");
+  if (!routed_dims_ok(w->E, w->hs, w->moe_is))
+    return fail(Q4T_ERR_INVALID, "hs and moe_is must be multiples of 128 and E <= 1024");
+  if (!x || !expert_ids || !router_w || !y || !workspace || !w->gu || !w->down) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(Q4T_ERR_INVALID, "workspace must be 256-byte aligned");
+  if (workspace_bytes < q4t_moe_bf16_workspace_bytes(M, k, w->hs, w->moe_is, w->E))
+    return fail(Q4T_ERR_WORKSPACE, "workspace too small");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  RoutedPtrs P;
+  routed_layout(M, k, w->hs, w->moe_is, w->E, &P.L);
+  P.base = static_cast<uint8_t*>(workspace);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  stage_begin(st);
+  stage_end(1, st);
+  uint16_t* compact = reinterpret_cast<uint16_t*>(P.base + align_up(P.L.total, 256));
+  if ((rc = run_routed_core_bf16(ds, x, expert_ids, w, P, compact, M, k, st, false)) != Q4T_OK) return rc;
+  cudaError_t e = q4t::launch_routed_combine(P.at<uint16_t>(P.L.dn_out), P.at<int32_t>(P.L.row_of_flat), router_w, y, M,
+                                             k, w->hs, st);
+  stage_end(7, st);
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("combine launch", e);
+}
+
+size_t q4t_moe_bf16_forward_workspace_bytes(int32_t T, int32_t k, int32_t hs, int32_t moe_is, int32_t shared_is,
+                                            int32_t E) {
+  if (T <= 0 || k <= 0 || shared_is <= 0 || !routed_dims_ok(E, hs, moe_is)) return 0;
+  q4t_forward_ws_layout F;
+  forward_layout(T, k, hs, moe_is, shared_is, E, &F);
+  return align_up(F.total + static_cast<size_t>(T) * k * hs * 2, 256);
+}
+
+int32_t q4t_moe_bf16_forward(const uint16_t* x, const q4t_bf16_expert_weights* routed, const q4t_extra_weights* extra,
+                             uint16_t* y, int32_t T, int32_t k, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  if (T > 0 && k > 0 && k <= 16 && (!routed || !routed->gu || !routed->down)) return fail(Q4T_ERR_INVALID, "null weights");
+  return moe_forward_impl(x, nullptr, routed, extra, y, T, k, workspace, workspace_bytes, nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------- expert parallelism

@@ -9,6 +9,7 @@
 #include <vector>
 
 #include "q4t/model/moe.h"
+#include "q4t/mtp/moe_bf16.h"
 #include "q4t/quant/act_quant.h"
 #include "q4t/quant/moe_gemm.h"
 #include "q4t/quant/moe_weights.h"
@@ -95,6 +96,22 @@ int main() {
   CHECK(quant::QuantizeActivationToFp4Async(d_x, static_cast<uint8_t*>(rws), static_cast<uint8_t*>(rws) + 4096, T, hs,
                                             0.002f, 0) == cudaSuccess);
   CHECK(cudaDeviceSynchronize() == cudaSuccess);
+  // the MTP draft layer's BF16 experts through the reference-shaped calls
+  mtp::MoeBf16Weights B;
+  B.E = E; B.hs = hs; B.moe_is = is;
+  upload_bf16(&B.gu, size_t(E) * 2 * is * hs);
+  upload_bf16(&B.down, size_t(E) * hs * is);
+  void* bws; cudaMalloc(&bws, q4t_moe_bf16_forward_workspace_bytes(T, k, hs, is, sis, E));
+  cudaMemset(d_yf, 0, size_t(T) * hs * 4);
+  s = mtp::MoeBf16RoutedForward(d_x, d_ids, d_rw, d_yf, B, bws, nullptr, 0, T, k, 0);
+  if (!s.ok()) std::printf("MoeBf16RoutedForward: %s\n", s.message().c_str());
+  CHECK(s.ok());
+  s = mtp::MoeBf16Forward(d_x, B, X, d_y, T, k, bws, q4t_moe_bf16_forward_workspace_bytes(T, k, hs, is, sis, E), nullptr,
+                          0, 0);
+  if (!s.ok()) std::printf("MoeBf16Forward: %s\n", s.message().c_str());
+  CHECK(s.ok());
+  CHECK(cudaDeviceSynchronize() == cudaSuccess);
+  CHECK(mtp::MoeBf16WorkspaceBytes(T, k, hs, is, E) > 0);
   std::printf("shim_test PASS\n");
   return 0;
 }

@@ -1,0 +1,75 @@
+"""The MTP draft layer's MoE (BF16 routed experts) against the oracle's restatement:
+routed experts alone with fixed routing, and the whole layer (router + experts + shared expert
++ gated combine)."""
+import numpy as np
+import pytest
+import torch
+
+import synth
+from gpu_util import dev, host
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _weights(E, hs, is_, seed):
+    rng = np.random.default_rng(seed)
+    gu = O.f32_to_bf16(rng.standard_normal((E, 2 * is_, hs), dtype=np.float32) * np.float32(0.02))
+    down = O.f32_to_bf16(rng.standard_normal((E, hs, is_), dtype=np.float32) * np.float32(0.02))
+    return gu, down
+
+
+@pytest.mark.parametrize("E,hs,is_,T,k", [(8, 256, 128, 5, 2), (16, 2560, 640, 40, 4), (32, 512, 256, 300, 6)])
+def test_bf16_routed_vs_oracle(q4t, gpu_lib, E, hs, is_, T, k):
+    gu, down = _weights(E, hs, is_, seed=E + T)
+    x = synth.make_x(T, hs, seed=3)
+    ids_h, rw_h = synth.random_routing(T, k, E, seed=5)
+    if T > 10:
+        ids_h[3, 0] = -1          # a skipped entry
+    moe = q4t.Bf16MoE(dev(gu).view(torch.bfloat16), dev(down).view(torch.bfloat16), None, T, k)
+    y = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
+    moe.routed(dev(x), dev(ids_h), dev(rw_h), y)
+    torch.cuda.synchronize()
+    want = O.moe_bf16_routed_forward(x, ids_h, rw_h, gu, down)
+    got = host(y)
+    # bf16 roundings after each GEMM and after SwiGLU: one flipped rounding of an intermediate
+    # moves an output by a fraction of a bf16 step of that intermediate
+    assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
+    # a second call accumulates into y
+    moe.routed(dev(x), dev(ids_h), dev(rw_h), y)
+    torch.cuda.synchronize()
+    assert np.abs(host(y) - 2 * want).max() <= 4e-3 * np.abs(want).max()
+
+
+def test_bf16_layer_vs_oracle(q4t, gpu_lib):
+    E, hs, is_, sis, k, T = 32, 1024, 256, 256, 4, 50
+    L = synth.make_layer(E=E, hs=hs, moe_is=128, shared_is=sis, seed=77)   # router + shared expert weights
+    dl = q4t.DeviceLayer.from_host(L)
+    gu, down = _weights(E, hs, is_, seed=9)
+    x = synth.make_x(T, hs, seed=10)
+    moe = q4t.Bf16MoE(dev(gu).view(torch.bfloat16), dev(down).view(torch.bfloat16), dl, T, k)
+    y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    moe.forward(dev(x), y)
+    torch.cuda.synchronize()
+    # routing from the oracle's logits can differ from the tensor cores' by a near tie: take ours
+    lay = q4t.forward_ws_layout(T, k, hs, is_, sis, E)
+    ids = host(moe.ws[lay.expert_ids:lay.expert_ids + T * k * 4].view(torch.int32)).reshape(T, k)
+    rw = host(moe.ws[lay.router_w:lay.router_w + T * k * 4].view(torch.float32)).reshape(T, k)
+    logits = host(moe.ws[lay.logits:lay.logits + T * E * 2].view(torch.int16)).reshape(T, E)
+    want_ids, want_rw = O.router_topk(logits, k)
+    assert np.array_equal(ids, want_ids) and np.abs(rw - want_rw).max() <= 2e-6
+    routed = O.moe_bf16_routed_forward(x, ids, rw, gu, down)
+    want = O.bf16_to_f32(O.shared_combine(x, routed, L, 1))
+    got = O.bf16_to_f32(host(y))
+    assert np.abs(got - want).max() <= (2e-3 + 2.0 ** -8) * np.abs(want).max()
+
+
+def test_bf16_errors(q4t, gpu_lib):
+    gu, down = _weights(4, 256, 128, seed=1)
+    moe = q4t.Bf16MoE(dev(gu).view(torch.bfloat16), dev(down).view(torch.bfloat16), None, 4, 2)
+    x = dev(synth.make_x(4, 256))
+    ids_h, rw_h = synth.random_routing(4, 2, 4)
+    y = torch.zeros((4, 256), dtype=torch.float32, device="cuda")
+    rc = q4t.load().q4t_moe_bf16_routed_forward(x.data_ptr(), dev(ids_h).data_ptr(), dev(rw_h).data_ptr(), y.data_ptr(),
+                                                q4t.C.byref(moe.w), moe.ws.data_ptr(), 1024, 4, 2, None)
+    assert rc != 0 and b"workspace too small" in q4t.load().q4t_last_error()

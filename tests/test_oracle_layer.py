@@ -174,3 +174,30 @@ def test_rmsnorm_matches_float64_and_residual_step():
         assert np.array_equal(h2, O.rmsnorm_bf16(x2))
         x3, h3 = O.residual_rmsnorm_bf16(x, None)
         assert np.array_equal(x3, x) and np.array_equal(h3, O.rmsnorm_bf16(x))
+
+
+def test_bf16_routed_experts_match_float64():
+    """The MTP draft layer's BF16 experts: the oracle's chain of bf16 roundings stays within
+    bf16 rounding of an unrounded float64 evaluation, skips invalid ids and accumulates."""
+    rng = np.random.default_rng(8)
+    E, hs, is_, T, k = 6, 128, 64, 5, 2
+    gu = O.f32_to_bf16(rng.standard_normal((E, 2 * is_, hs), dtype=np.float32) * np.float32(0.05))
+    down = O.f32_to_bf16(rng.standard_normal((E, hs, is_), dtype=np.float32) * np.float32(0.05))
+    x = O.f32_to_bf16(rng.standard_normal((T, hs), dtype=np.float32))
+    ids = np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int32)
+    ids[2, 1] = -1
+    rw = rng.random((T, k), dtype=np.float32)
+    y = O.moe_bf16_routed_forward(x, ids, rw, gu, down)
+    xf, gf, df = (O.bf16_to_f32(a).astype(np.float64) for a in (x, gu, down))
+    ref = np.zeros((T, hs))
+    for t in range(T):
+        for s in range(k):
+            e = ids[t, s]
+            if e < 0:
+                continue
+            h = gf[e] @ xf[t]
+            g, u = h[:is_], h[is_:]
+            ref[t] += rw[t, s] * (df[e] @ ((g / (1 + np.exp(-g))) * u))
+    assert np.abs(y - ref).max() <= 2.0 ** -6 * np.abs(ref).max()
+    y2 = O.moe_bf16_routed_forward(x, ids, rw, gu, down, y0=y)
+    assert np.allclose(y2, 2 * y, rtol=1e-6, atol=1e-7)
