@@ -32,13 +32,20 @@ def test_bf16_routed_vs_oracle(q4t, gpu_lib, E, hs, is_, T, k):
     torch.cuda.synchronize()
     want = O.moe_bf16_routed_forward(x, ids_h, rw_h, gu, down)
     got = host(y)
-    # bf16 roundings after each GEMM and after SwiGLU: one flipped rounding of an intermediate
-    # moves an output by a fraction of a bf16 step of that intermediate
-    assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()
+    # Three bf16 roundings (gate/up, SwiGLU, down) sit on fp32 dot products whose summation
+    # order differs between the tensor cores and the oracle, so a share of the intermediates
+    # lands one bf16 step apart; unlike the NVFP4 path (exact dots) this cannot be bit-equal.
+    # The reference states no bound for this path either (its check prints max_abs and the
+    # relative L2 error); the bounds here are one bf16 step of the largest output and 0.4 % L2.
+    assert np.isfinite(got).all()
+    rel_l2 = float(np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum()))
+    max_abs = float(np.abs(got - want).max())
+    print(f"bf16 experts E={E} hs={hs} is={is_} T={T}: relative_l2={rel_l2:.3e} max_abs/max={max_abs / np.abs(want).max():.3e}")
+    assert rel_l2 <= 4e-3 and max_abs <= 2.0 ** -7 * np.abs(want).max()
     # a second call accumulates into y
     moe.routed(dev(x), dev(ids_h), dev(rw_h), y)
     torch.cuda.synchronize()
-    assert np.abs(host(y) - 2 * want).max() <= 4e-3 * np.abs(want).max()
+    assert np.abs(host(y) - 2 * got).max() <= 1e-6 * np.abs(want).max()
 
 
 def test_bf16_layer_vs_oracle(q4t, gpu_lib):
