@@ -48,7 +48,7 @@ struct DeviceState {
   // library-owned stream beside the router / permutation / quantise chain and
   // joins before the combine (fork and join by events, no host involvement).
   cudaStream_t side_stream = nullptr;
-  cudaEvent_t fork_event = nullptr, join_event = nullptr;
+  cudaEvent_t fork_event = nullptr, join_event = nullptr, mid_event = nullptr;
 };
 constexpr int kMaxDevices = 16;
 DeviceState g_dev[kMaxDevices];
@@ -81,7 +81,8 @@ int device_state(const DeviceState** out) {
     if ((e = q4t::routing_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = cudaStreamCreateWithFlags(&s.side_stream, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&s.fork_event, cudaEventDisableTiming)) != cudaSuccess ||
-        (e = cudaEventCreateWithFlags(&s.join_event, cudaEventDisableTiming)) != cudaSuccess)
+        (e = cudaEventCreateWithFlags(&s.join_event, cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&s.mid_event, cudaEventDisableTiming)) != cudaSuccess)
       return fail_cuda("side stream set-up", e);
     s.encode = reinterpret_cast<EncodeFn>(fn);
     s.num_sms = prop.multiProcessorCount;
@@ -1098,23 +1099,27 @@ int32_t q4t_ep_route_publish(const uint16_t* x, const q4t_extra_weights* extra, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* base = static_cast<uint8_t*>(finish_workspace);
   cudaError_t e;
-  // the shared expert needs nothing from the other ranks: it runs beside everything up to the combine
+  // Side stream: the publish kernel (bound by the links, hardly by the SMs), then the shared
+  // expert, which nothing needs before the combine.  Caller's stream: the router.  The
+  // caller's stream then waits for the publish kernel only, so the exchange of ids that
+  // follows is ordered behind "published" and the step's critical path is
+  // max(publish, router) instead of their sum.
   if ((e = cudaEventRecord(ds->fork_event, st)) != cudaSuccess ||
       (e = cudaStreamWaitEvent(ds->side_stream, ds->fork_event, 0)) != cudaSuccess)
     return fail_cuda("fork", e);
+  if ((rc = q4t_ep_publish(x, peers, extra->hs, input_scale, ds->side_stream)) != Q4T_OK) return rc;
+  if ((e = cudaEventRecord(ds->mid_event, ds->side_stream)) != cudaSuccess) return fail_cuda("publish record", e);
   q4t::chain_break();
   if ((rc = run_shared_expert(ds, x, extra, reinterpret_cast<uint16_t*>(base + F.shared_gu),
                               reinterpret_cast<uint16_t*>(base + F.shared_act),
                               reinterpret_cast<uint16_t*>(base + F.shared_down), T, 0, ds->side_stream)) != Q4T_OK)
     return rc;
   if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return fail_cuda("join record", e);
-  // The publish kernel first: it is bound by the links, not by the SMs, so it overlaps with
-  // the shared expert's GEMMs that have just started on the side stream; the router follows.
-  if ((rc = q4t_ep_publish(x, peers, extra->hs, input_scale, stream)) != Q4T_OK) return rc;
   q4t::chain_break();
   if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, extra->E, extra->hs, st)) != Q4T_OK) return rc;
   if ((e = q4t::launch_topk(logits, nullptr, expert_ids, router_w, T, extra->E, k, st)) != cudaSuccess)
     return fail_cuda("topk launch", e);
+  if ((e = cudaStreamWaitEvent(st, ds->mid_event, 0)) != cudaSuccess) return fail_cuda("publish join", e);
   return Q4T_OK;
 }
 
