@@ -193,13 +193,6 @@ void forward_layout(int T, int k, int hs, int is, int sis, int E, q4t_forward_ws
   F->total = align_up(off, 256);
 }
 
-// Q4T_DN_NARROW=1 in the environment moves the down GEMM of small batches to the double-buffered
-// 128-column tiles (off unless asked for).
-bool dn_narrow_enabled() {
-  static const bool on = getenv("Q4T_DN_NARROW") != nullptr;
-  return on;
-}
-
 bool routed_dims_ok(int E, int hs, int is) {
   // hs and 2*is multiples of 128 (per-expert scale blocks), is a multiple of
   // 128 (gate and up rows of one tile come from whole scale atoms), E within
@@ -313,19 +306,12 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
 
   // down: A = intermediate codes [R, is/2], B = all experts' down rows
   if ((rc = make_tmap(ds, &tm_a, false, P.at<uint8_t>(L.inter_packed), is / 2, R, is / 2)) != Q4T_OK) return rc;
-  // Small batches stream the down weights with two k-blocks per tile: 128-column tiles with
-  // two accumulator buffers keep the loads flowing across the accumulator hand-over.  Large
-  // batches (and the scatter variant) stay on 256-column tiles, which re-read A half as often.
-  const bool dn_narrow = !peer && R <= 8192 && dn_narrow_enabled();
-  const int dn_cols = dn_narrow ? 128 : 256;
-  if ((rc = make_tmap(ds, &tm_b, false, w->dn_packed, is / 2, static_cast<uint64_t>(E) * hs, is / 2, dn_cols / 2)) !=
-      Q4T_OK)
+  if ((rc = make_tmap(ds, &tm_b, false, w->dn_packed, is / 2, static_cast<uint64_t>(E) * hs, is / 2)) != Q4T_OK)
     return rc;
   q4t::GemmArgs d{};
   d.K = is;
-  d.tile_cols = dn_cols;
-  d.n_tiles = (hs + dn_cols - 1) / dn_cols;
-  d.n_per_tile = dn_cols;
+  d.n_tiles = (hs + 255) / 256;
+  d.n_per_tile = 256;
   d.b_rows_per_group = hs;
   d.b_rows_valid = hs;
   d.ntiles_dev = pt.ntiles;

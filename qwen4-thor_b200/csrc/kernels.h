@@ -146,8 +146,7 @@ struct GemmArgs {
   int K;                 // reduction length (elements)
   int n_tiles;           // column tiles per row tile
   int n_per_tile;        // output columns produced per tile (tile_cols, or half of it for the SwiGLU epilogues)
-  int tile_cols;         // accumulator columns per tile: 256 (0 means 256); 64 for BF16 narrow tiles; 128 for
-                         // the double-buffered block-scaled tiles (kStoreBf16 only; operand B box = 64 rows)
+  int tile_cols;         // accumulator columns per tile: 256 (0 means 256), or 64 for BF16 narrow tiles
   int up_row_offset;     // SwiGLU: row distance between a gate row and its up row in B
   int b_rows_per_group;  // rows of B belonging to one expert (0 for a dense GEMM)
   int b_rows_valid;      // output columns that exist (N); columns beyond are neither loaded as scales nor stored

@@ -27,16 +27,9 @@ namespace {
 constexpr int kMaxStages = 4;
 // Shared-memory ring depth.  Three 54 KB stages measured faster than four for the
 // block-scaled tiles (decode gate/up 101 vs 108 us); the BF16 tiles keep four.
-template <bool NVF4, int BN>
+template <bool NVF4>
 constexpr int num_stages() {
-  return NVF4 ? (BN == 128 ? 4 : 3) : 4;
-}
-// Accumulator buffers in tensor memory.  The 128-column block-scaled tiles (down GEMM of small
-// batches: two k-blocks per tile) keep two, so that the MMAs of the next tile start while
-// the epilogue still drains the previous one; 256-column tiles fill the accumulator space.
-template <bool NVF4, int BN>
-constexpr int acc_buffers() {
-  return (NVF4 && BN == 128) ? 2 : 1;
+  return NVF4 ? 3 : 4;
 }
 constexpr int kEpiWarpsPerQuad = 4;                       // epilogue warps sharing one TMEM lane quadrant
 constexpr int kEpiWarps = 4 * kEpiWarpsPerQuad;
@@ -61,8 +54,8 @@ constexpr uint32_t kStoreStageBytes = 32 * 64;
 struct Barriers {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
+  uint64_t acc_full;
+  uint64_t acc_empty;
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -83,16 +76,14 @@ template <bool NVF4, Epilogue EPI, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ GemmArgs args) {
-  static_assert(!NVF4 || BN == 256 || BN == 128, "block-scaled tiles are 256 or 128 columns wide");
-  static_assert(!(NVF4 && BN == 128) || EPI == Epilogue::kStoreBf16, "128-column block-scaled tiles only store bf16");
-  constexpr int kAccBufs = acc_buffers<NVF4, BN>();
+  static_assert(!NVF4 || BN == 256, "block-scaled tiles are 256 columns wide");
   extern __shared__ uint8_t smem_raw[];
   __shared__ Barriers bars;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   constexpr uint32_t kBBytes = BN * 128;
   constexpr uint32_t kStage = stage_bytes<NVF4, BN>();
-  constexpr int kStages = num_stages<NVF4, BN>();
+  constexpr int kStages = num_stages<NVF4>();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile uint32_t* abort_flag = &bars.abort_flag;
 
@@ -101,10 +92,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(smem_u32(&bars.full[s]), 1);
       mbar_init(smem_u32(&bars.empty[s]), 1);
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(smem_u32(&bars.acc_full[a]), 1);
-      mbar_init(smem_u32(&bars.acc_empty[a]), kEpiWarps);
-    }
+    mbar_init(smem_u32(&bars.acc_full), 1);
+    mbar_init(smem_u32(&bars.acc_empty), kEpiWarps);
     bars.abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
@@ -160,7 +149,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // scale atoms of B: row blocks of 128 inside the group's buffer
         const uint32_t rb0 = static_cast<uint32_t>(nt * args.n_per_tile) >> 7;
         const uint32_t rb1 = rb0 + (kSwiglu ? static_cast<uint32_t>(args.up_row_offset) >> 7 : 1u);
-        const bool second_half = BN == 256 && (kSwiglu || (nt * args.n_per_tile + 128 < args.b_rows_valid));
+        const bool second_half = kSwiglu || (nt * args.n_per_tile + 128 < args.b_rows_valid);
         // per-tile bases; the k loop below only adds constants
         const uint8_t* ga = NVF4 ? args.sfa_tiles + static_cast<size_t>(mt) * ntk * 512u : nullptr;
         const uint8_t* gbase = NVF4 ? args.sfb + static_cast<size_t>(group) * args.sfb_group_stride : nullptr;
@@ -210,7 +199,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       constexpr uint32_t idesc_bf16 = (1u << 4) | (1u << 7) | (1u << 10) |
                                       ((static_cast<uint32_t>(BN) >> 3) << 17) | ((128u >> 4) << 24);
       int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       // descriptors of stage 0; later stages differ by a constant in the
       // 14-bit start-address field, so plain 64-bit adds never carry out of it
@@ -218,14 +207,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint64_t sfa0 = umma_desc_sf(smem_base + kABytes + kBBytes);
       const uint64_t sfb0 = umma_desc_sf(smem_base + kABytes + kBBytes + kSfaBytes);
       const uint32_t bar_full0 = smem_u32(&bars.full[0]), bar_empty0 = smem_u32(&bars.empty[0]);
+      const uint32_t bar_acc_full = smem_u32(&bars.acc_full), bar_acc_empty = smem_u32(&bars.acc_empty);
       int tcount = 0;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
         Q4T_STAMP(1, tcount, 0);
-        // accumulator buffer of this tile and the parity of its barriers (each buffer is used every kAccBufs-th tile)
-        const int ab = tcount % kAccBufs;
-        const uint32_t acc_phase = static_cast<uint32_t>(tcount / kAccBufs) & 1u;
-        const uint32_t bar_acc_full = smem_u32(&bars.acc_full[ab]), bar_acc_empty = smem_u32(&bars.acc_empty[ab]);
-        const uint32_t tacc = tmem + static_cast<uint32_t>(ab * BN);
         if (!mbar_try_wait(bar_acc_empty, acc_phase ^ 1u) && !mbar_wait(bar_acc_empty, acc_phase ^ 1u, abort_flag)) {
           ok = false;
           break;
@@ -252,32 +237,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               for (uint32_t kk = 0; kk < 4; ++kk) {
                 tc_cp_sf(tsf + kk * 4u, sfa + kk * 32u);
                 tc_cp_sf(tsf + 16u + kk * 8u, sfb + kk * 32u);
-                if constexpr (BN == 256) tc_cp_sf(tsf + 20u + kk * 8u, sfb + (kSfbBytes / 32) + kk * 32u);
+                tc_cp_sf(tsf + 20u + kk * 8u, sfb + (kSfbBytes / 32) + kk * 32u);
               }
 #pragma unroll
               for (uint32_t kk = 0; kk < 4; ++kk)
-                tc_mma_nvf4(tacc, adesc + kk * 2u, bdesc + kk * 2u, idesc_nvf4, tsf + kk * 4u,
+                tc_mma_nvf4(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_nvf4, tsf + kk * 4u,
                             tsf + 16u + kk * 8u, kk == 0 ? first : 1u);
             } else {
               const uint32_t nm = k_left >> 5;
               for (uint32_t kk = 0; kk < nm; ++kk) {
                 tc_cp_sf(tsf + kk * 4u, sfa + kk * 32u);
                 tc_cp_sf(tsf + 16u + kk * 8u, sfb + kk * 32u);
-                if constexpr (BN == 256) tc_cp_sf(tsf + 20u + kk * 8u, sfb + (kSfbBytes / 32) + kk * 32u);
+                tc_cp_sf(tsf + 20u + kk * 8u, sfb + (kSfbBytes / 32) + kk * 32u);
               }
               for (uint32_t kk = 0; kk < nm; ++kk)
-                tc_mma_nvf4(tacc, adesc + kk * 2u, bdesc + kk * 2u, idesc_nvf4, tsf + kk * 4u,
+                tc_mma_nvf4(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_nvf4, tsf + kk * 4u,
                             tsf + 16u + kk * 8u, kk == 0 ? first : 1u);
             }
           } else {
             if (k_left >= 128u) {
 #pragma unroll
               for (uint32_t kk = 0; kk < 4; ++kk)
-                tc_mma_f16(tacc, adesc + kk * 2u, bdesc + kk * 2u, idesc_bf16, kk == 0 ? first : 1u);
+                tc_mma_f16(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_bf16, kk == 0 ? first : 1u);
             } else {
               const uint32_t nm = k_left >> 5;
               for (uint32_t kk = 0; kk < nm; ++kk)
-                tc_mma_f16(tacc, adesc + kk * 2u, bdesc + kk * 2u, idesc_bf16, kk == 0 ? first : 1u);
+                tc_mma_f16(tmem, adesc + kk * 2u, bdesc + kk * 2u, idesc_bf16, kk == 0 ? first : 1u);
             }
           }
           tc_commit(bar_empty0 + stage * 8u);  // frees the stage once these MMAs have read it
@@ -289,6 +274,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         if (ok) tc_commit(bar_acc_full);
         Q4T_STAMP(1, tcount, 2);
+        acc_phase ^= 1u;
       }
       if (!ok && args.status) atomicMax(args.status, 2);
     }
@@ -302,18 +288,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int quad = warp & 3;
     const int sub = (warp - kFirstEpiWarp) >> 2;  // 0..3 within the quadrant
     const int row = quad * 32 + lane;
-    const uint32_t tacc0 = tmem + (static_cast<uint32_t>(quad * 32) << 16);
+    const uint32_t tacc = tmem + (static_cast<uint32_t>(quad * 32) << 16);
     constexpr int kUnitCols = 16;
     constexpr int kUnits = kSwiglu ? kHalf / kUnitCols : BN / kUnitCols;
     constexpr int kUnitsPerWarp = (kUnits + kEpiWarpsPerQuad - 1) / kEpiWarpsPerQuad;
+    uint32_t acc_phase = 0;
     bool ok = true;
     int tcount = 0;
     const bool stamp = warp == kFirstEpiWarp + 2 && lane == 0;  // quadrant 0, first of its four warps
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
       const int mt = tile / args.n_tiles, nt = tile - mt * args.n_tiles;
-      const int ab = tcount % kAccBufs;  // accumulator buffer of this tile, parity of its barriers
-      const uint32_t acc_phase = static_cast<uint32_t>(tcount / kAccBufs) & 1u;
-      const uint32_t tacc = tacc0 + static_cast<uint32_t>(ab * BN);
       const int group = args.tile_expert ? args.tile_expert[mt] : 0;
       const int row0 = args.tile_expert ? args.tile_row0[mt] : mt * kTileM;
       if (stamp) Q4T_STAMP(2, tcount, 0);
@@ -341,7 +325,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
       }
-      if (!mbar_wait(smem_u32(&bars.acc_full[ab]), acc_phase, abort_flag)) {
+      if (!mbar_wait(smem_u32(&bars.acc_full), acc_phase, abort_flag)) {
         ok = false;
         break;
       }
@@ -379,8 +363,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[ab]));
+      if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty));
       if (stamp) Q4T_STAMP(2, tcount, 2);
+      acc_phase ^= 1u;
       if (!warp_has_rows) continue;
 
       // ---- per unit: convert, compute, store (unit by unit keeps few registers live).
@@ -562,7 +547,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 template <bool NVF4, int BN>
 cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a, Epilogue epi,
                    int num_sms, cudaStream_t stream) {
-  const size_t smem = num_stages<NVF4, BN>() * stage_bytes<NVF4, BN>() + kEpiWarps * kStoreStageBytes + 1024;
+  const size_t smem = num_stages<NVF4>() * stage_bytes<NVF4, BN>() + kEpiWarps * kStoreStageBytes + 1024;
   const int grid = a.ntiles_dev ? num_sms : min(num_sms, a.ntiles_host * a.n_tiles);
   if (grid <= 0) return cudaSuccess;
   switch (epi) {
@@ -591,7 +576,7 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs&
 template <bool NVF4, Epilogue E, int BN>
 cudaError_t set_attr() {
   return cudaFuncSetAttribute(gemm_kernel<NVF4, E, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(num_stages<NVF4, BN>() * stage_bytes<NVF4, BN>() + kEpiWarps * kStoreStageBytes + 1024));
+                              static_cast<int>(num_stages<NVF4>() * stage_bytes<NVF4, BN>() + kEpiWarps * kStoreStageBytes + 1024));
 }
 
 }  // namespace
@@ -603,7 +588,6 @@ cudaError_t gemm_set_attributes() {
   if ((e = set_attr<true, Epilogue::kSwigluBf16, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<true, Epilogue::kSwigluQuant, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<true, Epilogue::kStoreBf16Rows, 256>()) != cudaSuccess) return e;
-  if ((e = set_attr<true, Epilogue::kStoreBf16, 128>()) != cudaSuccess) return e;
   if ((e = set_attr<false, Epilogue::kStoreBf16, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<false, Epilogue::kStoreF32, 256>()) != cudaSuccess) return e;
   if ((e = set_attr<false, Epilogue::kSwigluBf16, 256>()) != cudaSuccess) return e;
@@ -615,14 +599,6 @@ cudaError_t gemm_set_attributes() {
 
 cudaError_t launch_gemm_nvf4(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& a,
                              Epilogue epi, int num_sms, cudaStream_t stream) {
-  if (a.tile_cols == 128) {  // double-buffered 128-column tiles: bf16 stores only
-    if (epi != Epilogue::kStoreBf16) return cudaErrorInvalidValue;
-    const size_t smem = num_stages<true, 128>() * stage_bytes<true, 128>() + kEpiWarps * kStoreStageBytes + 1024;
-    const int grid = a.ntiles_dev ? num_sms : min(num_sms, a.ntiles_host * a.n_tiles);
-    if (grid <= 0) return cudaSuccess;
-    return launch_chained(gemm_kernel<true, Epilogue::kStoreBf16, 128>, dim3(grid), dim3(kThreads), smem, stream, ta,
-                          tb, a);
-  }
   return launch<true, 256>(ta, tb, a, epi, num_sms, stream);
 }
 
