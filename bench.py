@@ -266,13 +266,16 @@ def run_prefill_point(torch, q4t, T, steps, warmup, seed=7):
     return out
 
 
-def cpu_reference_run(q4t_layer_host, T, steps, warmup):
+def cpu_reference_run(q4t_layer_host, T, steps, warmup, bias_column=False):
     """Times the CPU formulation (oracle 'test twin' mode: dequantise, fp32
     sequential dots, expf) on all host threads; returns (tokens/s, ms, threads)."""
     from oracle import oracle as O
     import numpy as np
     rng = np.random.default_rng(5)
-    x = O.f32_to_bf16(rng.standard_normal((T, HS), dtype=np.float32))
+    xf = rng.standard_normal((T, HS), dtype=np.float32)
+    if bias_column:      # the column that carries the router's popularity bias
+        xf[:, 0] = 1.0
+    x = O.f32_to_bf16(xf)
     for _ in range(warmup):
         O.moe_forward(x, q4t_layer_host, K_TOP, 0, 0, 0)
     t0 = time.perf_counter()
@@ -355,17 +358,22 @@ def main_single(args):
         print(json.dumps(dict(prefill=run_prefill_point(torch, q4t, args.prefill_tokens, args.steps, args.warmup))))
         return
     n_layers = 1 if args.impl == "reference" else args.layers
-    layers = [syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=20260921 + 1000 + i) for i in range(n_layers)]
+    multi_ref = args.impl == "reference" and args.gpus > 1   # the CPU arm of the expert-parallel workload
+    layers = [syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=20260921 + (4000 if multi_ref else 1000 + i),
+                               zipf_s=1.1 if multi_ref else None) for i in range(n_layers)]
 
     if args.impl == "reference":
         host_layer = host_layer_from_device(torch, layers[0])
         T = pick_cpu_tokens(host_layer)
-        tps, ms, threads = cpu_reference_run(host_layer, T, args.steps, min(args.warmup, 1))
-        line = dict(impl="reference", metric="moe_layer_tokens_per_s", value=tps, unit="tokens/s", n_gpus=1,
+        tps, ms, threads = cpu_reference_run(host_layer, T, args.steps, min(args.warmup, 1), bias_column=multi_ref)
+        line = dict(impl="reference", metric="moe_layer_tokens_per_s", value=tps, unit="tokens/s", n_gpus=args.gpus,
                     steps=args.steps, warmup=min(args.warmup, 1), ms_per_step=ms, higher_is_better=True,
-                    scaling="weak", vs_baseline=None, dtype="nvfp4 (e2m1 x ue4m3) weights and activations, fp32 accumulate",
+                    scaling="strong" if multi_ref else "weak", vs_baseline=None,
+                    dtype="nvfp4 (e2m1 x ue4m3) weights and activations, fp32 accumulate",
                     data="synthetic",
-                    config=dict(workload="decode-shaped MoE layer, hs=2048 E=512 top-10 is=512 shared=512", tokens=T),
+                    config=dict(workload=("prefill MoE layer with the Zipf(1.1) router of the expert-parallel workload, "
+                                          "hs=2048 E=512 top-10 is=512 shared=512, one host" if multi_ref else
+                                          "decode-shaped MoE layer, hs=2048 E=512 top-10 is=512 shared=512"), tokens=T),
                     cpu_baseline=dict(value=tps, unit="tokens/s", cores=threads, kind="port",
                                       sample=f"one layer forward of {T} tokens per step"),
                     e2e=dict(value=tps, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
