@@ -363,6 +363,9 @@ def main_single(args):
                                zipf_s=1.1 if multi_ref else None) for i in range(n_layers)]
 
     if args.impl == "reference":
+        if multi_ref:   # the launcher pins every rank to one OpenMP thread; this arm is alone on the host
+            from oracle import oracle as O
+            O.set_num_threads(os.cpu_count() or 1)
         host_layer = host_layer_from_device(torch, layers[0])
         T = pick_cpu_tokens(host_layer)
         tps, ms, threads = cpu_reference_run(host_layer, T, args.steps, min(args.warmup, 1), bias_column=multi_ref)

@@ -339,5 +339,9 @@ def moe_bf16_routed_forward(x, ids, rw, gu, down, y0=None):
     return y
 
 
+def set_num_threads(n: int) -> None:
+    lib().q4o_set_num_threads(C.c_int(int(n)))
+
+
 def num_threads() -> int:
     return int(lib().q4o_num_threads())

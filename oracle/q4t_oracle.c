@@ -810,6 +810,16 @@ void q4o_moe_bf16_routed_forward(const uint16_t* x, const int32_t* ids, const fl
   }
 }
 
+/* Sets the number of OpenMP threads of this library (a launcher may have pinned the process
+ * to one thread through the environment before the runtime was loaded). */
+void q4o_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int q4o_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -168,6 +168,7 @@ void q4o_residual_rmsnorm_bf16(uint16_t* x, const uint16_t* y, int T, int hs, fl
 void q4o_moe_bf16_routed_forward(const uint16_t* x, const int32_t* ids, const float* rw, const uint16_t* gu,
                                  const uint16_t* down, int T, int k, int E, int hs, int is, float* y);
 
+void q4o_set_num_threads(int n);
 int q4o_num_threads(void);
 
 #ifdef __cplusplus

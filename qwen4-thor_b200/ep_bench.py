@@ -56,8 +56,6 @@ def main_multi(args):
     if args.impl == "reference":
         # the CPU formulation runs on rank 0 only; the other ranks have nothing to do
         if rank == 0:
-            # the launcher pins every rank to one OpenMP thread; this arm is alone on the host
-            os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
             bench.main_single(args)
         return
     # NCCL's version banner goes to stdout, and the bench prints exactly one line there:
