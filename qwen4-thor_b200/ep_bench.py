@@ -126,17 +126,41 @@ def main_multi(args):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
 
-    # end to end: inputs from pinned host memory, result read back, every step
+    # End to end: every step copies its input from pinned host memory and its result back.
+    # The copies run on their own streams with two buffers each way, so the input of step i+1
+    # and the result of step i-1 move while step i computes; the timed region ends only when
+    # the last result has reached the host.
     hx = [x.cpu().pin_memory() for x in xs]
-    hy = torch.empty((T_loc, HS), dtype=torch.bfloat16).pin_memory()
-    dx = torch.empty((T_loc, HS), dtype=torch.bfloat16, device="cuda")
+    hy = [torch.empty((T_loc, HS), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dx = [torch.empty((T_loc, HS), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    dy = [torch.empty((T_loc, HS), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    main_s, s_in, s_out = torch.cuda.current_stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    for ev in ev_done + ev_out:
+        ev.record(main_s)
 
     def step_e2e(i):
-        dx.copy_(hx[i % 2], non_blocking=True)
-        drv.forward(dx, y)
-        hy.copy_(y, non_blocking=True)
+        b = i & 1
+        s_in.wait_event(ev_done[b])            # the step that last read dx[b] is over
+        with torch.cuda.stream(s_in):
+            dx[b].copy_(hx[i % 2], non_blocking=True)
+            ev_in[b].record(s_in)
+        main_s.wait_event(ev_in[b])
+        main_s.wait_event(ev_out[b])           # dy[b] has been copied out
+        drv.forward(dx[b], dy[b])
+        ev_done[b].record(main_s)
+        s_out.wait_event(ev_done[b])
+        with torch.cuda.stream(s_out):
+            hy[b].copy_(dy[b], non_blocking=True)
+            ev_out[b].record(s_out)
 
-    ms_e = bench.time_steps(torch, step_e2e, args.steps, args.warmup, barrier)
+    def drain():
+        main_s.wait_event(ev_out[0])
+        main_s.wait_event(ev_out[1])
+
+    ms_e = bench.time_steps(torch, step_e2e, args.steps, args.warmup, barrier, finish=drain)
     t = torch.tensor([ms_e], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_e = float(t.item())
