@@ -181,6 +181,45 @@ __global__ void __launch_bounds__(256) plan_hist_kernel(const int32_t* __restric
   for (int e = threadIdx.x; e < E; e += blockDim.x) blk_counts[static_cast<size_t>(blockIdx.x) * E + e] = hist[e];
 }
 
+// Inclusive scan of two values over the 1024 threads of a block (thread e holds element e):
+// shuffles inside each warp, one shared-memory step across the 32 warps.  Results land in
+// s_a[e] / s_b[e]; s_a[1023] / s_b[1023] are the totals.  Two barriers instead of twenty.
+__device__ __forceinline__ void block_scan_pair(int32_t a, int32_t b, int32_t* s_a, int32_t* s_b) {
+  __shared__ int32_t w_a[32], w_b[32];
+  const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int32_t ua = __shfl_up_sync(0xffffffffu, a, off), ub = __shfl_up_sync(0xffffffffu, b, off);
+    if (lane >= off) {
+      a += ua;
+      b += ub;
+    }
+  }
+  if (lane == 31) {
+    w_a[warp] = a;
+    w_b[warp] = b;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int32_t ta = w_a[lane], tb = w_b[lane];
+    const int32_t own_a = ta, own_b = tb;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int32_t ua = __shfl_up_sync(0xffffffffu, ta, off), ub = __shfl_up_sync(0xffffffffu, tb, off);
+      if (lane >= off) {
+        ta += ua;
+        tb += ub;
+      }
+    }
+    w_a[lane] = ta - own_a;  // what the warps before this one add up to
+    w_b[lane] = tb - own_b;
+  }
+  __syncthreads();
+  s_a[e] = a + w_a[warp];
+  s_b[e] = b + w_b[warp];
+  __syncthreads();
+}
+
 // One block of 1024 threads, E <= 1024.  Turns the per-block counts into
 // per-block bases, builds offsets[E+1], the row-tile list and its count.
 __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int max_tiles, PlanTables p) {
@@ -206,20 +245,7 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int ma
     p.counts[e] = c;
   }
   const int32_t tiles = (c + kTileM - 1) / kTileM;
-  s_rows[e] = c;
-  s_tiles[e] = tiles;
-  __syncthreads();
-  for (int off = 1; off < 1024; off <<= 1) {  // inclusive Hillis-Steele scan of both arrays
-    int32_t a = 0, b = 0;
-    if (e >= off) {
-      a = s_rows[e - off];
-      b = s_tiles[e - off];
-    }
-    __syncthreads();
-    s_rows[e] += a;
-    s_tiles[e] += b;
-    __syncthreads();
-  }
+  block_scan_pair(c, tiles, s_rows, s_tiles);  // inclusive scans of rows and row tiles over the experts
   const int32_t row_base = s_rows[e] - c, tile_base = s_tiles[e] - tiles;
   const int32_t total_rows = s_rows[1023], total_tiles = s_tiles[1023];
   __syncthreads();
@@ -369,20 +395,7 @@ __global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* ids, in
     }
   }
   const int32_t tiles = (c + kTileM - 1) / kTileM;
-  s_rows[e] = c;
-  s_tiles[e] = tiles;
-  __syncthreads();
-  for (int off = 1; off < 1024; off <<= 1) {
-    int32_t a = 0, b = 0;
-    if (e >= off) {
-      a = s_rows[e - off];
-      b = s_tiles[e - off];
-    }
-    __syncthreads();
-    s_rows[e] += a;
-    s_tiles[e] += b;
-    __syncthreads();
-  }
+  block_scan_pair(c, tiles, s_rows, s_tiles);  // inclusive scans of rows and row tiles over the experts
   const int32_t row_base = s_rows[e] - c, tile_base = s_tiles[e] - tiles;
   const int32_t total_rows = s_rows[1023], total_tiles = s_tiles[1023];
   __syncthreads();
