@@ -139,25 +139,40 @@ class ClockSampler:
                     samples=len(sm))
 
 
-def time_steps(torch, fn, steps, warmup, barrier=None, finish=None):
+def time_steps(torch, fn, steps, warmup, barrier=None, finish=None, repeats=1):
     """W untimed steps, then exactly K timed steps between CUDA events on the
-    current stream, with a synchronise (and barrier) on both sides."""
+    current stream, with a synchronise (and barrier) on both sides.  With repeats > 1 the
+    K-step region is timed that many times back to back and the list of per-step times (ms)
+    is returned instead of one number."""
     for i in range(warmup):
         fn(i)
-    torch.cuda.synchronize()
-    if barrier:
-        barrier()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(steps):
-        fn(warmup + i)
-    if finish:      # e.g. make the timing stream wait for copies still running on other streams
-        finish()
-    t1.record()
-    torch.cuda.synchronize()
-    if barrier:
-        barrier()
-    return t0.elapsed_time(t1) / steps
+    out = []
+    n = warmup
+    for _ in range(max(1, repeats)):
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(steps):
+            fn(n + i)
+        n += steps
+        if finish:      # e.g. make the timing stream wait for copies still running on other streams
+            finish()
+        t1.record()
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        out.append(t0.elapsed_time(t1) / steps)
+    return out if repeats > 1 else out[0]
+
+
+def spread(ms_list):
+    """min / median / p95 of repeated timings of the same K-step region (ms per step)."""
+    v = sorted(ms_list)
+    n = len(v)
+    return dict(repeats=n, min=v[0], median=v[n // 2] if n % 2 else 0.5 * (v[n // 2 - 1] + v[n // 2]),
+                p95=v[min(n - 1, int(round(0.95 * (n - 1))))], max=v[-1])
 
 
 def unique_experts(torch, fwd, T):
@@ -169,7 +184,7 @@ def layer_bytes(U, T):
     return U * EXPERT_BYTES + LAYER_FIXED_BYTES + 2 * T * HS * 2
 
 
-def run_decode_point(torch, q4t, layers, T, steps, warmup, n_inputs=8, with_e2e=False, with_stages=False):
+def run_decode_point(torch, q4t, layers, T, steps, warmup, n_inputs=8, with_e2e=False, with_stages=False, repeats=1):
     syn = importlib.import_module("qwen4-thor_b200.synthetic")
     xs = [syn.make_x(T, HS, seed=100 + i) for i in range(n_inputs)]
     fwds = [q4t.MoEForward(l, T, K_TOP) for l in layers]
@@ -179,7 +194,12 @@ def run_decode_point(torch, q4t, layers, T, steps, warmup, n_inputs=8, with_e2e=
     def step(i):
         fwds[i % len(fwds)](xs[i % n_inputs], y)
 
-    ms = time_steps(torch, step, steps, warmup)
+    timing = None
+    if repeats > 1:     # the K-step region repeated: the median is the reported time
+        timing = spread(time_steps(torch, step, steps, warmup, repeats=repeats))
+        ms = timing["median"]
+    else:
+        ms = time_steps(torch, step, steps, warmup)
     fwds[0].status()
     # distinct experts per step (algorithmic bytes), averaged over the rotation
     us = []
@@ -190,6 +210,8 @@ def run_decode_point(torch, q4t, layers, T, steps, warmup, n_inputs=8, with_e2e=
     U = sum(us) / len(us)
     out = dict(T=T, ms_per_step=ms, tokens_per_s=T / (ms * 1e-3), unique_experts=U,
                layer_bytes=layer_bytes(U, T), layer_gbs=layer_bytes(U, T) / (ms * 1e-3) / 1e9)
+    if timing:
+        out["ms_per_step_spread"] = timing
     if with_stages:
         q4t.stage_timing(True)
         acc = {}
@@ -235,20 +257,27 @@ def run_decode_point(torch, q4t, layers, T, steps, warmup, n_inputs=8, with_e2e=
             main.wait_event(ev_out[0])
             main.wait_event(ev_out[1])
 
-        ms_e = time_steps(torch, step_e2e, steps, warmup, finish=drain)
+        if repeats > 1:
+            sp = spread(time_steps(torch, step_e2e, steps, warmup, finish=drain, repeats=repeats))
+            ms_e = sp["median"]
+        else:
+            sp, ms_e = None, time_steps(torch, step_e2e, steps, warmup, finish=drain)
         out["e2e"] = dict(value=T / (ms_e * 1e-3), unit="tokens/s", ms_per_step=ms_e,
                           h2d_bytes_per_step=T * HS * 2, d2h_bytes_per_step=T * HS * 2)
+        if sp:
+            out["e2e"]["ms_per_step_spread"] = sp
     del fwds
     return out
 
 
-def run_prefill_point(torch, q4t, T, steps, warmup, seed=7):
+def run_prefill_point(torch, q4t, T, steps, warmup, seed=7, repeats=5):
     syn = importlib.import_module("qwen4-thor_b200.synthetic")
     layer = syn.device_layer(q4t, E, HS, MOE_IS, SHARED_IS, seed=seed, zipf_s=1.1)
     xs = [syn.make_x(T, HS, seed=200 + i, bias_column=True) for i in range(2)]
     fwd = q4t.MoEForward(layer, T, K_TOP)
     y = torch.empty((T, HS), dtype=torch.bfloat16, device="cuda")
-    ms = time_steps(torch, lambda i: fwd(xs[i % 2], y), steps, warmup)
+    sp = spread(time_steps(torch, lambda i: fwd(xs[i % 2], y), steps, warmup, repeats=max(1, repeats)))
+    ms = sp["median"]
     fwd.status()
     counts = fwd.routed_region("counts", torch.int32, E).float()
     q4t.stage_timing(True)
@@ -259,18 +288,44 @@ def run_prefill_point(torch, q4t, T, steps, warmup, seed=7):
             acc[kname] = acc.get(kname, 0.0) + v / 3
     q4t.stage_timing(False)
     flops = 6.0 * T * K_TOP * HS * MOE_IS
-    out = dict(T=T, ms_per_step=ms, tokens_per_s=T / (ms * 1e-3), routed_tflops=flops / (ms * 1e-3) / 1e12,
+    out = dict(T=T, ms_per_step=ms, ms_per_step_spread=sp, tokens_per_s=T / (ms * 1e-3),
+               routed_tflops=flops / (ms * 1e-3) / 1e12,
                rows_per_expert_max=float(counts.max()), rows_per_expert_mean=float(counts.mean()),
                stage_ms=acc, routing="zipf(s=1.1) bias on router column 0")
     del fwd, layer
     return out
 
 
-def cpu_reference_run(q4t_layer_host, T, steps, warmup, bias_column=False):
+def run_dense_fp4_point(torch, q4t, M, N, Kd, secs=0.3):
+    """A dense NVFP4 GEMM of M x N x K through q4t_fp4_gemm (bf16 output, random codes): what the
+    block-scaled tensor-core mainloop of this library sustains when every row tile is full."""
+    import ctypes as C
+    L = q4t.load()
+    w = torch.randint(0, 256, (N, Kd // 2), dtype=torch.uint8, device="cuda")
+    a = torch.randint(0, 256, (M, Kd // 2), dtype=torch.uint8, device="cuda")
+    wsf = torch.full((L.q4t_sf_buffer_size(N, Kd),), 0x38, dtype=torch.uint8, device="cuda")
+    asf = torch.full((L.q4t_sf_buffer_size(M, Kd),), 0x38, dtype=torch.uint8, device="cuda")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def f(_i=0):
+        q4t.check(L.q4t_fp4_gemm(w.data_ptr(), wsf.data_ptr(), a.data_ptr(), asf.data_ptr(), out.data_ptr(), 1, M, N, Kd,
+                                 C.c_float(1.0), C.c_float(1.0), st))
+
+    ms1 = time_steps(torch, f, 3, 3)
+    iters = max(5, int(secs * 1e3 / max(ms1, 1e-3)))
+    ms = time_steps(torch, f, iters, 0)
+    return dict(M=M, N=N, K=Kd, ms=ms, tflops=2.0 * M * N * Kd / (ms * 1e-3) / 1e12, iters=iters)
+
+
+def cpu_reference_run(q4t_layer_host, T, steps, warmup, bias_column=False, threads=None):
     """Times the CPU formulation (oracle 'test twin' mode: dequantise, fp32
-    sequential dots, expf) on all host threads; returns (tokens/s, ms, threads)."""
+    sequential dots, expf) on `threads` host threads (default: all); returns
+    (tokens/s, ms, threads)."""
     from oracle import oracle as O
     import numpy as np
+    if threads is not None:
+        O.set_num_threads(threads)
     rng = np.random.default_rng(5)
     xf = rng.standard_normal((T, HS), dtype=np.float32)
     if bias_column:      # the column that carries the router's popularity bias
@@ -385,7 +440,8 @@ def main_single(args):
 
     T = 128
     with ClockSampler(0) as clocks:
-        main = run_decode_point(torch, q4t, layers, T, args.steps, args.warmup, with_e2e=True, with_stages=True)
+        main = run_decode_point(torch, q4t, layers, T, args.steps, args.warmup, with_e2e=True, with_stages=True,
+                                repeats=args.repeats)
     clk = clocks.summary()
     also = {}
     if not args.quick:
@@ -399,6 +455,16 @@ def main_single(args):
         pf = also["prefill_T16384"]
         pf["frac_of_4x_measured_bf16"] = pf["routed_tflops"] / (4 * peaks["bf16_tflops"])
         pf["frac_of_9pf_nominal"] = pf["routed_tflops"] / 9000.0
+        # what this library's own block-scaled mainloop reaches on a dense problem of the gate/up
+        # shape with every row tile full (no routing, no epilogue arithmetic): the practical
+        # ceiling of the expert GEMMs on this GPU, measured beside the layer
+        also["nvfp4_dense_gemm"] = run_dense_fp4_point(torch, q4t, 16384 * K_TOP, 2 * MOE_IS, HS)
+        # the same expert-parallel batch the multi-GPU runs shard, on this one GPU
+        ep1 = run_prefill_point(torch, q4t, 32768, max(3, min(args.steps, 10)), 3, seed=20260921 + 4000, repeats=3)
+        also["ep_prefill_T32768_single_gpu"] = dict(metric="moe_ep_prefill_tokens_per_s", value=ep1["tokens_per_s"],
+                                                    ms_per_step=ep1["ms_per_step"],
+                                                    note="the workload of the --gpus N > 1 runs on one GPU "
+                                                         "(strong-scaling reference)")
 
     # roofline of the dominant kernel (gate/up GEMM with fused SwiGLU + requantise)
     st = main["stage_ms"]
@@ -416,15 +482,35 @@ def main_single(args):
 
     cpu = None
     if not args.no_cpu:
+        from oracle import oracle as O
         host_layer = host_layer_from_device(torch, layers[0])
+        all_threads = O.num_threads()
         Tc = pick_cpu_tokens(host_layer)
         tps, ms_c, threads = cpu_reference_run(host_layer, Tc, 2, 1)
+        # the reference's loop nest as written runs on one thread: timed on a smaller sample
+        T1 = max(1, min(8, Tc // 8))
+        tps1, ms_1, _ = cpu_reference_run(host_layer, T1, 1, 1, threads=1)
+        O.set_num_threads(all_threads)
         cpu = dict(value=tps, unit="tokens/s", cores=threads, kind="port",
-                   sample=f"2 layer forwards of {Tc} tokens (oracle restatement of the reference's host-side MoE)")
+                   sample=f"2 layer forwards of {Tc} tokens (oracle restatement of the reference's host-side MoE)",
+                   single_thread=dict(value=tps1, unit="tokens/s", cores=1,
+                                      sample=f"1 layer forward of {T1} tokens, one thread"))
 
     if not args.quick and args.stack_layers > 0:   # last: the graph capture attempt must not disturb the rest
         also["stack"] = run_stack_point(torch, q4t, syn, layers, args.stack_layers, T, 5, main["layer_bytes"])
 
+    prefill_roofline = None
+    if "prefill_T16384" in also:
+        pf = also["prefill_T16384"]
+        dense = also.get("nvfp4_dense_gemm") or {}
+        prefill_roofline = dict(bound="tensor", workload="prefill MoE layer, T=16384, Zipf(1.1) router",
+                                flops=6.0 * 16384 * K_TOP * HS * MOE_IS, achieved=pf["routed_tflops"], unit="TFLOP/s",
+                                peak=4 * peaks["bf16_tflops"], peak_source="4 x measured dense bf16 (no NVFP4 peak is measured by the driver)",
+                                frac=pf["routed_tflops"] / (4 * peaks["bf16_tflops"]),
+                                frac_of_9pf_nominal=pf["routed_tflops"] / 9000.0,
+                                own_dense_nvfp4_gemm_tflops=dense.get("tflops"),
+                                frac_of_own_dense_nvfp4_gemm=(pf["routed_tflops"] / dense["tflops"]) if dense.get("tflops") else None,
+                                ms_per_step=pf["ms_per_step"], stage_ms=pf["stage_ms"])
     launches_per_step = 3 + 3 + 1 + 1 + 1 + 1 + 1 + 1   # logits, topk, plan x3, quant, gu, dn, shared x2, combine
     line = dict(metric="moe_layer_tokens_per_s", value=main["tokens_per_s"], unit="tokens/s", n_gpus=1,
                 steps=args.steps, warmup=args.warmup, ms_per_step=main["ms_per_step"], higher_is_better=True,
@@ -435,8 +521,8 @@ def main_single(args):
                             l2=f"{args.layers} layer weight sets (0.9 GB each) and 8 inputs rotated per step; one step touches ~840 MB > L2",
                             unique_experts_per_step=main["unique_experts"]),
                 clocks=clk, e2e={k: v for k, v in main["e2e"].items() if k != "ms_per_step"},
-                gpu_launches=launches_per_step * args.steps, roofline=roofline, cpu_baseline=cpu,
-                stage_ms=st, also=also)
+                gpu_launches=launches_per_step * args.steps, roofline=roofline, prefill=prefill_roofline,
+                cpu_baseline=cpu, ms_per_step_spread=main.get("ms_per_step_spread"), stage_ms=st, also=also)
     print(json.dumps(line))
 
 
@@ -451,6 +537,8 @@ def main():
     ap.add_argument("--hot-experts", type=int, default=32,
                     help="multi-GPU peer exchange: experts replicated on every GPU (0 = none, interleaved sharding)")
     ap.add_argument("--quick", action="store_true", help="headline point only (no sweep, no prefill)")
+    ap.add_argument("--repeats", type=int, default=10,
+                    help="how many times the K-step timed region of the headline point is repeated (median reported)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=4, help="independent layer weight sets rotated per step")
     ap.add_argument("--stack-layers", type=int, default=48,

@@ -81,6 +81,15 @@ typedef struct {
   const uint16_t* shared_gate_scalar; /* [hs]               */
 } q4t_extra_weights;
 
+/* ---- CTA-pair GEMMs (no reference counterpart).  GEMMs with at least `rows` A
+ * rows (grouped: rows of the whole batch) run as pairs of CTAs on neighbouring
+ * SMs sharing each weight tile (tcgen05 cta_group::2).  rows <= 0 (the default)
+ * never uses them: on B200 the pair form measured slower than one CTA per tile.
+ * The routed workspace of such batches holds more row tiles (every expert is
+ * padded to an even tile count), so call this BEFORE sizing workspaces.  The
+ * environment variable Q4T_PAIR_MIN_ROWS gives the initial value.              */
+int32_t q4t_set_pair_min_rows(int64_t rows);
+
 /* ---- layout helpers: SfNumGtiles / SfBufferSize / SfOffset
  *      (include/q4t/quant/swizzle.h:34-57)                                   */
 int32_t q4t_sf_num_gtiles(int32_t K);
@@ -215,6 +224,14 @@ int32_t q4t_moe_routed_forward_noalloc(const uint16_t* x, const int32_t* expert_
                                        const q4t_routed_weights* weights,
                                        int32_t M, int32_t k, uint32_t flags,
                                        void* stream);
+/* The kernel status words of the built-in scratch (no reference counterpart
+ * either): q4t_moe_workspace_status for the workspace the caller of the entry
+ * point above never sees.  Call it with the dimensions of the last
+ * q4t_moe_routed_forward_noalloc on the current device, after synchronising
+ * its stream: 0 = clean, Q4T_ERR_KERNEL = a bounded device-side wait ran out
+ * and y is undefined.  Reads four bytes with cudaMemcpy; allocates nothing.    */
+int32_t q4t_moe_noalloc_status(int32_t M, int32_t k, int32_t hs, int32_t moe_is,
+                               int32_t E);
 
 /* ---- MoEForwardWorkspaceBytes (include/q4t/model/moe.h:72-76,
  * src/model/moe.cu:403-417).                                                  */
@@ -226,7 +243,9 @@ size_t q4t_moe_forward_workspace_bytes(int32_t T, int32_t k, int32_t hs,
  * shared gate/up, shared activation, shared down.                             */
 typedef struct {
   size_t routed_ws, logits, expert_ids, router_w, routed, shared_gu,
-      shared_act, shared_down, total;
+      shared_act, shared_down;
+  size_t slot_ids;   /* int32 [T,k]: slot mode only, the ids the GEMMs consumed */
+  size_t total;
 } q4t_forward_ws_layout;
 int32_t q4t_moe_forward_workspace_layout(int32_t T, int32_t k, int32_t hs,
                                          int32_t moe_is, int32_t shared_is,
@@ -247,6 +266,38 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
                         const q4t_extra_weights* extra, uint16_t* y, int32_t T,
                         int32_t k, void* workspace, size_t workspace_bytes,
                         const int32_t* fixed_ids, uint32_t flags, void* stream);
+
+/* ---- MoEForward with the two optional per-layer hooks the engine passes on
+ * every layer (src/model/decoder_layer.cu:700-703):
+ *   trace_ids_out  : RouterCollector::CaptureLayer (src/model/moe.cu:485-488,
+ *                    src/trace/router_collector.cpp:245-266): when not NULL, the
+ *                    selected expert ids int32 [T,k] are copied to this device
+ *                    buffer on the stream right after the top-k (the ORIGINAL
+ *                    ids, also in slot mode).  NULL: nothing is captured.
+ *   slot_of_expert : slot mode (include/q4t/quant/moe_weights.h:47-51,
+ *                    include/q4t/model/moe.h:96-103).  `routed` then describes
+ *                    routed->E RESIDENT SLOTS (each slot's bytes are one expert
+ *                    slice) while the router still chooses among extra->E
+ *                    experts; this device table int32 [extra->E] maps an expert
+ *                    to its slot (negative or >= routed->E: not resident, its
+ *                    (token,slot) entries are skipped).  The reference resolves
+ *                    the slots on the host after reading the ids back; here the
+ *                    residency tier (out of this library's scope) publishes its
+ *                    table to the device and no host synchronisation happens.
+ *                    The workspace keeps the original ids in `expert_ids` and
+ *                    the slots in `slot_ids`.  NULL: routed->E == extra->E.
+ * fixed_ids and flags as in q4t_moe_forward.                                   */
+typedef struct q4t_forward_options {
+  const int32_t* fixed_ids;
+  int32_t* trace_ids_out;
+  const int32_t* slot_of_expert;
+  uint32_t flags;
+  uint32_t reserved;
+} q4t_forward_options;
+int32_t q4t_moe_forward_ex(const uint16_t* x, const q4t_routed_weights* routed,
+                           const q4t_extra_weights* extra, uint16_t* y, int32_t T,
+                           int32_t k, void* workspace, size_t workspace_bytes,
+                           const q4t_forward_options* options, void* stream);
 
 /* ---- BF16 routed experts: the MTP draft layer's MoE (include/q4t/mtp/moe_bf16.h:
  * 36-123, src/mtp/moe_bf16.cu).  Same orchestration as the NVFP4 layer with
@@ -375,6 +426,12 @@ typedef struct q4t_ep_peer_table {
   const int32_t* placement;
   int32_t experts_total;
   int32_t reserved;
+  /* expert_map 2, optional: device table int32 [experts_total], the same on every
+   * rank: the rank that serves expert e for all tokens, or a negative value for an
+   * expert replicated on every rank.  With it q4t_ep_route_publish sends a token only
+   * to the ranks that serve one of its selected experts; without it (NULL) every
+   * token goes to every rank.  Maps 0 and 1 need no table.                      */
+  const int32_t* expert_owner;
 } q4t_ep_peer_table;
 #define Q4T_EP_REPLICATED (1 << 30)
 int32_t q4t_peer_buffer_alloc(size_t bytes, void** ptr);
@@ -385,10 +442,20 @@ int32_t q4t_peer_buffer_close(void* ptr);
 /* x: bf16 [tokens_per_rank, hs]; hs a multiple of 64.                         */
 int32_t q4t_ep_publish(const uint16_t* x, const q4t_ep_peer_table* peers, int32_t hs,
                        float input_scale, void* stream);
+/* The selective form of step 1: expert_ids int32 [tokens_per_rank,k] (already
+ * selected); a token's codes are stored only into the gathered buffers of the
+ * ranks that own one of its k experts (by expert_map / expert_owner) and into
+ * this rank's own.  Ranks read only the tokens of entries they serve, so the
+ * other slots of their buffers may keep stale rows.  At 8 ranks with the most
+ * used experts replicated this moves a twelfth of the bytes of q4t_ep_publish. */
+int32_t q4t_ep_publish_selected(const uint16_t* x, const int32_t* expert_ids,
+                                const q4t_ep_peer_table* peers, int32_t k, int32_t E,
+                                int32_t hs, float input_scale, void* stream);
 /* Steps 1 and 4 as single calls, for drivers that count host overhead:
  * q4t_ep_route_publish = router logits (scratch bf16 [tokens_per_rank, E]) + top-k
- * (expert_ids, router_w) + q4t_ep_publish, and it starts the shared expert on
- * the library's side stream (result left in finish_workspace);
+ * (expert_ids, router_w) + q4t_ep_publish_selected (q4t_ep_publish for expert_map 2
+ * without an owner table), and it starts the shared expert on the library's side
+ * stream (result left in finish_workspace);
  * q4t_ep_combine = wait for that shared expert + q4t_ep_flat_rows (row_of_flat:
  * int32 [T*k] scratch) + q4t_moe_combine on the landing buffer.                */
 int32_t q4t_ep_route_publish(const uint16_t* x, const q4t_extra_weights* extra,

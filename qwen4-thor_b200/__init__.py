@@ -52,21 +52,28 @@ class EpPeerTable(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("tokens_per_rank", C.c_int32),
                 ("expert_map", C.c_int32), ("xq_packed", C.c_void_p * 8), ("xq_sf", C.c_void_p * 8),
                 ("dn_rows", C.c_void_p * 8), ("placement", C.c_void_p), ("experts_total", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("reserved", C.c_int32), ("expert_owner", C.c_void_p)]
 
 
 class ForwardWsLayout(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in (
         "routed_ws", "logits", "expert_ids", "router_w", "routed", "shared_gu", "shared_act",
-        "shared_down", "total")]
+        "shared_down", "slot_ids", "total")]
+
+
+class ForwardOptions(C.Structure):
+    """q4t_forward_options: the replay table, the router-trace observer and the slot-mode table."""
+    _fields_ = [("fixed_ids", C.c_void_p), ("trace_ids_out", C.c_void_p), ("slot_of_expert", C.c_void_p),
+                ("flags", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 EXPORTS = [
-    "q4t_last_error", "q4t_version", "q4t_sf_num_gtiles", "q4t_sf_buffer_size", "q4t_sf_offset",
+    "q4t_last_error", "q4t_version", "q4t_set_pair_min_rows", "q4t_sf_num_gtiles", "q4t_sf_buffer_size", "q4t_sf_offset",
     "q4t_pack_expert_host", "q4t_quantize_activation_fp4", "q4t_dequant_fp4_to_bf16", "q4t_fp4_gemm",
     "q4t_fp4_gemm_check", "q4t_router_topk", "q4t_bf16_linear", "q4t_moe_routed_workspace_bytes",
     "q4t_moe_routed_workspace_layout", "q4t_moe_routed_forward", "q4t_moe_forward_workspace_bytes",
-    "q4t_moe_forward_workspace_layout", "q4t_moe_forward", "q4t_moe_workspace_status",
+    "q4t_moe_forward_workspace_layout", "q4t_moe_forward", "q4t_moe_forward_ex", "q4t_moe_workspace_status",
+    "q4t_moe_noalloc_status",
     "q4t_selftest_encoders", "q4t_stage_timing_enable", "q4t_stage_timing_read",
     "q4t_moe_routed_forward_noalloc", "q4t_ep_dispatch_workspace_bytes", "q4t_ep_dispatch",
     "q4t_moe_expert_rows", "q4t_moe_finish_workspace_bytes", "q4t_moe_finish",
@@ -74,7 +81,7 @@ EXPORTS = [
     "q4t_moe_bf16_workspace_bytes", "q4t_moe_bf16_routed_forward", "q4t_moe_bf16_forward_workspace_bytes",
     "q4t_moe_bf16_forward",
     "q4t_peer_buffer_alloc", "q4t_peer_buffer_free", "q4t_peer_buffer_export", "q4t_peer_buffer_open",
-    "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_ep_route_publish", "q4t_ep_combine", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
+    "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_ep_publish_selected", "q4t_ep_route_publish", "q4t_ep_combine", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
 ]
 EP_MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
@@ -95,6 +102,7 @@ def load():
     L = C.CDLL(LIB_PATH)
     L.q4t_last_error.restype = C.c_char_p
     L.q4t_version.restype = C.c_char_p
+    L.q4t_set_pair_min_rows.argtypes = [C.c_int64]
     L.q4t_sf_num_gtiles.restype = C.c_int32
     L.q4t_sf_buffer_size.restype = C.c_size_t
     L.q4t_sf_buffer_size.argtypes = [C.c_int32, C.c_int32]
@@ -141,6 +149,7 @@ def load():
                                        sz, vp]
     L.q4t_ep_combine.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, vp, sz, vp]
     L.q4t_ep_publish.argtypes = [vp, C.POINTER(EpPeerTable), i32, f32, vp]
+    L.q4t_ep_publish_selected.argtypes = [vp, vp, C.POINTER(EpPeerTable), i32, i32, i32, f32, vp]
     L.q4t_moe_expert_peer_workspace_bytes.restype = C.c_size_t
     L.q4t_moe_expert_peer_workspace_bytes.argtypes = [i32] * 5
     L.q4t_moe_expert_peer.argtypes = [vp, C.POINTER(EpPeerTable), C.POINTER(RoutedWeights), i32, vp, sz, u32, vp]
@@ -148,7 +157,10 @@ def load():
     L.q4t_moe_forward_workspace_layout.argtypes = [i32] * 6 + [C.POINTER(ForwardWsLayout)]
     L.q4t_moe_forward.argtypes = [vp, C.POINTER(RoutedWeights), C.POINTER(ExtraWeights), vp, i32, i32,
                                   vp, sz, vp, u32, vp]
+    L.q4t_moe_forward_ex.argtypes = [vp, C.POINTER(RoutedWeights), C.POINTER(ExtraWeights), vp, i32, i32,
+                                     vp, sz, C.POINTER(ForwardOptions), vp]
     L.q4t_moe_workspace_status.argtypes = [vp, i32, i32, i32, i32, i32]
+    L.q4t_moe_noalloc_status.argtypes = [i32] * 5
     L.q4t_selftest_encoders.argtypes = [i32, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64),
                                         C.POINTER(C.c_uint32), vp]
     _lib = L
@@ -319,20 +331,38 @@ def routed_forward_noalloc(layer: DeviceLayer, x, ids, rw, y, flags=0, stream=No
     return y
 
 
+def noalloc_status(layer: DeviceLayer, M: int, k: int):
+    """Raises if a bounded device-side wait ran out during the last no-allocation call of
+    these dimensions (synchronises the device first)."""
+    import torch
+    torch.cuda.synchronize()
+    check(load().q4t_moe_noalloc_status(M, k, layer.hs, layer.moe_is, layer.E))
+
+
 class MoEForward:
     """MoEForward (router + routed experts + shared expert + gated combine)."""
 
     def __init__(self, layer: DeviceLayer, T: int, k: int, device="cuda"):
         import torch
         self.layer, self.T, self.k = layer, T, k
-        self.layout = forward_ws_layout(T, k, layer.hs, layer.moe_is, layer.shared_is, layer.E)
-        self.routed_layout = routed_ws_layout(T, k, layer.hs, layer.moe_is, layer.E)
+        # the workspace is sized by the experts the router chooses among (more than layer.E in slot mode)
+        self.layout = forward_ws_layout(T, k, layer.hs, layer.moe_is, layer.shared_is, layer.E_router)
+        self.routed_layout = routed_ws_layout(T, k, layer.hs, layer.moe_is, layer.E_router)
         self.ws = torch.empty(self.layout.total, dtype=torch.uint8, device=device)
 
-    def __call__(self, x, y, fixed_ids=None, flags=0, stream=None):
-        check(load().q4t_moe_forward(_ptr(x), C.byref(self.layer.routed), C.byref(self.layer.extra), _ptr(y),
-                                     self.T, self.k, _ptr(self.ws), self.layout.total, _ptr(fixed_ids),
-                                     flags, _stream_ptr(stream)))
+    def __call__(self, x, y, fixed_ids=None, flags=0, stream=None, trace_ids_out=None, slot_of_expert=None):
+        """trace_ids_out: CUDA int32 [T,k] that receives the selected expert ids (the router-trace
+        observer); slot_of_expert: CUDA int32 [E] expert -> resident slot table (slot mode: the
+        layer's routed weights then hold layer.E slots, the router chooses among layer.E_router)."""
+        if trace_ids_out is None and slot_of_expert is None:
+            check(load().q4t_moe_forward(_ptr(x), C.byref(self.layer.routed), C.byref(self.layer.extra), _ptr(y),
+                                         self.T, self.k, _ptr(self.ws), self.layout.total, _ptr(fixed_ids),
+                                         flags, _stream_ptr(stream)))
+            return y
+        opt = ForwardOptions(_ptr(fixed_ids), _ptr(trace_ids_out), _ptr(slot_of_expert), flags, 0)
+        check(load().q4t_moe_forward_ex(_ptr(x), C.byref(self.layer.routed), C.byref(self.layer.extra), _ptr(y),
+                                        self.T, self.k, _ptr(self.ws), self.layout.total, C.byref(opt),
+                                        _stream_ptr(stream)))
         return y
 
     def region(self, name, dtype, count):
@@ -352,7 +382,7 @@ class MoEForward:
         torch.cuda.synchronize()
         ws = self.ws[self.layout.routed_ws:]
         check(load().q4t_moe_workspace_status(_ptr(ws), self.T, self.k, self.layer.hs, self.layer.moe_is,
-                                              self.layer.E))
+                                              self.layer.E_router))
 
 
 STAGES = ("router_logits", "topk", "permutation", "gather_quantise", "gate_up_gemm", "down_gemm",

@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <string>
 
@@ -78,6 +79,7 @@ int device_state(const DeviceState** out) {
     if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess)
       return fail(Q4T_ERR_DEVICE, "cuTensorMapEncodeTiled entry point unavailable");
     if ((e = q4t::gemm_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+    if ((e = q4t::gemm_pair_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = q4t::routing_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = cudaStreamCreateWithFlags(&s.side_stream, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&s.fork_event, cudaEventDisableTiming)) != cudaSuccess ||
@@ -109,6 +111,39 @@ int make_tmap(const DeviceState* ds, CUtensorMap* tm, bool bf16, const void* bas
   return Q4T_OK;
 }
 
+// [atoms, 512 bytes] view of a buffer of block-scale atoms for the CTA-pair GEMMs: rows of
+// 128 uint32, a box of four atoms (the four k-steps of one 256-element k-block), no swizzle.
+// Atoms past the end read as zeros.
+int make_sf_tmap(const DeviceState* ds, CUtensorMap* tm, const void* base, uint64_t atoms) {
+  if (reinterpret_cast<uintptr_t>(base) & 15u) return fail(Q4T_ERR_INVALID, "scale buffers must be 16-byte aligned");
+  cuuint64_t dims[2] = {128, atoms ? atoms : 1};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 4};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = ds->encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(Q4T_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+  return Q4T_OK;
+}
+
+// GEMMs with at least this many A rows run as CTA pairs (tc_gemm_pair.cu).  Off by default:
+// on B200 the pair form measured 5-10 % slower than one CTA per tile, because the block-scaled
+// mainloop is bound by each SM's tensor pipe, not by the operand traffic a pair halves.
+// q4t_set_pair_min_rows() or the environment variable Q4T_PAIR_MIN_ROWS turn it on.
+constexpr int64_t kPairNever = static_cast<int64_t>(1) << 62;
+std::atomic<int64_t> g_pair_min_rows{-1};
+int64_t pair_min_rows() {
+  int64_t v = g_pair_min_rows.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* e = std::getenv("Q4T_PAIR_MIN_ROWS");
+    const long long n = e ? std::atoll(e) : 0;
+    v = n <= 0 ? kPairNever : static_cast<int64_t>(n);
+    g_pair_min_rows.store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
 // Optional event marks between stages (off by default).
 struct StageTimer {
   bool enabled = false;
@@ -136,7 +171,11 @@ size_t sf_buffer_size(int rows, int K) {
 
 void routed_layout(int M, int k, int hs, int is, int E, q4t_routed_ws_layout* L) {
   const size_t R = static_cast<size_t>(M) * k;
-  const size_t max_tiles = R / 128 + (R < static_cast<size_t>(E) ? R : static_cast<size_t>(E)) + 1;
+  // every expert with rows ends in one partial row tile; batches that run as CTA pairs pad
+  // each such expert to an even tile count
+  const size_t active = R < static_cast<size_t>(E) ? R : static_cast<size_t>(E);
+  const size_t max_tiles = static_cast<int64_t>(R) >= pair_min_rows() ? ((R / 128 + 2 * active + 2) & ~static_cast<size_t>(1))
+                                                                      : R / 128 + active + 1;
   const size_t nblk = (R + q4t::kPlanChunk - 1) / q4t::kPlanChunk;
   size_t off = 0;
   auto take = [&](size_t bytes, size_t align = 256) {
@@ -190,6 +229,7 @@ void forward_layout(int T, int k, int hs, int is, int sis, int E, q4t_forward_ws
   F->shared_gu = take(static_cast<size_t>(T) * 2 * sis * 2);
   F->shared_act = take(static_cast<size_t>(T) * sis * 2);
   F->shared_down = take(static_cast<size_t>(T) * hs * 2);
+  F->slot_ids = take(static_cast<size_t>(T) * k * 4);
   F->total = align_up(off, 256);
 }
 
@@ -244,8 +284,10 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   const q4t_routed_ws_layout& L = P.L;
   cudaError_t e;
   const q4t::PlanTables pt = plan_tables(P, E);  // the planner also clears the status words
+  // large batches: CTA-pair GEMMs over pairs of row tiles of one expert
+  const bool pair = !plan_done && static_cast<int64_t>(R) >= pair_min_rows();
   if (!plan_done) {
-    if ((e = q4t::launch_plan(ids, R, E, static_cast<int>(L.max_tiles), pt, st)) != cudaSuccess)
+    if ((e = q4t::launch_plan(ids, R, E, static_cast<int>(L.max_tiles), pt, st, pair)) != cudaSuccess)
       return fail_cuda("plan launch", e);
   }
   stage_end(2, st);
@@ -259,7 +301,7 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
                                             pt.flat_of_row, pt.row_tile, pt.tile_row0, pt.offsets + E, k, st)) !=
         cudaSuccess)
       return fail_cuda("block code gather launch", e);
-  } else if (w->gu_input_scale_uniform > 0.0f && k > 1 && R >= 8192) {
+  } else if (w->gu_input_scale_uniform > 0.0f && k > 1 && k <= 16 && hs >= 128 && R >= 8192) {
     if ((e = q4t::launch_quantize_scatter(x, a_packed, a_sf_tiles, M, hs, w->gu_input_scale_uniform, pt.row_of_flat,
                                           pt.row_tile, pt.tile_row0, k, st)) != cudaSuccess)
       return fail_cuda("quantise-scatter launch", e);
@@ -300,8 +342,16 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
   g.gu_dump = (flags & 1u) ? P.at<uint16_t>(L.gu_out) : nullptr;
   g.gu_dump_ld = 2 * is;
   g.status = P.at<int32_t>(L.status);
-  if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, g, q4t::Epilogue::kSwigluQuant, ds->num_sms, st)) != cudaSuccess)
-    return fail_cuda("gate/up GEMM launch", e);
+  if (pair) {
+    CUtensorMap tm_sfa, tm_sfb;
+    g.sfb_group_atoms = static_cast<int>(g.sfb_group_stride / 512);
+    if ((rc = make_sf_tmap(ds, &tm_sfa, a_sf_tiles, L.max_tiles * static_cast<uint64_t>((hs + 63) / 64))) != Q4T_OK) return rc;
+    if ((rc = make_sf_tmap(ds, &tm_sfb, w->gu_sf, static_cast<uint64_t>(E) * g.sfb_group_atoms)) != Q4T_OK) return rc;
+    e = q4t::launch_gemm_nvf4_pair(tm_a, tm_b, tm_sfa, tm_sfb, g, q4t::Epilogue::kSwigluQuant, ds->num_sms, st);
+  } else {
+    e = q4t::launch_gemm_nvf4(tm_a, tm_b, g, q4t::Epilogue::kSwigluQuant, ds->num_sms, st);
+  }
+  if (e != cudaSuccess) return fail_cuda("gate/up GEMM launch", e);
   stage_end(4, st);
 
   // down: A = intermediate codes [R, is/2], B = all experts' down rows
@@ -332,9 +382,17 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
     d.scatter_rows_per_rank = peer->rows_per_rank;
     for (int i = 0; i < q4t::kMaxPeers; ++i) d.scatter_base[i] = peer->dn_rows[i];
   }
-  if ((e = q4t::launch_gemm_nvf4(tm_a, tm_b, d, peer ? q4t::Epilogue::kStoreBf16Rows : q4t::Epilogue::kStoreBf16,
-                                 ds->num_sms, st)) != cudaSuccess)
-    return fail_cuda("down GEMM launch", e);
+  const q4t::Epilogue dn_epi = peer ? q4t::Epilogue::kStoreBf16Rows : q4t::Epilogue::kStoreBf16;
+  if (pair) {
+    CUtensorMap tm_sfa, tm_sfb;
+    d.sfb_group_atoms = static_cast<int>(d.sfb_group_stride / 512);
+    if ((rc = make_sf_tmap(ds, &tm_sfa, d.sfa_tiles, L.max_tiles * static_cast<uint64_t>((is + 63) / 64))) != Q4T_OK) return rc;
+    if ((rc = make_sf_tmap(ds, &tm_sfb, w->dn_sf, static_cast<uint64_t>(E) * d.sfb_group_atoms)) != Q4T_OK) return rc;
+    e = q4t::launch_gemm_nvf4_pair(tm_a, tm_b, tm_sfa, tm_sfb, d, dn_epi, ds->num_sms, st);
+  } else {
+    e = q4t::launch_gemm_nvf4(tm_a, tm_b, d, dn_epi, ds->num_sms, st);
+  }
+  if (e != cudaSuccess) return fail_cuda("down GEMM launch", e);
   stage_end(5, st);
   return Q4T_OK;
 }
@@ -415,9 +473,11 @@ int run_routed_core_bf16(const DeviceState* ds, const uint16_t* x, const int32_t
 int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
                     int K, cudaStream_t st) {
   cudaError_t e;
-  if (M <= 8) {
-    if (K % 8 || static_cast<size_t>(M) * K * 2 > 98304)
-      return fail(Q4T_ERR_INVALID, "K must be a multiple of 8 and M*K at most 49152");
+  // the exact-order GEMV keeps the M rows of x in shared memory (at most 96 KB); beyond
+  // that, shapes the tensor-core kernel accepts fall through to it
+  const bool gemv_fits = K % 8 == 0 && static_cast<size_t>(M) * K * 2 <= 98304;
+  if (M <= 8 && (gemv_fits || K % 16 || N % 16)) {
+    if (!gemv_fits) return fail(Q4T_ERR_INVALID, "K must be a multiple of 8 and M*K at most 49152");
     if ((e = q4t::launch_small_m_linear(x, w, y, M, N, K, st)) != cudaSuccess) return fail_cuda("linear launch", e);
     return Q4T_OK;
   }
@@ -441,8 +501,9 @@ int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w,
   g.out = y;
   g.ldo = N;
   g.alpha_const = 1.0f;
-  if ((e = q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kStoreBf16, ds->num_sms, st)) != cudaSuccess)
-    return fail_cuda("bf16 GEMM launch", e);
+  e = (!narrow && M >= pair_min_rows()) ? q4t::launch_gemm_bf16_pair(ta, tb, g, q4t::Epilogue::kStoreBf16, ds->num_sms, st)
+                                        : q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kStoreBf16, ds->num_sms, st);
+  if (e != cudaSuccess) return fail_cuda("bf16 GEMM launch", e);
   return Q4T_OK;
 }
 
@@ -479,8 +540,9 @@ int run_shared_expert(const DeviceState* ds, const uint16_t* x, const q4t_extra_
     g.alpha_const = 1.0f;
     g.gu_dump = (flags & 1u) ? sgu : nullptr;
     g.gu_dump_ld = 2 * sis;
-    if ((e = q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kSwigluBf16, ds->num_sms, st)) != cudaSuccess)
-      return fail_cuda("shared gate/up GEMM launch", e);
+    e = (!narrow && T >= pair_min_rows()) ? q4t::launch_gemm_bf16_pair(ta, tb, g, q4t::Epilogue::kSwigluBf16, ds->num_sms, st)
+                                          : q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kSwigluBf16, ds->num_sms, st);
+    if (e != cudaSuccess) return fail_cuda("shared gate/up GEMM launch", e);
   }
   return run_bf16_linear(ds, sact, extra->shared_down, sdown, T, hs, sis, st);
 }
@@ -491,6 +553,11 @@ extern "C" {
 
 const char* q4t_last_error(void) { return g_error.c_str(); }
 const char* q4t_version(void) { return "q4t-moe-b200 0.1 (sm_100a)"; }
+
+int32_t q4t_set_pair_min_rows(int64_t rows) {
+  g_pair_min_rows.store(rows <= 0 ? kPairNever : rows, std::memory_order_relaxed);
+  return Q4T_OK;
+}
 
 int32_t q4t_sf_num_gtiles(int32_t K) { return (K / 16 + 3) / 4; }
 size_t q4t_sf_buffer_size(int32_t rows, int32_t K) { return sf_buffer_size(rows, K); }
@@ -581,8 +648,17 @@ int32_t q4t_fp4_gemm(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t
 #ifdef Q4T_TRACE
   if (const char* t = std::getenv("Q4T_TRACE_PTR")) g.trace = reinterpret_cast<long long*>(std::strtoull(t, nullptr, 0));
 #endif
-  cudaError_t e = q4t::launch_gemm_nvf4(ta, tb, g, out_is_bf16 ? q4t::Epilogue::kStoreBf16 : q4t::Epilogue::kStoreF32,
-                                        ds->num_sms, static_cast<cudaStream_t>(stream));
+  const q4t::Epilogue epi = out_is_bf16 ? q4t::Epilogue::kStoreBf16 : q4t::Epilogue::kStoreF32;
+  cudaError_t e;
+  if (M >= pair_min_rows()) {  // large M: CTA pairs share the weight tiles
+    const uint64_t ntk = static_cast<uint64_t>(K + 63) / 64;
+    CUtensorMap tsa, tsb;
+    if ((rc = make_sf_tmap(ds, &tsa, a_sf, static_cast<uint64_t>((M + 127) / 128) * ntk)) != Q4T_OK) return rc;
+    if ((rc = make_sf_tmap(ds, &tsb, w_sf, static_cast<uint64_t>((N + 127) / 128) * ntk)) != Q4T_OK) return rc;
+    e = q4t::launch_gemm_nvf4_pair(ta, tb, tsa, tsb, g, epi, ds->num_sms, static_cast<cudaStream_t>(stream));
+  } else {
+    e = q4t::launch_gemm_nvf4(ta, tb, g, epi, ds->num_sms, static_cast<cudaStream_t>(stream));
+  }
   return e == cudaSuccess ? Q4T_OK : fail_cuda("NVFP4 GEMM launch", e);
 }
 
@@ -683,16 +759,24 @@ int32_t q4t_moe_forward_workspace_layout(int32_t T, int32_t k, int32_t hs, int32
 
 namespace {
 // The whole layer for either kind of routed experts (exactly one of routed / routed_bf16 is set).
+// trace_ids_out (optional): the selected expert ids are copied there right after the top-k.
+// slot_of_expert (optional, NVFP4 only): the routed weights hold `routed->E` resident slots
+// and expert id e runs as slot slot_of_expert[e] (negative: skipped).
 int moe_forward_impl(const uint16_t* x, const q4t_routed_weights* routed, const q4t_bf16_expert_weights* routed_bf16,
                      const q4t_extra_weights* extra, uint16_t* y, int32_t T, int32_t k, void* workspace,
-                     size_t workspace_bytes, const int32_t* fixed_ids, uint32_t flags, void* stream) {
+                     size_t workspace_bytes, const int32_t* fixed_ids, int32_t* trace_ids_out,
+                     const int32_t* slot_of_expert, uint32_t flags, void* stream) {
   if (T <= 0) return Q4T_OK;                                           // src/model/moe.cu:442
   if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");  // moe.cu:443
   if ((!routed && !routed_bf16) || !extra) return fail(Q4T_ERR_INVALID, "null weights");
   const int E = extra->E, hs = extra->hs, sis = extra->shared_is;
   const int is = routed ? routed->moe_is : routed_bf16->moe_is;
-  if ((routed ? routed->E : routed_bf16->E) != E || (routed ? routed->hs : routed_bf16->hs) != hs)
+  const int E_routed = routed ? routed->E : routed_bf16->E;
+  if (slot_of_expert && !routed) return fail(Q4T_ERR_INVALID, "slot mode needs NVFP4 routed weights");
+  if ((routed ? routed->hs : routed_bf16->hs) != hs || (!slot_of_expert && E_routed != E))
     return fail(Q4T_ERR_INVALID, "routed and extra weights disagree on E/hs");
+  if (slot_of_expert && (E_routed <= 0 || E_routed > E))
+    return fail(Q4T_ERR_INVALID, "slot count must be in [1, number of experts]");
   if (!routed_dims_ok(E, hs, is) || E > 512 || k > E || sis <= 0 || sis % 128)
     return fail(Q4T_ERR_INVALID, "unsupported dims (hs, moe_is, shared_is multiples of 128; E <= 512)");
   q4t_forward_ws_layout F;
@@ -721,44 +805,76 @@ int moe_forward_impl(const uint16_t* x, const q4t_routed_weights* routed, const 
   // The shared expert runs beside the routed chain unless the stage timer is on
   // (its marks assume one stream) or the batch is large enough to fill the GPU.
   const bool fork = !g_timer.enabled && T <= 1024;
+  // Once the side stream has been forked, every way out joins it again: an error
+  // return that left it dangling would, under stream capture, invalidate the graph.
+  bool forked = false;
+  auto leave = [&](int code) {
+    if (forked) {
+      const std::string kept = g_error;
+      if (cudaEventRecord(ds->join_event, ds->side_stream) == cudaSuccess) cudaStreamWaitEvent(st, ds->join_event, 0);
+      g_error = kept;
+    }
+    return code;
+  };
   if (fork) {
     if ((e = cudaEventRecord(ds->fork_event, st)) != cudaSuccess ||
         (e = cudaStreamWaitEvent(ds->side_stream, ds->fork_event, 0)) != cudaSuccess)
       return fail_cuda("fork", e);
+    forked = true;
     q4t::chain_break();  // first kernel behind an event wait
-    if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, ds->side_stream)) != Q4T_OK) return rc;
-    if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return fail_cuda("join record", e);
+    if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, ds->side_stream)) != Q4T_OK) return leave(rc);
+    if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return leave(fail_cuda("join record", e));
     q4t::chain_break();  // back on the caller's stream, behind the caller's own work
   }
 
   // 1-2. router logits and top-k
   stage_begin(st);
-  if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, E, hs, st)) != Q4T_OK) return rc;
+  if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, E, hs, st)) != Q4T_OK) return leave(rc);
   stage_end(0, st);
   RoutedPtrs P;
   routed_layout(T, k, hs, is, E, &P.L);
   P.base = base + F.routed_ws;
-  const bool fused_route = q4t::route_and_plan_fits(T, k);
+  const bool observe = trace_ids_out != nullptr || slot_of_expert != nullptr;
+  const bool fused_route = !observe && q4t::route_and_plan_fits(T, k);
   if (fused_route) {  // small batch: top-k and the permutation tables in one launch
     if ((e = q4t::launch_route_and_plan(logits, fixed_ids, ids, rw, T, E, k, static_cast<int>(P.L.max_tiles),
                                         plan_tables(P, E), st)) != cudaSuccess)
-      return fail_cuda("route+plan launch", e);
+      return leave(fail_cuda("route+plan launch", e));
   } else {
-    if ((e = q4t::launch_topk(logits, fixed_ids, ids, rw, T, E, k, st)) != cudaSuccess) return fail_cuda("topk launch", e);
+    if ((e = q4t::launch_topk(logits, fixed_ids, ids, rw, T, E, k, st)) != cudaSuccess)
+      return leave(fail_cuda("topk launch", e));
+  }
+  // the router-trace observer sees the experts as selected (src/model/moe.cu:485-488,
+  // RouterCollector::CaptureLayer: a device-to-device copy of [T,k] ids on the stream)
+  if (trace_ids_out) {
+    if ((e = cudaMemcpyAsync(trace_ids_out, ids, static_cast<size_t>(T) * k * 4, cudaMemcpyDeviceToDevice, st)) !=
+        cudaSuccess)
+      return leave(fail_cuda("trace copy", e));
+    q4t::chain_break();
+  }
+  // slot mode (include/q4t/quant/moe_weights.h:47-51): the GEMMs consume slot ids; the
+  // workspace keeps the original ids in `expert_ids` and the slots in `slot_ids`
+  const int32_t* routed_ids = ids;
+  if (slot_of_expert) {
+    int32_t* slots = reinterpret_cast<int32_t*>(base + F.slot_ids);
+    if ((e = q4t::launch_remap_ids(ids, slot_of_expert, slots, T * k, E, E_routed, st)) != cudaSuccess)
+      return leave(fail_cuda("slot remap launch", e));
+    routed_ids = slots;
   }
   stage_end(1, st);
 
   // 3. routed experts
   if (routed) {
-    if ((rc = run_routed_core(ds, x, ids, routed, P, T, k, flags, st, fused_route)) != Q4T_OK) return rc;
+    if ((rc = run_routed_core(ds, x, routed_ids, routed, P, T, k, flags, st, fused_route)) != Q4T_OK) return leave(rc);
   } else if ((rc = run_routed_core_bf16(ds, x, ids, routed_bf16, P, reinterpret_cast<uint16_t*>(base + compact_at), T, k,
                                         st, fused_route)) != Q4T_OK) {
-    return rc;
+    return leave(rc);
   }
 
   // 4-6. shared expert
   if (fork) {
     if ((e = cudaStreamWaitEvent(st, ds->join_event, 0)) != cudaSuccess) return fail_cuda("join", e);
+    forked = false;
     q4t::chain_break();
   } else {
     if ((rc = run_shared_expert(ds, x, extra, sgu, sact, sdown, T, flags, st)) != Q4T_OK) return rc;
@@ -780,7 +896,17 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed, con
                         uint16_t* y, int32_t T, int32_t k, void* workspace, size_t workspace_bytes,
                         const int32_t* fixed_ids, uint32_t flags, void* stream) {
   if (T > 0 && k > 0 && k <= 16 && !routed) return fail(Q4T_ERR_INVALID, "null weights");
-  return moe_forward_impl(x, routed, nullptr, extra, y, T, k, workspace, workspace_bytes, fixed_ids, flags, stream);
+  return moe_forward_impl(x, routed, nullptr, extra, y, T, k, workspace, workspace_bytes, fixed_ids, nullptr, nullptr,
+                          flags, stream);
+}
+
+int32_t q4t_moe_forward_ex(const uint16_t* x, const q4t_routed_weights* routed, const q4t_extra_weights* extra,
+                           uint16_t* y, int32_t T, int32_t k, void* workspace, size_t workspace_bytes,
+                           const q4t_forward_options* opt, void* stream) {
+  if (T > 0 && k > 0 && k <= 16 && !routed) return fail(Q4T_ERR_INVALID, "null weights");
+  if (!opt) return fail(Q4T_ERR_INVALID, "null options");
+  return moe_forward_impl(x, routed, nullptr, extra, y, T, k, workspace, workspace_bytes, opt->fixed_ids,
+                          opt->trace_ids_out, opt->slot_of_expert, opt->flags, stream);
 }
 
 // ---- BF16 routed experts (the MTP draft layer)
@@ -831,7 +957,8 @@ int32_t q4t_moe_bf16_forward(const uint16_t* x, const q4t_bf16_expert_weights* r
                              uint16_t* y, int32_t T, int32_t k, void* workspace, size_t workspace_bytes,
                              void* stream) {
   if (T > 0 && k > 0 && k <= 16 && (!routed || !routed->gu || !routed->down)) return fail(Q4T_ERR_INVALID, "null weights");
-  return moe_forward_impl(x, nullptr, routed, extra, y, T, k, workspace, workspace_bytes, nullptr, 0, stream);
+  return moe_forward_impl(x, nullptr, routed, extra, y, T, k, workspace, workspace_bytes, nullptr, nullptr, nullptr, 0,
+                          stream);
 }
 
 // ---------------------------------------------------------------- expert parallelism
@@ -1084,6 +1211,36 @@ int32_t q4t_ep_publish(const uint16_t* x, const q4t_ep_peer_table* peers, int32_
   return e == cudaSuccess ? Q4T_OK : fail_cuda("publish launch", e);
 }
 
+int32_t q4t_ep_publish_selected(const uint16_t* x, const int32_t* expert_ids, const q4t_ep_peer_table* peers,
+                                int32_t k, int32_t E, int32_t hs, float input_scale, void* stream) {
+  if (!x || !peers || !expert_ids) return fail(Q4T_ERR_INVALID, "null pointer");
+  const int world = peers->world, rank = peers->rank, tpr = peers->tokens_per_rank;
+  if (world <= 0 || world > Q4T_EP_MAX_RANKS || rank < 0 || rank >= world || tpr <= 0)
+    return fail(Q4T_ERR_INVALID, "invalid peer table (world in [1,8], rank < world, tokens_per_rank > 0)");
+  if (hs <= 0 || hs % 64) return fail(Q4T_ERR_INVALID, "hs must be a multiple of 64");
+  if (k <= 0 || k > 16 || E <= 0) return fail(Q4T_ERR_INVALID, "k out of range");
+  if (!(input_scale > 0.0f)) return fail(Q4T_ERR_INVALID, "input scale must be positive");
+  const int map = peers->expert_map;
+  if (map < 0 || map > 2) return fail(Q4T_ERR_INVALID, "expert_map must be 0, 1 or 2");
+  if (map == 2 && (!peers->expert_owner || peers->experts_total != E))
+    return fail(Q4T_ERR_INVALID, "expert_map 2 needs an owner table over all experts");
+  if (map != 2 && E % world) return fail(Q4T_ERR_INVALID, "E must be a multiple of the number of ranks");
+  const DeviceState* ds;
+  int rc = device_state(&ds);
+  if (rc != Q4T_OK) return rc;
+  q4t::PublishTargets dst{};
+  dst.n = world;
+  const size_t code_block = static_cast<size_t>(tpr) * (hs / 2), sf_block = static_cast<size_t>(tpr) * (hs / 16);
+  for (int p = 0; p < world; ++p) {
+    if (!peers->xq_packed[p] || !peers->xq_sf[p]) return fail(Q4T_ERR_INVALID, "peer table has a null buffer");
+    dst.packed[p] = const_cast<uint8_t*>(peers->xq_packed[p]) + code_block * rank;
+    dst.sf[p] = const_cast<uint8_t*>(peers->xq_sf[p]) + sf_block * rank;
+  }
+  cudaError_t e = q4t::launch_publish_selected(x, expert_ids, dst, tpr, hs, k, E, map, rank, peers->expert_owner,
+                                               input_scale, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("publish launch", e);
+}
+
 int32_t q4t_ep_route_publish(const uint16_t* x, const q4t_extra_weights* extra, const q4t_ep_peer_table* peers,
                              int32_t k, float input_scale, uint16_t* logits, int32_t* expert_ids, float* router_w,
                              void* finish_workspace, size_t finish_workspace_bytes, void* stream) {
@@ -1099,28 +1256,47 @@ int32_t q4t_ep_route_publish(const uint16_t* x, const q4t_extra_weights* extra, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* base = static_cast<uint8_t*>(finish_workspace);
   cudaError_t e;
-  // Side stream: the publish kernel (bound by the links, hardly by the SMs), then the shared
-  // expert, which nothing needs before the combine.  Caller's stream: the router.  The
-  // caller's stream then waits for the publish kernel only, so the exchange of ids that
-  // follows is ordered behind "published" and the step's critical path is
-  // max(publish, router) instead of their sum.
+  // A token is published only to the ranks that serve one of its experts, so the publish
+  // step follows the top-k on the caller's stream (a few megabytes over the links instead of
+  // every token to every rank).  Without an owner table (expert_map 2, older callers) every
+  // token goes everywhere, from the side stream, beside the router.  The shared expert, which
+  // nothing needs before the combine, runs on the side stream in both cases.
+  const bool selective = peers->expert_map != 2 || peers->expert_owner != nullptr;
+  bool forked = false;
+  auto leave = [&](int code) {   // every way out joins the side stream again
+    if (forked) {
+      const std::string kept = g_error;
+      if (cudaEventRecord(ds->join_event, ds->side_stream) == cudaSuccess) cudaStreamWaitEvent(st, ds->join_event, 0);
+      g_error = kept;
+    }
+    return code;
+  };
   if ((e = cudaEventRecord(ds->fork_event, st)) != cudaSuccess ||
       (e = cudaStreamWaitEvent(ds->side_stream, ds->fork_event, 0)) != cudaSuccess)
     return fail_cuda("fork", e);
-  if ((rc = q4t_ep_publish(x, peers, extra->hs, input_scale, ds->side_stream)) != Q4T_OK) return rc;
-  if ((e = cudaEventRecord(ds->mid_event, ds->side_stream)) != cudaSuccess) return fail_cuda("publish record", e);
+  forked = true;
   q4t::chain_break();
+  if (!selective) {
+    if ((rc = q4t_ep_publish(x, peers, extra->hs, input_scale, ds->side_stream)) != Q4T_OK) return leave(rc);
+    if ((e = cudaEventRecord(ds->mid_event, ds->side_stream)) != cudaSuccess) return leave(fail_cuda("publish record", e));
+    q4t::chain_break();
+  }
   if ((rc = run_shared_expert(ds, x, extra, reinterpret_cast<uint16_t*>(base + F.shared_gu),
                               reinterpret_cast<uint16_t*>(base + F.shared_act),
                               reinterpret_cast<uint16_t*>(base + F.shared_down), T, 0, ds->side_stream)) != Q4T_OK)
-    return rc;
-  if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return fail_cuda("join record", e);
+    return leave(rc);
+  if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return leave(fail_cuda("join record", e));
   q4t::chain_break();
-  if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, extra->E, extra->hs, st)) != Q4T_OK) return rc;
+  if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, extra->E, extra->hs, st)) != Q4T_OK) return leave(rc);
   if ((e = q4t::launch_topk(logits, nullptr, expert_ids, router_w, T, extra->E, k, st)) != cudaSuccess)
-    return fail_cuda("topk launch", e);
-  if ((e = cudaStreamWaitEvent(st, ds->mid_event, 0)) != cudaSuccess) return fail_cuda("publish join", e);
-  return Q4T_OK;
+    return leave(fail_cuda("topk launch", e));
+  if (selective) {
+    if ((rc = q4t_ep_publish_selected(x, expert_ids, peers, k, extra->E, extra->hs, input_scale, st)) != Q4T_OK)
+      return leave(rc);
+  } else if ((e = cudaStreamWaitEvent(st, ds->mid_event, 0)) != cudaSuccess) {
+    return leave(fail_cuda("publish join", e));
+  }
+  return Q4T_OK;   // the side stream is joined by q4t_ep_combine (the shared expert's result is needed there)
 }
 
 int32_t q4t_ep_combine(const uint16_t* x, const uint16_t* landed_rows, const int32_t* expert_ids,

@@ -40,6 +40,28 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same for a kernel whose blocks form clusters of `cluster_x` along x.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                   unsigned cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  const bool plain = chain_break_pending();
+  cfg.numAttrs = (chaining_enabled() && !plain) ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 constexpr int kPlanChunk = 2048;   // (token,slot) entries handled by one planning block
 
 // ---- quantise / dequantise (quant_kernels.cu)
@@ -66,6 +88,11 @@ struct PublishTargets {
 };
 cudaError_t launch_publish_tokens(const uint16_t* x, const PublishTargets& dst, int M, int K, float global_scale,
                                   cudaStream_t stream);
+// The selective form: packed[r] / sf[r] are rank r's buffers (rank order); a token is stored
+// only on the ranks that own one of its k selected experts, and on `self`.
+cudaError_t launch_publish_selected(const uint16_t* x, const int32_t* ids, const PublishTargets& dst, int M, int K,
+                                    int k, int E, int map, int self, const int32_t* owner, float global_scale,
+                                    cudaStream_t stream);
 // Copies each grouped row's codes and scales out of the gathered buffers of all ranks' tokens:
 // xq_packed [tokens, K/2], xq_sf [tokens, K/16] row-major.
 cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* xq_sf, uint8_t* packed,
@@ -103,8 +130,10 @@ cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_
 bool route_and_plan_fits(int T, int k);
 cudaError_t launch_route_and_plan(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw, int T,
                                   int E, int k, int max_tiles, const PlanTables& p, cudaStream_t stream);
+// even_tiles: every expert with rows gets an even number of row tiles (the last one may be
+// empty), as the CTA-pair GEMMs need.
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
-                        cudaStream_t stream);
+                        cudaStream_t stream, bool even_tiles = false);
 cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_per_rank, int32_t* dest,
                                 int32_t* local, cudaStream_t stream);
 // local[f] = index of expert ids[f] on `rank` (-1 when it is served elsewhere or out of range).
@@ -115,6 +144,9 @@ cudaError_t launch_ep_split_ids(const int32_t* ids, int R, int E, int experts_pe
 cudaError_t launch_ep_localise_ids(const int32_t* ids, int R, int E, int world, int rank, int map,
                                    const int32_t* placement, int flats_per_rank, int32_t* local,
                                    cudaStream_t stream);
+// out[f] = slot_of_expert[ids[f]] (an id outside [0,E) or a slot outside [0,slots) gives -1).
+cudaError_t launch_remap_ids(const int32_t* ids, const int32_t* slot_of_expert, int32_t* out, int R, int E, int slots,
+                             cudaStream_t stream);
 // row_of_flat[f] = f for ids[f] in [0,E), else -1 (rows delivered in flat order).
 cudaError_t launch_ep_flat_rows(const int32_t* ids, int R, int E, int32_t* row_of_flat, cudaStream_t stream);
 cudaError_t launch_gather_rows(const uint16_t* src, const int32_t* index, int div, const int32_t* rows_dev,
@@ -161,6 +193,7 @@ struct GemmArgs {
   const uint8_t* sfa_tiles;    // tile-local atoms: tile t at t * ceil(K/64) * 512
   const uint8_t* sfb;          // standard swizzled buffer per group
   size_t sfb_group_stride;     // bytes between groups' scale buffers
+  int sfb_group_atoms;         // the same in 512-byte atoms (pair kernels address atoms through a tensor map)
   // epilogue
   void* out;                   // bf16 / f32 / packed codes
   int ldo;                     // leading dimension of out, in elements (bytes for codes)
@@ -185,7 +218,17 @@ cudaError_t launch_gemm_nvf4(const CUtensorMap& tmap_a, const CUtensorMap& tmap_
                              Epilogue epi, int num_sms, cudaStream_t stream);
 cudaError_t launch_gemm_bf16(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmArgs& a,
                              Epilogue epi, int num_sms, cudaStream_t stream);
+// CTA-pair forms (tc_gemm_pair.cu: tcgen05 cta_group::2; clusters of two CTAs share each weight tile).  Row
+// tiles 2j and 2j+1 of a grouped tile list must belong to the same expert.  tmap_sfa /
+// tmap_sfb: [atoms, 512 bytes] views of the scale buffers (make them with 128 x uint32
+// rows and a box of four atoms).
+cudaError_t launch_gemm_nvf4_pair(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_sfa,
+                                  const CUtensorMap& tmap_sfb, const GemmArgs& a, Epilogue epi, int num_sms,
+                                  cudaStream_t stream);
+cudaError_t launch_gemm_bf16_pair(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GemmArgs& a,
+                                  Epilogue epi, int num_sms, cudaStream_t stream);
 cudaError_t gemm_set_attributes();
+cudaError_t gemm_pair_set_attributes();   // tc_gemm_pair.cu
 
 // ---- verification GEMM on CUDA cores (simt_check.cu): exact integer dot,
 // out = float(exact * alpha); used by tests to check the tensor-core path at

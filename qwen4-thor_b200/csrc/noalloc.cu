@@ -85,3 +85,13 @@ extern "C" int32_t q4t_moe_routed_forward_noalloc(const uint16_t* x, const int32
   return q4t_moe_routed_forward(x, expert_ids, router_w, y, weights, scratch, Q4T_NOALLOC_SCRATCH_BYTES, M, k,
                                 flags, stream);
 }
+
+extern "C" int32_t q4t_moe_noalloc_status(int32_t M, int32_t k, int32_t hs, int32_t moe_is, int32_t E) {
+  const size_t need = q4t_moe_routed_workspace_bytes(M, k, hs, moe_is, E);
+  if (need == 0 || need > static_cast<size_t>(Q4T_NOALLOC_SCRATCH_BYTES))
+    return q4t_internal_fail(Q4T_ERR_INVALID, "these dimensions do not fit the built-in scratch");
+  void* scratch = nullptr;
+  const int rc = scratch_address(&scratch);
+  if (rc != Q4T_OK) return rc;
+  return q4t_moe_workspace_status(scratch, M, k, hs, moe_is, E);
+}

@@ -122,6 +122,61 @@ __global__ void __launch_bounds__(256) publish_tokens_kernel(const uint16_t* __r
   }
 }
 
+// The same, but a token travels only to the ranks that serve one of its selected experts
+// (and always to its own rank).  dst.packed[r] / dst.sf[r] are indexed by RANK here.  The
+// owner of expert e: map 0 -> e / (E/world), map 1 -> e % world, map 2 -> owner[e] (a rank,
+// or negative for an expert replicated on every rank, which the token's own rank serves).
+// One warp per token: lanes 0..k-1 look up the owners, the warp ORs them into a mask.
+__global__ void __launch_bounds__(256) publish_selected_kernel(const uint16_t* __restrict__ x,
+                                                               const int32_t* __restrict__ ids,
+                                                               const __grid_constant__ PublishTargets dst,
+                                                               int rows, int K, int k, int E, int map, int self,
+                                                               const int32_t* __restrict__ owner,
+                                                               float global_scale) {
+  chain_wait();
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int world = dst.n;
+  uint32_t mine = 0;
+  if (lane < k) {
+    const int e = ids[row * k + lane];
+    if (e >= 0 && e < E) {
+      int o;
+      if (map == 2) o = owner[e];
+      else if (map == 1) o = e % world;
+      else o = e / (E / world);
+      if (o >= 0 && o < world) mine = 1u << o;
+    }
+  }
+  const uint32_t mask = __reduce_or_sync(0xffffffffu, mine) | (1u << self);
+  const int groups = K >> 4;
+  for (int g0 = lane * 4; g0 < groups; g0 += 128) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * K + g0 * 16);
+    uint32_t codes[8], sfw = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v0 = __ldg(src + 2 * j), v1 = __ldg(src + 2 * j + 1);
+      const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+      float a[16];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        a[2 * i] = bf16x2_lo(w[i]);
+        a[2 * i + 1] = bf16x2_hi(w[i]);
+      }
+      sfw |= quantize_group16(a, global_scale, codes[2 * j], codes[2 * j + 1]) << (8 * j);
+    }
+    const size_t code_at = static_cast<size_t>(row) * (K >> 1) + static_cast<size_t>(g0) * 8;
+    const size_t sf_at = static_cast<size_t>(row) * groups + g0;
+    for (uint32_t m = mask; m != 0; m &= m - 1) {
+      const int d = __ffs(m) - 1;
+      uint4* c = reinterpret_cast<uint4*>(dst.packed[d] + code_at);
+      c[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      c[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+      *reinterpret_cast<uint32_t*>(dst.sf[d] + sf_at) = sfw;
+    }
+  }
+}
+
 // Quantises every token once (one input scale for all experts) and writes the codes and
 // scale bytes straight to the token's k grouped rows.  One thread per group of 16 values, as
 // in the plain quantiser (neighbouring lanes read and write neighbouring 32 / 8 bytes; four
@@ -317,6 +372,15 @@ cudaError_t launch_publish_tokens(const uint16_t* x, const PublishTargets& dst, 
   if (M == 0 || dst.n == 0) return cudaSuccess;
   publish_tokens_kernel<<<(M + 7) / 8, 256, 0, stream>>>(x, dst, M, K, global_scale);
   return cudaGetLastError();
+}
+
+cudaError_t launch_publish_selected(const uint16_t* x, const int32_t* ids, const PublishTargets& dst, int M, int K,
+                                    int k, int E, int map, int self, const int32_t* owner, float global_scale,
+                                    cudaStream_t stream) {
+  if (M == 0 || dst.n == 0) return cudaSuccess;
+  if (k > 32) return cudaErrorInvalidValue;
+  return launch_chained(publish_selected_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, x, ids, dst, M, K, k, E, map,
+                        self, owner, global_scale);
 }
 
 cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,

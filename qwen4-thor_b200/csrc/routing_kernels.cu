@@ -222,7 +222,10 @@ __device__ __forceinline__ void block_scan_pair(int32_t a, int32_t b, int32_t* s
 
 // One block of 1024 threads, E <= 1024.  Turns the per-block counts into
 // per-block bases, builds offsets[E+1], the row-tile list and its count.
-__global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int max_tiles, PlanTables p) {
+// even_tiles: an expert with rows gets an even number of row tiles; the extra one is empty
+// (zero rows, first row just past the expert's last).
+__global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int max_tiles, PlanTables p,
+                                                         int even_tiles) {
   chain_wait();
   __shared__ int32_t s_rows[1024];
   __shared__ int32_t s_tiles[1024];
@@ -244,7 +247,8 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int ma
     }
     p.counts[e] = c;
   }
-  const int32_t tiles = (c + kTileM - 1) / kTileM;
+  int32_t tiles = (c + kTileM - 1) / kTileM;
+  if (even_tiles) tiles = (tiles + 1) & ~1;
   block_scan_pair(c, tiles, s_rows, s_tiles);  // inclusive scans of rows and row tiles over the experts
   const int32_t row_base = s_rows[e] - c, tile_base = s_tiles[e] - tiles;
   const int32_t total_rows = s_rows[1023], total_tiles = s_tiles[1023];
@@ -275,7 +279,7 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int nblk, int E, int ma
     const int32_t rows_e = (lo + 1 < E ? s_rows[lo + 1] : total_rows) - s_rows[lo];
     p.tile_expert[t] = lo;
     p.tile_row0[t] = s_rows[lo] + i * kTileM;
-    p.tile_nrows[t] = min(kTileM, rows_e - i * kTileM);
+    p.tile_nrows[t] = max(0, min(kTileM, rows_e - i * kTileM));
   }
 }
 
@@ -358,7 +362,8 @@ template <bool ROUTE>
 __global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* ids, int R, int E, int max_tiles,
                                                           PlanTables p, const uint16_t* __restrict__ logits,
                                                           const int32_t* __restrict__ fixed_ids, int32_t* ids_out,
-                                                          float* rw_out, int T, int k, int E_logits) {
+                                                          float* rw_out, int T, int k, int E_logits,
+                                                          int even_tiles) {
   chain_wait();
   extern __shared__ uint16_t s_cnt[];  // [32][E]: counts, later exclusive bases, then cursors
   __shared__ int32_t s_rows[1024];
@@ -394,7 +399,8 @@ __global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* ids, in
       c += v;
     }
   }
-  const int32_t tiles = (c + kTileM - 1) / kTileM;
+  int32_t tiles = (c + kTileM - 1) / kTileM;
+  if (even_tiles) tiles = (tiles + 1) & ~1;
   block_scan_pair(c, tiles, s_rows, s_tiles);  // inclusive scans of rows and row tiles over the experts
   const int32_t row_base = s_rows[e] - c, tile_base = s_tiles[e] - tiles;
   const int32_t total_rows = s_rows[1023], total_tiles = s_tiles[1023];
@@ -410,7 +416,7 @@ __global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* ids, in
       if (t < max_tiles) {
         p.tile_expert[t] = e;
         p.tile_row0[t] = row_base + i * kTileM;
-        p.tile_nrows[t] = min(kTileM, c - i * kTileM);
+        p.tile_nrows[t] = max(0, min(kTileM, c - i * kTileM));
       }
     }
   }
@@ -480,6 +486,23 @@ __global__ void __launch_bounds__(256) ep_localise_ids_kernel(const int32_t* __r
     }
   }
   local[f] = out;
+}
+
+// Slot mode: out[f] = slot_of_expert[ids[f]] when the id is a valid expert and the slot a
+// valid resident slot, else -1 (the planner skips negative ids).
+__global__ void __launch_bounds__(256) remap_ids_kernel(const int32_t* __restrict__ ids,
+                                                        const int32_t* __restrict__ slot_of_expert,
+                                                        int32_t* __restrict__ out, int R, int E, int slots) {
+  chain_wait();
+  const int f = blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= R) return;
+  const int e = ids[f];
+  int v = -1;
+  if (e >= 0 && e < E) {
+    v = slot_of_expert[e];
+    if (v < 0 || v >= slots) v = -1;
+  }
+  out[f] = v;
 }
 
 __global__ void __launch_bounds__(256) ep_flat_rows_kernel(const int32_t* __restrict__ ids, int R, int E,
@@ -745,21 +768,23 @@ cudaError_t launch_route_and_plan(const uint16_t* logits, const int32_t* fixed_i
                                   int E, int k, int max_tiles, const PlanTables& p, cudaStream_t stream) {
   return launch_chained(plan_small_kernel<true>, dim3(1), dim3(1024), 32 * E * sizeof(uint16_t), stream,
                         static_cast<const int32_t*>(nullptr), T * k, E, max_tiles, p, logits, fixed_ids, ids, rw, T, k,
-                        E);
+                        E, 0);
 }
 
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, bool even_tiles) {
+  const int even = even_tiles ? 1 : 0;
+  if (even) max_tiles &= ~1;  // the tile count handed to the GEMMs stays even when it is capped
   if (R <= kPlanSmallMax)
     return launch_chained(plan_small_kernel<false>, dim3(1), dim3(1024), 32 * E * sizeof(uint16_t), stream, ids, R, E,
                           max_tiles, p, static_cast<const uint16_t*>(nullptr), static_cast<const int32_t*>(nullptr),
-                          static_cast<int32_t*>(nullptr), static_cast<float*>(nullptr), 0, 0, 0);
+                          static_cast<int32_t*>(nullptr), static_cast<float*>(nullptr), 0, 0, 0, even);
   const int nblk = (R + kPlanChunk - 1) / kPlanChunk;
   cudaError_t e;
   if ((e = launch_chained(plan_hist_kernel, dim3(nblk), dim3(256), E * sizeof(int32_t), stream, ids, R, E,
                           p.blk_counts)) != cudaSuccess)
     return e;
-  if ((e = launch_chained(plan_scan_kernel, dim3(1), dim3(1024), 0, stream, nblk, E, max_tiles, p)) != cudaSuccess)
+  if ((e = launch_chained(plan_scan_kernel, dim3(1), dim3(1024), 0, stream, nblk, E, max_tiles, p, even)) != cudaSuccess)
     return e;
   return launch_chained(plan_scatter_kernel, dim3(nblk), dim3(256), 7 * E * sizeof(int32_t), stream, ids, R, E, p);
 }
@@ -777,6 +802,13 @@ cudaError_t launch_ep_localise_ids(const int32_t* ids, int R, int E, int world, 
   ep_localise_ids_kernel<<<(R + 255) / 256, 256, 0, stream>>>(ids, R, E, world, rank, map, placement, flats_per_rank,
                                                               local);
   return cudaGetLastError();
+}
+
+cudaError_t launch_remap_ids(const int32_t* ids, const int32_t* slot_of_expert, int32_t* out, int R, int E, int slots,
+                             cudaStream_t stream) {
+  if (R == 0) return cudaSuccess;
+  return launch_chained(remap_ids_kernel, dim3((R + 255) / 256), dim3(256), 0, stream, ids, slot_of_expert, out, R, E,
+                        slots);
 }
 
 cudaError_t launch_ep_flat_rows(const int32_t* ids, int R, int E, int32_t* row_of_flat, cudaStream_t stream) {

@@ -150,7 +150,8 @@ def plan_placement(counts, world: int, hot: int):
     that owns the token, which also balances them perfectly); the others are dealt out one by
     one, busiest first, to the rank with the least load so far.  Returns (experts, tables):
     experts[r] = global ids served by rank r in local order, tables[r] = the int32 [E] table
-    q4t_ep_peer_table.placement expects on rank r."""
+    q4t_ep_peer_table.placement expects on rank r.  owner_table(tables) gives the table
+    q4t_ep_peer_table.expert_owner expects (the same on every rank)."""
     import numpy as np
     counts = np.asarray(counts, dtype=np.int64)
     E = counts.shape[0]
@@ -175,6 +176,18 @@ def plan_placement(counts, world: int, hot: int):
     return experts, tables
 
 
+def owner_table(tables):
+    """int32 [E]: the rank that serves expert e for every rank's tokens, or -1 for an expert
+    replicated on all ranks (tables: plan_placement's second result)."""
+    import numpy as np
+    E = tables[0].shape[0]
+    owner = np.full(E, -1, dtype=np.int32)
+    for r, t in enumerate(tables):
+        sharded = (t >= 0) & ((t >> 30) & 1 == 0)
+        owner[sharded] = r
+    return owner
+
+
 def local_layer_from_list(q4t, full, experts):
     """The experts `experts` (global ids, local order) of a full device layer, copied."""
     import torch
@@ -196,8 +209,10 @@ class PeerBuffers:
     through exported handles (`connect`).  A single-process test can instead fill the
     table with plain device pointers (`from_pointers`)."""
 
-    def __init__(self, q4t, world, rank, T_local, k, hs, expert_map=1, placement=None):
-        """placement: this rank's device int32 [E] table (plan_placement) -> expert_map 2."""
+    def __init__(self, q4t, world, rank, T_local, k, hs, expert_map=1, placement=None, expert_owner=None):
+        """placement: this rank's device int32 [E] table (plan_placement) -> expert_map 2;
+        expert_owner: device int32 [E] (owner_table), lets the publish step send a token only
+        to the ranks that serve one of its experts."""
         self.q4t, self.lib = q4t, q4t.load()
         self.world, self.rank, self.T, self.k, self.hs = world, rank, T_local, k, hs
         self.table = q4t.EpPeerTable()
@@ -208,6 +223,9 @@ class PeerBuffers:
             self.table.expert_map = 2
             self.table.placement = placement.data_ptr()
             self.table.experts_total = placement.numel()
+        self.expert_owner = expert_owner    # keeps the device table alive
+        if expert_owner is not None:
+            self.table.expert_owner = expert_owner.data_ptr()
         # gathered codes, gathered scale blocks (all ranks' tokens), landing rows (own tokens)
         self.sizes = (world * T_local * (hs // 2), world * T_local * (hs // 16), T_local * k * hs * 2)
         self.own = None

@@ -8,12 +8,11 @@
 
 #include "q4t/quant/moe_gemm.h"
 #include "q4t/io/weight_loader.h"
+#include "q4t/quant/moe_residency.h"
 #include "q4t/quant/moe_weights.h"
 #include "q4t/status.h"
+#include "q4t/trace/router_collector.h"
 #include "q4t_moe_b200.h"
-
-namespace q4t::trace { class RouterCollector; }
-namespace q4t::quant { class MoEResidency; }
 
 namespace q4t::model {
 
@@ -80,21 +79,42 @@ inline size_t MoEForwardWorkspaceBytes(int T, int k, int hs, int moe_is, int sha
   return q4t_moe_forward_workspace_bytes(T, k, hs, moe_is, shared_is, E);
 }
 
-// trace / residency: the router-trace hook and the slot-mode residency tier of
-// the engine are not part of this library; passing them is reported as an error
-// instead of being ignored.
+// trace: the router-trace observer.  As in the reference (src/model/moe.cu:485-488) the
+// collector receives the ORIGINAL selected expert ids of this layer through
+// CaptureLayer(layer_id, ids, T, k, stream), a device-to-device copy ordered on the stream;
+// the ids are read from the workspace's expert_ids region, which nothing overwrites after
+// the top-k, so the copy is enqueued behind the layer.
+// residency: slot mode (include/q4t/model/moe.h:96-103 of the reference).  `routed` must be
+// residency->Layout() (E = slot count); the selected experts are mapped to slots on the
+// device through residency->DeviceSlotOfExpert() with no host round trip, and experts
+// that are not resident contribute nothing (the engine's tier decides what is resident).
 inline Status MoEForward(const uint16_t* x, const quant::MoEWeightLayout& routed, const MoEExtraWeights& extra,
                          uint16_t* y, int T, int k, void* workspace, size_t workspace_bytes, void* /*gemm_ws*/,
                          size_t /*gemm_ws_bytes*/, cudaStream_t stream, trace::RouterCollector* trace = nullptr,
-                         int /*layer_id*/ = -1, const quant::MoEResidency* residency = nullptr,
+                         int layer_id = -1, const quant::MoEResidency* residency = nullptr,
                          MoEForwardDiagnostics* diagnostics = nullptr) {
   if (diagnostics) *diagnostics = {};
-  if (residency != nullptr) return Status::Fail("slot-mode residency is not supported by the B200 MoE library");
-  if (trace != nullptr) return Status::Fail("router trace capture is not supported by the B200 MoE library");
   const q4t_routed_weights rw = routed.Abi();
   const q4t_extra_weights ew = extra.Abi();
-  if (q4t_moe_forward(x, &rw, &ew, y, T, k, workspace, workspace_bytes, nullptr, 0, stream) != Q4T_OK)
+  if (residency != nullptr) {
+    if (residency->Slots() < k) return Status::Fail("residency slots below top-k");  // moe.cu:507
+    if (residency->Slots() != routed.E || !routed.slot_mode)
+      return Status::Fail("slot mode: routed weights must be the residency layout");
+    q4t_forward_options opt{};
+    opt.slot_of_expert = residency->DeviceSlotOfExpert();
+    if (q4t_moe_forward_ex(x, &rw, &ew, y, T, k, workspace, workspace_bytes, &opt, stream) != Q4T_OK)
+      return Status::Fail(q4t_last_error());
+  } else if (q4t_moe_forward(x, &rw, &ew, y, T, k, workspace, workspace_bytes, nullptr, 0, stream) != Q4T_OK) {
     return Status::Fail(q4t_last_error());
+  }
+  if (trace != nullptr && T > 0) {
+    q4t_forward_ws_layout F;
+    if (q4t_moe_forward_workspace_layout(T, k, ew.hs, rw.moe_is, ew.shared_is, ew.E, &F) != Q4T_OK)
+      return Status::Fail(q4t_last_error());
+    const int32_t* ids = reinterpret_cast<const int32_t*>(static_cast<const uint8_t*>(workspace) + F.expert_ids);
+    Status s = trace->CaptureLayer(static_cast<uint32_t>(layer_id), ids, T, k, stream);
+    if (!s.ok()) return s;
+  }
   return Status();
 }
 

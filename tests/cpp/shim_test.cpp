@@ -1,8 +1,12 @@
 // Exercises the C++ shims (reference-shaped signatures) end to end on a GPU:
-// loader -> MoEWorkspace -> MoERoutedForward / MoEForward, plus error strings.
+// loader -> MoEWorkspace -> MoERoutedForward / MoEForward (with the router-trace observer
+// and slot mode), MoEDeviceDecode[Multi], Fp4Gemm<float|uint16_t>, the quantiser and the
+// dequantiser, the BF16 MoE, plus error strings.
 // Prints "shim_test PASS" on success.
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <random>
@@ -11,6 +15,7 @@
 #include "q4t/model/moe.h"
 #include "q4t/mtp/moe_bf16.h"
 #include "q4t/quant/act_quant.h"
+#include "q4t/quant/dequant.h"
 #include "q4t/quant/moe_gemm.h"
 #include "q4t/quant/moe_weights.h"
 
@@ -96,6 +101,167 @@ int main() {
   CHECK(quant::QuantizeActivationToFp4Async(d_x, static_cast<uint8_t*>(rws), static_cast<uint8_t*>(rws) + 4096, T, hs,
                                             0.002f, 0) == cudaSuccess);
   CHECK(cudaDeviceSynchronize() == cudaSuccess);
+  // ---- the fixed-shape decode entries (include/q4t/quant/moe_decode.h:11-36): same result
+  // as the generic call on the same rows, bit for bit (the reference's own grouped-vs-per-row
+  // check, tests/moe_decode_grouped_test.cpp:328-411)
+  {
+    std::vector<float> want(size_t(T) * hs), got(want.size());
+    cudaMemcpy(want.data(), d_yf, want.size() * 4, cudaMemcpyDeviceToHost);
+    quant::MoEWorkspace mw;
+    mw.a_packed = static_cast<uint8_t*>(rws);
+    cudaMemset(d_yf, 0, size_t(T) * hs * 4);
+    s = quant::MoEDeviceDecodeMulti(d_x, d_ids, d_rw, d_yf, L, mw, nullptr, 0, T, k, 0);
+    CHECK(s.ok());
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    cudaMemcpy(got.data(), d_yf, got.size() * 4, cudaMemcpyDeviceToHost);
+    CHECK(std::memcmp(want.data(), got.data(), got.size() * 4) == 0);
+    // single token, top-10: against ten one-slot calls accumulated in slot order
+    std::vector<int32_t> ids1 = {3, 0, 7, 12, 5, 9, 1, 15, 2, 11};
+    std::vector<float> rw1(10, 0.1f);
+    int32_t* d_ids1; float* d_rw1;
+    cudaMalloc(reinterpret_cast<void**>(&d_ids1), 40);
+    cudaMalloc(reinterpret_cast<void**>(&d_rw1), 40);
+    cudaMemcpy(d_ids1, ids1.data(), 40, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_rw1, rw1.data(), 40, cudaMemcpyHostToDevice);
+    void* ws1; cudaMalloc(&ws1, quant::MoEWorkspace::RequiredBytes(1, 10, hs, is));
+    mw.a_packed = static_cast<uint8_t*>(ws1);
+    cudaMemset(d_yf, 0, size_t(hs) * 4);
+    s = quant::MoEDeviceDecode(d_x, d_ids1, d_rw1, d_yf, L, mw, nullptr, 0, 0);
+    CHECK(s.ok());
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    cudaMemcpy(got.data(), d_yf, size_t(hs) * 4, cudaMemcpyDeviceToHost);
+    cudaMemset(d_yf, 0, size_t(hs) * 4);
+    CHECK(quant::MoERoutedForward(d_x, d_ids1, d_rw1, d_yf, L, ws1, nullptr, 0, 1, 10, 0).ok());
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    cudaMemcpy(want.data(), d_yf, size_t(hs) * 4, cudaMemcpyDeviceToHost);
+    CHECK(std::memcmp(want.data(), got.data(), size_t(hs) * 4) == 0);
+    bool any = false;
+    for (int i = 0; i < hs; ++i) any |= got[i] != 0.0f;
+    CHECK(any);
+  }
+  // ---- Fp4Gemm<float> / Fp4Gemm<uint16_t> (include/q4t/quant/fp4_gemm.h:58-213) and
+  // DequantFp4ToBf16Async (include/q4t/quant/dequant.h:22-25): quantise, multiply, and check
+  // against a host dot product of the dequantised operands (the reference's 0.02 bound)
+  {
+    const int M = 8, N = 256, K = 256;
+    uint16_t *d_a, *d_w, *d_ad, *d_wd, *d_o16;
+    float* d_o32;
+    upload_bf16(&d_a, size_t(M) * K);
+    upload_bf16(&d_w, size_t(N) * K);
+    const float ga = 0.02f * 5 / (6 * 448), gw = ga;
+    uint8_t *d_ap, *d_asf, *d_wp, *d_wsf, *d_arm, *d_wrm;
+    cudaMalloc(reinterpret_cast<void**>(&d_ap), size_t(M) * K / 2);
+    cudaMalloc(reinterpret_cast<void**>(&d_wp), size_t(N) * K / 2);
+    cudaMalloc(reinterpret_cast<void**>(&d_asf), q4t_sf_buffer_size(M, K));
+    cudaMalloc(reinterpret_cast<void**>(&d_wsf), q4t_sf_buffer_size(N, K));
+    cudaMemset(d_asf, 0, q4t_sf_buffer_size(M, K));
+    cudaMemset(d_wsf, 0, q4t_sf_buffer_size(N, K));
+    CHECK(quant::QuantizeActivationToFp4Async(d_a, d_ap, d_asf, M, K, ga, 0) == cudaSuccess);
+    CHECK(quant::QuantizeActivationToFp4Async(d_w, d_wp, d_wsf, N, K, gw, 0) == cudaSuccess);
+    cudaMalloc(reinterpret_cast<void**>(&d_o32), size_t(M) * N * 4);
+    cudaMalloc(reinterpret_cast<void**>(&d_o16), size_t(M) * N * 2);
+    auto r32 = quant::Fp4Gemm<float>(d_wp, d_wsf, d_ap, d_asf, d_o32, M, N, K, gw, ga, nullptr, 0, 0);
+    auto r16 = quant::Fp4Gemm<uint16_t>(d_wp, d_wsf, d_ap, d_asf, d_o16, M, N, K, gw, ga, nullptr, 0, 0);
+    CHECK(r32.status == 0 && r32.has_algo && r16.status == 0 && r16.has_algo);
+    // un-swizzle the scale bytes on the host (SfOffset) for the dequantiser, which takes row-major scales
+    std::vector<uint8_t> asw(q4t_sf_buffer_size(M, K)), wsw(q4t_sf_buffer_size(N, K));
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    cudaMemcpy(asw.data(), d_asf, asw.size(), cudaMemcpyDeviceToHost);
+    cudaMemcpy(wsw.data(), d_wsf, wsw.size(), cudaMemcpyDeviceToHost);
+    std::vector<uint8_t> arm(size_t(M) * K / 16), wrm(size_t(N) * K / 16);
+    const int ntk = q4t_sf_num_gtiles(K);
+    for (int r = 0; r < M; ++r) for (int g = 0; g < K / 16; ++g) arm[size_t(r) * (K / 16) + g] = asw[q4t_sf_offset(r, g, ntk)];
+    for (int r = 0; r < N; ++r) for (int g = 0; g < K / 16; ++g) wrm[size_t(r) * (K / 16) + g] = wsw[q4t_sf_offset(r, g, ntk)];
+    cudaMalloc(reinterpret_cast<void**>(&d_arm), arm.size());
+    cudaMalloc(reinterpret_cast<void**>(&d_wrm), wrm.size());
+    cudaMemcpy(d_arm, arm.data(), arm.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(d_wrm, wrm.data(), wrm.size(), cudaMemcpyHostToDevice);
+    cudaMalloc(reinterpret_cast<void**>(&d_ad), size_t(M) * K * 2);
+    cudaMalloc(reinterpret_cast<void**>(&d_wd), size_t(N) * K * 2);
+    CHECK(quant::DequantFp4ToBf16Async(d_ap, d_arm, d_ad, ga, M, K, 0) == cudaSuccess);
+    CHECK(quant::DequantFp4ToBf16Async(d_wp, d_wrm, d_wd, gw, N, K, 0) == cudaSuccess);
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    std::vector<uint16_t> ad(size_t(M) * K), wd(size_t(N) * K), o16(size_t(M) * N);
+    std::vector<float> o32(size_t(M) * N);
+    cudaMemcpy(ad.data(), d_ad, ad.size() * 2, cudaMemcpyDeviceToHost);
+    cudaMemcpy(wd.data(), d_wd, wd.size() * 2, cudaMemcpyDeviceToHost);
+    cudaMemcpy(o32.data(), d_o32, o32.size() * 4, cudaMemcpyDeviceToHost);
+    cudaMemcpy(o16.data(), d_o16, o16.size() * 2, cudaMemcpyDeviceToHost);
+    auto f = [](uint16_t b) { uint32_t u = uint32_t(b) << 16; float v; std::memcpy(&v, &u, 4); return v; };
+    double worst32 = 0, worst16 = 0, scale = 0;
+    for (int m = 0; m < M; ++m)
+      for (int n = 0; n < N; ++n) {
+        // the dequantised operands are bf16-rounded; the GEMM multiplies the unrounded ones, so this
+        // host product is within bf16 rounding of each factor (2^-8 relative per term) of the truth
+        double acc = 0;
+        for (int c = 0; c < K; ++c) acc += double(f(ad[size_t(m) * K + c])) * f(wd[size_t(n) * K + c]);
+        scale = std::max(scale, std::fabs(acc));
+        worst32 = std::max(worst32, std::fabs(o32[size_t(m) * N + n] - acc));
+        worst16 = std::max(worst16, std::fabs(f(o16[size_t(m) * N + n]) - acc));
+      }
+    if (!(scale > 0 && worst32 <= 0.02 * scale && worst16 <= 0.02 * scale))
+      std::printf("Fp4Gemm: scale %g worst32 %g worst16 %g\n", scale, worst32, worst16);
+    CHECK(scale > 0 && worst32 <= 0.02 * scale && worst16 <= 0.02 * scale);
+  }
+  // ---- the two per-layer hooks of MoEForward: router-trace observer and slot mode
+  {
+    int32_t* d_cap; cudaMalloc(reinterpret_cast<void**>(&d_cap), size_t(2) * T * k * 4);
+    cudaMemset(d_cap, 0xff, size_t(2) * T * k * 4);
+    trace::RouterCollector col;
+    col.Begin(d_cap, 2, T, k);
+    CHECK(model::MoEForward(d_x, L, X, d_y, T, k, ws, ws_bytes, nullptr, 0, 0, &col, 0).ok());
+    CHECK(model::MoEForward(d_x, L, X, d_y, T, k, ws, ws_bytes, nullptr, 0, 0, &col, 1).ok());
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    CHECK(col.captured_layers() == 2 && !col.failed());
+    std::vector<int32_t> cap(size_t(2) * T * k), ws_ids(size_t(T) * k);
+    cudaMemcpy(cap.data(), d_cap, cap.size() * 4, cudaMemcpyDeviceToHost);
+    q4t_forward_ws_layout F;
+    CHECK(q4t_moe_forward_workspace_layout(T, k, hs, is, sis, E, &F) == Q4T_OK);
+    cudaMemcpy(ws_ids.data(), static_cast<uint8_t*>(ws) + F.expert_ids, ws_ids.size() * 4, cudaMemcpyDeviceToHost);
+    for (size_t i = 0; i < ws_ids.size(); ++i) {
+      CHECK(cap[i] == ws_ids[i] && cap[ws_ids.size() + i] == ws_ids[i]);
+      CHECK(ws_ids[i] >= 0 && ws_ids[i] < E);
+    }
+    // slot mode with every expert resident in slot (E-1-e): the same layer through permuted
+    // weights must give the same bits as the plain layout
+    std::vector<uint16_t> y_plain(size_t(T) * hs), y_slots(y_plain.size());
+    cudaMemcpy(y_plain.data(), d_y, y_plain.size() * 2, cudaMemcpyDeviceToHost);
+    quant::MoEWeightLayout S = L;
+    S.slot_mode = true;
+    const size_t gup = size_t(2) * is * (hs / 2), gus = L.gu_sf_block(), dnp = size_t(hs) * (is / 2), dns = L.dn_sf_block();
+    cudaMalloc(reinterpret_cast<void**>(&S.gu_packed), E * gup);
+    cudaMalloc(reinterpret_cast<void**>(&S.gu_sf), E * gus);
+    cudaMalloc(reinterpret_cast<void**>(&S.dn_packed), E * dnp);
+    cudaMalloc(reinterpret_cast<void**>(&S.dn_sf), E * dns);
+    cudaMalloc(reinterpret_cast<void**>(&S.gu_w_scale2), E * 4);
+    cudaMalloc(reinterpret_cast<void**>(&S.gu_input_scale), E * 4);
+    cudaMalloc(reinterpret_cast<void**>(&S.dn_w_scale2), E * 4);
+    cudaMalloc(reinterpret_cast<void**>(&S.dn_input_scale), E * 4);
+    std::vector<int32_t> table(E);
+    for (int e = 0; e < E; ++e) {
+      const int slot = E - 1 - e;
+      table[e] = slot;
+      cudaMemcpy(S.gu_packed + slot * gup, L.gu_packed + e * gup, gup, cudaMemcpyDeviceToDevice);
+      cudaMemcpy(S.gu_sf + slot * gus, L.gu_sf + e * gus, gus, cudaMemcpyDeviceToDevice);
+      cudaMemcpy(S.dn_packed + slot * dnp, L.dn_packed + e * dnp, dnp, cudaMemcpyDeviceToDevice);
+      cudaMemcpy(S.dn_sf + slot * dns, L.dn_sf + e * dns, dns, cudaMemcpyDeviceToDevice);
+      cudaMemcpy(S.gu_w_scale2 + slot, L.gu_w_scale2 + e, 4, cudaMemcpyDeviceToDevice);
+      cudaMemcpy(S.gu_input_scale + slot, L.gu_input_scale + e, 4, cudaMemcpyDeviceToDevice);
+      cudaMemcpy(S.dn_w_scale2 + slot, L.dn_w_scale2 + e, 4, cudaMemcpyDeviceToDevice);
+      cudaMemcpy(S.dn_input_scale + slot, L.dn_input_scale + e, 4, cudaMemcpyDeviceToDevice);
+    }
+    int32_t* d_table; cudaMalloc(reinterpret_cast<void**>(&d_table), E * 4);
+    cudaMemcpy(d_table, table.data(), E * 4, cudaMemcpyHostToDevice);
+    quant::MoEResidency res(S, d_table, E);
+    s = model::MoEForward(d_x, res.Layout(), X, d_y, T, k, ws, ws_bytes, nullptr, 0, 0, nullptr, -1, &res);
+    if (!s.ok()) std::printf("MoEForward(slot mode): %s\n", s.message().c_str());
+    CHECK(s.ok());
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    cudaMemcpy(y_slots.data(), d_y, y_slots.size() * 2, cudaMemcpyDeviceToHost);
+    CHECK(std::memcmp(y_plain.data(), y_slots.data(), y_plain.size() * 2) == 0);
+    CHECK(model::MoEForward(d_x, L, X, d_y, T, k, ws, ws_bytes, nullptr, 0, 0, nullptr, -1, &res).message() ==
+          "slot mode: routed weights must be the residency layout");
+  }
   // the MTP draft layer's BF16 experts through the reference-shaped calls
   mtp::MoeBf16Weights B;
   B.E = E; B.hs = hs; B.moe_is = is;

@@ -5,8 +5,10 @@
 //     std::mt19937(7), normal(0,1), global scale 0.00167);
 //   * W4A4 GEMM cases of tests/quant_fp4_test.cpp:367-471 (std::mt19937(1234),
 //     shapes 640x2560 and 2560x640, weight_scale_2 0.29, input_scale 0.41),
-//     restricted to M in {1, 8} to keep the fixture small; the expected value
-//     is that test's CPU check (dequantise both sides, sequential fp32 dot);
+//     all four M of that test (1, 8, 64, 256); the expected value is that
+//     test's CPU check (dequantise both sides, sequential fp32 dot).  To keep
+//     the fixture small the M = 256 cases store the expected rows 0, 8, 16, ...
+//     only (gemm*_m256_out_rows8); the operands are stored in full;
 //   * encoder tables: FloatToE4m3 over every non-negative bf16 bit pattern and
 //     FloatToE2m1Code over every bf16 bit pattern.
 // The quantisation loop below follows HostQuantize (tests/quant_fp4_test.cpp:
@@ -128,23 +130,26 @@ int main(int argc, char** argv) {
       for (int M : Ms) {
         std::vector<float> a(size_t(M) * K);
         for (auto& x : a) x = dist(rng);  // consumed for every M to keep the stream in step
-        if (M > 8) continue;
         Q aq = quantize(a, M, K, ia);
         std::vector<uint8_t> asw = SwizzleSf(aq.sf.data(), M, K);
         std::vector<float> ad = dequant(aq, M, K, ia);
-        std::vector<float> out(size_t(M) * N);
-        for (int m = 0; m < M; ++m)
+        const int row_step = M > 64 ? 8 : 1;  // rows of the expected output that are stored
+        const int rows_out = (M + row_step - 1) / row_step;
+        std::vector<float> out(size_t(rows_out) * N);
+        for (int mi = 0; mi < rows_out; ++mi) {
+          const int m = mi * row_step;
           for (int n = 0; n < N; ++n) {
             float acc = 0.0f;
             for (int k = 0; k < K; ++k) acc += ad[size_t(m) * K + k] * wd[size_t(n) * K + k];
-            out[size_t(m) * N + n] = acc;
+            out[size_t(mi) * N + n] = acc;
           }
+        }
         std::snprintf(nm, sizeof nm, "gemm%d_m%d_a_packed", s, M);
         dump(dir, nm, aq.packed.data(), aq.packed.size(), "u1", {size_t(M), size_t(K / 2)});
         std::snprintf(nm, sizeof nm, "gemm%d_m%d_a_sf_swz", s, M);
         dump(dir, nm, asw.data(), asw.size(), "u1", {asw.size()});
-        std::snprintf(nm, sizeof nm, "gemm%d_m%d_out", s, M);
-        dump(dir, nm, out.data(), out.size() * 4, "f4", {size_t(M), size_t(N)});
+        std::snprintf(nm, sizeof nm, row_step == 1 ? "gemm%d_m%d_out" : "gemm%d_m%d_out_rows8", s, M);
+        dump(dir, nm, out.data(), out.size() * 4, "f4", {size_t(rows_out), size_t(N)});
       }
     }
   }

@@ -57,3 +57,22 @@ def test_replication_balances_a_skewed_router(ep):
 
     assert worst_over_mean(0) > 1.25
     assert worst_over_mean(3) < 1.01
+
+
+@pytest.mark.parametrize("world,hot", [(2, 3), (8, 32), (4, 0)])
+def test_owner_table_matches_placement(ep, world, hot):
+    """The table the selective publish step uses: a sharded expert names its one serving rank,
+    a replicated expert is marked -1 (served where the token lives)."""
+    E = 512
+    counts = _zipf_counts(E, 100000, 1.1, seed=7 * world + hot)
+    experts, tables = ep.plan_placement(counts, world, hot)
+    owner = ep.owner_table(tables)
+    assert owner.dtype == np.int32 and owner.shape == (E,)
+    REPL = 1 << 30
+    for e in range(E):
+        serving = [r for r in range(world) if tables[r][e] >= 0]
+        if tables[0][e] >= 0 and tables[0][e] & REPL:
+            assert owner[e] == -1 and len(serving) == world
+        else:
+            assert serving == [int(owner[e])]
+    assert int((owner < 0).sum()) == hot

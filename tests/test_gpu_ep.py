@@ -107,15 +107,17 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
         experts, tables = ep.plan_placement(np.bincount(ids_ref, minlength=E), W, hot=3)
         assert sorted(e for lst in experts for e in lst[:-3]) == sorted(set(range(E)) - set(experts[0][-3:]))
     for r in range(W):
-        placement = None
+        placement = owner = None
         if expert_map == 2:
             local = ep.local_layer_from_list(q4t, full, experts[r])
             placement = torch.from_numpy(tables[r]).cuda()
+            owner = torch.from_numpy(ep.owner_table(tables)).cuda()
         elif expert_map == 1:
             local = epb._local_layer_interleaved(q4t, full, r, W)
         else:
             local = _slice_layer(q4t, full, r * per, (r + 1) * per)
-        buf = ep.PeerBuffers(q4t, W, r, Tl, k, hs, expert_map=expert_map, placement=placement).from_pointers(ptrs)
+        buf = ep.PeerBuffers(q4t, W, r, Tl, k, hs, expert_map=expert_map, placement=placement,
+                             expert_owner=owner).from_pointers(ptrs)
         drv.append(ep.PeerExpertParallelMoE(q4t, local, E, hs, k, W, r, Tl, buf))
     xs = [x[r * Tl:(r + 1) * Tl].contiguous() for r in range(W)]
     # first step: the separate entry points; second step below: the two single-call entries
@@ -127,7 +129,10 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
     for d in drv:
         q4t.check(q4t.load().q4t_moe_workspace_status(d.ws.data_ptr(), W * Tl, k, hs, is_, d.L.E))
     assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
-    # a second step over the same buffers (stale rows from step one must not leak)
+    # a second step over the same buffers (stale rows from step one must not leak); this one
+    # publishes selectively: a token is stored only on the ranks that serve one of its experts
+    for p in pub:
+        p[0].fill_(0xEE)     # whatever is not published this step must not be read either
     x2 = dev(synth.make_x(T, hs, seed=12)).view(torch.bfloat16)
     fwd(x2, y_ref)
     xs = [x2[r * Tl:(r + 1) * Tl].contiguous() for r in range(W)]

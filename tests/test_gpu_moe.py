@@ -47,26 +47,33 @@ def test_routed_forward_vs_oracle(q4t, gpu_lib, E, hs, is_, T, k):
     tile_row0 = host(rf.region("tile_row0", torch.int32, nt))
     a_sf = host(rf.region("a_sf_tiles", torch.uint8, rf.layout.max_tiles * ((hs + 63) // 64) * 512))
     assert np.array_equal(_tile_local_sf(a_sf, row_tile, tile_row0, R, hs), taps["a_sf"])
-    # gate/up projection rounded to bf16
+    # gate/up projection rounded to bf16: every value equals the oracle's bf16(exact dot * alpha)
     gu = host(rf.region("gu_out", torch.int16, R * 2 * is_)).reshape(R, -1)
     ulp = bf16_ulp_diff(gu, taps["gu_out"])
-    print(f"gu_out mismatches {(ulp > 0).sum()} of {ulp.size}, max ulp {ulp.max()}")
-    assert ulp.max() <= 1 and (ulp > 0).mean() < 1e-3
-    # intermediate codes/scales: equal except where a bf16 mismatch or the
-    # device exp intrinsic moved a value across a rounding boundary
+    gu_bad = int((ulp > 0).sum())
+    # intermediate codes/scales: equal except where the device exp intrinsic (the oracle uses
+    # the C library's expf) moved a SwiGLU value across a rounding boundary
     ip = host(rf.region("inter_packed", torch.uint8, R * is_ // 2)).reshape(R, -1)
-    byte_mismatch = (ip != taps["i_packed"]).mean()
+    code_bad = int((ip != taps["i_packed"]).sum())
     i_sf = host(rf.region("inter_sf_tiles", torch.uint8, rf.layout.max_tiles * ((is_ + 63) // 64) * 512))
-    sf_mismatch = (_tile_local_sf(i_sf, row_tile, tile_row0, R, is_) != taps["i_sf"]).mean()
-    print(f"intermediate code bytes differing: {byte_mismatch:.2e}, scales differing: {sf_mismatch:.2e}")
-    assert byte_mismatch < 2e-3 and sf_mismatch < 2e-3
-    # down projection rows and the combined output
+    sf_bad = int((_tile_local_sf(i_sf, row_tile, tile_row0, R, is_) != taps["i_sf"]).sum())
+    # down projection rows: a flipped intermediate code moves the dot product, so rows that
+    # hold one are compared by value; all others bit for bit
     dn = host(rf.region("dn_out", torch.int16, R * hs)).reshape(R, -1)
+    clean_rows = ~(ip != taps["i_packed"]).any(axis=1)
+    dn_bad_clean = int((dn[clean_rows] != taps["dn_out"][clean_rows]).sum())
     dn_f, want_dn = O.bf16_to_f32(dn), O.bf16_to_f32(taps["dn_out"])
-    assert np.abs(dn_f - want_dn).max() <= 2e-2 * np.abs(want_dn).max()
+    dn_err = float(np.abs(dn_f - want_dn).max() / np.abs(want_dn).max())
     scale = np.abs(want_y).max()
     err = np.abs(y - want_y).max() / scale
-    print(f"routed output: max |diff| / max |ref| = {err:.3e}")
+    print(f"[routed E={E} hs={hs} is={is_} T={T} k={k}] gu_out values differing {gu_bad} of {ulp.size} (max ulp {ulp.max()}); "
+          f"intermediate code bytes differing {code_bad} of {ip.size}, scale bytes {sf_bad}; dn_out values differing in rows "
+          f"with equal codes {dn_bad_clean}; dn_out max|diff|/max {dn_err:.2e}; y max|diff|/max|ref| {err:.3e}")
+    assert gu_bad == 0, "the tensor-core gate/up projection must round to the oracle's bf16 value everywhere"
+    # observed on B200: no differing code or scale byte in these four cases; a handful would
+    # be the exp intrinsic (1 in 6e7 codes in the reference's own audit), more is a bug
+    assert code_bad <= 2 and sf_bad <= 1
+    assert dn_bad_clean == 0
     assert err <= 2e-3      # north-star tolerance on the layer output
 
 
@@ -235,3 +242,70 @@ def test_config0_full_size_layer_vs_oracle(q4t, gpu_lib):
     print(f"config 0 layer output: max |diff| / max |ref| = {err:.3e}; routed equal bits: "
           f"{np.array_equal(got_routed, routed)}")
     assert err <= 2e-3 + 2.0 ** -8
+
+
+def test_router_trace_observer_and_slot_mode(q4t, gpu_lib):
+    """The two per-layer hooks of the engine's MoEForward call (src/model/decoder_layer.cu:700-703):
+    the router-trace observer receives the ORIGINAL selected ids [T,k] (src/model/moe.cu:485-488),
+    and slot mode runs the layer on 64 resident slots out of 128 experts (include/q4t/quant/
+    moe_weights.h:47-51): resident experts give the bits of the full layer's routed rows,
+    non-resident ones contribute nothing."""
+    E, slots, hs, is_, sis, k, T = 128, 64, 512, 256, 128, 6, 40
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=91, per_expert_input_scale=True)
+    full = q4t.DeviceLayer.from_host(L)
+    x = synth.make_x(T, hs, seed=9)
+    rng = np.random.default_rng(4)
+    resident = np.sort(rng.choice(E, size=slots, replace=False))
+    order = rng.permutation(slots)                       # expert resident[i] lives in slot order[i]
+    table = np.full(E, -1, np.int32)
+    table[resident] = order.astype(np.int32)
+    expert_of_slot = np.empty(slots, np.int64)
+    expert_of_slot[order] = resident
+    pick = torch.from_numpy(expert_of_slot).cuda()
+    t = dict(full.t)
+    t["gu_packed"] = full.t["gu_packed"].view(E, -1).index_select(0, pick).view(-1, hs // 2)
+    t["gu_sf"] = full.t["gu_sf"].view(E, -1).index_select(0, pick).view(-1)
+    t["dn_packed"] = full.t["dn_packed"].view(E, -1).index_select(0, pick).view(-1, is_ // 2)
+    t["dn_sf"] = full.t["dn_sf"].view(E, -1).index_select(0, pick).view(-1)
+    for n in ("gu_w_scale2", "gu_input_scale", "dn_w_scale2", "dn_input_scale"):
+        t[n] = full.t[n].index_select(0, pick)
+    slot_layer = q4t.DeviceLayer(slots, hs, is_, sis, t, E_router=E)
+    slot_layer.routed.slot_mode = 1
+    fwd = q4t.MoEForward(slot_layer, T, k)
+    y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    captured = torch.full((T, k), -7, dtype=torch.int32, device="cuda")
+    fwd(dev(x), y, flags=2, trace_ids_out=captured, slot_of_expert=dev(table))
+    fwd.status()
+    # the observer sees the ids the router selected among all E experts
+    logits = host(fwd.region("logits", torch.int16, T * E)).reshape(T, E)
+    ids = host(fwd.region("expert_ids", torch.int32, T * k)).reshape(T, k)
+    rw = host(fwd.region("router_w", torch.float32, T * k)).reshape(T, k)
+    want_ids, _ = O.router_topk(logits, k)
+    assert np.array_equal(ids, want_ids)
+    assert np.array_equal(host(captured), want_ids)
+    got_slots = host(fwd.region("slot_ids", torch.int32, T * k)).reshape(T, k)
+    assert np.array_equal(got_slots, table[ids])
+    assert (got_slots < 0).any() and (got_slots >= 0).any(), "the case must mix resident and absent experts"
+    # oracle on the FULL layer with the absent experts' entries skipped
+    masked = np.where(table[ids] >= 0, ids, -1).astype(np.int32)
+    routed = O.routed_forward(x, masked, rw, L, 1)
+    got_routed = host(fwd.region("routed", torch.float32, T * hs)).reshape(T, hs)
+    assert np.abs(got_routed - routed).max() <= 2e-3 * np.abs(routed).max()
+    want_y = O.bf16_to_f32(O.shared_combine(x, routed, L, 1))
+    err = np.abs(O.bf16_to_f32(host(y)) - want_y).max() / np.abs(want_y).max()
+    assert err <= 2e-3 + 2.0 ** -8
+    # the routed experts of the FULL layout on the same ids (absent experts skipped) and the
+    # same weights give the same bits
+    rf = q4t.RoutedForward(full, T, k)
+    y32 = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
+    rf(dev(x), dev(masked), dev(rw), y32)
+    rf.status()
+    assert np.array_equal(host(y32), got_routed)
+    # slot count out of range is refused
+    import ctypes as C
+    bad = q4t.ForwardOptions(None, None, dev(table).data_ptr(), 0, 0)
+    slot_layer.routed.E = E + 1
+    rc = q4t.load().q4t_moe_forward_ex(dev(x).data_ptr(), C.byref(slot_layer.routed), C.byref(slot_layer.extra),
+                                       y.data_ptr(), T, k, fwd.ws.data_ptr(), fwd.layout.total, C.byref(bad), None)
+    assert rc != 0 and b"slot count" in q4t.load().q4t_last_error()
+    slot_layer.routed.E = slots
