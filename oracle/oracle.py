@@ -26,6 +26,18 @@ def build(force: bool = False) -> None:
         subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
 
 
+def build_ref_gpu() -> bool:
+    """Compile the reference's own GPU implementation of the routed experts into
+    oracle/_ref/libq4t_ref_gpu.so (the second oracle of the GPU tests) when the reference tree
+    and nvcc are present; returns whether the library exists afterwards.  A failure to build is
+    not an error: the tests that use it skip."""
+    try:
+        subprocess.run(["make", "-C", _HERE, "ref_gpu"], check=True, capture_output=True, timeout=900)
+    except (subprocess.SubprocessError, OSError):
+        pass
+    return os.path.exists(os.path.join(_HERE, "_ref", "libq4t_ref_gpu.so"))
+
+
 def _p(a, t):
     return a.ctypes.data_as(C.POINTER(t)) if a is not None else None
 

@@ -1,10 +1,19 @@
 """bench.py's multi-GPU arm: the expert-parallel prefill layer.
 
-T = 32768 tokens per step sharded contiguously over the ranks, hidden 2048,
-512 experts in contiguous blocks of 512/N per GPU, top-10, intermediate 512,
-shared expert 512, Zipf(s=1.1) expert popularity (the popularity rank is a
-seeded permutation of the experts, so hot experts are spread over the GPUs).
-One process per GPU under torchrun; NCCL all-to-all for dispatch and return.
+T = 32768 tokens per step sharded contiguously over the ranks, hidden 2048, 512 experts,
+top-10, intermediate 512, shared expert 512, Zipf(s=1.1) expert popularity (the popularity
+rank is a seeded permutation of the experts).  One process per GPU under torchrun.
+
+Default exchange ("peer"): no row collectives.  After routing, each rank's quantiser stores a
+token's NVFP4 codes into the gathered buffer of exactly the ranks that serve one of its
+experts (peer stores over NVLink); the int32 expert ids are all-gathered with NCCL; every
+rank runs its experts and the down GEMM's epilogue stores each result row straight into the
+token owner's landing buffer; one tiny all-reduce says "all rows have landed"; the owner
+combines.  Placement: the --hot-experts most used experts of a profiling batch (a batch that
+is not one of the timed inputs) are replicated on every GPU, the rest dealt out by load; the
+line also carries the time of plain contiguous sharding (512/N experts per GPU, nothing
+replicated: the placement the benchmark configuration names) as `plain_sharding`.
+--exchange rows is the all-to-all of bf16 rows over NCCL with contiguous blocks.
 """
 from __future__ import annotations
 
@@ -83,23 +92,37 @@ def main_multi(args):
     drv_rows = ep.ExpertParallelMoE(ops, world, rank)
     drv = drv_rows
     placement = None
+    drv_plain = None
     if peer_mode:
-        # Placement from a profiling batch: the most used experts are replicated on every rank,
-        # the others dealt out by load (hot_experts 0: plain interleaving e % N instead).
+        def connect(buf):
+            gathered = [None] * world
+            dist.all_gather_object(gathered, buf.handles())
+            buf.connect(gathered)
+            return buf
+
+        # Placement from a profiling batch that is NOT one of the timed inputs: the most used
+        # experts are replicated on every rank, the others dealt out by load (hot_experts 0:
+        # plain interleaving e % N instead).
+        owner = None
         if args.hot_experts > 0:
-            ops.router(xs[0])
+            x_prof = syn.make_x(T_loc, HS, seed=7000 + rank, bias_column=True)
+            ops.router(x_prof)
             counts = torch.bincount(ops.ids.flatten().long(), minlength=E)
             dist.all_reduce(counts)
             experts, tables = ep.plan_placement(counts.cpu().numpy(), world, args.hot_experts)
             local_i = ep.local_layer_from_list(q4t, full, experts[rank])
             placement = torch.from_numpy(tables[rank]).cuda()
+            owner = torch.from_numpy(ep.owner_table(tables)).cuda()
+            del x_prof
         else:
             local_i = _local_layer_interleaved(q4t, full, rank, world)
-        buf = ep.PeerBuffers(q4t, world, rank, T_loc, K_TOP, HS, expert_map=1, placement=placement).allocate()
-        gathered = [None] * world
-        dist.all_gather_object(gathered, buf.handles())
-        buf.connect(gathered)
+        buf = connect(ep.PeerBuffers(q4t, world, rank, T_loc, K_TOP, HS, expert_map=1, placement=placement,
+                                     expert_owner=owner).allocate())
         drv = ep.PeerExpertParallelMoE(q4t, local_i, E, HS, K_TOP, world, rank, T_loc, buf)
+        if not args.quick and args.hot_experts > 0:
+            # the benchmark configuration's own placement: contiguous blocks of 512/N experts
+            buf_p = connect(ep.PeerBuffers(q4t, world, rank, T_loc, K_TOP, HS, expert_map=0).allocate())
+            drv_plain = ep.PeerExpertParallelMoE(q4t, local, E, HS, K_TOP, world, rank, T_loc, buf_p)
         # both paths must give the same bits
         y2 = torch.empty_like(y)
         drv.forward(xs[0], y)
@@ -125,6 +148,21 @@ def main_multi(args):
     t = torch.tensor([ms], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
+    plain = None
+    if drv_plain is not None:
+        y_p = torch.empty_like(y)
+        drv_plain.forward(xs[0], y_p)
+        drv.forward(xs[0], y)
+        torch.cuda.synchronize()
+        same = torch.tensor([int(torch.equal(y.view(torch.int16), y_p.view(torch.int16)))], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        ms_p = bench.time_steps(torch, lambda i: drv_plain.forward(xs[i % 2], y_p), max(3, min(args.steps, 10)), 3, barrier)
+        t = torch.tensor([ms_p], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        plain = dict(ms_per_step=float(t.item()), tokens_per_s=T_TOTAL / (float(t.item()) * 1e-3),
+                     placement=f"contiguous blocks of {per} experts per GPU, nothing replicated",
+                     equals_replicated_placement_bits=bool(int(same.item())))
+        del y_p
 
     # End to end: every step copies its input from pinned host memory and its result back.
     # The copies run on their own streams with two buffers each way, so the input of step i+1
@@ -223,11 +261,13 @@ def main_multi(args):
         t_comm = float(mx_bytes.item()) / 770e9
         t_flop = flops_max / (4 * peaks["bf16_tflops"] * 1e12)
         target = max(t_comm, t_flop)
-        line = dict(metric="moe_layer_tokens_per_s", value=T_TOTAL / (ms * 1e-3), unit="tokens/s", n_gpus=world,
+        if plain is not None and n1 is not None:
+            plain["strong_scaling_efficiency"] = n1["ms_per_step"] / (world * plain["ms_per_step"])
+        line = dict(metric="moe_ep_prefill_tokens_per_s", value=T_TOTAL / (ms * 1e-3), unit="tokens/s", n_gpus=world,
                     steps=args.steps, warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="strong",
                     vs_baseline=None, dtype="nvfp4 (e2m1 x ue4m3, fp32 accumulate); bf16 router and shared expert",
                     data="synthetic",
-                    config=dict(workload=f"expert-parallel prefill MoE layer, T={T_TOTAL} total, {per} experts per GPU",
+                    config=dict(workload=f"expert-parallel prefill MoE layer, T={T_TOTAL} total over {world} GPUs",
                                 expert_map=(f"{args.hot_experts} most used experts of a profiling batch replicated on every GPU, "
                                             "the rest dealt out by load" if placement is not None else
                                             "interleaved (e % N)" if peer_mode else "contiguous blocks"),
@@ -235,7 +275,8 @@ def main_multi(args):
                                 hidden=HS, experts=E, top_k=K_TOP, moe_intermediate=MOE_IS, shared_intermediate=SHARED_IS,
                                 routing="zipf(s=1.1) bias on router column 0", parallelism=f"ep{world}",
                                 l2="2 inputs alternated; one step moves > 1 GB per GPU",
-                                exchange=("quantised tokens stored into every GPU's gathered buffer by the quantiser, bf16 result "
+                                exchange=("quantised tokens stored by the quantiser into the gathered buffers of the GPUs that "
+                                          "serve one of their experts, bf16 result "
                                           "rows stored into the token owner's buffer by the down GEMM's epilogue (peer memory "
                                           "over NVLink); NCCL only for the id all-gather and one barrier; "
                                           "checked bit-identical to the row-exchange path") if peer_mode else
@@ -251,7 +292,11 @@ def main_multi(args):
                     cpu_baseline=None,
                     load=dict(rows_received_max=float(mx_rows.item()), rows_received_mean=T_TOTAL * K_TOP / world,
                               imbalance=float(mx_rows.item()) / (T_TOTAL * K_TOP / world)),
-                    phase_ms_rank0=phases, expert_stage_ms_by_rank=stage_all, single_gpu_same_workload=n1)
+                    phase_ms_rank0=phases, expert_stage_ms_by_rank=stage_all, single_gpu_same_workload=n1,
+                    strong_scaling_efficiency=(n1["ms_per_step"] / (world * ms)) if n1 else None,
+                    plain_sharding=plain,
+                    note="N = 1 of this metric is `also.ep_prefill_T32768_single_gpu` of the single-GPU line "
+                         "(whose headline metric is the decode-shaped layer, another workload)")
         sys.stdout.flush()
         os.dup2(real_stdout, 1)
         print(json.dumps(line), flush=True)

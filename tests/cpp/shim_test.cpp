@@ -35,7 +35,10 @@ int main() {
   // a fake checkpoint: random codes, scales in a benign range, scalars per expert
   auto read = [&](const std::string& name, void* dst, size_t bytes) {
     if (name.find("scale_2") != std::string::npos || name.find("input_scale") != std::string::npos) {
-      const float v = name.find("input") != std::string::npos ? 0.004f : 0.0007f;
+      // the SwiGLU values of this toy layer are of order 1e-7: the down projection's input scale
+      // must be small enough for them to survive quantisation, or every routed output is zero
+      const bool input = name.find("input") != std::string::npos;
+      const float v = !input ? 0.0007f : name.find("down_proj") != std::string::npos ? 2e-9f : 0.004f;
       std::memcpy(dst, &v, sizeof(float));
       return bytes == sizeof(float);
     }
