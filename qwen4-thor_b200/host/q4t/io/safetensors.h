@@ -57,9 +57,16 @@ struct TensorInfo {
   std::vector<int64_t> shape;
   uint64_t data_start = 0;  // byte offset into the data region
   uint64_t data_end = 0;    // exclusive
+  // Element count; UINT64_MAX when a dimension is negative or the product does not fit
+  // (a hostile header), which no extent check can then accept.
   uint64_t numel() const {
     uint64_t n = 1;
-    for (int64_t d : shape) n *= static_cast<uint64_t>(d);
+    for (int64_t d : shape) {
+      if (d < 0) return UINT64_MAX;
+      const uint64_t u = static_cast<uint64_t>(d);
+      if (u != 0 && n > UINT64_MAX / u) return UINT64_MAX;
+      n *= u;
+    }
     return n;
   }
   uint64_t byte_size() const { return data_end - data_start; }
@@ -157,7 +164,10 @@ class JsonCursor {
         return Eat(close) ? true : fail();
       }
     }
-    while (p_ < end_ && *p_ != ',' && *p_ != '}' && *p_ != ']' && *p_ != ' ' && *p_ != '\n') ++p_;
+    // a bare scalar ends at a separator, a closing bracket or any JSON whitespace
+    while (p_ < end_ && *p_ != ',' && *p_ != '}' && *p_ != ']' && *p_ != ' ' && *p_ != '\n' && *p_ != '\t' &&
+           *p_ != '\r')
+      ++p_;
     return true;
   }
   // Calls f(key) for every member of the object at the cursor; f consumes the value.
@@ -259,7 +269,9 @@ class SafetensorsFile {
         problem = "incomplete entry for " + name;
         return false;
       }
-      if (t.data_end > data_bytes || t.numel() * DtypeSize(t.dtype) != t.byte_size()) {
+      const uint64_t n = t.numel(), esz = DtypeSize(t.dtype);
+      if (t.data_end > data_bytes || n == UINT64_MAX || esz == 0 || t.byte_size() % esz != 0 ||
+          t.byte_size() / esz != n) {
         problem = "extent of " + name + " does not match its shape or the file";
         return false;
       }
