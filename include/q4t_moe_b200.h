@@ -509,24 +509,6 @@ int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k,
 int32_t q4t_stage_timing_enable(int32_t enable);
 int32_t q4t_stage_timing_read(float* ms_out);
 
-/* ---- device self-checks used by the GPU tests (no reference counterpart):
- * sweep float bit patterns [first, first+count) through the kernels' hardware
- * encoders and through a compare-chain restatement of format.h and return the
- * number of disagreements in *mismatches (host pointer).  which: 0 = e2m1,
- * 1 = ue4m3 (non-negative inputs only), 2 = the epilogue's branch-free
- * reciprocal against IEEE 1/x on [1, 2^126).  Synchronises the stream.        */
-int32_t q4t_selftest_encoders(int32_t which, uint64_t first, uint64_t count,
-                              uint64_t* mismatches, uint32_t* first_bad,
-                              void* stream);
-/* Exact-arithmetic NVFP4 GEMM on CUDA cores (fp32 out = float(exact * alpha),
- * alpha = inv_w_global * inv_a_global); the device twin of the CPU oracle's
- * exact mode, for checking the tensor-core path at sizes the CPU cannot
- * reach.  Same operand layout as q4t_fp4_gemm, any N, K % 16 == 0.            */
-int32_t q4t_fp4_gemm_check(const uint8_t* w_packed, const uint8_t* w_sf,
-                           const uint8_t* a_packed, const uint8_t* a_sf,
-                           float* out, int32_t M, int32_t N, int32_t K,
-                           float inv_w_global, float inv_a_global, void* stream);
-
 #ifdef __cplusplus
 }
 #endif

@@ -70,11 +70,11 @@ class ForwardOptions(C.Structure):
 EXPORTS = [
     "q4t_last_error", "q4t_version", "q4t_set_pair_min_rows", "q4t_sf_num_gtiles", "q4t_sf_buffer_size", "q4t_sf_offset",
     "q4t_pack_expert_host", "q4t_quantize_activation_fp4", "q4t_dequant_fp4_to_bf16", "q4t_fp4_gemm",
-    "q4t_fp4_gemm_check", "q4t_router_topk", "q4t_bf16_linear", "q4t_moe_routed_workspace_bytes",
+    "q4t_router_topk", "q4t_bf16_linear", "q4t_moe_routed_workspace_bytes",
     "q4t_moe_routed_workspace_layout", "q4t_moe_routed_forward", "q4t_moe_forward_workspace_bytes",
     "q4t_moe_forward_workspace_layout", "q4t_moe_forward", "q4t_moe_forward_ex", "q4t_moe_workspace_status",
     "q4t_moe_noalloc_status",
-    "q4t_selftest_encoders", "q4t_stage_timing_enable", "q4t_stage_timing_read",
+    "q4t_stage_timing_enable", "q4t_stage_timing_read",
     "q4t_moe_routed_forward_noalloc", "q4t_ep_dispatch_workspace_bytes", "q4t_ep_dispatch",
     "q4t_moe_expert_rows", "q4t_moe_finish_workspace_bytes", "q4t_moe_finish",
     "q4t_moe_shared_expert", "q4t_moe_combine", "q4t_residual_rmsnorm_bf16",
@@ -83,6 +83,9 @@ EXPORTS = [
     "q4t_peer_buffer_alloc", "q4t_peer_buffer_free", "q4t_peer_buffer_export", "q4t_peer_buffer_open",
     "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_ep_publish_selected", "q4t_ep_route_publish", "q4t_ep_combine", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
 ]
+# libq4t_moe_b200_check.so (include/q4t_moe_b200_check.h): device-side checkers for the GPU tests only.
+CHECK_EXPORTS = ["q4t_check_last_error", "q4t_fp4_gemm_check", "q4t_selftest_encoders"]
+CHECK_LIB_PATH = os.path.join(_HERE, "libq4t_moe_b200_check.so")
 EP_MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
 EP_REPLICATED = 1 << 30
@@ -117,7 +120,6 @@ def load():
     L.q4t_quantize_activation_fp4.argtypes = [vp, vp, vp, i32, i32, f32, vp]
     L.q4t_dequant_fp4_to_bf16.argtypes = [vp, vp, vp, f32, i32, i32, vp]
     L.q4t_fp4_gemm.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, f32, vp]
-    L.q4t_fp4_gemm_check.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, f32, f32, vp]
     L.q4t_router_topk.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     L.q4t_bf16_linear.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     L.q4t_moe_routed_workspace_layout.argtypes = [i32] * 5 + [C.POINTER(RoutedWsLayout)]
@@ -161,10 +163,32 @@ def load():
                                      vp, sz, C.POINTER(ForwardOptions), vp]
     L.q4t_moe_workspace_status.argtypes = [vp, i32, i32, i32, i32, i32]
     L.q4t_moe_noalloc_status.argtypes = [i32] * 5
-    L.q4t_selftest_encoders.argtypes = [i32, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64),
-                                        C.POINTER(C.c_uint32), vp]
     _lib = L
     return L
+
+
+_check_lib = None
+
+
+def load_check():
+    """Loads the test-only companion library (exact CUDA-core GEMM, encoder sweeps)."""
+    global _check_lib
+    if _check_lib is None:
+        if not os.path.exists(CHECK_LIB_PATH):
+            raise Q4TError(f"{CHECK_LIB_PATH} is missing: build it with `python qwen4-thor_b200/build.py`")
+        L = C.CDLL(CHECK_LIB_PATH)
+        vp, i32, f32 = C.c_void_p, C.c_int32, C.c_float
+        L.q4t_check_last_error.restype = C.c_char_p
+        L.q4t_fp4_gemm_check.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, f32, f32, vp]
+        L.q4t_selftest_encoders.argtypes = [i32, C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64),
+                                            C.POINTER(C.c_uint32), vp]
+        _check_lib = L
+    return _check_lib
+
+
+def _check_rc(rc: int) -> None:
+    if rc != 0:
+        raise Q4TError(f"[{rc}] {load_check().q4t_check_last_error().decode()}")
 
 
 def check(rc: int) -> None:
@@ -267,8 +291,9 @@ def fp4_gemm(w_packed, w_sf, a_packed, a_sf, M, N, K, inv_w, inv_a, out_bf16=Fal
     dt = torch.bfloat16 if out_bf16 else torch.float32
     out = torch.empty((M, N), dtype=dt, device=w_packed.device)
     if check_kernel:
-        check(load().q4t_fp4_gemm_check(_ptr(w_packed), _ptr(w_sf), _ptr(a_packed), _ptr(a_sf), _ptr(out),
-                                        M, N, K, float(inv_w), float(inv_a), _stream_ptr(stream)))
+        _check_rc(load_check().q4t_fp4_gemm_check(_ptr(w_packed), _ptr(w_sf), _ptr(a_packed), _ptr(a_sf),
+                                                  _ptr(out), M, N, K, float(inv_w), float(inv_a),
+                                                  _stream_ptr(stream)))
     else:
         check(load().q4t_fp4_gemm(_ptr(w_packed), _ptr(w_sf), _ptr(a_packed), _ptr(a_sf), _ptr(out),
                                   1 if out_bf16 else 0, M, N, K, float(inv_w), float(inv_a),
@@ -466,5 +491,5 @@ def stage_timing_read() -> dict:
 def selftest_encoders(which: int, first: int, count: int):
     m = C.c_uint64(0)
     b = C.c_uint32(0)
-    check(load().q4t_selftest_encoders(which, first, count, C.byref(m), C.byref(b), _stream_ptr()))
+    _check_rc(load_check().q4t_selftest_encoders(which, first, count, C.byref(m), C.byref(b), _stream_ptr()))
     return m.value, b.value

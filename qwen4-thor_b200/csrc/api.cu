@@ -662,18 +662,6 @@ int32_t q4t_fp4_gemm(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t
   return e == cudaSuccess ? Q4T_OK : fail_cuda("NVFP4 GEMM launch", e);
 }
 
-int32_t q4t_fp4_gemm_check(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t* a_packed,
-                           const uint8_t* a_sf, float* out, int32_t M, int32_t N, int32_t K,
-                           float inv_w_global, float inv_a_global, void* stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || K % 16) return fail(Q4T_ERR_INVALID, "invalid GEMM dims");
-  const DeviceState* ds;
-  int rc = device_state(&ds);
-  if (rc != Q4T_OK) return rc;
-  cudaError_t e = q4t::launch_fp4_gemm_check(w_packed, w_sf, a_packed, a_sf, out, M, N, K,
-                                             inv_w_global * inv_a_global, static_cast<cudaStream_t>(stream));
-  return e == cudaSuccess ? Q4T_OK : fail_cuda("check GEMM launch", e);
-}
-
 int32_t q4t_router_topk(const uint16_t* logits, int32_t* expert_ids, float* router_w, int32_t T, int32_t E,
                         int32_t k, void* stream) {
   if (T <= 0) return Q4T_OK;
@@ -1439,35 +1427,6 @@ int32_t q4t_stage_timing_read(float* ms_out) {
       return fail_cuda("cudaEventElapsedTime", e);
     prev = i + 1;
   }
-  return Q4T_OK;
-}
-
-int32_t q4t_selftest_encoders(int32_t which, uint64_t first, uint64_t count, uint64_t* mismatches,
-                              uint32_t* first_bad, void* stream) {
-  if (!mismatches || !first_bad) return fail(Q4T_ERR_INVALID, "null pointer");
-  const DeviceState* ds;
-  int rc = device_state(&ds);
-  if (rc != Q4T_OK) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  unsigned long long* d_m = nullptr;
-  uint32_t* d_b = nullptr;
-  cudaError_t e;
-  if ((e = cudaMalloc(&d_m, 8)) != cudaSuccess) return fail_cuda("cudaMalloc", e);
-  if ((e = cudaMalloc(&d_b, 4)) != cudaSuccess) {
-    cudaFree(d_m);
-    return fail_cuda("cudaMalloc", e);
-  }
-  cudaMemsetAsync(d_m, 0, 8, st);
-  cudaMemsetAsync(d_b, 0xff, 4, st);
-  e = q4t::launch_encoder_selftest(which, first, count, d_m, d_b, st);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-  unsigned long long m = 0;
-  if (e == cudaSuccess) e = cudaMemcpy(&m, d_m, 8, cudaMemcpyDeviceToHost);
-  if (e == cudaSuccess) e = cudaMemcpy(first_bad, d_b, 4, cudaMemcpyDeviceToHost);
-  cudaFree(d_m);
-  cudaFree(d_b);
-  if (e != cudaSuccess) return fail_cuda("encoder self-check", e);
-  *mismatches = m;
   return Q4T_OK;
 }
 

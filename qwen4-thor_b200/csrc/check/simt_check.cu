@@ -1,9 +1,11 @@
 // Verification GEMM on CUDA cores: exact integer evaluation of the NVFP4 dot
 // product, out = float(exact * alpha).  It is the device-side twin of the CPU
 // oracle's exact mode and exists so that tests can check the tensor-core
-// kernels at sizes the CPU cannot reach; the layer entry points never use it.
-#include "kernels.h"
-#include "q4t_device.cuh"
+// kernels at sizes the CPU cannot reach.  Part of libq4t_moe_b200_check.so, the test-only
+// companion of the product library; the product never links it.
+#include "../kernels.h"
+#include "../q4t_device.cuh"
+#include "check_kernels.h"
 
 namespace q4t {
 

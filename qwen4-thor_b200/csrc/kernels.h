@@ -101,10 +101,6 @@ cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* x
                                       int k, cudaStream_t stream);
 cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,
                            float inv_global, int N, int K, cudaStream_t stream);
-cudaError_t launch_encoder_selftest(int which, uint64_t first, uint64_t count,
-                                    unsigned long long* d_mismatches, uint32_t* d_first_bad,
-                                    cudaStream_t stream);
-
 // ---- routing, permutation, combine (routing_kernels.cu)
 // Tables produced by the planning step, all in the routed workspace.
 struct PlanTables {
@@ -229,12 +225,5 @@ cudaError_t launch_gemm_bf16_pair(const CUtensorMap& tmap_a, const CUtensorMap& 
                                   Epilogue epi, int num_sms, cudaStream_t stream);
 cudaError_t gemm_set_attributes();
 cudaError_t gemm_pair_set_attributes();   // tc_gemm_pair.cu
-
-// ---- verification GEMM on CUDA cores (simt_check.cu): exact integer dot,
-// out = float(exact * alpha); used by tests to check the tensor-core path at
-// sizes the CPU oracle cannot reach.  Swizzled scales on both sides.
-cudaError_t launch_fp4_gemm_check(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t* a_packed,
-                                  const uint8_t* a_sf, float* out, int M, int N, int K, float alpha,
-                                  cudaStream_t stream);
 
 }  // namespace q4t

@@ -34,6 +34,18 @@ def test_exports_match_header(lib, q4t):
     assert declared == set(q4t.EXPORTS)
 
 
+def test_check_library_is_separate(lib, q4t):
+    """The device-side checkers the GPU tests use live in their own shared object: the product
+    library exports none of them, the companion exports exactly what its header declares."""
+    text = open(os.path.join(ROOT, "include", "q4t_moe_b200_check.h")).read()
+    declared = set(re.findall(r"\b(q4t_[a-z0-9_]+)\s*\(", text))
+    assert declared == set(q4t.CHECK_EXPORTS)
+    chk = q4t.load_check()
+    for name in declared:
+        assert hasattr(chk, name), f"{name} declared in the check header but not exported"
+        assert not hasattr(lib, name), f"{name} is test-only and must not be exported by the product library"
+
+
 def test_sf_helpers_match_oracle(lib):
     for rows, K in [(1, 2560), (8, 640), (129, 640), (640, 2560), (1024, 2048), (2048, 512)]:
         assert lib.q4t_sf_buffer_size(rows, K) == O.sf_buffer_size(rows, K)
