@@ -86,6 +86,10 @@ EXPORTS = [
 # libq4t_moe_b200_check.so (include/q4t_moe_b200_check.h): device-side checkers for the GPU tests only.
 CHECK_EXPORTS = ["q4t_check_last_error", "q4t_fp4_gemm_check", "q4t_selftest_encoders"]
 CHECK_LIB_PATH = os.path.join(_HERE, "libq4t_moe_b200_check.so")
+# q4t_moe_forward / q4t_moe_routed_forward flags
+FLAG_DUMP_GATE_UP = 1      # materialise the bf16 gate|up projections
+FLAG_ROUTED_F32 = 2        # materialise the fp32 routed sum (q4t_moe_forward)
+FLAG_GENERAL_PATH = 4      # batches of at most 16 tokens: take the grouped path of larger batches anyway
 EP_MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
 EP_REPLICATED = 1 << 30

@@ -81,6 +81,7 @@ int device_state(const DeviceState** out) {
     if ((e = q4t::gemm_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = q4t::gemm_pair_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = q4t::routing_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+    if ((e = q4t::small_batch_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = cudaStreamCreateWithFlags(&s.side_stream, cudaStreamNonBlocking)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&s.fork_event, cudaEventDisableTiming)) != cudaSuccess ||
         (e = cudaEventCreateWithFlags(&s.join_event, cudaEventDisableTiming)) != cudaSuccess ||
@@ -276,12 +277,98 @@ struct PeerRoute {
   uint16_t* dn_rows[q4t::kMaxPeers];
   int rows_per_rank;  // tokens_per_rank * k
 };
+// Tensor-memory columns of the decode-sized kernels: the accumulator (32) and one slot of
+// scale atoms per ring stage (16 weight-side + 16 token-side columns); at most 10 stages.
+uint32_t small_tmem_cols(int stages) {
+  const uint32_t need = 32u + 32u * static_cast<uint32_t>(stages);
+  uint32_t c = 32;
+  while (c < need) c <<= 1;
+  return c;
+}
+
+// Decode-sized batches (decode_small.cu) unless the caller asks for the general path
+// (flags bit 2) or the reduction lengths do not fit its shared-memory operand.
+bool small_batch_applies(int M, int k, int hs, int is, uint32_t flags) {
+  static const bool off = std::getenv("Q4T_NO_SMALL_BATCH") != nullptr;
+  return !off && !(flags & 4u) && M <= q4t::kSmallMaxTokens && M * k <= q4t::kSmallMaxEntries &&
+         q4t::small_batch_stages(hs, 1 << 20) > 0 && q4t::small_batch_stages(is, 1 << 20) > 0;
+}
+
+// Gate/up and down for at most 16 tokens: two launches, rows in (token,slot) order.
+int run_routed_small(const DeviceState* ds, const uint16_t* x, const int32_t* ids, const q4t_routed_weights* w,
+                     const RoutedPtrs& P, int M, int k, cudaStream_t st) {
+  const int E = w->E, hs = w->hs, is = w->moe_is, R = M * k;
+  const q4t_routed_ws_layout& L = P.L;
+  stage_end(2, st);
+  stage_end(3, st);
+  CUtensorMap tm;
+  int rc;
+  if ((rc = make_tmap(ds, &tm, false, w->gu_packed, hs / 2, static_cast<uint64_t>(E) * 2 * is, hs / 2)) != Q4T_OK)
+    return rc;
+  q4t::SmallBatchArgs g{};
+  g.ids = ids;
+  g.R = R;
+  g.k = k;
+  g.E = E;
+  g.K = hs;
+  g.n_tiles = 2 * is / 128;
+  g.w_rows_per_expert = 2 * is;
+  g.w_sf = w->gu_sf;
+  g.w_sf_stride = sf_buffer_size(2 * is, hs);
+  g.alpha_w = w->gu_w_scale2;
+  g.alpha_a = w->gu_input_scale;
+  g.in_scale = w->gu_input_scale;
+  g.src = x;
+  g.src_ld = hs;
+  g.out = P.at<uint16_t>(L.gu_out);
+  g.ldo = 2 * is;
+  g.row_of_flat = P.at<int32_t>(L.row_of_flat);
+  g.status = P.at<int32_t>(L.status);
+  g.stages = q4t::small_batch_stages(hs, R * g.n_tiles);
+  g.tmem_cols = small_tmem_cols(g.stages);
+#ifdef Q4T_TRACE
+  if (const char* t = std::getenv("Q4T_TRACE_PTR")) g.trace = reinterpret_cast<long long*>(std::strtoull(t, nullptr, 0));
+  if (const char* t = std::getenv("Q4T_TRACE_ENTRY")) g.trace_entry = std::atoi(t);
+#endif
+  cudaError_t e = q4t::launch_small_batch(0, tm, g, st);
+  if (e != cudaSuccess) return fail_cuda("decode gate/up launch", e);
+  stage_end(4, st);
+  if ((rc = make_tmap(ds, &tm, false, w->dn_packed, is / 2, static_cast<uint64_t>(E) * hs, is / 2)) != Q4T_OK) return rc;
+  q4t::SmallBatchArgs d{};
+  d.ids = ids;
+  d.R = R;
+  d.k = k;
+  d.E = E;
+  d.K = is;
+  d.n_tiles = hs / 128;
+  d.w_rows_per_expert = hs;
+  d.w_sf = w->dn_sf;
+  d.w_sf_stride = sf_buffer_size(hs, is);
+  d.alpha_w = w->dn_w_scale2;
+  d.alpha_a = w->dn_input_scale;
+  d.in_scale = w->dn_input_scale;
+  d.src = P.at<uint16_t>(L.gu_out);
+  d.src_ld = 2 * is;
+  d.out = P.at<uint16_t>(L.dn_out);
+  d.ldo = hs;
+  d.row_of_flat = nullptr;
+  d.status = P.at<int32_t>(L.status);
+  d.stages = q4t::small_batch_stages(is, R * d.n_tiles);
+  d.tmem_cols = small_tmem_cols(d.stages);
+  d.trace = g.trace;
+  d.trace_entry = g.trace_entry;
+  if ((e = q4t::launch_small_batch(1, tm, d, st)) != cudaSuccess) return fail_cuda("decode down launch", e);
+  stage_end(5, st);
+  return Q4T_OK;
+}
+
 int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids,
                     const q4t_routed_weights* w, const RoutedPtrs& P, int M, int k, uint32_t flags,
                     cudaStream_t st, bool plan_done = false, const PeerRoute* peer = nullptr) {
   const int E = w->E, hs = w->hs, is = w->moe_is;
   const int R = M * k;
   const q4t_routed_ws_layout& L = P.L;
+  if (!plan_done && !peer && small_batch_applies(M, k, hs, is, flags)) return run_routed_small(ds, x, ids, w, P, M, k, st);
   cudaError_t e;
   const q4t::PlanTables pt = plan_tables(P, E);  // the planner also clears the status words
   // large batches: CTA-pair GEMMs over pairs of row tiles of one expert
@@ -823,10 +910,19 @@ int moe_forward_impl(const uint16_t* x, const q4t_routed_weights* routed, const 
   routed_layout(T, k, hs, is, E, &P.L);
   P.base = base + F.routed_ws;
   const bool observe = trace_ids_out != nullptr || slot_of_expert != nullptr;
-  const bool fused_route = !observe && q4t::route_and_plan_fits(T, k);
+  // decode-sized NVFP4 batches need no permutation tables
+  const bool small = routed && small_batch_applies(T, k, hs, is, flags);
+  const bool fused_route = !observe && !small && q4t::route_and_plan_fits(T, k);
+  static const bool no_cluster_route = std::getenv("Q4T_NO_CLUSTER_ROUTE") != nullptr;
+  const bool cluster_route = !observe && !small && !fused_route && !no_cluster_route &&
+                             static_cast<int64_t>(T) * k < pair_min_rows() && q4t::route_plan_cluster_fits(T, k, E);
   if (fused_route) {  // small batch: top-k and the permutation tables in one launch
     if ((e = q4t::launch_route_and_plan(logits, fixed_ids, ids, rw, T, E, k, static_cast<int>(P.L.max_tiles),
                                         plan_tables(P, E), st)) != cudaSuccess)
+      return leave(fail_cuda("route+plan launch", e));
+  } else if (cluster_route) {  // up to 256 tokens: the same by a cluster of eight CTAs
+    if ((e = q4t::launch_route_plan_cluster(logits, fixed_ids, ids, rw, T, E, k, static_cast<int>(P.L.max_tiles),
+                                            plan_tables(P, E), st)) != cudaSuccess)
       return leave(fail_cuda("route+plan launch", e));
   } else {
     if ((e = q4t::launch_topk(logits, fixed_ids, ids, rw, T, E, k, st)) != cudaSuccess)
@@ -853,9 +949,9 @@ int moe_forward_impl(const uint16_t* x, const q4t_routed_weights* routed, const 
 
   // 3. routed experts
   if (routed) {
-    if ((rc = run_routed_core(ds, x, routed_ids, routed, P, T, k, flags, st, fused_route)) != Q4T_OK) return leave(rc);
+    if ((rc = run_routed_core(ds, x, routed_ids, routed, P, T, k, flags, st, fused_route || cluster_route)) != Q4T_OK) return leave(rc);
   } else if ((rc = run_routed_core_bf16(ds, x, ids, routed_bf16, P, reinterpret_cast<uint16_t*>(base + compact_at), T, k,
-                                        st, fused_route)) != Q4T_OK) {
+                                        st, fused_route || cluster_route)) != Q4T_OK) {
     return leave(rc);
   }
 

@@ -1,0 +1,392 @@
+// The routed experts for decode-sized batches (at most 16 tokens), the counterpart of the
+// reference's device-routed decode path (MoEDeviceDecode / MoEDeviceDecodeMulti,
+// include/q4t/quant/moe_decode.h:8-36, src/quant/moe_decode.cu:762-823): no permutation
+// step, no separate quantise step, and tiles shaped for streaming weights rather than for
+// arithmetic.
+//
+// With a handful of tokens every selected expert has one or two rows, so the work is reading
+// each selected expert's weights once.  The general grouped GEMM puts the token rows on the
+// 128-row side of the tcgen05 instruction and 256 weight rows on the other, which gives 4 (gate
+// /up) or 8 (down) tiles per expert: 40 tiles for one token on 148 SMs.  Here the operands trade
+// places: a tile is 128 WEIGHT rows (the M side, one full block-scale atom per 64 elements of K)
+// against up to 16 token rows (the N side), so an expert gives 2*is/128 gate/up tiles and hs/128
+// down tiles, and each CTA streams 128 x K/2 bytes of codes through a ring of TMA stages.
+//
+// One CTA per ((token,slot) entry f, weight tile).  The CTA of the first entry that names an
+// expert serves every later entry of that expert too (up to 16 per pass); CTAs of later entries
+// leave at once.  The token-side operand never exists in global memory: four warps build it in
+// shared memory, in the 128-byte-swizzled K-major layout and the scale-atom layout that TMA
+// would have produced --
+//   gate/up: the bf16 token rows quantised with the expert's input scale (the arithmetic of
+//            the row quantiser, src/quant/act_quant.cu:62-90 of the reference);
+//   down:    SwiGLU of the bf16 gate|up rows the first kernel stored, quantised with the
+//            expert's down input scale (src/quant/moe_gemm.cu:173-241) --
+// while the weight tiles are already in flight.  Every output element is the same sequence of
+// block-scaled tcgen05 MMAs over K as in the general kernel (operands swapped), followed by the
+// same alpha multiply and bf16 rounding.  Rows are stored in (token,slot) order: row_of_flat is
+// the identity (-1 for skipped entries), which is what the combine kernels consume.
+#include "kernels.h"
+#include "q4t_device.cuh"
+
+namespace q4t {
+
+namespace {
+
+constexpr int kSmallThreads = 192;                // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: operand + epilogue
+constexpr int kWorkers = 128;
+constexpr uint32_t kWTileBytes = 128 * 128;       // 128 weight rows x 128 bytes of codes
+constexpr uint32_t kWSfBytes = 4 * 512;           // their scale atoms for the four MMAs of a k-block
+constexpr uint32_t kSmallStage = kWTileBytes + kWSfBytes;
+constexpr uint32_t kOpTileBytes = kSmallN * 128;  // 16 token rows x 128 bytes
+// Token-side scale atoms are laid down 256 bytes apart: rows 0-15 of an atom are its first 256
+// bytes, and the other half (rows 16-31, never used with 16 token rows) overlaps the next atom.
+constexpr uint32_t kOpSfStride = 256;
+constexpr int kSmallMaxStages = 10;
+
+struct SmallBars {
+  uint64_t full[kSmallMaxStages];
+  uint64_t empty[kSmallMaxStages];
+  uint64_t operand_ready;   // 128 worker arrivals per pass
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  int members[kSmallMaxEntries];
+};
+
+#ifdef Q4T_TRACE
+// Debug builds: nanosecond stamps of one CTA per launch, [mode][slot].
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define Q4T_SSTAMP(slot)                                                                          \
+  do {                                                                                            \
+    if (args.trace && blockIdx.x == gridDim.x - 1 && blockIdx.y == args.trace_entry) args.trace[MODE * 32 + (slot)] = global_ns(); \
+  } while (0)
+#else
+#define Q4T_SSTAMP(slot) do {} while (0)
+#endif
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
+
+// MODE 0: gate/up (operand = quantised token rows); MODE 1: down (operand = quantised SwiGLU rows).
+template <int MODE>
+__global__ void __launch_bounds__(kSmallThreads)
+small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ SmallBatchArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ SmallBars bars;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nt = blockIdx.x, f = blockIdx.y;
+  if (threadIdx.x == 0) Q4T_SSTAMP(0);
+  const int stages = args.stages;
+  const uint32_t k_bytes = static_cast<uint32_t>(args.K) >> 1;
+  const int nkb = static_cast<int>((k_bytes + 127u) >> 7);
+  const uint32_t ntk = (static_cast<uint32_t>(args.K) + 63u) >> 6;
+  const uint32_t op_base = smem_base + static_cast<uint32_t>(stages) * kSmallStage;   // token-side codes
+  const uint32_t opsf_base = op_base + static_cast<uint32_t>(nkb) * kOpTileBytes;      // token-side scale atoms
+  volatile uint32_t* abort_flag = &bars.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&bars.full[s]), 1);
+      mbar_init(smem_u32(&bars.empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bars.operand_ready), kWorkers);
+    mbar_init(smem_u32(&bars.acc_full), 1);
+    bars.abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&bars.tmem_base), args.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars.tmem_base;
+  if (threadIdx.x == 0) Q4T_SSTAMP(1);
+  // The gate/up kernel follows the kernel that selected the experts; the down kernel reads the
+  // same ids, which were complete before the gate/up kernel started, and waits later, just
+  // before it touches the gate|up rows.
+  if (MODE == 0) chain_wait();
+  if (threadIdx.x == 0) Q4T_SSTAMP(2);
+
+  // Every warp reads the whole id table once (at most 256 entries, eight per lane, the loads
+  // all in flight together) and derives from it whether an earlier entry already serves this
+  // expert and how many entries from f on belong to it.
+  const int e = args.ids[f];
+  int idv[kSmallMaxEntries / 32];
+#pragma unroll
+  for (int c = 0; c < kSmallMaxEntries / 32; ++c) {
+    const int i = c * 32 + lane;
+    idv[c] = i < args.R ? args.ids[i] : -1;
+  }
+  bool serve = e >= 0 && e < args.E;
+  if (MODE == 0 && nt == 0 && threadIdx.x == 0) {
+    args.row_of_flat[f] = serve ? f : -1;
+    // the first CTA also clears the status word (it starts long before any bounded wait of
+    // this launch could run out)
+    if (f == 0 && args.status) *args.status = 0;
+  }
+  int n_members = 0;
+  uint32_t earlier = 0;
+#pragma unroll
+  for (int c = 0; c < kSmallMaxEntries / 32; ++c) {
+    const uint32_t m = __ballot_sync(0xffffffffu, idv[c] == e);
+    const int lo = c * 32;
+    const uint32_t below = f >= lo + 32 ? 0xffffffffu : (f <= lo ? 0u : (1u << (f - lo)) - 1u);   // entries before f
+    earlier |= m & below;
+    const uint32_t mine = m & ~below;
+    if (warp == 2 && ((mine >> lane) & 1u) && serve) bars.members[n_members + __popc(mine & ((1u << lane) - 1u))] = lo + lane;
+    n_members += __popc(mine);
+  }
+  if (earlier) serve = false;
+  const int passes = (n_members + kSmallN - 1) / kSmallN;
+  if (threadIdx.x == 0) Q4T_SSTAMP(3);
+
+  if (serve) {
+    const int w_row0 = e * args.w_rows_per_expert + nt * 128;
+    const uint8_t* w_sf = args.w_sf + static_cast<size_t>(e) * args.w_sf_stride + static_cast<size_t>(nt) * ntk * 512u;
+
+    if (warp == 0) {
+      // ---------------------------------------------------------- weight tiles by TMA
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int p = 0; p < passes && ok; ++p) {
+          uint32_t k_left = k_bytes;
+          const uint8_t* sf = w_sf;
+          for (int kb = 0; kb < nkb; ++kb) {
+            const uint32_t full = smem_u32(&bars.full[stage]), empty = smem_u32(&bars.empty[stage]);
+            if (!mbar_try_wait(empty, phase ^ 1u) && !mbar_wait(empty, phase ^ 1u, abort_flag)) {
+              ok = false;
+              break;
+            }
+            const uint32_t nm = k_left >= 128u ? 4u : k_left >> 5;
+            const uint32_t sa = smem_base + static_cast<uint32_t>(stage) * kSmallStage;
+            mbar_expect_tx(full, kWTileBytes + nm * 512u);
+            tma_load_2d(sa, &tmap_w, kb * 128, w_row0, full);
+            bulk_load(sa + kWTileBytes, sf, nm * 512u, full);
+            sf += 2048;
+            k_left -= 128u;
+            if (p == 0 && (kb == 0 || kb == nkb - 1)) Q4T_SSTAMP(kb == 0 ? 4 : 11);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+        if (!ok && args.status) atomicMax(args.status, 1);
+      }
+      if (MODE == 1) chain_wait();
+    } else if (warp == 1) {
+      // ---------------------------------------------------------- MMA issuer
+      if (MODE == 1) chain_wait();
+      if (lane == 0) {
+        // M = 128 weight rows, N = 16 token rows, both operands K-major e2m1, ue4m3 scales
+        constexpr uint32_t idesc =
+            (1u << 7) | (1u << 10) | ((static_cast<uint32_t>(kSmallN) >> 3) << 17) | ((128u >> 4) << 24);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const uint64_t wdesc0 = umma_desc_sw128(smem_base), sfw0 = umma_desc_sf(smem_base + kWTileBytes);
+        const uint64_t odesc0 = umma_desc_sw128(op_base), sfo0 = umma_desc_sf(opsf_base);
+        const uint32_t bar_full0 = smem_u32(&bars.full[0]), bar_empty0 = smem_u32(&bars.empty[0]);
+        for (int p = 0; p < passes && ok; ++p) {
+          if (!mbar_wait(smem_u32(&bars.operand_ready), static_cast<uint32_t>(p) & 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (p == 0) Q4T_SSTAMP(12);
+          uint32_t k_left = k_bytes;
+          for (int kb = 0; kb < nkb; ++kb) {
+            const uint32_t full = bar_full0 + static_cast<uint32_t>(stage) * 8u;
+            if (!mbar_try_wait(full, phase) && !mbar_wait(full, phase, abort_flag)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            if (p == 0 && (kb == 0 || kb == nkb - 1)) Q4T_SSTAMP(kb == 0 ? 13 : 20);
+            // descriptors differ from those of stage 0 / k-block 0 by constants in the 14-bit
+            // start-address field (16-byte units), so plain 64-bit adds never carry out of it
+            const uint64_t soff = static_cast<uint64_t>(stage) * (kSmallStage >> 4);
+            const uint64_t wdesc = wdesc0 + soff, sfw = sfw0 + soff;
+            const uint64_t odesc = odesc0 + static_cast<uint64_t>(kb) * (kOpTileBytes >> 4);
+            const uint64_t sfo = sfo0 + static_cast<uint64_t>(kb) * (4u * kOpSfStride >> 4);
+            const uint32_t tsf = tmem + 32u + static_cast<uint32_t>(stage) * 32u;   // this stage's scale columns
+            const uint32_t tso = tsf + 16u;
+            const uint32_t first = kb != 0;
+            if (k_left >= 128u) {
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4; ++kk) {
+                tc_cp_sf(tsf + kk * 4u, sfw + kk * 32u);
+                tc_cp_sf(tso + kk * 4u, sfo + kk * (kOpSfStride >> 4));
+              }
+#ifdef Q4T_EXP_ACC   // timing experiment only (wrong results): four independent accumulators
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4; ++kk)
+                tc_mma_nvf4(tmem + kk * 16u, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u, first);
+#else
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4; ++kk)
+                tc_mma_nvf4(tmem, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u,
+                            kk == 0 ? first : 1u);
+#endif
+            } else {
+              const uint32_t nm = k_left >> 5;
+              for (uint32_t kk = 0; kk < nm; ++kk) {
+                tc_cp_sf(tsf + kk * 4u, sfw + kk * 32u);
+                tc_cp_sf(tso + kk * 4u, sfo + kk * (kOpSfStride >> 4));
+              }
+              for (uint32_t kk = 0; kk < nm; ++kk)
+                tc_mma_nvf4(tmem, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u,
+                            kk == 0 ? first : 1u);
+            }
+            tc_commit(bar_empty0 + static_cast<uint32_t>(stage) * 8u);
+            k_left -= 128u;
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) tc_commit(smem_u32(&bars.acc_full));
+        }
+        if (!ok && args.status) atomicMax(args.status, 2);
+      }
+    } else {
+      // ---------------------------------------------------------- operand builders / epilogue
+      if (MODE == 1) chain_wait();
+      worker_sync();  // the member list is in shared memory
+      if (threadIdx.x == 64) Q4T_SSTAMP(21);
+      const int w = static_cast<int>(threadIdx.x) - 64;
+      const int quad = warp & 3;
+      const int groups = args.K >> 4;
+      const float in_scale = args.in_scale[e];
+      const float alpha = args.alpha_w[e] * args.alpha_a[e];
+      const int n_out = nt * 128 + quad * 32 + lane;   // the output column this thread's TMEM lane holds
+      bool ok = true;
+      int pass = 0;
+      for (int m0 = 0; m0 < n_members && ok; m0 += kSmallN, ++pass) {
+        const int rows = min(kSmallN, n_members - m0);
+        // ---- build the token-side operand of this pass
+        for (int item = w; item < rows * groups; item += kWorkers) {
+          const int j = item / groups, g = item - j * groups;
+          const int entry = bars.members[m0 + j];
+          float a[16];
+          if (MODE == 0) {
+            const uint4* src = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry / args.k) * args.src_ld + g * 16);
+            const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+            const uint32_t wv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              a[2 * i] = bf16x2_lo(wv[i]);
+              a[2 * i + 1] = bf16x2_hi(wv[i]);
+            }
+          } else {
+            // written by the previous kernel: plain loads, not the read-only path
+            const uint4* gsrc = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry) * args.src_ld + g * 16);
+            const uint4* usrc = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry) * args.src_ld + args.K + g * 16);
+            const uint4 g0 = gsrc[0], g1 = gsrc[1], u0 = usrc[0], u1 = usrc[1];
+            const uint32_t gb[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            const uint32_t ub[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            // (g * sigmoid(g)) * u on the bf16 projections, sigmoid through an IEEE reciprocal
+            // of 1 + __expf(-g): the general kernel's epilogue arithmetic
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float gl = bf16x2_lo(gb[i]), gh = bf16x2_hi(gb[i]);
+              const float dl = 1.0f + __expf(-gl), dh = 1.0f + __expf(-gh);
+              const float sl = dl < Q4T_RCP_FAST_MAX ? rcp_rn_ge1(dl) : __frcp_rn(dl);
+              const float sh = dh < Q4T_RCP_FAST_MAX ? rcp_rn_ge1(dh) : __frcp_rn(dh);
+              a[2 * i] = (gl * sl) * bf16x2_lo(ub[i]);
+              a[2 * i + 1] = (gh * sh) * bf16x2_hi(ub[i]);
+            }
+          }
+          uint32_t lo, hi;
+          const uint32_t sf = quantize_group16(a, in_scale, lo, hi);
+          const uint32_t kb = static_cast<uint32_t>(g) >> 4, gi = static_cast<uint32_t>(g) & 15u;
+          const uint32_t off = kb * kOpTileBytes + static_cast<uint32_t>(j) * 128u +
+                               (((gi >> 1) ^ (static_cast<uint32_t>(j) & 7u)) << 4) + (gi & 1u) * 8u;
+          *reinterpret_cast<uint2*>(smem_gen + (op_base - smem_base) + off) = make_uint2(lo, hi);
+          smem_gen[(opsf_base - smem_base) + (static_cast<uint32_t>(g) >> 2) * kOpSfStride + static_cast<uint32_t>(j) * 16u +
+                   (static_cast<uint32_t>(g) & 3u)] = static_cast<uint8_t>(sf);
+        }
+        fence_async_smem();   // the tensor core reads these bytes through the async proxy
+        mbar_arrive(smem_u32(&bars.operand_ready));
+        if (threadIdx.x == 64 && pass == 0) Q4T_SSTAMP(22);
+        // ---- epilogue of this pass
+        if (!mbar_wait(smem_u32(&bars.acc_full), static_cast<uint32_t>(pass) & 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (threadIdx.x == 64 && pass == 0) Q4T_SSTAMP(23);
+        uint32_t v[16];
+        tmem_ld16(tmem + (static_cast<uint32_t>(quad * 32) << 16), v);
+        tmem_ld_wait();
+        tc_fence_before();
+        if (n_out < args.w_rows_per_expert) {
+#pragma unroll
+          for (int j = 0; j < kSmallN; ++j)
+            if (j < rows)
+              args.out[static_cast<size_t>(bars.members[m0 + j]) * args.ldo + n_out] =
+                  f32_to_bf16(alpha * __uint_as_float(v[j]));
+        }
+      }
+      if (threadIdx.x == 64) Q4T_SSTAMP(24);
+      if (!ok && args.status && lane == 0) atomicMax(args.status, 3);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem, args.tmem_cols);
+  }
+  if (threadIdx.x == 0) Q4T_SSTAMP(25);
+}
+
+size_t small_smem_bytes(int K, int stages) {
+  const size_t nkb = (static_cast<size_t>(K) / 2 + 127) / 128, ntk = (static_cast<size_t>(K) + 63) / 64;
+  return 1024 + static_cast<size_t>(stages) * kSmallStage + nkb * kOpTileBytes + ntk * kOpSfStride + 256;
+}
+
+}  // namespace
+
+// The ring holds a whole tile (every k-block in flight at once: with a handful of tiles the
+// kernel is one memory round trip long) when there are few enough tiles for one CTA per SM;
+// otherwise four stages, so that two CTAs share an SM and one streams while the other builds
+// its operand or stores its rows.
+int small_batch_stages(int K, int tiles) {
+  const int nkb = (K / 2 + 127) / 128;
+  int stages = nkb < kSmallMaxStages ? nkb : kSmallMaxStages;
+  if (tiles > 2 * 148 && stages > 4) stages = 4;
+  if (tiles > 2 * 148)
+    while (stages > 2 && small_smem_bytes(K, stages) > 112 * 1024) --stages;
+  while (stages > 2 && small_smem_bytes(K, stages) > 200 * 1024) --stages;
+  return small_smem_bytes(K, stages) <= 200 * 1024 ? stages : 0;
+}
+
+cudaError_t small_batch_set_attributes() {
+  cudaError_t e;
+  if ((e = cudaFuncSetAttribute(small_batch_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)) != cudaSuccess)
+    return e;
+  return cudaFuncSetAttribute(small_batch_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+}
+
+cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallBatchArgs& a, cudaStream_t stream) {
+  if (a.R <= 0 || a.R > kSmallMaxEntries || a.stages <= 0) return cudaErrorInvalidValue;
+  const dim3 grid(static_cast<unsigned>(a.n_tiles), static_cast<unsigned>(a.R));
+  const size_t smem = small_smem_bytes(a.K, a.stages);
+  if (mode == 0) return launch_chained(small_batch_kernel<0>, grid, dim3(kSmallThreads), smem, stream, tmap_w, a);
+  return launch_chained(small_batch_kernel<1>, grid, dim3(kSmallThreads), smem, stream, tmap_w, a);
+}
+
+}  // namespace q4t

@@ -126,6 +126,11 @@ cudaError_t launch_topk(const uint16_t* logits, const int32_t* fixed_ids, int32_
 bool route_and_plan_fits(int T, int k);
 cudaError_t launch_route_and_plan(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw, int T,
                                   int E, int k, int max_tiles, const PlanTables& p, cudaStream_t stream);
+// 17..256 tokens: the same in one launch of an eight-CTA cluster (counts exchanged through
+// distributed shared memory).
+bool route_plan_cluster_fits(int T, int k, int E);
+cudaError_t launch_route_plan_cluster(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw,
+                                      int T, int E, int k, int max_tiles, const PlanTables& p, cudaStream_t stream);
 // even_tiles: every expert with rows gets an even number of row tiles (the last one may be
 // empty), as the CTA-pair GEMMs need.
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,
@@ -159,6 +164,39 @@ cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_f
                                  const uint16_t* shared_down, const uint16_t* x,
                                  const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
                                  int k, int hs, cudaStream_t stream);
+
+// ---- routed experts for decode-sized batches (decode_small.cu)
+constexpr int kSmallN = 16;            // token rows per pass of one CTA (the N side of the MMA)
+constexpr int kSmallMaxTokens = 16;    // largest batch that takes this path
+constexpr int kSmallMaxEntries = 256;  // (token,slot) entries: 16 tokens x top-16
+struct SmallBatchArgs {
+  const int32_t* ids;        // [R] expert (or slot) of each (token,slot) entry; outside [0,E) = skipped
+  int R, k, E;
+  int K;                     // reduction length: hs (gate/up) or moe_is (down)
+  int n_tiles;               // 128-row weight tiles per expert
+  int w_rows_per_expert;     // 2*moe_is (gate/up) or hs (down)
+  const uint8_t* w_sf;       // the experts' swizzled scale buffers
+  size_t w_sf_stride;        // bytes between two experts' buffers
+  const float* alpha_w;      // per-expert weight scale
+  const float* alpha_a;      // per-expert activation scale
+  const float* in_scale;     // per-expert global scale the token-side operand is quantised with
+  const uint16_t* src;       // gate/up: x [T, hs]; down: the bf16 gate|up rows [R, 2*moe_is]
+  int src_ld;
+  uint16_t* out;             // [R, ldo] bf16, rows in (token,slot) order
+  int ldo;
+  int32_t* row_of_flat;      // gate/up only: written as the identity (-1 for skipped entries)
+  int32_t* status;
+  int stages;                // TMA ring depth (small_batch_stages)
+  uint32_t tmem_cols;        // tensor-memory columns: 32 (accumulator) + 32 per stage, rounded up to a power of two
+  long long* trace;          // time stamps of one CTA (only read by builds with Q4T_TRACE; null otherwise)
+  int trace_entry;
+};
+// Ring depth for reduction length K and `tiles` CTAs, 0 when the token-side operand does not
+// fit shared memory.
+int small_batch_stages(int K, int tiles);
+cudaError_t small_batch_set_attributes();
+// mode 0 = gate/up, 1 = down.
+cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallBatchArgs& a, cudaStream_t stream);
 
 // ---- tensor-core GEMMs (tc_gemm.cu)
 enum class Epilogue : int {

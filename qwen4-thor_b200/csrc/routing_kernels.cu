@@ -448,6 +448,119 @@ __global__ void __launch_bounds__(1024) plan_small_kernel(const int32_t* ids, in
   }
 }
 
+// Top-k and the permutation tables for 17..256 tokens in one launch: a cluster of eight CTAs.
+// CTA c of the cluster owns the tokens [c*tpc, (c+1)*tpc), tpc = ceil(T/8) <= 32: one warp per
+// token selects the experts (as topk_kernel), one thread per (token,slot) entry ranks it among
+// the CTA's entries of the same expert, and the CTAs read each other's per-expert counts
+// through distributed shared memory, so that every CTA knows where its entries start inside
+// each expert's rows.  The stable order (expert ascending, then (token,slot) ascending) falls
+// out of the CTA order.  All eight CTAs scan the same totals; CTA 0 writes the tables that do
+// not belong to entries.  No global counters, no second launch.
+constexpr int kRouteClusterCtas = 8;
+__device__ __forceinline__ int32_t ld_cluster_s32(uint32_t cluster_addr) {
+  int32_t v;
+  asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+__global__ void __launch_bounds__(1024) route_plan_cluster_kernel(const uint16_t* __restrict__ logits,
+                                                                  const int32_t* __restrict__ fixed_ids,
+                                                                  int32_t* ids_out, float* rw_out, int T, int k, int E,
+                                                                  int max_tiles, PlanTables p, int even_tiles) {
+  chain_wait();
+  extern __shared__ uint16_t s_wcnt[];  // [16][E]: entries per (warp of entries, expert), then exclusive bases
+  __shared__ int32_t s_own[1024];       // this CTA's entries per expert; later: entries of earlier CTAs
+  __shared__ int32_t s_rows[1024];
+  __shared__ int32_t s_tiles[1024];
+  const int e = threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_cta_rank());
+  const int tpc = (T + kRouteClusterCtas - 1) / kRouteClusterCtas;
+  const int t0 = min(T, rank * tpc);
+  const int n_tok = min(T - t0, tpc);
+  const int f0 = t0 * k, n_ent = n_tok * k;    // this CTA's (token,slot) entries: [f0, f0 + n_ent), at most 512
+  const int n_ew = (n_ent + 31) >> 5;          // warps of entries
+  if (warp < n_tok)
+    topk_token(logits + static_cast<size_t>(t0 + warp) * E,
+               fixed_ids ? fixed_ids + static_cast<size_t>(t0 + warp) * k : nullptr,
+               ids_out + static_cast<size_t>(t0 + warp) * k, rw_out + static_cast<size_t>(t0 + warp) * k, E, k, lane);
+  for (int i = threadIdx.x; i < n_ew * E; i += 1024) s_wcnt[i] = 0;
+  __threadfence_block();  // the ids are read back below by other warps
+  __syncthreads();
+  // thread i owns entry f0 + i
+  const bool have = e < n_ent;
+  const int v = have ? ids_out[f0 + e] : -1;
+  const bool valid = v >= 0 && v < E;
+  uint32_t peers = 0;
+  if (warp < n_ew) {
+    peers = __match_any_sync(0xffffffffu, valid ? v : -1 - lane);
+    if (valid && __popc(peers & ((1u << lane) - 1u)) == 0) s_wcnt[warp * E + v] = static_cast<uint16_t>(__popc(peers));
+  }
+  __syncthreads();
+  int32_t own = 0;
+  if (e < E) {
+    for (int w = 0; w < n_ew; ++w) {
+      const int32_t c = s_wcnt[w * E + e];
+      s_wcnt[w * E + e] = static_cast<uint16_t>(own);
+      own += c;
+    }
+  }
+  s_own[e] = own;
+  cluster_sync();  // every CTA's counts are in its shared memory
+  int32_t c = 0, before = 0;
+  if (e < E) {
+    const uint32_t mine = smem_u32(&s_own[e]);
+#pragma unroll
+    for (int r = 0; r < kRouteClusterCtas; ++r) {
+      const int32_t o = ld_cluster_s32(cluster_map(mine, static_cast<uint32_t>(r)));
+      c += o;
+      if (r < rank) before += o;
+    }
+  }
+  cluster_sync();  // no CTA reads another's shared memory after this point
+  int32_t tiles = (c + kTileM - 1) / kTileM;
+  if (even_tiles) tiles = (tiles + 1) & ~1;
+  block_scan_pair(c, tiles, s_rows, s_tiles);  // inclusive scans of rows and row tiles over the experts
+  const int32_t row_base = s_rows[e] - c, tile_base = s_tiles[e] - tiles;
+  const int32_t total_rows = s_rows[1023], total_tiles = s_tiles[1023];
+  __syncthreads();
+  s_rows[e] = row_base;   // from here on: first grouped row / first row tile of expert e
+  s_tiles[e] = tile_base;
+  s_own[e] = before;      // entries of expert e that belong to earlier CTAs
+  if (rank == 0) {
+    if (e < E) {
+      p.counts[e] = c;
+      p.offsets[e] = row_base;
+      p.tile_off[e] = tile_base;
+      for (int i = 0; i < tiles; ++i) {
+        const int t = tile_base + i;
+        if (t < max_tiles) {
+          p.tile_expert[t] = e;
+          p.tile_row0[t] = row_base + i * kTileM;
+          p.tile_nrows[t] = max(0, min(kTileM, c - i * kTileM));
+        }
+      }
+    }
+    if (e == 0) {
+      p.offsets[E] = total_rows;
+      p.tile_off[E] = total_tiles;
+      p.ntiles[0] = min(total_tiles, max_tiles);
+    }
+    if (e < 4 && p.status) p.status[e] = 0;
+  }
+  __syncthreads();
+  if (have) {
+    const int f = f0 + e;
+    if (valid) {
+      const int in_expert = s_own[v] + s_wcnt[warp * E + v] + __popc(peers & ((1u << lane) - 1u));
+      const int row = s_rows[v] + in_expert;
+      p.row_of_flat[f] = row;
+      p.flat_of_row[row] = f;
+      p.row_tile[row] = s_tiles[v] + in_expert / kTileM;
+    } else {
+      p.row_of_flat[f] = -1;
+    }
+  }
+}
+
 // ---- expert-parallel helpers
 // dest[f] = owner rank of expert ids[f] (experts are split into contiguous
 // blocks of experts_per_rank); local[f] = index of that expert on its owner.
@@ -769,6 +882,17 @@ cudaError_t launch_route_and_plan(const uint16_t* logits, const int32_t* fixed_i
   return launch_chained(plan_small_kernel<true>, dim3(1), dim3(1024), 32 * E * sizeof(uint16_t), stream,
                         static_cast<const int32_t*>(nullptr), T * k, E, max_tiles, p, logits, fixed_ids, ids, rw, T, k,
                         E, 0);
+}
+
+bool route_plan_cluster_fits(int T, int k, int E) {
+  return T > 16 && T <= kRouteClusterCtas * 32 && k >= 1 && k <= 16 && E <= 1024;
+}
+
+cudaError_t launch_route_plan_cluster(const uint16_t* logits, const int32_t* fixed_ids, int32_t* ids, float* rw, int T,
+                                      int E, int k, int max_tiles, const PlanTables& p, cudaStream_t stream) {
+  return launch_chained_cluster(route_plan_cluster_kernel, dim3(kRouteClusterCtas), dim3(1024),
+                                16 * static_cast<size_t>(E) * sizeof(uint16_t), stream, kRouteClusterCtas, logits,
+                                fixed_ids, ids, rw, T, k, E, max_tiles, p, 0);
 }
 
 cudaError_t launch_plan(const int32_t* ids, int R, int E, int max_tiles, const PlanTables& p,

@@ -21,7 +21,7 @@ def _tile_local_sf(buf, row_tile, tile_row0, rows, K):
     return buf[off]
 
 
-def _run_routed(q4t, L, T, k, seed, flags=1):
+def _run_routed(q4t, L, T, k, seed, flags=1 | 4):   # the grouped path at every T: its workspace taps are compared
     dl = q4t.DeviceLayer.from_host(L)
     x = synth.make_x(T, L.hs, seed=seed)
     ids, rw = synth.random_routing(T, k, L.E, seed=seed + 1)

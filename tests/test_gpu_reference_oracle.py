@@ -108,7 +108,8 @@ def _sorted_rows(a, offsets):
     return out
 
 
-@pytest.mark.parametrize("E,hs,is_,T,k", [(512, 2048, 512, 16, 10), (64, 2560, 640, 40, 10), (32, 1024, 256, 300, 4)])
+@pytest.mark.parametrize("E,hs,is_,T,k", [(512, 2048, 512, 16, 10), (64, 2560, 640, 40, 10), (32, 1024, 256, 300, 4),
+                                          (256, 2560, 640, 1, 10), (256, 2560, 640, 8, 10)])
 def test_routed_forward_equals_reference_gpu(q4t, ref_gpu, gemm_ws, E, hs, is_, T, k):
     """MoERoutedForward of the reference (per-expert cuBLASLt loop) and q4t_moe_routed_forward on
     the same seeded layer and routing: the grouped down-projection rows (as per-expert sets of
@@ -149,7 +150,7 @@ def test_routed_forward_equals_reference_gpu(q4t, ref_gpu, gemm_ws, E, hs, is_, 
     # this library
     rf = q4t.RoutedForward(dl, T, k)
     y = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
-    rf(x, ids, rw, y)
+    rf(x, ids, rw, y, flags=q4t.FLAG_GENERAL_PATH)
     rf.status()
     offsets = host(rf.region("offsets", torch.int32, E + 1))
     o_dn = host(rf.region("dn_out", torch.int16, R * hs)).reshape(R, -1)
@@ -159,3 +160,15 @@ def test_routed_forward_equals_reference_gpu(q4t, ref_gpu, gemm_ws, E, hs, is_, 
           f"dn_out bf16 values {dn_bad} of {o_dn.size}, routed fp32 values {y_bad} of {y.numel()}")
     assert dn_bad == 0
     assert y_bad == 0
+    if T <= 16:
+        # the decode-sized path (rows in (token,slot) order) against the same reference output
+        fofr = host(rf.region("flat_of_row", torch.int32, R))[:offsets[-1]]
+        y2 = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
+        rf(x, ids, rw, y2)
+        rf.status()
+        assert np.array_equal(host(rf.region("row_of_flat", torch.int32, R)), np.arange(R))
+        s_dn = host(rf.region("dn_out", torch.int16, R * hs)).reshape(R, -1)[fofr]
+        dn_bad = int((_sorted_rows(s_dn, offsets) != _sorted_rows(r_dn, offsets)).sum())
+        y_bad = int((host(y2) != host(y_ref)).sum())
+        print(f"    decode-sized path: dn_out bf16 values differing {dn_bad}, routed fp32 values differing {y_bad}")
+        assert dn_bad == 0 and y_bad == 0

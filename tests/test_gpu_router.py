@@ -80,7 +80,7 @@ def test_permutation_tables(q4t, gpu_lib, T, k, E):
     x = synth.make_x(T, L.hs)
     rf = q4t.RoutedForward(dl, T, k)
     y = torch.zeros((T, L.hs), dtype=torch.float32, device="cuda")
-    rf(dev(x), dev(ids), dev(rw), y)
+    rf(dev(x), dev(ids), dev(rw), y, flags=4)     # the grouped path also for decode-sized batches
     rf.status()
     counts, offsets, rof, fofr = O.permutation(ids, E)
     R = T * k
