@@ -8,9 +8,9 @@ experts, top-10, intermediate 512, shared expert 512, T = 128 tokens per step,
 uniform-random routing, NVFP4 weights ~ N(0, 0.02).  Each step runs one layer
 forward; successive steps rotate over several independent layer weight sets
 and inputs so that no step finds its weights in L2.  The line also carries the
-sweep over T in {1, 8, 32, 64}, the 16384-token Zipf-skewed prefill layer and
-the 48-layer decode stack (x <- x + MoE(RMSNorm(x)), eager and as one CUDA
-graph) under "also".  "e2e" is the same step fed from pinned host memory with
+sweep over T in {1, 8, 16, 32, 64}, the 16384-token Zipf-skewed prefill layer,
+the MTP draft layer's BF16-expert MoE and the 48-layer decode stack
+(x <- x + MoE(RMSNorm(x)), eager and as one CUDA graph) under "also".  "e2e" is the same step fed from pinned host memory with
 the result copied back, copies on their own streams.
 
 N > 1 (launched by torchrun, one rank per GPU): the expert-parallel prefill
@@ -296,6 +296,39 @@ def run_prefill_point(torch, q4t, T, steps, warmup, seed=7, repeats=5):
     return out
 
 
+def run_mtp_bf16_point(torch, q4t, Ts=(1, 4, 8), steps=20, warmup=3):
+    """The MTP draft layer's MoE (BF16 routed experts, src/mtp/moe_bf16.cu of the reference) at the
+    reference's shapes: hidden 2560, 512 experts of intermediate 640, top-10.  A decode-sized step
+    streams the selected experts' BF16 weights once, so the bound is HBM."""
+    syn = importlib.import_module("qwen4-thor_b200.synthetic")
+    E_, hs, is_, sis = 512, 2560, 640, 640
+    g = torch.Generator(device="cuda").manual_seed(20260921 + 77)
+    gu = torch.empty((E_, 2 * is_, hs), dtype=torch.bfloat16, device="cuda")
+    down = torch.empty((E_, hs, is_), dtype=torch.bfloat16, device="cuda")
+    for e0 in range(0, E_, 64):     # in slices: the fp32 staging of all 512 experts would take 10 GB
+        gu[e0:e0 + 64] = (torch.randn((64, 2 * is_, hs), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+        down[e0:e0 + 64] = (torch.randn((64, hs, is_), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    extra = syn.device_layer(q4t, E_, hs, 128, sis, seed=20260921 + 78)   # router and shared expert of the layer
+    peaks = load_peaks()
+    out = []
+    for T in Ts:
+        moe = q4t.Bf16MoE(gu, down, extra, T, K_TOP)
+        xs = [syn.make_x(T, hs, seed=300 + i) for i in range(8)]
+        y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+        ms = time_steps(torch, lambda i: moe.forward(xs[i % 8], y), steps, warmup)
+        ws = moe.ws
+        fl = q4t.forward_ws_layout(T, K_TOP, hs, is_, sis, E_)
+        ids = ws[fl.expert_ids:fl.expert_ids + T * K_TOP * 4].view(torch.int32)
+        U = int(torch.unique(ids).numel())
+        nbytes = U * 3 * is_ * hs * 2 + (E_ + 3 * sis + 1) * hs * 2
+        out.append(dict(T=T, ms_per_step=ms, tokens_per_s=T / (ms * 1e-3), unique_experts=U, bytes=nbytes,
+                        gbs=nbytes / (ms * 1e-3) / 1e9, hbm_frac_of_measured=nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]))
+    del gu, down
+    torch.cuda.empty_cache()
+    return dict(workload="MTP draft layer MoE, BF16 routed experts, hidden 2560, 512 experts x intermediate 640, top-10",
+                l2="each step selects its own experts; 7 to 300 MB of weights per step, inputs rotated", points=out)
+
+
 def run_dense_fp4_point(torch, q4t, M, N, Kd, secs=0.3):
     """A dense NVFP4 GEMM of M x N x K through q4t_fp4_gemm (bf16 output, random codes): what the
     block-scaled tensor-core mainloop of this library sustains when every row tile is full."""
@@ -446,7 +479,7 @@ def main_single(args):
     also = {}
     if not args.quick:
         sweep = []
-        for t in (1, 8, 32, 64):
+        for t in (1, 8, 16, 32, 64):
             r = run_decode_point(torch, q4t, layers, t, max(args.steps, 20), args.warmup, with_stages=True)
             r["hbm_frac_of_measured"] = r["layer_gbs"] / peaks["hbm_gbs"]
             sweep.append(r)
@@ -496,6 +529,8 @@ def main_single(args):
                    single_thread=dict(value=tps1, unit="tokens/s", cores=1,
                                       sample=f"1 layer forward of {T1} tokens, one thread"))
 
+    if not args.quick:
+        also["mtp_bf16_moe"] = run_mtp_bf16_point(torch, q4t)
     if not args.quick and args.stack_layers > 0:   # last: the graph capture attempt must not disturb the rest
         also["stack"] = run_stack_point(torch, q4t, syn, layers, args.stack_layers, T, 5, main["layer_bytes"])
 
@@ -511,7 +546,9 @@ def main_single(args):
                                 own_dense_nvfp4_gemm_tflops=dense.get("tflops"),
                                 frac_of_own_dense_nvfp4_gemm=(pf["routed_tflops"] / dense["tflops"]) if dense.get("tflops") else None,
                                 ms_per_step=pf["ms_per_step"], stage_ms=pf["stage_ms"])
-    launches_per_step = 3 + 3 + 1 + 1 + 1 + 1 + 1 + 1   # logits, topk, plan x3, quant, gu, dn, shared x2, combine
+    # router logits, top-k + permutation (one cluster launch), gather-quantise, gate/up, down, combine;
+    # shared expert: gate|up with SwiGLU, down
+    launches_per_step = 1 + 1 + 1 + 1 + 1 + 1 + 2
     line = dict(metric="moe_layer_tokens_per_s", value=main["tokens_per_s"], unit="tokens/s", n_gpus=1,
                 steps=args.steps, warmup=args.warmup, ms_per_step=main["ms_per_step"], higher_is_better=True,
                 scaling="weak", vs_baseline=None,

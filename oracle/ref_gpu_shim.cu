@@ -7,6 +7,9 @@
 // for bit, which pins the tensor-core GEMM parity that the CPU oracle can only assert against
 // the reference's documents.  Nothing of the product links or loads it.
 //
+// The BF16 routed experts of the MTP draft layer come from src/mtp/moe_bf16.cu with the GEMV
+// helpers its Bf16Gemm dispatches to (src/model/gemv.cu, gemv_hc_inject.cu, small_m_gemm.cu).
+//
 // src/quant/moe_decode.cu does not compile with CUDA 12.9 (it needs cuBLASLt's grouped-layout
 // API); its two entry points are only reached for M <= 8 at hidden 2560 / intermediate 640 and
 // are stubbed here to fail loudly.
@@ -16,6 +19,7 @@
 #include <cstring>
 #include <string>
 
+#include "q4t/mtp/moe_bf16.h"
 #include "q4t/quant/act_quant.h"
 #include "q4t/quant/fp4_gemm.h"
 #include "q4t/quant/moe_decode.h"
@@ -32,6 +36,14 @@ Status MoEDeviceDecodeMulti(const uint16_t*, const int32_t*, const float*, float
   return Status::Fail("MoEDeviceDecodeMulti is not part of this build of the reference");
 }
 }  // namespace q4t::quant
+
+// LoadMoeBf16 (same file as the BF16 forward) reads a checkpoint through the reference's
+// loader, which is not part of this build; the tests hand over device tensors directly.
+namespace q4t::io {
+Status WeightLoader::LoadTensorToDevice(const std::string&, void*, size_t, cudaStream_t) const {
+  return Status::Fail("the checkpoint loader is not part of this build of the reference");
+}
+}  // namespace q4t::io
 
 namespace {
 thread_local std::string g_msg;
@@ -97,6 +109,33 @@ int ref_gpu_fp4_gemm(const uint8_t* w_packed, const uint8_t* w_sf, const uint8_t
                                                inv_a, gemm_ws, gemm_ws_bytes, static_cast<cudaStream_t>(stream));
   if (has_algo) *has_algo = r.has_algo ? 1 : 0;
   return static_cast<int>(r.status);
+}
+
+// The reference's BF16 routed experts of the MTP draft layer (src/mtp/moe_bf16.cu:271-426:
+// per-expert gather, cuBLASLt / GEMV BF16 projections, SwiGLU, router-weighted atomicAdd into
+// y).  gu [E, 2*moe_is, hs] and down [E, hs, moe_is] are device bf16; y fp32 [M, hs] zeroed by
+// the caller.  The call synchronises the stream once (the reference reads the counts back).
+size_t ref_gpu_moe_bf16_workspace_bytes(int M, int k, int hs, int moe_is, int E) {
+  return q4t::mtp::MoeBf16WorkspaceBytes(M, k, hs, moe_is, E);
+}
+int ref_gpu_moe_bf16_routed_forward(const uint16_t* x, const int32_t* ids, const float* rw, float* y, int E, int hs,
+                                    int moe_is, uint16_t* gu, uint16_t* down, void* workspace, void* gemm_ws,
+                                    size_t gemm_ws_bytes, int M, int k, void* stream) {
+  q4t::mtp::MoeBf16Weights W;
+  W.E = E;
+  W.hs = hs;
+  W.moe_is = moe_is;
+  W.gu = gu;
+  W.down = down;
+  q4t::Status s = q4t::mtp::MoeBf16RoutedForward(x, ids, rw, y, W, workspace, gemm_ws, gemm_ws_bytes, M, k,
+                                                 static_cast<cudaStream_t>(stream));
+  W.gu = nullptr;   // borrowed: nothing for the destructor-less struct to release
+  W.down = nullptr;
+  if (!s.ok()) {
+    g_msg = s.message();
+    return 1;
+  }
+  return 0;
 }
 
 int ref_gpu_quantize_activation(const uint16_t* bf16, uint8_t* packed, uint8_t* sf, int M, int K, float global_scale,

@@ -8,6 +8,11 @@ the tolerance-level GEMM parity into a bit-level statement: bf16 outputs of the 
 GEMMs, the grouped down-projection rows of the routed experts and the fp32 routed sum are
 compared bit for bit.
 
+The same library holds the reference's BF16 routed experts of the MTP draft layer
+(src/mtp/moe_bf16.cu:271-426, cuBLASLt / GEMV projections): its output pins both the CPU
+oracle's restatement of that path and the tensor-core kernels, at the tolerance three bf16
+roundings over differently ordered fp32 sums allow.
+
 Skipped where the library was not built (no reference tree at build time) or where cuBLASLt
 offers no NVFP4 algorithm."""
 import ctypes as C
@@ -41,6 +46,11 @@ def ref_gpu(gpu_lib):
     R.ref_gpu_fp4_gemm.argtypes = [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, vp,
                                    C.c_size_t, C.POINTER(C.c_int), vp]
     R.ref_gpu_quantize_activation.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_float, vp]
+    if hasattr(R, "ref_gpu_moe_bf16_routed_forward"):
+        R.ref_gpu_moe_bf16_workspace_bytes.restype = C.c_size_t
+        R.ref_gpu_moe_bf16_workspace_bytes.argtypes = [C.c_int] * 5
+        R.ref_gpu_moe_bf16_routed_forward.argtypes = [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp,
+                                                      C.c_size_t, C.c_int, C.c_int, vp]
     return R
 
 
@@ -172,3 +182,76 @@ def test_routed_forward_equals_reference_gpu(q4t, ref_gpu, gemm_ws, E, hs, is_, 
         y_bad = int((host(y2) != host(y_ref)).sum())
         print(f"    decode-sized path: dn_out bf16 values differing {dn_bad}, routed fp32 values differing {y_bad}")
         assert dn_bad == 0 and y_bad == 0
+
+
+# The reference's own fixture for this path (tests/mtp_moe_path_test.cpp:29-38, 153-170): activations
+# ((c*37 + row*113 + 17) mod 509 - 254) / 128, first-row experts and binary-fraction router weights.
+_MTP_FIRST_IDS = [37, 3, 91, 7, 211, 19, 401, 23, 127, 53]
+_MTP_ROUTER_W = [0.25, 0.125, 0.125, 0.125, 0.0625, 0.0625, 0.0625, 0.0625, 0.0625, 0.0625]
+
+
+def _mtp_fixture(rows, hs, k, E):
+    c = np.arange(hs, dtype=np.int64)[None, :]
+    r = np.arange(rows, dtype=np.int64)[:, None]
+    x = O.f32_to_bf16((((c * 37 + r * 113 + 17) % 509 - 254).astype(np.float32) / np.float32(128.0)))
+    ids = np.empty((rows, k), np.int32)
+    ids[0] = _MTP_FIRST_IDS[:k]
+    for row in range(1, rows):
+        ids[row] = (260 + row * k + np.arange(k)) % E
+    rw = np.tile(np.array(_MTP_ROUTER_W[:k], np.float32), (rows, 1))
+    return x, ids, rw
+
+
+@pytest.mark.parametrize("E,hs,is_,T,k,fixture", [(512, 2560, 640, 4, 10, True), (512, 2560, 640, 1, 10, True),
+                                                  (64, 1024, 256, 40, 6, False)])
+def test_mtp_bf16_experts_vs_reference_gpu(q4t, ref_gpu, gemm_ws, E, hs, is_, T, k, fixture):
+    """MoeBf16RoutedForward of the reference, q4t_moe_bf16_routed_forward and the CPU oracle's
+    restatement on the same weights and routing."""
+    if not hasattr(ref_gpu, "ref_gpu_moe_bf16_routed_forward"):
+        pytest.skip("oracle/_ref/libq4t_ref_gpu.so was built without the BF16 experts")
+    g = torch.Generator(device="cuda").manual_seed(E + T)
+    gu = (torch.randn((E, 2 * is_, hs), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    down = (torch.randn((E, hs, is_), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    if fixture:
+        x_h, ids_h, rw_h = _mtp_fixture(T, hs, k, E)
+    else:
+        import synth
+        x_h = synth.make_x(T, hs, seed=3)
+        ids_h, rw_h = synth.random_routing(T, k, E, seed=5)
+    x, ids, rw = dev(x_h), dev(ids_h), dev(rw_h)
+    # the reference
+    ws = torch.zeros(ref_gpu.ref_gpu_moe_bf16_workspace_bytes(T, k, hs, is_, E) + 256, dtype=torch.uint8, device="cuda")
+    y_ref = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
+    rc = ref_gpu.ref_gpu_moe_bf16_routed_forward(x.data_ptr(), ids.data_ptr(), rw.data_ptr(), y_ref.data_ptr(), E, hs, is_,
+                                                 gu.data_ptr(), down.data_ptr(), ws.data_ptr(), gemm_ws.data_ptr(),
+                                                 gemm_ws.numel(), T, k, None)
+    torch.cuda.synchronize()
+    if rc != 0:
+        msg = ref_gpu.ref_gpu_last_error().decode()
+        if "GEMM failed" in msg:
+            pytest.skip(f"the reference's cuBLASLt BF16 path is unavailable here: {msg}")
+        raise AssertionError(f"reference MoeBf16RoutedForward failed: {msg}")
+    want = host(y_ref)
+    # this library
+    moe = q4t.Bf16MoE(gu, down, None, T, k)
+    y = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
+    moe.routed(x, ids, rw, y)
+    torch.cuda.synchronize()
+    got = host(y)
+    # the CPU oracle on the experts that are used (ids renumbered into the compacted set)
+    used, inv = np.unique(ids_h, return_inverse=True)
+    sel = torch.from_numpy(used.astype(np.int64)).cuda()
+    gu_h = host(gu[sel].view(torch.int16)).view(np.uint16)
+    down_h = host(down[sel].view(torch.int16)).view(np.uint16)
+    orc = O.moe_bf16_routed_forward(x_h, inv.reshape(ids_h.shape).astype(np.int32), rw_h, gu_h, down_h)
+    scale = np.abs(want).max()
+
+    def dist(a):
+        return float(np.sqrt(((a - want) ** 2).sum() / (want ** 2).sum())), float(np.abs(a - want).max() / scale)
+
+    (l2_k, mx_k), (l2_o, mx_o) = dist(got), dist(orc)
+    print(f"[MTP bf16 experts vs reference GPU E={E} hs={hs} is={is_} T={T} k={k}] kernels: relative_l2 {l2_k:.3e} "
+          f"max|diff|/max {mx_k:.3e}; CPU oracle: relative_l2 {l2_o:.3e} max|diff|/max {mx_o:.3e}")
+    # one bf16 step of the largest output and 0.4 % L2, the bounds of the oracle comparison
+    assert l2_k <= 4e-3 and mx_k <= 2.0 ** -7
+    assert l2_o <= 4e-3 and mx_o <= 2.0 ** -7
