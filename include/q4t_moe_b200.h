@@ -294,13 +294,27 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
  *                    table to the device and no host synchronisation happens.
  *                    The workspace keeps the original ids in `expert_ids` and
  *                    the slots in `slot_ids`.  NULL: routed->E == extra->E.
+ * hc_*            : the layer's gated residual write fused into the final
+ *                    combine (GatedResidualFrame::Write after MoEForward,
+ *                    src/model/decoder_layer.cu:708, CombineWithGateKernel,
+ *                    src/model/hyperconnection.cu:286-305): with hc_count = hc
+ *                    branches (0 = off), hc_out[t, b, c] = bf16(hc_residual[t, b, c]
+ *                    + y[t, c] * hc_inject_gate[t, b]) for b < hc, computed from
+ *                    the bf16-rounded y with one fused multiply-add as the
+ *                    reference's kernel compiles to.  hc_residual / hc_out are
+ *                    bf16 [T, hc*hs] (16-byte aligned, may not overlap y),
+ *                    hc_inject_gate is bf16 [T, hc] as ApplyInjectGateKernel
+ *                    leaves it (2*sigmoid(inject/hc)).  y is still written.
  * fixed_ids and flags as in q4t_moe_forward.                                   */
 typedef struct q4t_forward_options {
   const int32_t* fixed_ids;
   int32_t* trace_ids_out;
   const int32_t* slot_of_expert;
   uint32_t flags;
-  uint32_t reserved;
+  int32_t hc_count;
+  const uint16_t* hc_residual;
+  const uint16_t* hc_inject_gate;
+  uint16_t* hc_out;
 } q4t_forward_options;
 int32_t q4t_moe_forward_ex(const uint16_t* x, const q4t_routed_weights* routed,
                            const q4t_extra_weights* extra, uint16_t* y, int32_t T,

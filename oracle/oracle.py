@@ -333,6 +333,20 @@ def residual_rmsnorm_bf16(x, y, eps: float = 1e-6):
     return x, h
 
 
+def gated_residual_write(y, residual, gate):
+    """out[t, b, :] = bf16(residual[t, b, :] + y[t, :] * gate[t, b]) on bf16 bit patterns
+    (q4o_gated_residual_write); y [T, hs], residual [T, hc*hs], gate [T, hc]."""
+    y = np.ascontiguousarray(y, np.uint16)
+    residual = np.ascontiguousarray(residual, np.uint16)
+    gate = np.ascontiguousarray(gate, np.uint16)
+    T, hs = y.shape
+    hc = gate.shape[1]
+    out = np.empty_like(residual)
+    lib().q4o_gated_residual_write(_p(y, C.c_uint16), _p(residual, C.c_uint16), _p(gate, C.c_uint16), C.c_int(T),
+                                   C.c_int(hc), C.c_int(hs), _p(out, C.c_uint16))
+    return out
+
+
 def moe_bf16_routed_forward(x, ids, rw, gu, down, y0=None):
     """The MTP draft layer's BF16 routed experts (q4o_moe_bf16_routed_forward): gu [E, 2*is, hs],
     down [E, hs, is] bf16 bit patterns; returns fp32 [T, hs] (added to y0 when given)."""

@@ -769,6 +769,22 @@ void q4o_residual_rmsnorm_bf16(uint16_t* x, const uint16_t* y, int T, int hs, fl
   q4o_rmsnorm_bf16(x, T, hs, eps, h);
 }
 
+/* The layer's gated residual write (CombineWithGateKernel, src/model/hyperconnection.cu:286-305;
+ * GatedResidualFrame::Write after MoEForward, src/model/decoder_layer.cu:708): out[t, b, c] =
+ * bf16(R[t, b, c] + y[t, c] * gate[t, b]), all operands bf16.  The device compiler contracts the
+ * multiply-add, so it is one fused multiply-add here. */
+void q4o_gated_residual_write(const uint16_t* y, const uint16_t* residual, const uint16_t* gate, int T, int hc, int hs,
+                              uint16_t* out) {
+  for (int t = 0; t < T; ++t)
+    for (int b = 0; b < hc; ++b) {
+      const float inj = q4o_bf16_to_float(gate[(size_t)t * hc + b]);
+      const size_t at = ((size_t)t * hc + b) * hs;
+      for (int c = 0; c < hs; ++c)
+        out[at + c] = q4o_float_to_bf16(fmaf(q4o_bf16_to_float(y[(size_t)t * hs + c]), inj,
+                                             q4o_bf16_to_float(residual[at + c])));
+    }
+}
+
 /* The MTP draft layer's BF16 routed experts (src/mtp/moe_bf16.cu:93-131, 340-420): per
  * (token, slot) h = bf16(x . W_gu[e]^T) with fp32 accumulation (sequential here; the
  * reference's library GEMM leaves the order open), inter = bf16((g * (1/(1+expf(-g)))) * u),

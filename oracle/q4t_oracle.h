@@ -165,6 +165,9 @@ int q4o_moe_forward(const uint16_t* x, const q4o_layer* L, int T, int k,
 void q4o_rmsnorm_bf16(const uint16_t* x, int T, int hs, float eps,
                       uint16_t* out);
 void q4o_residual_rmsnorm_bf16(uint16_t* x, const uint16_t* y, int T, int hs, float eps, uint16_t* h);
+/* out[t,b,:] = bf16(residual[t,b,:] + y[t,:] * gate[t,b]) (src/model/hyperconnection.cu:286-305). */
+void q4o_gated_residual_write(const uint16_t* y, const uint16_t* residual, const uint16_t* gate, int T, int hc, int hs,
+                              uint16_t* out);
 void q4o_moe_bf16_routed_forward(const uint16_t* x, const int32_t* ids, const float* rw, const uint16_t* gu,
                                  const uint16_t* down, int T, int k, int E, int hs, int is, float* y);
 

@@ -64,7 +64,8 @@ class ForwardWsLayout(C.Structure):
 class ForwardOptions(C.Structure):
     """q4t_forward_options: the replay table, the router-trace observer and the slot-mode table."""
     _fields_ = [("fixed_ids", C.c_void_p), ("trace_ids_out", C.c_void_p), ("slot_of_expert", C.c_void_p),
-                ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+                ("flags", C.c_uint32), ("hc_count", C.c_int32), ("hc_residual", C.c_void_p),
+                ("hc_inject_gate", C.c_void_p), ("hc_out", C.c_void_p)]
 
 
 EXPORTS = [
@@ -379,16 +380,24 @@ class MoEForward:
         self.routed_layout = routed_ws_layout(T, k, layer.hs, layer.moe_is, layer.E_router)
         self.ws = torch.empty(self.layout.total, dtype=torch.uint8, device=device)
 
-    def __call__(self, x, y, fixed_ids=None, flags=0, stream=None, trace_ids_out=None, slot_of_expert=None):
+    def __call__(self, x, y, fixed_ids=None, flags=0, stream=None, trace_ids_out=None, slot_of_expert=None,
+                 hc_write=None):
         """trace_ids_out: CUDA int32 [T,k] that receives the selected expert ids (the router-trace
         observer); slot_of_expert: CUDA int32 [E] expert -> resident slot table (slot mode: the
-        layer's routed weights then hold layer.E slots, the router chooses among layer.E_router)."""
-        if trace_ids_out is None and slot_of_expert is None:
+        layer's routed weights then hold layer.E slots, the router chooses among layer.E_router);
+        hc_write: (residual bf16 [T, hc*hs], inject_gate bf16 [T, hc], out bf16 [T, hc*hs]), the
+        layer's gated residual write fused into the final combine."""
+        if trace_ids_out is None and slot_of_expert is None and hc_write is None:
             check(load().q4t_moe_forward(_ptr(x), C.byref(self.layer.routed), C.byref(self.layer.extra), _ptr(y),
                                          self.T, self.k, _ptr(self.ws), self.layout.total, _ptr(fixed_ids),
                                          flags, _stream_ptr(stream)))
             return y
-        opt = ForwardOptions(_ptr(fixed_ids), _ptr(trace_ids_out), _ptr(slot_of_expert), flags, 0)
+        hc, res, gate, out = 0, None, None, None
+        if hc_write is not None:
+            res, gate, out = hc_write
+            hc = gate.shape[1]
+        opt = ForwardOptions(_ptr(fixed_ids), _ptr(trace_ids_out), _ptr(slot_of_expert), flags, hc, _ptr(res),
+                             _ptr(gate), _ptr(out))
         check(load().q4t_moe_forward_ex(_ptr(x), C.byref(self.layer.routed), C.byref(self.layer.extra), _ptr(y),
                                         self.T, self.k, _ptr(self.ws), self.layout.total, C.byref(opt),
                                         _stream_ptr(stream)))

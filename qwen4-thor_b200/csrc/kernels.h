@@ -160,10 +160,18 @@ cudaError_t launch_swiglu(const uint16_t* gu, uint16_t* out, int T, int inner, c
 // x <- bf16(x + y) (y may be null), h <- RMSNorm(x) without a weight; hs % 8 == 0.
 cudaError_t launch_residual_rmsnorm(uint16_t* x, const uint16_t* y, uint16_t* h, int T, int hs, float eps,
                                     cudaStream_t stream);
+// Optional gated residual write fused into the final combine: out[t, b, :] =
+// bf16(residual[t, b, :] + y[t, :] * inject_gate[t, b]) for b < hc (hc = 0: nothing).
+struct HcWrite {
+  const uint16_t* residual;     // [T, hc, hs] bf16
+  const uint16_t* inject_gate;  // [T, hc] bf16
+  uint16_t* out;                // [T, hc, hs] bf16
+  int hc;
+};
 cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,
                                  const uint16_t* shared_down, const uint16_t* x,
                                  const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
-                                 int k, int hs, cudaStream_t stream);
+                                 int k, int hs, cudaStream_t stream, const HcWrite& hcw = HcWrite{});
 
 // ---- routed experts for decode-sized batches (decode_small.cu)
 constexpr int kSmallN = 16;            // token rows per pass of one CTA (the N side of the MMA)

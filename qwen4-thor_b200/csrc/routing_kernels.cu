@@ -757,7 +757,7 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
     const uint16_t* __restrict__ dn_out, const int32_t* __restrict__ row_of_flat,
     const float* __restrict__ rw, const uint16_t* __restrict__ shared_down,
     const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate_scalar,
-    float* __restrict__ routed, uint16_t* __restrict__ y, int T, int k, int hs) {
+    float* __restrict__ routed, uint16_t* __restrict__ y, int T, int k, int hs, const HcWrite hcw) {
   chain_wait();
   __shared__ float part[256];
   __shared__ int s_row[16];
@@ -828,6 +828,20 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
       o[j] = f32x2_to_bf16x2(fmaf(gate, bf16x2_lo(sw[j]), a[2 * j]),
                              fmaf(gate, bf16x2_hi(sw[j]), a[2 * j + 1]));
     *(reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * hs) + c8) = make_uint4(o[0], o[1], o[2], o[3]);
+    // The gated residual write of the layer (GatedResidualFrame::Write, CombineWithGateKernel,
+    // src/model/hyperconnection.cu:286-305): out[t, b, c] = bf16(R[t, b, c] + y[t, c] * gate[t, b])
+    // with the bf16-rounded y and one fused multiply-add, for every hyper-connection branch b.
+    for (int b = 0; b < hcw.hc; ++b) {
+      const float inj = bf16_to_f32(hcw.inject_gate[static_cast<size_t>(t) * hcw.hc + b]);
+      const size_t at = (static_cast<size_t>(t) * hcw.hc + b) * hs;
+      const uint4 rv = __ldg(reinterpret_cast<const uint4*>(hcw.residual + at) + c8);
+      const uint32_t r[4] = {rv.x, rv.y, rv.z, rv.w};
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        w[j] = f32x2_to_bf16x2(fmaf(bf16x2_lo(o[j]), inj, bf16x2_lo(r[j])), fmaf(bf16x2_hi(o[j]), inj, bf16x2_hi(r[j])));
+      *(reinterpret_cast<uint4*>(hcw.out + at) + c8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
   }
 }
 
@@ -972,12 +986,12 @@ cudaError_t launch_residual_rmsnorm(uint16_t* x, const uint16_t* y, uint16_t* h,
 cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,
                                  const uint16_t* shared_down, const uint16_t* x,
                                  const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
-                                 int k, int hs, cudaStream_t stream) {
+                                 int k, int hs, cudaStream_t stream, const HcWrite& hcw) {
   if (T <= 1024)
     return launch_chained(final_combine_kernel<true>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
-                          shared_down, x, gate_scalar, routed, y, T, k, hs);
+                          shared_down, x, gate_scalar, routed, y, T, k, hs, hcw);
   return launch_chained(final_combine_kernel<false>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
-                        shared_down, x, gate_scalar, routed, y, T, k, hs);
+                        shared_down, x, gate_scalar, routed, y, T, k, hs, hcw);
 }
 
 }  // namespace q4t

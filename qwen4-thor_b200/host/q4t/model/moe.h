@@ -88,20 +88,38 @@ inline size_t MoEForwardWorkspaceBytes(int T, int k, int hs, int moe_is, int sha
 // residency->Layout() (E = slot count); the selected experts are mapped to slots on the
 // device through residency->DeviceSlotOfExpert() with no host round trip, and experts
 // that are not resident contribute nothing (the engine's tier decides what is resident).
-inline Status MoEForward(const uint16_t* x, const quant::MoEWeightLayout& routed, const MoEExtraWeights& extra,
-                         uint16_t* y, int T, int k, void* workspace, size_t workspace_bytes, void* /*gemm_ws*/,
-                         size_t /*gemm_ws_bytes*/, cudaStream_t stream, trace::RouterCollector* trace = nullptr,
-                         int layer_id = -1, const quant::MoEResidency* residency = nullptr,
-                         MoEForwardDiagnostics* diagnostics = nullptr) {
+// The gated residual write that follows the layer (GatedResidualFrame::Write,
+// src/model/decoder_layer.cu:708 of the reference), when it is to be fused into the layer's
+// last kernel: out[t, b, :] = bf16(residual[t, b, :] + y[t, :] * inject_gate[t, b]).
+struct GatedResidualWrite {
+  const uint16_t* residual = nullptr;     // [T, hc, hs] bf16, the frame's residual
+  const uint16_t* inject_gate = nullptr;  // [T, hc] bf16, the frame's prepared gate
+  uint16_t* out = nullptr;                // [T, hc, hs] bf16
+  int hc = 0;
+};
+
+namespace detail {
+inline Status RunMoEForward(const uint16_t* x, const quant::MoEWeightLayout& routed, const MoEExtraWeights& extra,
+                            uint16_t* y, int T, int k, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                            trace::RouterCollector* trace, int layer_id, const quant::MoEResidency* residency,
+                            MoEForwardDiagnostics* diagnostics, const GatedResidualWrite* write) {
   if (diagnostics) *diagnostics = {};
   const q4t_routed_weights rw = routed.Abi();
   const q4t_extra_weights ew = extra.Abi();
+  q4t_forward_options opt{};
   if (residency != nullptr) {
     if (residency->Slots() < k) return Status::Fail("residency slots below top-k");  // moe.cu:507
     if (residency->Slots() != routed.E || !routed.slot_mode)
       return Status::Fail("slot mode: routed weights must be the residency layout");
-    q4t_forward_options opt{};
     opt.slot_of_expert = residency->DeviceSlotOfExpert();
+  }
+  if (write != nullptr && write->hc > 0) {
+    opt.hc_count = write->hc;
+    opt.hc_residual = write->residual;
+    opt.hc_inject_gate = write->inject_gate;
+    opt.hc_out = write->out;
+  }
+  if (residency != nullptr || opt.hc_count > 0) {
     if (q4t_moe_forward_ex(x, &rw, &ew, y, T, k, workspace, workspace_bytes, &opt, stream) != Q4T_OK)
       return Status::Fail(q4t_last_error());
   } else if (q4t_moe_forward(x, &rw, &ew, y, T, k, workspace, workspace_bytes, nullptr, 0, stream) != Q4T_OK) {
@@ -116,6 +134,30 @@ inline Status MoEForward(const uint16_t* x, const quant::MoEWeightLayout& routed
     if (!s.ok()) return s;
   }
   return Status();
+}
+}  // namespace detail
+
+inline Status MoEForward(const uint16_t* x, const quant::MoEWeightLayout& routed, const MoEExtraWeights& extra,
+                         uint16_t* y, int T, int k, void* workspace, size_t workspace_bytes, void* /*gemm_ws*/,
+                         size_t /*gemm_ws_bytes*/, cudaStream_t stream, trace::RouterCollector* trace = nullptr,
+                         int layer_id = -1, const quant::MoEResidency* residency = nullptr,
+                         MoEForwardDiagnostics* diagnostics = nullptr) {
+  return detail::RunMoEForward(x, routed, extra, y, T, k, workspace, workspace_bytes, stream, trace, layer_id, residency,
+                               diagnostics, nullptr);
+}
+
+// MoEForward followed by the frame's Write in one call (no counterpart in the reference, which
+// runs CombineWithGateKernel as a launch of its own): the call site in DecoderLayerForward
+// passes the frame's residual, gate and branch count and drops its mlp_frame.Write launch.
+inline Status MoEForwardAndWrite(const uint16_t* x, const quant::MoEWeightLayout& routed, const MoEExtraWeights& extra,
+                                 uint16_t* y, int T, int k, void* workspace, size_t workspace_bytes,
+                                 const GatedResidualWrite& write, cudaStream_t stream,
+                                 trace::RouterCollector* trace = nullptr, int layer_id = -1,
+                                 const quant::MoEResidency* residency = nullptr) {
+  if (write.hc <= 0 || !write.residual || !write.inject_gate || !write.out)
+    return Status::Fail("gated residual write needs a residual, a gate and an output");
+  return detail::RunMoEForward(x, routed, extra, y, T, k, workspace, workspace_bytes, stream, trace, layer_id, residency,
+                               nullptr, &write);
 }
 
 }  // namespace q4t::model

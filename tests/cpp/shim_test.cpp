@@ -265,6 +265,45 @@ int main() {
     CHECK(model::MoEForward(d_x, L, X, d_y, T, k, ws, ws_bytes, nullptr, 0, 0, nullptr, -1, &res).message() ==
           "slot mode: routed weights must be the residency layout");
   }
+  // ---- MoEForward with the frame's gated residual write fused in: y as before, and
+  // out[t, b, c] = bf16(fma(y[t, c], gate[t, b], R[t, b, c])) checked on the host
+  {
+    const int hc = 4;
+    std::vector<uint16_t> y_plain(size_t(T) * hs), y_fused(y_plain.size());
+    CHECK(model::MoEForward(d_x, L, X, d_y, T, k, ws, ws_bytes, nullptr, 0, 0).ok());
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    cudaMemcpy(y_plain.data(), d_y, y_plain.size() * 2, cudaMemcpyDeviceToHost);
+    std::vector<uint16_t> res_h(size_t(T) * hc * hs), gate_h(size_t(T) * hc), out_h(res_h.size());
+    for (size_t i = 0; i < res_h.size(); ++i) res_h[i] = static_cast<uint16_t>(0x3c00u + (i * 37u) % 0x300u);   // 0.0078 .. 0.5
+    for (size_t i = 0; i < gate_h.size(); ++i) gate_h[i] = static_cast<uint16_t>(0x3f00u + (i * 11u) % 0x100u); // 0.5 .. 2
+    uint16_t *d_res, *d_gate, *d_out;
+    cudaMalloc(reinterpret_cast<void**>(&d_res), res_h.size() * 2);
+    cudaMalloc(reinterpret_cast<void**>(&d_gate), gate_h.size() * 2);
+    cudaMalloc(reinterpret_cast<void**>(&d_out), res_h.size() * 2);
+    cudaMemcpy(d_res, res_h.data(), res_h.size() * 2, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_gate, gate_h.data(), gate_h.size() * 2, cudaMemcpyHostToDevice);
+    model::GatedResidualWrite wr;
+    wr.residual = d_res; wr.inject_gate = d_gate; wr.out = d_out; wr.hc = hc;
+    s = model::MoEForwardAndWrite(d_x, L, X, d_y, T, k, ws, ws_bytes, wr, 0);
+    if (!s.ok()) std::printf("MoEForwardAndWrite: %s\n", s.message().c_str());
+    CHECK(s.ok());
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    cudaMemcpy(y_fused.data(), d_y, y_fused.size() * 2, cudaMemcpyDeviceToHost);
+    cudaMemcpy(out_h.data(), d_out, out_h.size() * 2, cudaMemcpyDeviceToHost);
+    CHECK(std::memcmp(y_plain.data(), y_fused.data(), y_plain.size() * 2) == 0);
+    auto to_f = [](uint16_t b) { uint32_t u = uint32_t(b) << 16; float f; std::memcpy(&f, &u, 4); return f; };
+    auto to_b = [](float f) { uint32_t u; std::memcpy(&u, &f, 4); u += 0x7fffu + ((u >> 16) & 1u); return uint16_t(u >> 16); };
+    size_t bad = 0;
+    for (int t = 0; t < T; ++t)
+      for (int b = 0; b < hc; ++b)
+        for (int c = 0; c < hs; ++c) {
+          const size_t at = (size_t(t) * hc + b) * hs + c;
+          bad += out_h[at] != to_b(std::fma(to_f(y_fused[size_t(t) * hs + c]), to_f(gate_h[size_t(t) * hc + b]), to_f(res_h[at])));
+        }
+    CHECK(bad == 0);
+    wr.hc = 0;
+    CHECK(!model::MoEForwardAndWrite(d_x, L, X, d_y, T, k, ws, ws_bytes, wr, 0).ok());
+  }
   // the MTP draft layer's BF16 experts through the reference-shaped calls
   mtp::MoeBf16Weights B;
   B.E = E; B.hs = hs; B.moe_is = is;

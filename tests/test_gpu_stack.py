@@ -62,3 +62,27 @@ def test_stack_equals_composition_and_oracle(q4t, gpu_lib):
     xo, _ = O.residual_rmsnorm_bf16(xo, yo)
     got, ref = O.bf16_to_f32(host(xs).view(np.uint16)), O.bf16_to_f32(xo)
     assert np.max(np.abs(got - ref)) <= 2e-3 * np.max(np.abs(ref)) + 2.0 ** -8 * np.max(np.abs(ref))
+
+
+@pytest.mark.parametrize("T", [1, 9, 130])
+def test_gated_residual_write_fused_into_combine(q4t, gpu_lib, T):
+    """The layer's gated residual write (GatedResidualFrame::Write after MoEForward,
+    src/model/decoder_layer.cu:708 of the reference) fused into the final combine: y is
+    unchanged and out equals the oracle's bf16(R + y * gate) bit for bit."""
+    E, hs, is_, sis, k, hc = 64, 1024, 256, 256, 6, 4
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=5)
+    dl = q4t.DeviceLayer.from_host(L)
+    x = dev(synth.make_x(T, hs, seed=T))
+    rng = np.random.default_rng(T)
+    res = O.f32_to_bf16(rng.standard_normal((T, hc * hs)).astype(np.float32))
+    gate = O.f32_to_bf16((2.0 / (1.0 + np.exp(-rng.standard_normal((T, hc))))).astype(np.float32))
+    fwd = q4t.MoEForward(dl, T, k)
+    y0 = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    fwd(x, y0)
+    y1 = torch.empty_like(y0)
+    out = torch.zeros((T, hc * hs), dtype=torch.bfloat16, device="cuda")
+    fwd(x, y1, hc_write=(dev(res).view(torch.bfloat16), dev(gate).view(torch.bfloat16), out))
+    fwd.status()
+    assert torch.equal(y0.view(torch.int16), y1.view(torch.int16))
+    want = O.gated_residual_write(host(y1), res, gate)
+    assert np.array_equal(host(out), want)

@@ -201,3 +201,23 @@ def test_bf16_routed_experts_match_float64():
     assert np.abs(y - ref).max() <= 2.0 ** -6 * np.abs(ref).max()
     y2 = O.moe_bf16_routed_forward(x, ids, rw, gu, down, y0=y)
     assert np.allclose(y2, 2 * y, rtol=1e-6, atol=1e-7)
+
+
+def test_gated_residual_write_matches_float64():
+    """out = bf16(R + y * gate) with one rounding (a fused multiply-add): equal to the float64
+    evaluation rounded once to bf16, since products of two bf16 values plus a bf16 are exact
+    in float64 (src/model/hyperconnection.cu:286-305)."""
+    rng = np.random.default_rng(5)
+    T, hc, hs = 7, 4, 96
+    y = O.f32_to_bf16(rng.standard_normal((T, hs)).astype(np.float32))
+    res = O.f32_to_bf16(rng.standard_normal((T, hc * hs)).astype(np.float32) * 3)
+    gate = O.f32_to_bf16((2.0 / (1.0 + np.exp(-rng.standard_normal((T, hc))))).astype(np.float32))
+    got = O.gated_residual_write(y, res, gate)
+    yf, rf, gf = (O.bf16_to_f32(a).astype(np.float64) for a in (y, res, gate))
+    want64 = rf.reshape(T, hc, hs) + yf[:, None, :] * gf[:, :, None]
+    # float64 -> float32 -> bf16 would round twice; go through the exact value's bf16 neighbours
+    want = O.f32_to_bf16(want64.reshape(T, hc * hs).astype(np.float32))
+    diff = (got != want)
+    # double rounding can only matter where the float32 rounding lands exactly on a bf16 tie
+    assert diff.mean() < 1e-3
+    assert np.abs(O.bf16_to_f32(got).astype(np.float64) - want64.reshape(T, -1)).max() <= 2.0 ** -8 * np.abs(want64).max()
