@@ -6,8 +6,12 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
+#include <cstdlib>
+#include <mutex>
 #include <string>
+#include <thread>
 #include <type_traits>
 #include <vector>
 
@@ -84,37 +88,70 @@ Status LoadMoEWeights(ReadTensor&& read, int layer_id, int E, int hs, int moe_is
   out->gu_input_scale_h.resize(E);
   out->dn_w_scale2_h.resize(E);
   out->dn_input_scale_h.resize(E);
-  std::vector<uint8_t> gate_w(gu_w), up_w(gu_w), down_w(dn_w), gate_s(gu_s), up_s(gu_s), down_s(dn_s);
-  std::vector<uint8_t> gu_p(2 * gu_w), gu_sf(gu_blk), dn_p(dn_w), dn_sf(dn_blk);
-  for (int e = 0; e < E; ++e) {
-    auto name = [&](const char* proj, const char* suffix) { return MoEExpertTensorName(layer_id, e, proj, suffix); };
-    float sc[4];
-    if (!read(name("gate_proj", "weight"), gate_w.data(), gate_w.size()) ||
-        !read(name("up_proj", "weight"), up_w.data(), up_w.size()) ||
-        !read(name("down_proj", "weight"), down_w.data(), down_w.size()) ||
-        !read(name("gate_proj", "weight_scale"), gate_s.data(), gate_s.size()) ||
-        !read(name("up_proj", "weight_scale"), up_s.data(), up_s.size()) ||
-        !read(name("down_proj", "weight_scale"), down_s.data(), down_s.size()) ||
-        !read(name("gate_proj", "weight_scale_2"), &sc[0], sizeof(float)) ||
-        !read(name("gate_proj", "input_scale"), &sc[1], sizeof(float)) ||
-        !read(name("down_proj", "weight_scale_2"), &sc[2], sizeof(float)) ||
-        !read(name("down_proj", "input_scale"), &sc[3], sizeof(float)))
-      return Status::Fail("MoE expert load failed (layer " + std::to_string(layer_id) + ")");
-    if (q4t_pack_expert_host(gate_w.data(), up_w.data(), down_w.data(), gate_s.data(), up_s.data(), down_s.data(), hs,
-                             moe_is, gu_p.data(), gu_sf.data(), dn_p.data(), dn_sf.data()) != Q4T_OK)
-      return Status::Fail(q4t_last_error());
-    out->gu_w_scale2_h[e] = sc[0];
-    out->gu_input_scale_h[e] = sc[1];
-    out->dn_w_scale2_h[e] = sc[2];
-    out->dn_input_scale_h[e] = sc[3];
-    bool ok = cudaMemcpyAsync(out->gu_packed_expert(e), gu_p.data(), gu_p.size(), cudaMemcpyHostToDevice, stream) == cudaSuccess;
-    ok = ok && cudaMemcpyAsync(out->gu_sf_expert(e), gu_sf.data(), gu_blk, cudaMemcpyHostToDevice, stream) == cudaSuccess;
-    ok = ok && cudaMemcpyAsync(out->dn_packed_expert(e), dn_p.data(), dn_p.size(), cudaMemcpyHostToDevice, stream) == cudaSuccess;
-    ok = ok && cudaMemcpyAsync(out->dn_sf_expert(e), dn_sf.data(), dn_blk, cudaMemcpyHostToDevice, stream) == cudaSuccess;
-    // the staging vectors are reused by the next expert: finish these copies first
-    ok = ok && cudaStreamSynchronize(stream) == cudaSuccess;
-    if (!ok) return Status::Fail("expert upload failed");
+  // Experts are independent (disjoint device ranges, read-only checkpoint), so a pool of
+  // min(hardware threads, E) workers reads, packs and uploads them, each with its own
+  // staging buffers; Q4T_MOE_THREADS overrides the count (src/quant/moe_weights.cpp:111-125
+  // of the reference).  `read` is called from several threads at once.  Each worker copies
+  // with the blocking cudaMemcpy, so its staging is free for its next expert on return;
+  // `stream` orders only the final scalar upload.
+  int nthreads = static_cast<int>(std::thread::hardware_concurrency());
+  if (nthreads < 1) nthreads = 1;
+  if (nthreads > E) nthreads = E;
+  if (const char* env = std::getenv("Q4T_MOE_THREADS")) {
+    const int v = std::atoi(env);
+    if (v > 0) nthreads = v < E ? v : E;
   }
+  int device = 0;
+  cudaGetDevice(&device);
+  std::atomic<int> next_expert{0};
+  std::atomic<bool> failed{false};
+  std::mutex err_mu;
+  std::string err;
+  auto fail = [&](const std::string& msg) {
+    std::lock_guard<std::mutex> lock(err_mu);
+    if (!failed.exchange(true)) err = msg;
+  };
+  auto worker = [&]() {
+    if (cudaSetDevice(device) != cudaSuccess) return fail("cudaSetDevice failed in a loader thread");
+    std::vector<uint8_t> gate_w(gu_w), up_w(gu_w), down_w(dn_w), gate_s(gu_s), up_s(gu_s), down_s(dn_s);
+    std::vector<uint8_t> gu_p(2 * gu_w), gu_sf(gu_blk), dn_p(dn_w), dn_sf(dn_blk);
+    for (int e = next_expert.fetch_add(1); e < E && !failed.load(); e = next_expert.fetch_add(1)) {
+      auto name = [&](const char* proj, const char* suffix) { return MoEExpertTensorName(layer_id, e, proj, suffix); };
+      float sc[4];
+      if (!read(name("gate_proj", "weight"), gate_w.data(), gate_w.size()) ||
+          !read(name("up_proj", "weight"), up_w.data(), up_w.size()) ||
+          !read(name("down_proj", "weight"), down_w.data(), down_w.size()) ||
+          !read(name("gate_proj", "weight_scale"), gate_s.data(), gate_s.size()) ||
+          !read(name("up_proj", "weight_scale"), up_s.data(), up_s.size()) ||
+          !read(name("down_proj", "weight_scale"), down_s.data(), down_s.size()) ||
+          !read(name("gate_proj", "weight_scale_2"), &sc[0], sizeof(float)) ||
+          !read(name("gate_proj", "input_scale"), &sc[1], sizeof(float)) ||
+          !read(name("down_proj", "weight_scale_2"), &sc[2], sizeof(float)) ||
+          !read(name("down_proj", "input_scale"), &sc[3], sizeof(float)))
+        return fail("MoE expert load failed (layer " + std::to_string(layer_id) + ")");
+      if (q4t_pack_expert_host(gate_w.data(), up_w.data(), down_w.data(), gate_s.data(), up_s.data(), down_s.data(), hs,
+                               moe_is, gu_p.data(), gu_sf.data(), dn_p.data(), dn_sf.data()) != Q4T_OK)
+        return fail(q4t_last_error());
+      out->gu_w_scale2_h[e] = sc[0];
+      out->gu_input_scale_h[e] = sc[1];
+      out->dn_w_scale2_h[e] = sc[2];
+      out->dn_input_scale_h[e] = sc[3];
+      if (cudaMemcpy(out->gu_packed_expert(e), gu_p.data(), gu_p.size(), cudaMemcpyHostToDevice) != cudaSuccess ||
+          cudaMemcpy(out->gu_sf_expert(e), gu_sf.data(), gu_blk, cudaMemcpyHostToDevice) != cudaSuccess ||
+          cudaMemcpy(out->dn_packed_expert(e), dn_p.data(), dn_p.size(), cudaMemcpyHostToDevice) != cudaSuccess ||
+          cudaMemcpy(out->dn_sf_expert(e), dn_sf.data(), dn_blk, cudaMemcpyHostToDevice) != cudaSuccess)
+        return fail("expert upload failed");
+    }
+  };
+  if (nthreads == 1) {
+    worker();
+  } else {
+    std::vector<std::thread> pool;
+    pool.reserve(static_cast<size_t>(nthreads));
+    for (int i = 0; i < nthreads; ++i) pool.emplace_back(worker);
+    for (std::thread& th : pool) th.join();
+  }
+  if (failed.load()) return Status::Fail(err);
   const size_t sb = sizeof(float) * E;
   if (cudaMemcpyAsync(out->gu_w_scale2, out->gu_w_scale2_h.data(), sb, cudaMemcpyHostToDevice, stream) != cudaSuccess ||
       cudaMemcpyAsync(out->gu_input_scale, out->gu_input_scale_h.data(), sb, cudaMemcpyHostToDevice, stream) != cudaSuccess ||

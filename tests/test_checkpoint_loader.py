@@ -22,7 +22,7 @@ E, HS, IS, SIS, LAYER = 6, 2560, 640, 640, 3
 def _build():
     cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     pkg = os.path.join(ROOT, "qwen4-thor_b200")
-    cmd = ["g++", "-std=c++20", "-O1", "-Wall", f"-I{cuda}/include", f"-I{ROOT}/include", f"-I{pkg}/host",
+    cmd = ["g++", "-std=c++20", "-O1", "-Wall", "-pthread", f"-I{cuda}/include", f"-I{ROOT}/include", f"-I{pkg}/host",
            os.path.join(ROOT, "tests", "cpp", "loader_test.cpp"), "-o", EXE,
            f"-L{pkg}", "-lq4t_moe_b200", f"-Wl,-rpath,{pkg}", f"-L{cuda}/lib64", "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -31,7 +31,7 @@ def _build():
     inc, link = _nccl_flags()
     if inc is None:
         pytest.skip("no NCCL header on this machine")
-    cmd = ["g++", "-std=c++20", "-O1", "-Wall", f"-I{cuda}/include", f"-I{ROOT}/include", f"-I{pkg}/host", *inc,
+    cmd = ["g++", "-std=c++20", "-O1", "-Wall", "-pthread", f"-I{cuda}/include", f"-I{ROOT}/include", f"-I{pkg}/host", *inc,
            os.path.join(ROOT, "tests", "cpp", "ep_driver_test.cpp"), "-o", EXE,
            f"-L{pkg}", "-lq4t_moe_b200", f"-Wl,-rpath,{pkg}", f"-L{cuda}/lib64", "-lcudart", *link]
     return subprocess.run(cmd, capture_output=True, text=True)
