@@ -48,12 +48,32 @@ struct DeviceState {
   // The shared expert depends only on x, so q4t_moe_forward runs it on this
   // library-owned stream beside the router / permutation / quantise chain and
   // joins before the combine (fork and join by events, no host involvement).
+  // One stream and one set of events per HOST THREAD and device (see ThreadLanes):
+  // callers on different threads never meet on them.
   cudaStream_t side_stream = nullptr;
   cudaEvent_t fork_event = nullptr, join_event = nullptr, mid_event = nullptr;
 };
 constexpr int kMaxDevices = 16;
-DeviceState g_dev[kMaxDevices];
+DeviceState g_dev[kMaxDevices];   // per device: facts shared by all threads (no stream, no events)
 std::mutex g_dev_mutex;
+
+// What device_state() hands out: the calling thread's own copy of the device's facts plus
+// its own side stream and events, created on the thread's first call for that device and
+// released when the thread ends.
+struct ThreadLanes {
+  DeviceState dev[kMaxDevices];
+  ~ThreadLanes() {
+    for (DeviceState& d : dev) {
+      if (!d.ready) continue;
+      // at process exit the runtime may already be gone: failures are of no consequence
+      cudaEventDestroy(d.fork_event);
+      cudaEventDestroy(d.join_event);
+      cudaEventDestroy(d.mid_event);
+      cudaStreamDestroy(d.side_stream);
+    }
+  }
+};
+thread_local ThreadLanes t_lanes;
 
 // Per-device one-time set-up: architecture check, driver entry point for the
 // tensor-map encoder, shared-memory attribute of the GEMM kernels.
@@ -82,16 +102,21 @@ int device_state(const DeviceState** out) {
     if ((e = q4t::gemm_pair_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = q4t::routing_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = q4t::small_batch_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
-    if ((e = cudaStreamCreateWithFlags(&s.side_stream, cudaStreamNonBlocking)) != cudaSuccess ||
-        (e = cudaEventCreateWithFlags(&s.fork_event, cudaEventDisableTiming)) != cudaSuccess ||
-        (e = cudaEventCreateWithFlags(&s.join_event, cudaEventDisableTiming)) != cudaSuccess ||
-        (e = cudaEventCreateWithFlags(&s.mid_event, cudaEventDisableTiming)) != cudaSuccess)
-      return fail_cuda("side stream set-up", e);
     s.encode = reinterpret_cast<EncodeFn>(fn);
     s.num_sms = prop.multiProcessorCount;
     s.ready = true;
   }
-  *out = &s;
+  DeviceState& mine = t_lanes.dev[dev];
+  if (!mine.ready) {
+    DeviceState fresh = s;
+    if ((e = cudaStreamCreateWithFlags(&fresh.side_stream, cudaStreamNonBlocking)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&fresh.fork_event, cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&fresh.join_event, cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&fresh.mid_event, cudaEventDisableTiming)) != cudaSuccess)
+      return fail_cuda("side stream set-up", e);
+    mine = fresh;
+  }
+  *out = &mine;
   return Q4T_OK;
 }
 

@@ -310,3 +310,46 @@ def test_router_trace_observer_and_slot_mode(q4t, gpu_lib):
                                        y.data_ptr(), T, k, fwd.ws.data_ptr(), fwd.layout.total, C.byref(bad), None)
     assert rc != 0 and b"slot count" in q4t.load().q4t_last_error()
     slot_layer.routed.E = slots
+
+
+def test_two_host_threads_on_one_device(q4t, gpu_lib):
+    """Two host threads drive the same GPU at once, each on its own stream with its own
+    workspace: the side stream and the fork/join events belong to the calling thread, so the
+    only ordering a caller owes the library is its stream (as with the reference's seam).
+    Every result must equal the single-threaded one bit for bit."""
+    import threading
+    E, hs, is_, sis, k, T = 64, 1024, 256, 256, 6, 40
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=123)
+    dl = q4t.DeviceLayer.from_host(L)
+    xs = [dev(synth.make_x(T, hs, seed=200 + i)) for i in range(2)]
+    want = []
+    for x in xs:
+        fwd = q4t.MoEForward(dl, T, k)
+        y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+        fwd(x, y)
+        fwd.status()
+        want.append(host(y))
+    errors, results = [], [None, None]
+
+    def run(i):
+        try:
+            torch.cuda.set_device(0)
+            st = torch.cuda.Stream()
+            fwd = q4t.MoEForward(dl, T, k)
+            y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+            with torch.cuda.stream(st):
+                for _ in range(200):
+                    fwd(xs[i], y, stream=st)
+            st.synchronize()
+            results[i] = host(y)
+        except Exception as exc:  # surfaced in the main thread below
+            errors.append(exc)
+
+    threads = [threading.Thread(target=run, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for i in range(2):
+        assert np.array_equal(results[i], want[i])
