@@ -471,10 +471,18 @@ def main_single(args):
         print(json.dumps(line))
         return
 
-    T = 128
+    T = args.tokens
+    if args.profile_range:   # for `ncu --profile-from-start off`: only the steps of the headline point are seen
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
     with ClockSampler(0) as clocks:
-        main = run_decode_point(torch, q4t, layers, T, args.steps, args.warmup, with_e2e=True, with_stages=True,
-                                repeats=args.repeats)
+        main = run_decode_point(torch, q4t, layers, T, args.steps, args.warmup, with_e2e=not args.profile_range,
+                                with_stages=not args.profile_range, repeats=args.repeats)
+    if args.profile_range:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps(dict(profile_range=True, tokens=T, ms_per_step=main["ms_per_step"])))
+        return
     clk = clocks.summary()
     also = {}
     if not args.quick:
@@ -553,7 +561,7 @@ def main_single(args):
                 steps=args.steps, warmup=args.warmup, ms_per_step=main["ms_per_step"], higher_is_better=True,
                 scaling="weak", vs_baseline=None,
                 dtype="nvfp4 (e2m1 x ue4m3, fp32 accumulate); bf16 router and shared expert", data="synthetic",
-                config=dict(workload="decode-shaped MoE layer microbench, T=128", hidden=HS, experts=E, top_k=K_TOP,
+                config=dict(workload=f"decode-shaped MoE layer microbench, T={T}", hidden=HS, experts=E, top_k=K_TOP,
                             moe_intermediate=MOE_IS, shared_intermediate=SHARED_IS,
                             l2=f"{args.layers} layer weight sets (0.9 GB each) and 8 inputs rotated per step; one step touches ~840 MB > L2",
                             unique_experts_per_step=main["unique_experts"]),
@@ -580,6 +588,11 @@ def main():
     ap.add_argument("--layers", type=int, default=4, help="independent layer weight sets rotated per step")
     ap.add_argument("--stack-layers", type=int, default=48,
                     help="layers of the decode-stack point (x <- x + MoE(RMSNorm(x)), T=128); 0 skips it")
+    ap.add_argument("--tokens", type=int, default=128,
+                    help="tokens per step of the headline point (128 = the benchmark's configuration)")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="bracket the headline point's steps with cudaProfilerStart/Stop and print only its time "
+                         "(for launch lists and captures taken with ncu --profile-from-start off)")
     ap.add_argument("--prefill-tokens", type=int, default=0,
                     help="run only the Zipf-skewed prefill layer at this many tokens and print its result")
     args = ap.parse_args()

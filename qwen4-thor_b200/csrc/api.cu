@@ -1389,31 +1389,44 @@ int32_t q4t_ep_route_publish(const uint16_t* x, const q4t_extra_weights* extra, 
     }
     return code;
   };
-  if ((e = cudaEventRecord(ds->fork_event, st)) != cudaSuccess ||
-      (e = cudaStreamWaitEvent(ds->side_stream, ds->fork_event, 0)) != cudaSuccess)
-    return fail_cuda("fork", e);
-  forked = true;
-  q4t::chain_break();
-  if (!selective) {
-    if ((rc = q4t_ep_publish(x, peers, extra->hs, input_scale, ds->side_stream)) != Q4T_OK) return leave(rc);
-    if ((e = cudaEventRecord(ds->mid_event, ds->side_stream)) != cudaSuccess) return leave(fail_cuda("publish record", e));
+  auto fork = [&]() -> int {
+    if ((e = cudaEventRecord(ds->fork_event, st)) != cudaSuccess ||
+        (e = cudaStreamWaitEvent(ds->side_stream, ds->fork_event, 0)) != cudaSuccess)
+      return fail_cuda("fork", e);
+    forked = true;
     q4t::chain_break();
+    return Q4T_OK;
+  };
+  auto shared_on_side = [&]() -> int {
+    if ((rc = run_shared_expert(ds, x, extra, reinterpret_cast<uint16_t*>(base + F.shared_gu),
+                                reinterpret_cast<uint16_t*>(base + F.shared_act),
+                                reinterpret_cast<uint16_t*>(base + F.shared_down), T, 0, ds->side_stream)) != Q4T_OK)
+      return rc;
+    if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return fail_cuda("join record", e);
+    q4t::chain_break();
+    return Q4T_OK;
+  };
+  if (selective) {
+    // router, top-k and the selective publish first, alone on the GPU: the other ranks wait
+    // for these tokens.  The shared expert is forked after them, so that it fills the time
+    // this rank spends waiting for the exchange of ids instead of competing with the router.
+    if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, extra->E, extra->hs, st)) != Q4T_OK) return rc;
+    if ((e = q4t::launch_topk(logits, nullptr, expert_ids, router_w, T, extra->E, k, st)) != cudaSuccess)
+      return fail_cuda("topk launch", e);
+    if ((rc = q4t_ep_publish_selected(x, expert_ids, peers, k, extra->E, extra->hs, input_scale, st)) != Q4T_OK) return rc;
+    if ((rc = fork()) != Q4T_OK) return rc;
+    if ((rc = shared_on_side()) != Q4T_OK) return leave(rc);
+    return Q4T_OK;   // the side stream is joined by q4t_ep_combine
   }
-  if ((rc = run_shared_expert(ds, x, extra, reinterpret_cast<uint16_t*>(base + F.shared_gu),
-                              reinterpret_cast<uint16_t*>(base + F.shared_act),
-                              reinterpret_cast<uint16_t*>(base + F.shared_down), T, 0, ds->side_stream)) != Q4T_OK)
-    return leave(rc);
-  if ((e = cudaEventRecord(ds->join_event, ds->side_stream)) != cudaSuccess) return leave(fail_cuda("join record", e));
+  if ((rc = fork()) != Q4T_OK) return rc;
+  if ((rc = q4t_ep_publish(x, peers, extra->hs, input_scale, ds->side_stream)) != Q4T_OK) return leave(rc);
+  if ((e = cudaEventRecord(ds->mid_event, ds->side_stream)) != cudaSuccess) return leave(fail_cuda("publish record", e));
   q4t::chain_break();
+  if ((rc = shared_on_side()) != Q4T_OK) return leave(rc);
   if ((rc = run_bf16_linear(ds, x, extra->gate, logits, T, extra->E, extra->hs, st)) != Q4T_OK) return leave(rc);
   if ((e = q4t::launch_topk(logits, nullptr, expert_ids, router_w, T, extra->E, k, st)) != cudaSuccess)
     return leave(fail_cuda("topk launch", e));
-  if (selective) {
-    if ((rc = q4t_ep_publish_selected(x, expert_ids, peers, k, extra->E, extra->hs, input_scale, st)) != Q4T_OK)
-      return leave(rc);
-  } else if ((e = cudaStreamWaitEvent(st, ds->mid_event, 0)) != cudaSuccess) {
-    return leave(fail_cuda("publish join", e));
-  }
+  if ((e = cudaStreamWaitEvent(st, ds->mid_event, 0)) != cudaSuccess) return leave(fail_cuda("publish join", e));
   return Q4T_OK;   // the side stream is joined by q4t_ep_combine (the shared expert's result is needed there)
 }
 
