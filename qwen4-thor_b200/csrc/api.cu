@@ -905,6 +905,7 @@ int moe_forward_impl(const uint16_t* x, const q4t_routed_weights* routed, const 
 
   // The shared expert runs beside the routed chain unless the stage timer is on
   // (its marks assume one stream) or the batch is large enough to fill the GPU.
+  // (forking at 4096 and 16 384 tokens measured within 1.3 % of not forking)
   const bool fork = !g_timer.enabled && T <= 1024;
   // Once the side stream has been forked, every way out joins it again: an error
   // return that left it dangling would, under stream capture, invalidate the graph.

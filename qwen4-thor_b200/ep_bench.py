@@ -93,6 +93,7 @@ def main_multi(args):
     drv = drv_rows
     placement = None
     drv_plain = None
+    equals_single = None
     if peer_mode:
         def connect(buf):
             gathered = [None] * world
@@ -132,7 +133,15 @@ def main_multi(args):
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
         if int(same.item()) != 1:
             raise RuntimeError("peer path and row-exchange path disagree")
-        del y2
+        # and the same bits as the unsharded layer: every rank runs its own tokens through the
+        # whole layer on its GPU alone
+        fwd1 = q4t.MoEForward(full, T_loc, K_TOP)
+        fwd1(xs[0], y2)
+        torch.cuda.synchronize()
+        same1 = torch.tensor([int(torch.equal(y.view(torch.int16), y2.view(torch.int16)))], device="cuda")
+        dist.all_reduce(same1, op=dist.ReduceOp.MIN)
+        equals_single = bool(int(same1.item()))
+        del y2, fwd1
         if args.quick:
             del drv_rows, ops
             torch.cuda.empty_cache()
@@ -294,7 +303,7 @@ def main_multi(args):
                               imbalance=float(mx_rows.item()) / (T_TOTAL * K_TOP / world)),
                     phase_ms_rank0=phases, expert_stage_ms_by_rank=stage_all, single_gpu_same_workload=n1,
                     strong_scaling_efficiency=(n1["ms_per_step"] / (world * ms)) if n1 else None,
-                    plain_sharding=plain,
+                    plain_sharding=plain, equals_single_gpu_bits=equals_single,
                     note="N = 1 of this metric is `also.ep_prefill_T32768_single_gpu` of the single-GPU line "
                          "(whose headline metric is the decode-shaped layer, another workload)")
         sys.stdout.flush()

@@ -188,4 +188,12 @@ def test_ep_two_gpus_nccl(q4t, gpu_lib):
                         "--gpus", "2", "--steps", "2", "--warmup", "3", "--quick"],
                        capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stderr[-2000:]
-    assert '"n_gpus": 2' in r.stdout
+    import json
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["n_gpus"] == 2 and line["metric"] == "moe_ep_prefill_tokens_per_s" and line["scaling"] == "strong"
+    # the sharded step reproduces the single-GPU layer bit for bit
+    assert line["equals_single_gpu_bits"] is True
+    if line.get("plain_sharding"):     # timed only without --quick
+        assert line["plain_sharding"]["equals_replicated_placement_bits"] is True
+    assert line["value"] > 0 and 0 < line["ms_per_step"] < 50
+    assert set(line["phase_ms_rank0"]) >= {"publish", "ids_all_gather", "experts_pull_push", "landed_barrier", "combine"}
