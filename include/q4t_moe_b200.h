@@ -426,7 +426,7 @@ int32_t q4t_moe_combine(const uint16_t* x, const uint16_t* expert_rows,
  * otherwise use the row-exchange entry points above).
  *
  * q4t_peer_buffer_*: device buffers that another process on the same node can
- * map: alloc/free on the owner, export -> 64-byte handle to send to the peers
+ * map: alloc (zero-filled) / free on the owner, export -> 64-byte handle to send to the peers
  * (any host channel), open/close on a peer.                                    */
 #define Q4T_EP_MAX_RANKS 8
 #define Q4T_PEER_HANDLE_BYTES 64
@@ -454,8 +454,35 @@ typedef struct q4t_ep_peer_table {
    * to the ranks that serve one of its selected experts; without it (NULL) every
    * token goes to every rank.  Maps 0 and 1 need no table.                      */
   const int32_t* expert_owner;
+  /* Optional: rank r's SYNC buffer (q4t_ep_sync_buffer_bytes, zeroed once by its owner,
+   * peer-writable like the others).  With it the two collectives of a step can be
+   * replaced by q4t_ep_post_ids / q4t_ep_post_rows / q4t_ep_wait (below).            */
+  uint8_t* sync[Q4T_EP_MAX_RANKS];
 } q4t_ep_peer_table;
 #define Q4T_EP_REPLICATED (1 << 30)
+/* ---- the step's two collectives as kernels over peer memory (optional).
+ * A SYNC buffer holds, at offset 0, two rows of Q4T_EP_MAX_RANKS uint32 flags (row 0:
+ * "rank r's tokens and ids of step `epoch` are in your buffers", row 1: "rank r's
+ * result rows of step `epoch` have been stored"), at offset 128 an int32 status word,
+ * and from Q4T_EP_SYNC_IDS_OFFSET on the gathered ids int32 [world*tokens_per_rank, k]
+ * in rank order (what q4t_moe_expert_peer takes as ids_all).  Per step, with a counter
+ * `epoch` that every rank advances by one (start at 1; flags start at 0):
+ *   q4t_ep_route_publish; q4t_ep_post_ids(ids, …, epoch)    -- stores the ids block into
+ *       every rank's SYNC buffer, then raises flag row 0 there (after a system fence,
+ *       so the published tokens are visible too);
+ *   q4t_ep_wait(…, 0, epoch); q4t_moe_expert_peer(own SYNC + Q4T_EP_SYNC_IDS_OFFSET, …);
+ *   q4t_ep_post_rows(…, epoch); q4t_ep_wait(…, 1, epoch); q4t_ep_combine.
+ * All stream-ordered, no host synchronisation, no collective library call.  The waits
+ * are bounded (about two seconds): a rank that never posts makes the others' wait give
+ * up and raise the status word, which q4t_ep_sync_status reports (synchronise the
+ * stream first); the context stays usable.  Every rank must run the same sequence.    */
+#define Q4T_EP_SYNC_IDS_OFFSET 256
+size_t q4t_ep_sync_buffer_bytes(int32_t world, int32_t tokens_per_rank, int32_t k);
+int32_t q4t_ep_post_ids(const int32_t* expert_ids, const q4t_ep_peer_table* peers, int32_t k,
+                        uint32_t epoch, void* stream);
+int32_t q4t_ep_post_rows(const q4t_ep_peer_table* peers, uint32_t epoch, void* stream);
+int32_t q4t_ep_wait(const q4t_ep_peer_table* peers, int32_t phase, uint32_t epoch, void* stream);
+int32_t q4t_ep_sync_status(const q4t_ep_peer_table* peers);
 int32_t q4t_peer_buffer_alloc(size_t bytes, void** ptr);
 int32_t q4t_peer_buffer_free(void* ptr);
 int32_t q4t_peer_buffer_export(const void* ptr, uint8_t handle[Q4T_PEER_HANDLE_BYTES]);

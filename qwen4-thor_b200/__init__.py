@@ -52,7 +52,7 @@ class EpPeerTable(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("tokens_per_rank", C.c_int32),
                 ("expert_map", C.c_int32), ("xq_packed", C.c_void_p * 8), ("xq_sf", C.c_void_p * 8),
                 ("dn_rows", C.c_void_p * 8), ("placement", C.c_void_p), ("experts_total", C.c_int32),
-                ("reserved", C.c_int32), ("expert_owner", C.c_void_p)]
+                ("reserved", C.c_int32), ("expert_owner", C.c_void_p), ("sync", C.c_void_p * 8)]
 
 
 class ForwardWsLayout(C.Structure):
@@ -83,6 +83,7 @@ EXPORTS = [
     "q4t_moe_bf16_forward",
     "q4t_peer_buffer_alloc", "q4t_peer_buffer_free", "q4t_peer_buffer_export", "q4t_peer_buffer_open",
     "q4t_peer_buffer_close", "q4t_ep_publish", "q4t_ep_publish_selected", "q4t_ep_route_publish", "q4t_ep_combine", "q4t_moe_expert_peer_workspace_bytes", "q4t_moe_expert_peer", "q4t_ep_flat_rows",
+    "q4t_ep_sync_buffer_bytes", "q4t_ep_post_ids", "q4t_ep_post_rows", "q4t_ep_wait", "q4t_ep_sync_status",
 ]
 # libq4t_moe_b200_check.so (include/q4t_moe_b200_check.h): device-side checkers for the GPU tests only.
 CHECK_EXPORTS = ["q4t_check_last_error", "q4t_fp4_gemm_check", "q4t_selftest_encoders"]
@@ -93,6 +94,7 @@ FLAG_ROUTED_F32 = 2        # materialise the fp32 routed sum (q4t_moe_forward)
 FLAG_GENERAL_PATH = 4      # batches of at most 16 tokens: take the grouped path of larger batches anyway
 EP_MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
+EP_SYNC_IDS_OFFSET = 256
 EP_REPLICATED = 1 << 30
 NOALLOC_SCRATCH_BYTES = 3 << 20
 
@@ -157,6 +159,12 @@ def load():
     L.q4t_ep_combine.argtypes = [vp, vp, vp, vp, C.POINTER(ExtraWeights), vp, i32, i32, vp, vp, sz, vp]
     L.q4t_ep_publish.argtypes = [vp, C.POINTER(EpPeerTable), i32, f32, vp]
     L.q4t_ep_publish_selected.argtypes = [vp, vp, C.POINTER(EpPeerTable), i32, i32, i32, f32, vp]
+    L.q4t_ep_sync_buffer_bytes.restype = sz
+    L.q4t_ep_sync_buffer_bytes.argtypes = [i32, i32, i32]
+    L.q4t_ep_post_ids.argtypes = [vp, C.POINTER(EpPeerTable), i32, u32, vp]
+    L.q4t_ep_post_rows.argtypes = [C.POINTER(EpPeerTable), u32, vp]
+    L.q4t_ep_wait.argtypes = [C.POINTER(EpPeerTable), i32, u32, vp]
+    L.q4t_ep_sync_status.argtypes = [C.POINTER(EpPeerTable)]
     L.q4t_moe_expert_peer_workspace_bytes.restype = C.c_size_t
     L.q4t_moe_expert_peer_workspace_bytes.argtypes = [i32] * 5
     L.q4t_moe_expert_peer.argtypes = [vp, C.POINTER(EpPeerTable), C.POINTER(RoutedWeights), i32, vp, sz, u32, vp]

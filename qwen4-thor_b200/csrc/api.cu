@@ -1277,7 +1277,14 @@ int32_t q4t_peer_buffer_alloc(size_t bytes, void** ptr) {
   int rc = device_state(&ds);
   if (rc != Q4T_OK) return rc;
   cudaError_t e = cudaMalloc(ptr, align_up(bytes, 256));
-  return e == cudaSuccess ? Q4T_OK : fail_cuda("peer buffer allocation", e);
+  if (e != cudaSuccess) return fail_cuda("peer buffer allocation", e);
+  // zero-filled (a sync buffer's flags must start at zero); completes before the call returns
+  if ((e = cudaMemset(*ptr, 0, align_up(bytes, 256))) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess) {
+    cudaFree(*ptr);
+    *ptr = nullptr;
+    return fail_cuda("peer buffer clear", e);
+  }
+  return Q4T_OK;
 }
 int32_t q4t_peer_buffer_free(void* ptr) {
   cudaError_t e = cudaFree(ptr);
@@ -1506,6 +1513,73 @@ int32_t q4t_moe_expert_peer(const int32_t* ids_all, const q4t_ep_peer_table* pee
   stage_begin(st);
   stage_end(1, st);
   return run_routed_core(ds, nullptr, local_ids, w, P, T_all, k, flags, st, false, &route);
+}
+
+size_t q4t_ep_sync_buffer_bytes(int32_t world, int32_t tokens_per_rank, int32_t k) {
+  if (world <= 0 || world > Q4T_EP_MAX_RANKS || tokens_per_rank <= 0 || k <= 0) return 0;
+  return align_up(Q4T_EP_SYNC_IDS_OFFSET + static_cast<size_t>(world) * tokens_per_rank * k * 4, 256);
+}
+
+namespace {
+int sync_table_ok(const q4t_ep_peer_table* peers) {
+  if (!peers) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (peers->world <= 0 || peers->world > Q4T_EP_MAX_RANKS || peers->rank < 0 || peers->rank >= peers->world ||
+      peers->tokens_per_rank <= 0)
+    return fail(Q4T_ERR_INVALID, "invalid peer table (world in [1,8], rank < world, tokens_per_rank > 0)");
+  for (int i = 0; i < peers->world; ++i)
+    if (!peers->sync[i]) return fail(Q4T_ERR_INVALID, "peer table has no sync buffers");
+  return Q4T_OK;
+}
+int post(const int32_t* ids, const q4t_ep_peer_table* peers, int k, int row, uint32_t epoch, void* stream) {
+  int rc = sync_table_ok(peers);
+  if (rc != Q4T_OK) return rc;
+  const DeviceState* ds;
+  if ((rc = device_state(&ds)) != Q4T_OK) return rc;
+  q4t::EpPostTargets dst{};
+  const size_t block = static_cast<size_t>(peers->tokens_per_rank) * k * 4;
+  for (int p = 0; p < peers->world; ++p) {
+    dst.ids[p] = reinterpret_cast<int32_t*>(peers->sync[p] + Q4T_EP_SYNC_IDS_OFFSET + block * peers->rank);
+    dst.flag[p] = reinterpret_cast<uint32_t*>(peers->sync[p]) + row * Q4T_EP_MAX_RANKS + peers->rank;
+  }
+  cudaError_t e = q4t::launch_ep_post(ids, ids ? peers->tokens_per_rank * k : 0, dst, peers->world, epoch,
+                                      static_cast<cudaStream_t>(stream));
+  q4t::chain_break();
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("post launch", e);
+}
+}  // namespace
+
+int32_t q4t_ep_post_ids(const int32_t* expert_ids, const q4t_ep_peer_table* peers, int32_t k, uint32_t epoch,
+                        void* stream) {
+  if (!expert_ids) return fail(Q4T_ERR_INVALID, "null pointer");
+  if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");
+  return post(expert_ids, peers, k, 0, epoch, stream);
+}
+
+int32_t q4t_ep_post_rows(const q4t_ep_peer_table* peers, uint32_t epoch, void* stream) {
+  return post(nullptr, peers, 1, 1, epoch, stream);
+}
+
+int32_t q4t_ep_wait(const q4t_ep_peer_table* peers, int32_t phase, uint32_t epoch, void* stream) {
+  int rc = sync_table_ok(peers);
+  if (rc != Q4T_OK) return rc;
+  if (phase < 0 || phase > 1) return fail(Q4T_ERR_INVALID, "phase must be 0 or 1");
+  const DeviceState* ds;
+  if ((rc = device_state(&ds)) != Q4T_OK) return rc;
+  uint8_t* own = peers->sync[peers->rank];
+  cudaError_t e = q4t::launch_ep_wait(reinterpret_cast<const uint32_t*>(own) + phase * Q4T_EP_MAX_RANKS, peers->world,
+                                      epoch, reinterpret_cast<int32_t*>(own + 128), static_cast<cudaStream_t>(stream));
+  q4t::chain_break();   // what follows reads other ranks' writes: an ordinary launch
+  return e == cudaSuccess ? Q4T_OK : fail_cuda("wait launch", e);
+}
+
+int32_t q4t_ep_sync_status(const q4t_ep_peer_table* peers) {
+  int rc = sync_table_ok(peers);
+  if (rc != Q4T_OK) return rc;
+  int32_t word = 0;
+  cudaError_t e = cudaMemcpy(&word, peers->sync[peers->rank] + 128, 4, cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail_cuda("status read", e);
+  if (word != 0) return fail(Q4T_ERR_KERNEL, "a wait for another rank ran out (code " + std::to_string(word) + ")");
+  return Q4T_OK;
 }
 
 int32_t q4t_ep_flat_rows(const int32_t* expert_ids, int32_t rows, int32_t E, int32_t* row_of_flat, void* stream) {

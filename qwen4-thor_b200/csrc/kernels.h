@@ -99,6 +99,16 @@ cudaError_t launch_gather_codes_rowsf(const uint8_t* xq_packed, const uint8_t* x
                                       uint8_t* sf_tiles, int R, int K, const int32_t* flat_of_row,
                                       const int32_t* row_tile, const int32_t* tile_row0, const int32_t* rows_dev,
                                       int k, cudaStream_t stream);
+// Collective-free exchange of ids and "done" marks between expert-parallel ranks: ids[p] /
+// flag[p] are rank p's gathered-id block for this rank and this rank's slot in rank p's flag row.
+struct EpPostTargets {
+  int32_t* ids[kMaxPeers];
+  uint32_t* flag[kMaxPeers];
+};
+// ids may be null (flag only).  Plain launches: they follow and precede other ranks' work.
+cudaError_t launch_ep_post(const int32_t* ids, int n_ids, const EpPostTargets& dst, int world, uint32_t epoch,
+                           cudaStream_t stream);
+cudaError_t launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* status, cudaStream_t stream);
 cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,
                            float inv_global, int N, int K, cudaStream_t stream);
 // ---- routing, permutation, combine (routing_kernels.cu)

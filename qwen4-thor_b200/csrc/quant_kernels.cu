@@ -294,6 +294,52 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
   dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+// Expert parallelism without collectives: CTA p copies this rank's id block into rank p's
+// gathered id buffer (plain stores, possibly over NVLink), makes every earlier write of this
+// GPU visible system-wide and then raises this rank's flag in rank p's flag row.  Launched
+// after the kernels whose output the flag announces (stream order plus the fence).
+__global__ void __launch_bounds__(1024) ep_post_kernel(const int32_t* __restrict__ ids, int n_ids,
+                                                       const __grid_constant__ EpPostTargets dst, uint32_t epoch) {
+  const int p = blockIdx.x;
+  if (ids != nullptr) {
+    int32_t* out = dst.ids[p];
+    const int n4 = n_ids >> 2;
+    const uint4* src4 = reinterpret_cast<const uint4*>(ids);
+    uint4* out4 = reinterpret_cast<uint4*>(out);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) out4[i] = src4[i];
+    for (int i = (n4 << 2) + threadIdx.x; i < n_ids; i += blockDim.x) out[i] = ids[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst.flag[p]), "r"(epoch) : "memory");
+  }
+}
+
+// Waits until every rank has raised its flag in this rank's flag row to `epoch` (or later).
+// Bounded: after about two seconds the lane gives up and raises *status.
+__global__ void __launch_bounds__(32) ep_wait_kernel(const uint32_t* flags, int world, uint32_t epoch,
+                                                     int32_t* status) {
+  const int lane = threadIdx.x;
+  if (lane < world) {
+    const uint32_t* f = flags + lane;
+    const long long start = clock64();
+    bool ok = false;
+    for (uint32_t i = 0;; ++i) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (static_cast<int32_t>(v - epoch) >= 0) {
+        ok = true;
+        break;
+      }
+      if ((i & 63u) == 63u && clock64() - start > (1ll << 32)) break;
+      __nanosleep(64);
+    }
+    if (!ok && status) atomicMax(status, 4);
+  }
+  __threadfence_system();
+}
+
 }  // namespace
 
 cudaError_t launch_quantize(const uint16_t* x, uint8_t* packed, uint8_t* sf, int M, int K,
@@ -353,6 +399,17 @@ cudaError_t launch_publish_selected(const uint16_t* x, const int32_t* ids, const
   if (k > 32) return cudaErrorInvalidValue;
   return launch_chained(publish_selected_kernel, dim3((M + 7) / 8), dim3(256), 0, stream, x, ids, dst, M, K, k, E, map,
                         self, owner, global_scale);
+}
+
+cudaError_t launch_ep_post(const int32_t* ids, int n_ids, const EpPostTargets& dst, int world, uint32_t epoch,
+                           cudaStream_t stream) {
+  ep_post_kernel<<<world, 1024, 0, stream>>>(ids, n_ids, dst, epoch);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_wait(const uint32_t* flags, int world, uint32_t epoch, int32_t* status, cudaStream_t stream) {
+  ep_wait_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, status);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* group_scale, uint16_t* out,

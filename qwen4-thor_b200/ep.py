@@ -226,8 +226,10 @@ class PeerBuffers:
         self.expert_owner = expert_owner    # keeps the device table alive
         if expert_owner is not None:
             self.table.expert_owner = expert_owner.data_ptr()
-        # gathered codes, gathered scale blocks (all ranks' tokens), landing rows (own tokens)
-        self.sizes = (world * T_local * (hs // 2), world * T_local * (hs // 16), T_local * k * hs * 2)
+        # gathered codes, gathered scale blocks (all ranks' tokens), landing rows (own tokens),
+        # and the sync buffer (flags + gathered ids) of the collective-free exchange
+        self.sizes = (world * T_local * (hs // 2), world * T_local * (hs // 16), T_local * k * hs * 2,
+                      self.lib.q4t_ep_sync_buffer_bytes(world, T_local, k))
         self.own = None
         self.opened = []
 
@@ -238,7 +240,7 @@ class PeerBuffers:
             p = C.c_void_p()
             self.q4t.check(self.lib.q4t_peer_buffer_alloc(nbytes, C.byref(p)))
             own.append(p.value)
-        self.own = own
+        self.own = own       # zero-filled by the library: the sync buffer's flags start at zero
         return self
 
     def handles(self):
@@ -255,7 +257,7 @@ class PeerBuffers:
         import ctypes as C
         for r in range(self.world):
             ptrs = []
-            for i in range(3):
+            for i in range(4):
                 if r == self.rank:
                     ptrs.append(self.own[i])
                 else:
@@ -263,19 +265,34 @@ class PeerBuffers:
                     self.q4t.check(self.lib.q4t_peer_buffer_open(all_handles[r][i], C.byref(p)))
                     self.opened.append(p.value)
                     ptrs.append(p.value)
-            self.table.xq_packed[r], self.table.xq_sf[r], self.table.dn_rows[r] = ptrs
+            self.table.xq_packed[r], self.table.xq_sf[r], self.table.dn_rows[r], self.table.sync[r] = ptrs
         return self
 
     def from_pointers(self, ptrs_by_rank):
+        """ptrs_by_rank[r] = (codes, scales, landing rows[, sync]) of rank r; without sync
+        buffers the driver uses the process group's collectives."""
         for r, ptrs in enumerate(ptrs_by_rank):
-            self.table.xq_packed[r], self.table.xq_sf[r], self.table.dn_rows[r] = ptrs
+            self.table.xq_packed[r], self.table.xq_sf[r], self.table.dn_rows[r] = ptrs[:3]
+            self.table.sync[r] = ptrs[3] if len(ptrs) > 3 else None
         self.own = list(ptrs_by_rank[self.rank])
         return self
+
+    @property
+    def has_sync(self):
+        return self.own is not None and len(self.own) > 3 and bool(self.table.sync[self.rank])
 
     def close(self):
         for p in self.opened:
             self.lib.q4t_peer_buffer_close(p)
         self.opened = []
+
+
+class _DeviceArray:
+    """A device buffer owned by someone else, described through the CUDA array interface so that
+    torch can view it without a copy."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = dict(shape=tuple(shape), typestr=typestr, data=(int(ptr), False), version=2)
 
 
 class PeerExpertParallelMoE:
@@ -289,7 +306,11 @@ class PeerExpertParallelMoE:
     0: a contiguous block) plus the replicated router and shared expert."""
 
     def __init__(self, q4t, layer_local, E_total, hs, k, world, rank, T_local, buffers: PeerBuffers,
-                 group=None, device="cuda"):
+                 group=None, device="cuda", exchange="auto"):
+        """exchange: "flags" = ids and the two orderings travel by kernels over peer memory
+        (q4t_ep_post_ids / q4t_ep_post_rows / q4t_ep_wait; needs the buffers' sync region),
+        "collectives" = all-gather of the ids + a one-word all-reduce on the process group,
+        "auto" = flags when the buffers have a sync region."""
         import ctypes as C
         import torch
         import torch.distributed as dist
@@ -313,6 +334,15 @@ class PeerExpertParallelMoE:
         self.finish_ws = torch.empty(self.finish_ws_bytes, dtype=torch.uint8, device=dev)
         self.profile = False
         self.phase_ms = {}
+        self.flags = buffers.has_sync if exchange == "auto" else exchange == "flags"
+        if self.flags and not buffers.has_sync:
+            raise q4t.Q4TError("the flag exchange needs sync buffers in the peer table")
+        self.epoch = 0
+        if self.flags:
+            # the gathered ids live in the sync buffer (peers store into it): a zero-copy view
+            self.ids_all = torch.as_tensor(_DeviceArray(buffers.own[3] + q4t.EP_SYNC_IDS_OFFSET,
+                                                        (world * T_local, k), "<i4"), device=dev)
+        self._p_ids_all = self.ids_all.data_ptr()
         # argument values that never change, converted once
         self._extra, self._table = C.byref(layer_local.extra), C.byref(buffers.table)
         self._scale = float(layer_local.routed.gu_input_scale_uniform)
@@ -339,7 +369,8 @@ class PeerExpertParallelMoE:
         return self.ids
 
     def experts(self, ids_all):
-        self.q4t.check(self.lib.q4t_moe_expert_peer(ids_all.data_ptr(), self.C.byref(self.buf.table),
+        ids_all = ids_all if isinstance(ids_all, int) else ids_all.data_ptr()
+        self.q4t.check(self.lib.q4t_moe_expert_peer(ids_all, self.C.byref(self.buf.table),
                                                     self.C.byref(self.L.routed), self.k, self.ws.data_ptr(),
                                                     self.ws_bytes, 0, self._s()))
 
@@ -374,23 +405,43 @@ class PeerExpertParallelMoE:
                                                self.finish_ws_bytes, self._s()))
         return y
 
+    def sync_status(self):
+        """Raises if a wait for another rank ran out (flag exchange only; synchronises first)."""
+        if self.flags:
+            self.torch.cuda.synchronize()
+            self.q4t.check(self.lib.q4t_ep_sync_status(self._table))
+
     def forward(self, x, y):
-        """One step: three library calls and two collectives (host time per step matters once
-        the per-rank GPU work drops to a few hundred microseconds)."""
+        """One step.  Flag exchange: seven library calls, no collective; otherwise three library
+        calls and two collectives (host time per step matters once the per-rank GPU work drops
+        to a few hundred microseconds)."""
         marks = []
         self._mark(marks, "start")
         self.route_publish(x)
         self._mark(marks, "publish")
-        if self.world > 1:
-            self.dist.all_gather_into_tensor(self.ids_all, self.ids, group=self.group)
+        if self.flags:
+            # ids to every rank's sync buffer + "published" flag; wait for all ranks' flags
+            self.epoch += 1
+            q, lib, st = self.q4t, self.lib, self._s()
+            q.check(lib.q4t_ep_post_ids(self._p_ids, self._table, self.k, self.epoch, st))
+            q.check(lib.q4t_ep_wait(self._table, 0, self.epoch, st))
+            self._mark(marks, "ids_all_gather")
+            self.experts(self._p_ids_all)
+            self._mark(marks, "experts_pull_push")
+            q.check(lib.q4t_ep_post_rows(self._table, self.epoch, st))
+            q.check(lib.q4t_ep_wait(self._table, 1, self.epoch, st))
+            self._mark(marks, "landed_barrier")
         else:
-            self.ids_all.copy_(self.ids)
-        self._mark(marks, "ids_all_gather")
-        self.experts(self.ids_all)
-        self._mark(marks, "experts_pull_push")
-        if self.world > 1:      # every rank's rows have landed once this returns on the stream
-            self.dist.all_reduce(self.sync_word, group=self.group)
-        self._mark(marks, "landed_barrier")
+            if self.world > 1:
+                self.dist.all_gather_into_tensor(self.ids_all, self.ids, group=self.group)
+            else:
+                self.ids_all.copy_(self.ids)
+            self._mark(marks, "ids_all_gather")
+            self.experts(self.ids_all)
+            self._mark(marks, "experts_pull_push")
+            if self.world > 1:      # every rank's rows have landed once this returns on the stream
+                self.dist.all_reduce(self.sync_word, group=self.group)
+            self._mark(marks, "landed_barrier")
         self.combine_landed(x, y)
         self._mark(marks, "combine")
         if self.profile:

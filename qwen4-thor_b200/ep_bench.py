@@ -120,6 +120,9 @@ def main_multi(args):
         buf = connect(ep.PeerBuffers(q4t, world, rank, T_loc, K_TOP, HS, expert_map=1, placement=placement,
                                      expert_owner=owner).allocate())
         drv = ep.PeerExpertParallelMoE(q4t, local_i, E, HS, K_TOP, world, rank, T_loc, buf)
+        # the same step with the ids and the two orderings on NCCL collectives, for comparison
+        drv_coll = None if args.quick else ep.PeerExpertParallelMoE(q4t, local_i, E, HS, K_TOP, world, rank, T_loc, buf,
+                                                                   exchange="collectives")
         if not args.quick and args.hot_experts > 0:
             # the benchmark configuration's own placement: contiguous blocks of 512/N experts
             buf_p = connect(ep.PeerBuffers(q4t, world, rank, T_loc, K_TOP, HS, expert_map=0).allocate())
@@ -157,6 +160,15 @@ def main_multi(args):
     t = torch.tensor([ms], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
+    coll = None
+    if peer_mode and drv_coll is not None:
+        ms_c = bench.time_steps(torch, lambda i: drv_coll.forward(xs[i % 2], y), max(3, min(args.steps, 10)), 3, barrier)
+        t = torch.tensor([ms_c], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        coll = dict(ms_per_step=float(t.item()), tokens_per_s=T_TOTAL / (float(t.item()) * 1e-3),
+                    exchange="ids by NCCL all-gather, 'rows landed' by a one-word NCCL all-reduce")
+    if peer_mode:
+        drv.sync_status()
     plain = None
     if drv_plain is not None:
         y_p = torch.empty_like(y)
@@ -287,7 +299,7 @@ def main_multi(args):
                                 exchange=("quantised tokens stored by the quantiser into the gathered buffers of the GPUs that "
                                           "serve one of their experts, bf16 result "
                                           "rows stored into the token owner's buffer by the down GEMM's epilogue (peer memory "
-                                          "over NVLink); NCCL only for the id all-gather and one barrier; "
+                                          "over NVLink); expert ids and the two orderings of a step by flag kernels over peer memory, no collective call; "
                                           "checked bit-identical to the row-exchange path") if peer_mode else
                                 "bf16 rows both ways, NCCL all_to_all_single, one host sync per step for the split sizes"),
                     clocks=clocks.summary(),
@@ -303,7 +315,7 @@ def main_multi(args):
                               imbalance=float(mx_rows.item()) / (T_TOTAL * K_TOP / world)),
                     phase_ms_rank0=phases, expert_stage_ms_by_rank=stage_all, single_gpu_same_workload=n1,
                     strong_scaling_efficiency=(n1["ms_per_step"] / (world * ms)) if n1 else None,
-                    plain_sharding=plain, equals_single_gpu_bits=equals_single,
+                    plain_sharding=plain, equals_single_gpu_bits=equals_single, collectives_exchange=coll,
                     note="N = 1 of this metric is `also.ep_prefill_T32768_single_gpu` of the single-GPU line "
                          "(whose headline metric is the decode-shaped layer, another workload)")
         sys.stdout.flush()

@@ -6,8 +6,12 @@
 //
 //   PeerExpertParallel     the default: tokens and result rows travel as stores into peer
 //                          memory issued by the quantiser and by the down GEMM's epilogue;
-//                          NCCL carries the expert ids (ncclAllGather) and one barrier
-//                          (ncclAllReduce of one word).  No host synchronisation per step.
+//                          the expert ids and the two orderings of a step ("published",
+//                          "rows landed") travel the same way, as flag kernels over peer
+//                          memory (q4t_ep_post_ids / q4t_ep_post_rows / q4t_ep_wait), or, with
+//                          use_collectives, as ncclAllGather + a one-word ncclAllReduce.  NCCL
+//                          is otherwise only used once, to exchange the buffer handles.  No host
+//                          synchronisation per step.
 //   RowExchangeExpertParallel  the plain form: bf16 rows both ways with grouped
 //                          ncclSend / ncclRecv (an all-to-all-v); one host synchronisation per
 //                          step for the split sizes.  Contiguous expert blocks.
@@ -61,21 +65,25 @@ class PeerExpertParallel {
   // both device int32 [experts].  Collective: every rank calls it.
   Status Init(ncclComm_t comm, cudaStream_t stream, const EpShape& shape, const q4t_routed_weights& local,
               const q4t_extra_weights& extra, int expert_map = 0, const int32_t* placement = nullptr,
-              const int32_t* expert_owner = nullptr) {
+              const int32_t* expert_owner = nullptr, bool use_collectives = false) {
     using namespace detail;
     Free();
     comm_ = comm;
+    collectives_ = use_collectives;
+    epoch_ = 0;
     s_ = shape;
     local_ = local;
     extra_ = extra;
     if (s_.world < 1 || s_.world > Q4T_EP_MAX_RANKS) return Status::Fail("world must be in [1, 8]");
     if (!(local.gu_input_scale_uniform > 0.0f)) return Status::Fail("the peer path needs one gate/up input scale");
     const size_t T = s_.tokens_per_rank, k = s_.k, hs = s_.hs, W = s_.world;
-    const size_t sizes[3] = {W * T * (hs / 2), W * T * (hs / 16), T * k * hs * 2};
-    for (int i = 0; i < 3; ++i) Q4T_EP_TRY(Abi(q4t_peer_buffer_alloc(sizes[i], &own_[i])));
-    // exchange the handles: 3 x 64 bytes per rank, all-gathered through a device staging buffer
-    std::vector<uint8_t> mine(3 * Q4T_PEER_HANDLE_BYTES), all(W * mine.size());
-    for (int i = 0; i < 3; ++i) Q4T_EP_TRY(Abi(q4t_peer_buffer_export(own_[i], mine.data() + i * Q4T_PEER_HANDLE_BYTES)));
+    const size_t sizes[kBuffers] = {W * T * (hs / 2), W * T * (hs / 16), T * k * hs * 2,
+                                    q4t_ep_sync_buffer_bytes(s_.world, s_.tokens_per_rank, s_.k)};
+    for (int i = 0; i < kBuffers; ++i) Q4T_EP_TRY(Abi(q4t_peer_buffer_alloc(sizes[i], &own_[i])));
+    // exchange the handles: 4 x 64 bytes per rank, all-gathered through a device staging buffer
+    std::vector<uint8_t> mine(kBuffers * Q4T_PEER_HANDLE_BYTES), all(W * mine.size());
+    for (int i = 0; i < kBuffers; ++i)
+      Q4T_EP_TRY(Abi(q4t_peer_buffer_export(own_[i], mine.data() + i * Q4T_PEER_HANDLE_BYTES)));
     uint8_t* d_h = nullptr;
     Q4T_EP_TRY(Cuda(cudaMalloc(reinterpret_cast<void**>(&d_h), all.size() + mine.size()), "cudaMalloc"));
     Q4T_EP_TRY(Cuda(cudaMemcpyAsync(d_h + all.size(), mine.data(), mine.size(), cudaMemcpyHostToDevice, stream), "copy"));
@@ -92,18 +100,19 @@ class PeerExpertParallel {
     table_.experts_total = placement ? s_.experts : 0;
     table_.expert_owner = expert_owner;
     for (int r = 0; r < s_.world; ++r) {
-      void* p[3];
-      for (int i = 0; i < 3; ++i) {
+      void* p[kBuffers];
+      for (int i = 0; i < kBuffers; ++i) {
         if (r == s_.rank) {
           p[i] = own_[i];
         } else {
-          Q4T_EP_TRY(Abi(q4t_peer_buffer_open(all.data() + (r * 3 + i) * Q4T_PEER_HANDLE_BYTES, &p[i])));
+          Q4T_EP_TRY(Abi(q4t_peer_buffer_open(all.data() + (r * kBuffers + i) * Q4T_PEER_HANDLE_BYTES, &p[i])));
           opened_.push_back(p[i]);
         }
       }
       table_.xq_packed[r] = static_cast<const uint8_t*>(p[0]);
       table_.xq_sf[r] = static_cast<const uint8_t*>(p[1]);
       table_.dn_rows[r] = static_cast<uint16_t*>(p[2]);
+      table_.sync[r] = static_cast<uint8_t*>(p[3]);
     }
     // per-step scratch
     ws_bytes_ = q4t_moe_expert_peer_workspace_bytes(s_.world * s_.tokens_per_rank, s_.k, s_.hs, s_.moe_is, local.E);
@@ -129,19 +138,33 @@ class PeerExpertParallel {
     const int T = s_.tokens_per_rank, k = s_.k;
     Q4T_EP_TRY(Abi(q4t_ep_route_publish(x, &extra_, &table_, k, local_.gu_input_scale_uniform, logits_, ids_, rw_, fin_,
                                         fin_bytes_, stream)));
-    // the ids of all ranks, in rank order; also orders "published" before "used"
-    Q4T_EP_TRY(Nccl(ncclAllGather(ids_, ids_all_, static_cast<size_t>(T) * k, ncclInt32, comm_, stream),
-                    "ncclAllGather(ids)"));
-    Q4T_EP_TRY(Abi(q4t_moe_expert_peer(ids_all_, &table_, &local_, k, ws_, ws_bytes_, 0, stream)));
-    // "all rows have landed": every rank's down GEMM precedes its contribution in stream order
-    Q4T_EP_TRY(Nccl(ncclAllReduce(sync_, sync_, 1, ncclInt32, ncclSum, comm_, stream), "ncclAllReduce(barrier)"));
+    if (collectives_) {
+      // the ids of all ranks, in rank order; also orders "published" before "used"
+      Q4T_EP_TRY(Nccl(ncclAllGather(ids_, ids_all_, static_cast<size_t>(T) * k, ncclInt32, comm_, stream),
+                      "ncclAllGather(ids)"));
+      Q4T_EP_TRY(Abi(q4t_moe_expert_peer(ids_all_, &table_, &local_, k, ws_, ws_bytes_, 0, stream)));
+      // "all rows have landed": every rank's down GEMM precedes its contribution in stream order
+      Q4T_EP_TRY(Nccl(ncclAllReduce(sync_, sync_, 1, ncclInt32, ncclSum, comm_, stream), "ncclAllReduce(barrier)"));
+    } else {
+      // the same two steps as kernels over peer memory: ids stored into every rank's sync
+      // buffer, flags raised and awaited on the device
+      ++epoch_;
+      Q4T_EP_TRY(Abi(q4t_ep_post_ids(ids_, &table_, k, epoch_, stream)));
+      Q4T_EP_TRY(Abi(q4t_ep_wait(&table_, 0, epoch_, stream)));
+      const int32_t* gathered = reinterpret_cast<const int32_t*>(static_cast<uint8_t*>(own_[3]) + Q4T_EP_SYNC_IDS_OFFSET);
+      Q4T_EP_TRY(Abi(q4t_moe_expert_peer(gathered, &table_, &local_, k, ws_, ws_bytes_, 0, stream)));
+      Q4T_EP_TRY(Abi(q4t_ep_post_rows(&table_, epoch_, stream)));
+      Q4T_EP_TRY(Abi(q4t_ep_wait(&table_, 1, epoch_, stream)));
+    }
     return Abi(q4t_ep_combine(x, static_cast<const uint16_t*>(own_[2]), ids_, rw_, &extra_, y, T, k, rof_, fin_,
                               fin_bytes_, stream));
   }
 
   // After synchronising the stream: did a bounded device-side wait run out?
   Status CheckStatus() const {
-    return detail::Abi(q4t_moe_workspace_status(ws_, s_.world * s_.tokens_per_rank, s_.k, s_.hs, s_.moe_is, local_.E));
+    Status s = detail::Abi(q4t_moe_workspace_status(ws_, s_.world * s_.tokens_per_rank, s_.k, s_.hs, s_.moe_is, local_.E));
+    if (!s.ok() || collectives_) return s;
+    return detail::Abi(q4t_ep_sync_status(&table_));   // a wait for another rank that ran out
   }
 
   void Free() {
@@ -166,7 +189,10 @@ class PeerExpertParallel {
   q4t_routed_weights local_{};
   q4t_extra_weights extra_{};
   q4t_ep_peer_table table_{};
-  void* own_[3] = {nullptr, nullptr, nullptr};
+  static constexpr int kBuffers = 4;   // gathered codes, gathered scales, landing rows, sync (flags + gathered ids)
+  void* own_[kBuffers] = {nullptr, nullptr, nullptr, nullptr};
+  bool collectives_ = false;
+  uint32_t epoch_ = 0;
   std::vector<void*> opened_;
   void* ws_ = nullptr;
   void* fin_ = nullptr;

@@ -172,10 +172,12 @@ int main(int argc, char** argv) {
   uint16_t* y;
   CHECK(cudaMalloc(reinterpret_cast<void**>(&y), size_t(T) * hs * 2) == cudaSuccess);
 
-  {  // peer memory + ncclAllGather / ncclAllReduce, two steps over the same buffers
+  for (int collectives = 0; collectives < 2; ++collectives) {
+    // peer memory; ids and orderings by flag kernels over peer memory (0) or by ncclAllGather /
+    // ncclAllReduce (1); several steps over the same buffers
     parallel::PeerExpertParallel drv;
-    CHECK_OK(drv.Init(comm, stream, shape, mine, L.extra, /*expert_map=*/0));
-    for (int step = 0; step < 2; ++step) {
+    CHECK_OK(drv.Init(comm, stream, shape, mine, L.extra, /*expert_map=*/0, nullptr, nullptr, collectives != 0));
+    for (int step = 0; step < 4; ++step) {
       cudaMemsetAsync(y, 0, size_t(T) * hs * 2, stream);
       CHECK_OK(drv.Step(x, y, stream));
       CHECK(cudaStreamSynchronize(stream) == cudaSuccess);

@@ -97,9 +97,11 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
     fwd.status()
     Tl, per = T // W, E // W
     sf_bytes = Tl * (hs // 16)
+    sync_bytes = q4t.load().q4t_ep_sync_buffer_bytes(W, Tl, k)
     pub = [(torch.empty((W * Tl, hs // 2), dtype=torch.uint8, device="cuda"),
             torch.zeros(W * sf_bytes, dtype=torch.uint8, device="cuda"),
-            torch.full((Tl * k, hs), -1, dtype=torch.int16, device="cuda")) for _ in range(W)]
+            torch.full((Tl * k, hs), -1, dtype=torch.int16, device="cuda"),
+            torch.zeros(sync_bytes, dtype=torch.uint8, device="cuda")) for _ in range(W)]
     ptrs = [tuple(t.data_ptr() for t in p) for p in pub]
     drv = []
     if expert_map == 2:   # placement table: 3 experts replicated everywhere, the rest by load
@@ -142,6 +144,55 @@ def test_peer_path_emulated_ranks_equal_forward(q4t, gpu_lib, W, expert_map):
     ys = [d.combine_landed(xr, torch.empty((Tl, hs), dtype=torch.bfloat16, device="cuda")) for d, xr in zip(drv, xs)]
     torch.cuda.synchronize()
     assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
+    # a third step without any collective: the ids travel into every rank's sync buffer and the
+    # two orderings are flags (every rank posts before any rank waits, so nothing waits here)
+    lib = q4t.load()
+    x3 = dev(synth.make_x(T, hs, seed=13)).view(torch.bfloat16)
+    fwd(x3, y_ref)
+    xs = [x3[r * Tl:(r + 1) * Tl].contiguous() for r in range(W)]
+    st = q4t.C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    tabs = [q4t.C.byref(d.buf.table) for d in drv]
+    for d, xr, tab in zip(drv, xs, tabs):
+        d.route_publish(xr)
+        q4t.check(lib.q4t_ep_post_ids(d.ids.data_ptr(), tab, k, 7, st))
+    for d, tab, p in zip(drv, tabs, pub):
+        q4t.check(lib.q4t_ep_wait(tab, 0, 7, st))
+        d.experts(p[3].data_ptr() + q4t.EP_SYNC_IDS_OFFSET)
+        q4t.check(lib.q4t_ep_post_rows(tab, 7, st))
+    ys = []
+    for d, xr, tab in zip(drv, xs, tabs):
+        q4t.check(lib.q4t_ep_wait(tab, 1, 7, st))
+        ys.append(d.combine_landed(xr, torch.empty((Tl, hs), dtype=torch.bfloat16, device="cuda")))
+    torch.cuda.synchronize()
+    for tab in tabs:
+        q4t.check(lib.q4t_ep_sync_status(tab))
+    assert torch.equal(torch.cat(ys).view(torch.int16), y_ref.view(torch.int16))
+    gathered = pub[0][3][q4t.EP_SYNC_IDS_OFFSET:q4t.EP_SYNC_IDS_OFFSET + T * k * 4].view(torch.int32)
+    assert torch.equal(gathered, torch.cat([d.ids.flatten() for d in drv]))
+
+
+def test_wait_for_a_rank_that_never_posts_gives_up(q4t, gpu_lib):
+    """A rank that never posts (it died between steps) must not hang the others: the wait is
+    bounded (about two seconds), raises the sync buffer's status word and returns; the context
+    stays usable.  The failure is made on the host side: nothing ever raises the flag."""
+    ep = importlib.import_module("qwen4-thor_b200.ep")
+    W, Tl, k, hs = 2, 8, 2, 256
+    lib = q4t.load()
+    pub = [(torch.empty((W * Tl, hs // 2), dtype=torch.uint8, device="cuda"),
+            torch.zeros(W * Tl * (hs // 16), dtype=torch.uint8, device="cuda"),
+            torch.zeros((Tl * k, hs), dtype=torch.int16, device="cuda"),
+            torch.zeros(lib.q4t_ep_sync_buffer_bytes(W, Tl, k), dtype=torch.uint8, device="cuda")) for _ in range(W)]
+    buf = ep.PeerBuffers(q4t, W, 0, Tl, k, hs, expert_map=0).from_pointers([tuple(t.data_ptr() for t in p) for p in pub])
+    tab = q4t.C.byref(buf.table)
+    st = q4t.C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ids = torch.zeros((Tl, k), dtype=torch.int32, device="cuda")
+    q4t.check(lib.q4t_ep_post_ids(ids.data_ptr(), tab, k, 1, st))      # rank 0 posts, rank 1 never does
+    q4t.check(lib.q4t_ep_wait(tab, 0, 1, st))
+    torch.cuda.synchronize()
+    assert lib.q4t_ep_sync_status(tab) != 0
+    assert b"ran out" in lib.q4t_last_error()
+    # the device is still usable
+    assert int((torch.arange(10, device="cuda") * 2).sum().item()) == 90
 
 
 def test_peer_path_forward_one_rank(q4t, gpu_lib):
@@ -153,9 +204,11 @@ def test_peer_path_forward_one_rank(q4t, gpu_lib):
     full = q4t.DeviceLayer.from_host(L)
     pub = (torch.empty((T, hs // 2), dtype=torch.uint8, device="cuda"),
            torch.zeros(T * (hs // 16), dtype=torch.uint8, device="cuda"),
-           torch.full((T * k, hs), -1, dtype=torch.int16, device="cuda"))
+           torch.full((T * k, hs), -1, dtype=torch.int16, device="cuda"),
+           torch.zeros(q4t.load().q4t_ep_sync_buffer_bytes(1, T, k), dtype=torch.uint8, device="cuda"))
     buf = ep.PeerBuffers(q4t, 1, 0, T, k, hs, expert_map=0).from_pointers([tuple(t.data_ptr() for t in pub)])
     drv = ep.PeerExpertParallelMoE(q4t, full, E, hs, k, 1, 0, T, buf)
+    assert drv.flags       # ids and orderings through the sync buffer, no collective
     fwd = q4t.MoEForward(full, T, k)
     for seed in (21, 22):
         x = dev(synth.make_x(T, hs, seed=seed)).view(torch.bfloat16)
