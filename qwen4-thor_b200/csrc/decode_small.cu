@@ -229,16 +229,10 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 tc_cp_sf(tsf + kk * 4u, sfw + kk * 32u);
                 tc_cp_sf(tso + kk * 4u, sfo + kk * (kOpSfStride >> 4));
               }
-#ifdef Q4T_EXP_ACC   // timing experiment only (wrong results): four independent accumulators
-#pragma unroll
-              for (uint32_t kk = 0; kk < 4; ++kk)
-                tc_mma_nvf4(tmem + kk * 16u, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u, first);
-#else
 #pragma unroll
               for (uint32_t kk = 0; kk < 4; ++kk)
                 tc_mma_nvf4(tmem, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u,
                             kk == 0 ? first : 1u);
-#endif
             } else {
               const uint32_t nm = k_left >> 5;
               for (uint32_t kk = 0; kk < nm; ++kk) {
