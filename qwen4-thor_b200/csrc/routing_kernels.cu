@@ -767,6 +767,19 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
     s_row[threadIdx.x] = row_of_flat[t * k + threadIdx.x];
     s_w[threadIdx.x] = rw[t * k + threadIdx.x];
   }
+  __syncthreads();
+  // The rows of this thread's first column chunk are requested before the gate's dot product
+  // and reduction, so that the two memory round trips of the kernel overlap.
+  const int n8 = hs >> 3;
+  [[maybe_unused]] uint4 v[16];
+  if constexpr (PRELOAD) {
+    if (static_cast<int>(threadIdx.x) < n8) {
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        if (s < k && s_row[s] >= 0)
+          v[s] = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(s_row[s]) * hs) + threadIdx.x);
+    }
+  }
   float acc = 0.0f;
   for (int c = threadIdx.x; c < hs; c += 256)
     acc = fmaf(bf16_to_f32(x[static_cast<size_t>(t) * hs + c]), bf16_to_f32(gate_scalar[c]), acc);
@@ -777,16 +790,17 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
     __syncthreads();
   }
   const float gate = __frcp_rn(1.0f + __expf(-part[0]));
-  for (int c8 = threadIdx.x; c8 < (hs >> 3); c8 += 256) {
+  for (int c8 = threadIdx.x; c8 < n8; c8 += 256) {
     float a[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = 0.0f;
     if constexpr (PRELOAD) {
-      uint4 v[16];
+      if (c8 != static_cast<int>(threadIdx.x)) {   // later chunks of wide rows (hs > 2048)
 #pragma unroll
-      for (int s = 0; s < 16; ++s)
-        if (s < k && s_row[s] >= 0)
-          v[s] = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(s_row[s]) * hs) + c8);
+        for (int s = 0; s < 16; ++s)
+          if (s < k && s_row[s] >= 0)
+            v[s] = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(s_row[s]) * hs) + c8);
+      }
 #pragma unroll
       for (int s = 0; s < 16; ++s) {
         if (s < k && s_row[s] >= 0) {
@@ -804,8 +818,8 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
         const int r = s_row[s];
         if (r < 0) continue;
         const float wgt = s_w[s];
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(r) * hs) + c8);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const uint4 rv = __ldg(reinterpret_cast<const uint4*>(dn_out + static_cast<size_t>(r) * hs) + c8);
+        const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           a[2 * j] = fmaf(wgt, bf16x2_lo(w[j]), a[2 * j]);
