@@ -43,6 +43,8 @@ HS, E, K_TOP, MOE_IS, SHARED_IS = 2048, 512, 10, 512, 512
 EXPERT_BYTES = 1_048_576 + 131_072 + 524_288 + 65_536 + 16      # codes + scales + 4 scalars
 LAYER_FIXED_BYTES = 2_097_152 + 6_295_552                         # router + bf16 shared expert
 GU_EXPERT_BYTES = 1_048_576 + 131_072                             # gate/up codes + scales
+# 2*128*256*64 flops per 129 clocks per SM (measured), 148 SMs, 1965 MHz
+NVFP4_MMA_ISSUE_PEAK_TFLOPS = 2 * 128 * 256 * 64 / 129 * 148 * 1.965e9 / 1e12
 
 
 def load_peaks():
@@ -551,6 +553,10 @@ def main_single(args):
                                 peak=4 * peaks["bf16_tflops"], peak_source="4 x measured dense bf16 (no NVFP4 peak is measured by the driver)",
                                 frac=pf["routed_tflops"] / (4 * peaks["bf16_tflops"]),
                                 frac_of_9pf_nominal=pf["routed_tflops"] / 9000.0,
+                                # issue rate of the instruction itself, from a microbenchmark on this pool's B200s:
+                                # one tcgen05.mma kind::mxf4nvf4 128x256x64 per 129 clocks per SM
+                                nvfp4_mma_issue_peak_tflops=NVFP4_MMA_ISSUE_PEAK_TFLOPS,
+                                frac_of_mma_issue_peak=pf["routed_tflops"] / NVFP4_MMA_ISSUE_PEAK_TFLOPS,
                                 own_dense_nvfp4_gemm_tflops=dense.get("tflops"),
                                 frac_of_own_dense_nvfp4_gemm=(pf["routed_tflops"] / dense["tflops"]) if dense.get("tflops") else None,
                                 ms_per_step=pf["ms_per_step"], stage_ms=pf["stage_ms"])
