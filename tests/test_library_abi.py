@@ -124,3 +124,19 @@ def test_argument_errors_before_device_work(lib, q4t):
     assert lib.q4t_router_topk(dummy, dummy, dummy, 4, 512, 17, None) != 0
     assert lib.q4t_last_error() == b"k out of range"
     assert lib.q4t_quantize_activation_fp4(dummy, dummy, dummy, 4, 40, 1.0, None) != 0
+
+
+def test_ep_sync_entry_points_check_arguments(lib, q4t):
+    """The collective-free exchange of the expert-parallel step: sizing and the argument checks
+    that precede any device work."""
+    assert lib.q4t_ep_sync_buffer_bytes(8, 4096, 10) == 256 + 8 * 4096 * 10 * 4
+    assert lib.q4t_ep_sync_buffer_bytes(9, 4096, 10) == 0 and lib.q4t_ep_sync_buffer_bytes(2, 0, 10) == 0
+    table = q4t.EpPeerTable()
+    table.world, table.rank, table.tokens_per_rank = 2, 0, 8
+    assert lib.q4t_ep_wait(C.byref(table), 0, 1, None) != 0
+    assert lib.q4t_last_error() == b"peer table has no sync buffers"
+    assert lib.q4t_ep_post_rows(C.byref(table), 1, None) != 0
+    assert lib.q4t_ep_post_ids(None, C.byref(table), 2, 1, None) != 0
+    table.world = 9
+    assert lib.q4t_ep_sync_status(C.byref(table)) != 0
+    assert b"invalid peer table" in lib.q4t_last_error()
