@@ -1,6 +1,6 @@
 """Regenerates tests/golden/golden.npz by compiling gen_golden.cpp against the
 reference tree's headers and running it.  Needs the reference checkout
-(default /root/reference, or $Q4T_REFERENCE); the committed golden.npz is what
+(a `reference` directory beside this repository, or $Q4T_REFERENCE); the committed golden.npz is what
 the tests read, so this only has to run where the reference is available.
 
     python tests/golden/make_golden.py
@@ -13,7 +13,7 @@ import tempfile
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("Q4T_REFERENCE", "/root/reference")
+REF = os.environ.get("Q4T_REFERENCE", os.path.abspath(os.path.join(HERE, "..", "..", "..", "reference")))
 
 
 def main() -> int:
