@@ -351,6 +351,10 @@ int run_routed_small(const DeviceState* ds, const uint16_t* x, const int32_t* id
   g.status = P.at<int32_t>(L.status);
   g.stages = q4t::small_batch_stages(hs, R * g.n_tiles);
   g.tmem_cols = small_tmem_cols(g.stages);
+  {
+    static const int rel = [] { const char* v = std::getenv("Q4T_SMALL_RELEASE"); return v ? std::atoi(v) : 1; }();
+    g.release_next = rel;
+  }
 #ifdef Q4T_TRACE
   if (const char* t = std::getenv("Q4T_TRACE_PTR")) g.trace = reinterpret_cast<long long*>(std::strtoull(t, nullptr, 0));
   if (const char* t = std::getenv("Q4T_TRACE_ENTRY")) g.trace_entry = std::atoi(t);

@@ -113,7 +113,12 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   // The gate/up kernel follows the kernel that selected the experts; the down kernel reads the
   // same ids, which were complete before the gate/up kernel started, and waits later, just
   // before it touches the gate|up rows.
-  if (MODE == 0) chain_wait();
+  if (MODE == 0) {
+    chain_wait();
+    // the down kernel may start now: it fetches its weight tiles (which depend only on the
+    // ids) into shared memory while this kernel runs, and waits before it reads our rows
+    if (args.release_next) chain_release_next();
+  }
   if (threadIdx.x == 0) Q4T_SSTAMP(2);
 
   // Every warp reads the whole id table once (at most 256 entries, eight per lane, the loads

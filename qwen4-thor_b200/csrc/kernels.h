@@ -206,6 +206,7 @@ struct SmallBatchArgs {
   int32_t* status;
   int stages;                // TMA ring depth (small_batch_stages)
   uint32_t tmem_cols;        // tensor-memory columns: 32 (accumulator) + 32 per stage, rounded up to a power of two
+  int release_next;          // gate/up only: let the down kernel become resident while this one runs
   long long* trace;          // time stamps of one CTA (only read by builds with Q4T_TRACE; null otherwise)
   int trace_entry;
 };

@@ -143,12 +143,17 @@ __device__ __host__ __forceinline__ size_t sf_offset(uint32_t row, uint32_t grou
 // resident as soon as the blocks of the kernel before it in the stream have exited, before
 // that kernel's memory is flushed and its completion is processed; it must execute
 // chain_wait() before its first access to global memory (the wait returns once the earlier
-// kernel has completed and its writes are visible).  No kernel here signals its dependents
-// early: with griddepcontrol.launch_dependents issued BEFORE the kernel's own wait, a chain
-// of three kernels produced wrong results on B200 (the third no longer waited for the first),
-// and issuing it after the wait measured no faster than not issuing it at all.
+// kernel has completed and its writes are visible).  With griddepcontrol.launch_dependents
+// issued BEFORE the kernel's own wait, a chain of three kernels produced wrong results on B200
+// (the third no longer waited for the first); issued after the wait it is correct, and it only
+// pays where the next kernel has work to do before its own wait (chain_release_next below).
 // A no-op in a kernel launched the ordinary way.
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel of the chain become resident now instead of when this kernel's blocks
+// have exited.  Only ever issued AFTER this kernel's own chain_wait() (see above), and only by
+// a kernel whose successor has useful work to do before its own wait (prefetching operands
+// that do not depend on this kernel).
+__device__ __forceinline__ void chain_release_next() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
