@@ -326,7 +326,9 @@ def main_multi(args):
                     clocks=clocks.summary(),
                     e2e=dict(value=T_TOTAL / (ms_e * 1e-3), unit="tokens/s", h2d_bytes_per_step=T_TOTAL * HS * 2,
                              d2h_bytes_per_step=T_TOTAL * HS * 2),
-                    gpu_launches=(14 if peer_mode else 19) * args.steps * world,
+                    # peer path: router logits, top-k, selective publish, [ids + flag, wait], id localise, 3 planning
+                    # kernels, code gather, 2 expert GEMMs, [flag, wait], flat rows, combine, 2 shared-expert GEMMs
+                    gpu_launches=((19 if drv.flags else 15) if peer_mode else 19) * args.steps * world,
                     roofline=dict(bound="nvlink", achieved=float(mx_bytes.item()) / (ms * 1e-3) / 1e9, peak=770.0,
                                   unit="GB/s", frac=target / (ms * 1e-3), traffic=None,
                                   note="frac = max(link time at 770 GB/s per direction, routed flops at 4x measured bf16) / step time; "
