@@ -355,11 +355,7 @@ int run_routed_small(const DeviceState* ds, const uint16_t* x, const int32_t* id
     static const int rel = [] { const char* v = std::getenv("Q4T_SMALL_RELEASE"); return v ? std::atoi(v) : 1; }();
     g.release_next = rel;
   }
-#ifdef Q4T_TRACE
-  if (const char* t = std::getenv("Q4T_TRACE_PTR")) g.trace = reinterpret_cast<long long*>(std::strtoull(t, nullptr, 0));
-  if (const char* t = std::getenv("Q4T_TRACE_ENTRY")) g.trace_entry = std::atoi(t);
-#endif
-  cudaError_t e = q4t::launch_small_batch(0, tm, g, st);
+  cudaError_t e = q4t::launch_small_batch(0, tm, g, ds->num_sms, st);
   if (e != cudaSuccess) return fail_cuda("decode gate/up launch", e);
   stage_end(4, st);
   if ((rc = make_tmap(ds, &tm, false, w->dn_packed, is / 2, static_cast<uint64_t>(E) * hs, is / 2)) != Q4T_OK) return rc;
@@ -384,9 +380,7 @@ int run_routed_small(const DeviceState* ds, const uint16_t* x, const int32_t* id
   d.status = P.at<int32_t>(L.status);
   d.stages = q4t::small_batch_stages(is, R * d.n_tiles);
   d.tmem_cols = small_tmem_cols(d.stages);
-  d.trace = g.trace;
-  d.trace_entry = g.trace_entry;
-  if ((e = q4t::launch_small_batch(1, tm, d, st)) != cudaSuccess) return fail_cuda("decode down launch", e);
+  if ((e = q4t::launch_small_batch(1, tm, d, ds->num_sms, st)) != cudaSuccess) return fail_cuda("decode down launch", e);
   stage_end(5, st);
   return Q4T_OK;
 }

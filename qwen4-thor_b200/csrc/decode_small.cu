@@ -12,9 +12,13 @@
 // against up to 16 token rows (the N side), so an expert gives 2*is/128 gate/up tiles and hs/128
 // down tiles, and each CTA streams 128 x K/2 bytes of codes through a ring of TMA stages.
 //
-// One CTA per ((token,slot) entry f, weight tile).  The CTA of the first entry that names an
-// expert serves every later entry of that expert too (up to 16 per pass); CTAs of later entries
-// leave at once.  The token-side operand never exists in global memory: four warps build it in
+// The work is the list of (serving entry, weight tile) pairs, where an entry "serves" when it is
+// the first (token,slot) entry that names its expert; it then covers every later entry of that
+// expert too (16 per pass).  Every CTA derives the same list from the id table (at most 256
+// entries) and takes one contiguous share of it, so that its consecutive tiles mostly belong to
+// one expert and reuse the token-side operand; with few tiles that is one tile per CTA, with many
+// the CTAs are persistent and the weight ring keeps streaming across tiles while the previous
+// tile's rows are stored.  The token-side operand never exists in global memory: four warps build it in
 // shared memory, in the 128-byte-swizzled K-major layout and the scale-atom layout that TMA
 // would have produced --
 //   gate/up: the bf16 token rows quantised with the expert's input scale (the arithmetic of
@@ -46,27 +50,18 @@ constexpr int kSmallMaxStages = 10;
 struct SmallBars {
   uint64_t full[kSmallMaxStages];
   uint64_t empty[kSmallMaxStages];
-  uint64_t operand_ready;   // 128 worker arrivals per pass
-  uint64_t acc_full;
+  uint64_t operand_ready;   // 128 worker arrivals per operand build
+  uint64_t acc_full[2];     // one per accumulator buffer
+  uint64_t acc_empty[2];    // 4 worker warps per drain
   uint32_t tmem_base;
   uint32_t abort_flag;
-  int members[kSmallMaxEntries];
+  int n_serving;
+  int32_t ids[kSmallMaxEntries];
+  uint8_t first[kSmallMaxEntries];     // entry i is the first that names its expert
+  uint16_t count[kSmallMaxEntries];    // entries from i on with the same expert
+  int16_t serving[kSmallMaxEntries];   // the serving entries, ascending
+  int members[kSmallMaxEntries];       // entries of the expert being served, ascending
 };
-
-#ifdef Q4T_TRACE
-// Debug builds: nanosecond stamps of one CTA per launch, [mode][slot].
-__device__ __forceinline__ long long global_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define Q4T_SSTAMP(slot)                                                                          \
-  do {                                                                                            \
-    if (args.trace && blockIdx.x == gridDim.x - 1 && blockIdx.y == args.trace_entry) args.trace[MODE * 32 + (slot)] = global_ns(); \
-  } while (0)
-#else
-#define Q4T_SSTAMP(slot) do {} while (0)
-#endif
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kWorkers) : "memory"); }
@@ -80,8 +75,6 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* const smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nt = blockIdx.x, f = blockIdx.y;
-  if (threadIdx.x == 0) Q4T_SSTAMP(0);
   const int stages = args.stages;
   const uint32_t k_bytes = static_cast<uint32_t>(args.K) >> 1;
   const int nkb = static_cast<int>((k_bytes + 127u) >> 7);
@@ -96,7 +89,10 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       mbar_init(smem_u32(&bars.empty[s]), 1);
     }
     mbar_init(smem_u32(&bars.operand_ready), kWorkers);
-    mbar_init(smem_u32(&bars.acc_full), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bars.acc_full[b]), 1);
+      mbar_init(smem_u32(&bars.acc_empty[b]), kWorkers / 32);
+    }
     bars.abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_w);
@@ -109,7 +105,6 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars.tmem_base;
-  if (threadIdx.x == 0) Q4T_SSTAMP(1);
   // The gate/up kernel follows the kernel that selected the experts; the down kernel reads the
   // same ids, which were complete before the gate/up kernel started, and waits later, just
   // before it touches the gate|up rows.
@@ -119,51 +114,63 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // ids) into shared memory while this kernel runs, and waits before it reads our rows
     if (args.release_next) chain_release_next();
   }
-  if (threadIdx.x == 0) Q4T_SSTAMP(2);
 
-  // Every warp reads the whole id table once (at most 256 entries, eight per lane, the loads
-  // all in flight together) and derives from it whether an earlier entry already serves this
-  // expert and how many entries from f on belong to it.
-  const int e = args.ids[f];
-  int idv[kSmallMaxEntries / 32];
-#pragma unroll
-  for (int c = 0; c < kSmallMaxEntries / 32; ++c) {
-    const int i = c * 32 + lane;
-    idv[c] = i < args.R ? args.ids[i] : -1;
+  // ---- the work list, the same in every CTA: which entries serve, how many entries each covers
+  const int R = args.R;
+  for (int i = threadIdx.x; i < R; i += kSmallThreads) bars.ids[i] = args.ids[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < R; i += kSmallThreads) {
+    const int e = bars.ids[i];
+    const bool in_range = e >= 0 && e < args.E;
+    bool first = in_range;
+    int cnt = 0;
+    for (int j = 0; j < R; ++j) {
+      const bool same = bars.ids[j] == e;
+      if (same && j < i) first = false;
+      cnt += (same && j >= i) ? 1 : 0;
+    }
+    bars.first[i] = first ? 1 : 0;
+    bars.count[i] = static_cast<uint16_t>(cnt);
+    if (MODE == 0 && blockIdx.x == 0) args.row_of_flat[i] = in_range ? i : -1;
   }
-  bool serve = e >= 0 && e < args.E;
-  if (MODE == 0 && nt == 0 && threadIdx.x == 0) {
-    args.row_of_flat[f] = serve ? f : -1;
-    // the first CTA also clears the status word (it starts long before any bounded wait of
-    // this launch could run out)
-    if (f == 0 && args.status) *args.status = 0;
+  // the first CTA also clears the status word (it starts long before any bounded wait of this
+  // launch could run out)
+  if (MODE == 0 && blockIdx.x == 0 && threadIdx.x == 0 && args.status) *args.status = 0;
+  __syncthreads();
+  if (warp == 0) {
+    int n = 0;
+    for (int b = 0; b < R; b += 32) {
+      const int i = b + lane;
+      const bool f = i < R && bars.first[i] != 0;
+      const uint32_t m = __ballot_sync(0xffffffffu, f);
+      if (f) bars.serving[n + __popc(m & ((1u << lane) - 1u))] = static_cast<int16_t>(i);
+      n += __popc(m);
+    }
+    if (lane == 0) bars.n_serving = n;
   }
-  int n_members = 0;
-  uint32_t earlier = 0;
-#pragma unroll
-  for (int c = 0; c < kSmallMaxEntries / 32; ++c) {
-    const uint32_t m = __ballot_sync(0xffffffffu, idv[c] == e);
-    const int lo = c * 32;
-    const uint32_t below = f >= lo + 32 ? 0xffffffffu : (f <= lo ? 0u : (1u << (f - lo)) - 1u);   // entries before f
-    earlier |= m & below;
-    const uint32_t mine = m & ~below;
-    if (warp == 2 && ((mine >> lane) & 1u) && serve) bars.members[n_members + __popc(mine & ((1u << lane) - 1u))] = lo + lane;
-    n_members += __popc(mine);
+  __syncthreads();
+  // this CTA's share of the (serving entry, weight tile) pairs: contiguous, sizes differ by at most one
+  const int total = bars.n_serving * args.n_tiles;
+  const int ctas = min(static_cast<int>(gridDim.x), total);
+  int t_begin = 0, t_end = 0;
+  if (static_cast<int>(blockIdx.x) < ctas) {
+    const int base = total / ctas, rem = total - base * ctas, c = blockIdx.x;
+    t_begin = c * base + min(c, rem);
+    t_end = t_begin + base + (c < rem ? 1 : 0);
   }
-  if (earlier) serve = false;
-  const int passes = (n_members + kSmallN - 1) / kSmallN;
-  if (threadIdx.x == 0) Q4T_SSTAMP(3);
 
-  if (serve) {
-    const int w_row0 = e * args.w_rows_per_expert + nt * 128;
-    const uint8_t* w_sf = args.w_sf + static_cast<size_t>(e) * args.w_sf_stride + static_cast<size_t>(nt) * ntk * 512u;
-
-    if (warp == 0) {
-      // ---------------------------------------------------------- weight tiles by TMA
-      if (lane == 0) {
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
+  if (warp == 0) {
+    // ---------------------------------------------------------- weight tiles by TMA
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = t_begin; t < t_end && ok; ++t) {
+        const int u = t / args.n_tiles, nt = t - u * args.n_tiles;
+        const int f = bars.serving[u], e = bars.ids[f];
+        const int passes = (bars.count[f] + kSmallN - 1) / kSmallN;
+        const int w_row0 = e * args.w_rows_per_expert + nt * 128;
+        const uint8_t* w_sf = args.w_sf + static_cast<size_t>(e) * args.w_sf_stride + static_cast<size_t>(nt) * ntk * 512u;
         for (int p = 0; p < passes && ok; ++p) {
           uint32_t k_left = k_bytes;
           const uint8_t* sf = w_sf;
@@ -180,36 +187,50 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
             bulk_load(sa + kWTileBytes, sf, nm * 512u, full);
             sf += 2048;
             k_left -= 128u;
-            if (p == 0 && (kb == 0 || kb == nkb - 1)) Q4T_SSTAMP(kb == 0 ? 4 : 11);
             if (++stage == stages) {
               stage = 0;
               phase ^= 1u;
             }
           }
         }
-        if (!ok && args.status) atomicMax(args.status, 1);
       }
-      if (MODE == 1) chain_wait();
-    } else if (warp == 1) {
-      // ---------------------------------------------------------- MMA issuer
-      if (MODE == 1) chain_wait();
-      if (lane == 0) {
-        // M = 128 weight rows, N = 16 token rows, both operands K-major e2m1, ue4m3 scales
-        constexpr uint32_t idesc =
-            (1u << 7) | (1u << 10) | ((static_cast<uint32_t>(kSmallN) >> 3) << 17) | ((128u >> 4) << 24);
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        const uint64_t wdesc0 = umma_desc_sw128(smem_base), sfw0 = umma_desc_sf(smem_base + kWTileBytes);
-        const uint64_t odesc0 = umma_desc_sw128(op_base), sfo0 = umma_desc_sf(opsf_base);
-        const uint32_t bar_full0 = smem_u32(&bars.full[0]), bar_empty0 = smem_u32(&bars.empty[0]);
-        for (int p = 0; p < passes && ok; ++p) {
-          if (!mbar_wait(smem_u32(&bars.operand_ready), static_cast<uint32_t>(p) & 1u, abort_flag)) {
+      if (!ok && args.status) atomicMax(args.status, 1);
+    }
+    if (MODE == 1) chain_wait();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (MODE == 1) chain_wait();
+    if (lane == 0) {
+      // M = 128 weight rows, N = 16 token rows, both operands K-major e2m1, ue4m3 scales
+      constexpr uint32_t idesc =
+          (1u << 7) | (1u << 10) | ((static_cast<uint32_t>(kSmallN) >> 3) << 17) | ((128u >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint64_t wdesc0 = umma_desc_sw128(smem_base), sfw0 = umma_desc_sf(smem_base + kWTileBytes);
+      const uint64_t odesc0 = umma_desc_sw128(op_base), sfo0 = umma_desc_sf(opsf_base);
+      const uint32_t bar_full0 = smem_u32(&bars.full[0]), bar_empty0 = smem_u32(&bars.empty[0]);
+      uint32_t builds = 0, unit = 0;   // operand builds awaited so far; (tile, pass) units issued so far
+      int prev_u = -1;
+      for (int t = t_begin; t < t_end && ok; ++t) {
+        const int u = t / args.n_tiles;
+        const int passes = (bars.count[bars.serving[u]] + kSmallN - 1) / kSmallN;
+        for (int p = 0; p < passes && ok; ++p, ++unit) {
+          if (u != prev_u || passes > 1) {   // a new token-side operand
+            if (!mbar_wait(smem_u32(&bars.operand_ready), builds & 1u, abort_flag)) {
+              ok = false;
+              break;
+            }
+            ++builds;
+          }
+          prev_u = u;
+          const uint32_t ab = unit & 1u;
+          if (!mbar_wait(smem_u32(&bars.acc_empty[ab]), ((unit >> 1) & 1u) ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          if (p == 0) Q4T_SSTAMP(12);
+          const uint32_t acc = tmem + ab * 16u;
           uint32_t k_left = k_bytes;
           for (int kb = 0; kb < nkb; ++kb) {
             const uint32_t full = bar_full0 + static_cast<uint32_t>(stage) * 8u;
@@ -218,7 +239,6 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
               break;
             }
             tc_fence_after();
-            if (p == 0 && (kb == 0 || kb == nkb - 1)) Q4T_SSTAMP(kb == 0 ? 13 : 20);
             // descriptors differ from those of stage 0 / k-block 0 by constants in the 14-bit
             // start-address field (16-byte units), so plain 64-bit adds never carry out of it
             const uint64_t soff = static_cast<uint64_t>(stage) * (kSmallStage >> 4);
@@ -236,7 +256,7 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
               }
 #pragma unroll
               for (uint32_t kk = 0; kk < 4; ++kk)
-                tc_mma_nvf4(tmem, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u,
+                tc_mma_nvf4(acc, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u,
                             kk == 0 ? first : 1u);
             } else {
               const uint32_t nm = k_left >> 5;
@@ -245,7 +265,7 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                 tc_cp_sf(tso + kk * 4u, sfo + kk * (kOpSfStride >> 4));
               }
               for (uint32_t kk = 0; kk < nm; ++kk)
-                tc_mma_nvf4(tmem, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u,
+                tc_mma_nvf4(acc, wdesc + kk * 2u, odesc + kk * 2u, idesc, tsf + kk * 4u, tso + kk * 4u,
                             kk == 0 ? first : 1u);
             }
             tc_commit(bar_empty0 + static_cast<uint32_t>(stage) * 8u);
@@ -255,81 +275,110 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
               phase ^= 1u;
             }
           }
-          if (ok) tc_commit(smem_u32(&bars.acc_full));
+          if (ok) tc_commit(smem_u32(&bars.acc_full[ab]));
         }
-        if (!ok && args.status) atomicMax(args.status, 2);
       }
-    } else {
-      // ---------------------------------------------------------- operand builders / epilogue
-      if (MODE == 1) chain_wait();
-      worker_sync();  // the member list is in shared memory
-      if (threadIdx.x == 64) Q4T_SSTAMP(21);
-      const int w = static_cast<int>(threadIdx.x) - 64;
-      const int quad = warp & 3;
-      const int groups = args.K >> 4;
+      if (!ok && args.status) atomicMax(args.status, 2);
+    }
+  } else {
+    // ---------------------------------------------------------- operand builders / epilogue
+    if (MODE == 1) chain_wait();
+    const int w = static_cast<int>(threadIdx.x) - 64;
+    const int quad = warp & 3;
+    const int groups = args.K >> 4;
+    bool ok = true;
+    uint32_t unit = 0;
+    int prev_u = -1;
+    int n_members = 0;
+    for (int t = t_begin; t < t_end && ok; ++t) {
+      const int u = t / args.n_tiles, nt = t - u * args.n_tiles;
+      const int f = bars.serving[u], e = bars.ids[f];
+      const bool new_expert = u != prev_u;
+      if (new_expert) {
+        // entries of this expert from f on, ascending (the previous expert's member list is
+        // no longer needed: its rows were stored before this point)
+        worker_sync();
+        if (warp == 2) {
+          int n = 0;
+          for (int b = f & ~31; b < R; b += 32) {
+            const int i = b + lane;
+            const bool hit = i >= f && i < R && bars.ids[i] == e;
+            const uint32_t m = __ballot_sync(0xffffffffu, hit);
+            if (hit) bars.members[n + __popc(m & ((1u << lane) - 1u))] = i;
+            n += __popc(m);
+          }
+        }
+        worker_sync();
+        n_members = bars.count[f];
+      }
+      prev_u = u;
       const float in_scale = args.in_scale[e];
       const float alpha = args.alpha_w[e] * args.alpha_a[e];
       const int n_out = nt * 128 + quad * 32 + lane;   // the output column this thread's TMEM lane holds
-      bool ok = true;
-      int pass = 0;
-      for (int m0 = 0; m0 < n_members && ok; m0 += kSmallN, ++pass) {
+      const int passes = (n_members + kSmallN - 1) / kSmallN;
+      for (int p = 0; p < passes && ok; ++p, ++unit) {
+        const int m0 = p * kSmallN;
         const int rows = min(kSmallN, n_members - m0);
-        // ---- build the token-side operand of this pass
-        for (int item = w; item < rows * groups; item += kWorkers) {
-          const int j = item / groups, g = item - j * groups;
-          const int entry = bars.members[m0 + j];
-          float a[16];
-          if (MODE == 0) {
-            const uint4* src = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry / args.k) * args.src_ld + g * 16);
-            const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
-            const uint32_t wv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        if (new_expert || passes > 1) {
+          // ---- build the token-side operand (the MMAs that read the previous one have
+          // completed: their accumulators were awaited below before this point)
+          for (int item = w; item < rows * groups; item += kWorkers) {
+            const int j = item / groups, g = item - j * groups;
+            const int entry = bars.members[m0 + j];
+            float a[16];
+            if (MODE == 0) {
+              const uint4* src = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry / args.k) * args.src_ld + g * 16);
+              const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+              const uint32_t wv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              a[2 * i] = bf16x2_lo(wv[i]);
-              a[2 * i + 1] = bf16x2_hi(wv[i]);
-            }
-          } else {
-            // written by the previous kernel: plain loads, not the read-only path
-            const uint4* gsrc = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry) * args.src_ld + g * 16);
-            const uint4* usrc = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry) * args.src_ld + args.K + g * 16);
-            const uint4 g0 = gsrc[0], g1 = gsrc[1], u0 = usrc[0], u1 = usrc[1];
-            const uint32_t gb[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-            const uint32_t ub[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-            // (g * sigmoid(g)) * u on the bf16 projections, sigmoid through an IEEE reciprocal
-            // of 1 + __expf(-g): the general kernel's epilogue arithmetic
+              for (int i = 0; i < 8; ++i) {
+                a[2 * i] = bf16x2_lo(wv[i]);
+                a[2 * i + 1] = bf16x2_hi(wv[i]);
+              }
+            } else {
+              // written by the previous kernel: plain loads, not the read-only path
+              const uint4* gsrc = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry) * args.src_ld + g * 16);
+              const uint4* usrc = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry) * args.src_ld + args.K + g * 16);
+              const uint4 g0 = gsrc[0], g1 = gsrc[1], u0 = usrc[0], u1 = usrc[1];
+              const uint32_t gb[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+              const uint32_t ub[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+              // (g * sigmoid(g)) * u on the bf16 projections, sigmoid through an IEEE reciprocal
+              // of 1 + __expf(-g): the general kernel's epilogue arithmetic
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float gl = bf16x2_lo(gb[i]), gh = bf16x2_hi(gb[i]);
-              const float dl = 1.0f + __expf(-gl), dh = 1.0f + __expf(-gh);
-              const float sl = dl < Q4T_RCP_FAST_MAX ? rcp_rn_ge1(dl) : __frcp_rn(dl);
-              const float sh = dh < Q4T_RCP_FAST_MAX ? rcp_rn_ge1(dh) : __frcp_rn(dh);
-              a[2 * i] = (gl * sl) * bf16x2_lo(ub[i]);
-              a[2 * i + 1] = (gh * sh) * bf16x2_hi(ub[i]);
+              for (int i = 0; i < 8; ++i) {
+                const float gl = bf16x2_lo(gb[i]), gh = bf16x2_hi(gb[i]);
+                const float dl = 1.0f + __expf(-gl), dh = 1.0f + __expf(-gh);
+                const float sl = dl < Q4T_RCP_FAST_MAX ? rcp_rn_ge1(dl) : __frcp_rn(dl);
+                const float sh = dh < Q4T_RCP_FAST_MAX ? rcp_rn_ge1(dh) : __frcp_rn(dh);
+                a[2 * i] = (gl * sl) * bf16x2_lo(ub[i]);
+                a[2 * i + 1] = (gh * sh) * bf16x2_hi(ub[i]);
+              }
             }
+            uint32_t lo, hi;
+            const uint32_t sf = quantize_group16(a, in_scale, lo, hi);
+            const uint32_t kb = static_cast<uint32_t>(g) >> 4, gi = static_cast<uint32_t>(g) & 15u;
+            const uint32_t off = kb * kOpTileBytes + static_cast<uint32_t>(j) * 128u +
+                                 (((gi >> 1) ^ (static_cast<uint32_t>(j) & 7u)) << 4) + (gi & 1u) * 8u;
+            *reinterpret_cast<uint2*>(smem_gen + (op_base - smem_base) + off) = make_uint2(lo, hi);
+            smem_gen[(opsf_base - smem_base) + (static_cast<uint32_t>(g) >> 2) * kOpSfStride + static_cast<uint32_t>(j) * 16u +
+                     (static_cast<uint32_t>(g) & 3u)] = static_cast<uint8_t>(sf);
           }
-          uint32_t lo, hi;
-          const uint32_t sf = quantize_group16(a, in_scale, lo, hi);
-          const uint32_t kb = static_cast<uint32_t>(g) >> 4, gi = static_cast<uint32_t>(g) & 15u;
-          const uint32_t off = kb * kOpTileBytes + static_cast<uint32_t>(j) * 128u +
-                               (((gi >> 1) ^ (static_cast<uint32_t>(j) & 7u)) << 4) + (gi & 1u) * 8u;
-          *reinterpret_cast<uint2*>(smem_gen + (op_base - smem_base) + off) = make_uint2(lo, hi);
-          smem_gen[(opsf_base - smem_base) + (static_cast<uint32_t>(g) >> 2) * kOpSfStride + static_cast<uint32_t>(j) * 16u +
-                   (static_cast<uint32_t>(g) & 3u)] = static_cast<uint8_t>(sf);
+          fence_async_smem();   // the tensor core reads these bytes through the async proxy
+          mbar_arrive(smem_u32(&bars.operand_ready));
         }
-        fence_async_smem();   // the tensor core reads these bytes through the async proxy
-        mbar_arrive(smem_u32(&bars.operand_ready));
-        if (threadIdx.x == 64 && pass == 0) Q4T_SSTAMP(22);
-        // ---- epilogue of this pass
-        if (!mbar_wait(smem_u32(&bars.acc_full), static_cast<uint32_t>(pass) & 1u, abort_flag)) {
+        // ---- epilogue of this unit
+        const uint32_t ab = unit & 1u;
+        if (!mbar_wait(smem_u32(&bars.acc_full[ab]), (unit >> 1) & 1u, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (threadIdx.x == 64 && pass == 0) Q4T_SSTAMP(23);
         uint32_t v[16];
-        tmem_ld16(tmem + (static_cast<uint32_t>(quad * 32) << 16), v);
+        tmem_ld16(tmem + (static_cast<uint32_t>(quad * 32) << 16) + ab * 16u, v);
         tmem_ld_wait();
         tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars.acc_empty[ab]));
         if (n_out < args.w_rows_per_expert) {
 #pragma unroll
           for (int j = 0; j < kSmallN; ++j)
@@ -338,9 +387,8 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                   f32_to_bf16(alpha * __uint_as_float(v[j]));
         }
       }
-      if (threadIdx.x == 64) Q4T_SSTAMP(24);
-      if (!ok && args.status && lane == 0) atomicMax(args.status, 3);
     }
+    if (!ok && args.status && lane == 0) atomicMax(args.status, 3);
   }
 
   tc_fence_before();
@@ -349,7 +397,6 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     __syncwarp();
     tmem_dealloc(tmem, args.tmem_cols);
   }
-  if (threadIdx.x == 0) Q4T_SSTAMP(25);
 }
 
 size_t small_smem_bytes(int K, int stages) {
@@ -366,8 +413,9 @@ size_t small_smem_bytes(int K, int stages) {
 int small_batch_stages(int K, int tiles) {
   const int nkb = (K / 2 + 127) / 128;
   int stages = nkb < kSmallMaxStages ? nkb : kSmallMaxStages;
-  if (tiles > 2 * 148 && stages > 4) stages = 4;
-  if (tiles > 2 * 148)
+  constexpr int kDeepRingTiles = 148;  // one tile per SM of a B200
+  if (tiles > kDeepRingTiles && stages > 4) stages = 4;
+  if (tiles > kDeepRingTiles)
     while (stages > 2 && small_smem_bytes(K, stages) > 112 * 1024) --stages;
   while (stages > 2 && small_smem_bytes(K, stages) > 200 * 1024) --stages;
   return small_smem_bytes(K, stages) <= 200 * 1024 ? stages : 0;
@@ -380,10 +428,17 @@ cudaError_t small_batch_set_attributes() {
   return cudaFuncSetAttribute(small_batch_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
 }
 
-cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallBatchArgs& a, cudaStream_t stream) {
+cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallBatchArgs& a, int num_sms,
+                               cudaStream_t stream) {
   if (a.R <= 0 || a.R > kSmallMaxEntries || a.stages <= 0) return cudaErrorInvalidValue;
-  const dim3 grid(static_cast<unsigned>(a.n_tiles), static_cast<unsigned>(a.R));
   const size_t smem = small_smem_bytes(a.K, a.stages);
+  // as many CTAs as can be resident at once (shared memory, tensor-memory columns), but never
+  // more than there can be tiles; CTAs beyond the number of tiles that exist leave at once
+  int per_sm = static_cast<int>((227 * 1024) / (smem + 6 * 1024));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+  if (static_cast<int>(512u / a.tmem_cols) < per_sm) per_sm = static_cast<int>(512u / a.tmem_cols);
+  const int upper = a.R * a.n_tiles, resident = per_sm * num_sms;
+  const dim3 grid(static_cast<unsigned>(upper < resident ? upper : resident));
   if (mode == 0) return launch_chained(small_batch_kernel<0>, grid, dim3(kSmallThreads), smem, stream, tmap_w, a);
   return launch_chained(small_batch_kernel<1>, grid, dim3(kSmallThreads), smem, stream, tmap_w, a);
 }

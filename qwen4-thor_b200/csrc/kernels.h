@@ -207,15 +207,14 @@ struct SmallBatchArgs {
   int stages;                // TMA ring depth (small_batch_stages)
   uint32_t tmem_cols;        // tensor-memory columns: 32 (accumulator) + 32 per stage, rounded up to a power of two
   int release_next;          // gate/up only: let the down kernel become resident while this one runs
-  long long* trace;          // time stamps of one CTA (only read by builds with Q4T_TRACE; null otherwise)
-  int trace_entry;
 };
 // Ring depth for reduction length K and `tiles` CTAs, 0 when the token-side operand does not
 // fit shared memory.
 int small_batch_stages(int K, int tiles);
 cudaError_t small_batch_set_attributes();
 // mode 0 = gate/up, 1 = down.
-cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallBatchArgs& a, cudaStream_t stream);
+cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallBatchArgs& a, int num_sms,
+                               cudaStream_t stream);
 
 // ---- tensor-core GEMMs (tc_gemm.cu)
 enum class Epilogue : int {
