@@ -46,6 +46,7 @@ constexpr uint32_t kOpTileBytes = kSmallN * 128;  // 16 token rows x 128 bytes
 // bytes, and the other half (rows 16-31, never used with 16 token rows) overlaps the next atom.
 constexpr uint32_t kOpSfStride = 256;
 constexpr int kSmallMaxStages = 10;
+constexpr int kListTableExperts = 4096;           // expert ids the first-entry table (16 KB of the ring) can index
 
 struct SmallBars {
   uint64_t full[kSmallMaxStages];
@@ -58,7 +59,7 @@ struct SmallBars {
   int n_serving;
   int32_t ids[kSmallMaxEntries];
   uint8_t first[kSmallMaxEntries];     // entry i is the first that names its expert
-  uint16_t count[kSmallMaxEntries];    // entries from i on with the same expert
+  int count[kSmallMaxEntries];         // for a serving entry: the entries that name its expert
   int16_t serving[kSmallMaxEntries];   // the serving entries, ascending
   int members[kSmallMaxEntries];       // entries of the expert being served, ascending
 };
@@ -115,23 +116,48 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     if (args.release_next) chain_release_next();
   }
 
-  // ---- the work list, the same in every CTA: which entries serve, how many entries each covers
+  // ---- the work list, the same in every CTA: which entries serve, how many entries each covers.
+  // A table of the first entry per expert lives in the weight ring, which no copy has touched yet.
   const int R = args.R;
-  for (int i = threadIdx.x; i < R; i += kSmallThreads) bars.ids[i] = args.ids[i];
-  __syncthreads();
+  int32_t* const first_of = reinterpret_cast<int32_t*>(smem_gen);
+  const bool by_table = args.E <= kListTableExperts;
   for (int i = threadIdx.x; i < R; i += kSmallThreads) {
-    const int e = bars.ids[i];
-    const bool in_range = e >= 0 && e < args.E;
-    bool first = in_range;
-    int cnt = 0;
-    for (int j = 0; j < R; ++j) {
-      const bool same = bars.ids[j] == e;
-      if (same && j < i) first = false;
-      cnt += (same && j >= i) ? 1 : 0;
+    const int e = args.ids[i];
+    bars.ids[i] = e;
+    bars.count[i] = 0;
+    if (by_table && e >= 0 && e < args.E) first_of[e] = 0x7fffffff;
+  }
+  __syncthreads();
+  if (by_table) {
+    for (int i = threadIdx.x; i < R; i += kSmallThreads) {
+      const int e = bars.ids[i];
+      if (e >= 0 && e < args.E) atomicMin(&first_of[e], i);
     }
-    bars.first[i] = first ? 1 : 0;
-    bars.count[i] = static_cast<uint16_t>(cnt);
-    if (MODE == 0 && blockIdx.x == 0) args.row_of_flat[i] = in_range ? i : -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < R; i += kSmallThreads) {
+      const int e = bars.ids[i];
+      const bool in_range = e >= 0 && e < args.E;
+      const int f = in_range ? first_of[e] : -1;
+      bars.first[i] = f == i ? 1 : 0;
+      if (in_range) atomicAdd(&bars.count[f], 1);
+      if (MODE == 0 && blockIdx.x == 0) args.row_of_flat[i] = in_range ? i : -1;
+    }
+    fence_async_smem();   // the ring is written by TMA from here on
+  } else {
+    for (int i = threadIdx.x; i < R; i += kSmallThreads) {
+      const int e = bars.ids[i];
+      const bool in_range = e >= 0 && e < args.E;
+      bool first = in_range;
+      int cnt = 0;
+      for (int j = 0; j < R; ++j) {
+        const bool same = bars.ids[j] == e;
+        if (same && j < i) first = false;
+        cnt += (same && j >= i) ? 1 : 0;
+      }
+      bars.first[i] = first ? 1 : 0;
+      bars.count[i] = cnt;
+      if (MODE == 0 && blockIdx.x == 0) args.row_of_flat[i] = in_range ? i : -1;
+    }
   }
   // the first CTA also clears the status word (it starts long before any bounded wait of this
   // launch could run out)
@@ -282,7 +308,9 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     }
   } else {
     // ---------------------------------------------------------- operand builders / epilogue
-    if (MODE == 1) chain_wait();
+    // (the down kernel's member lists and scales depend only on the ids: it waits for the
+    // gate/up kernel just before the first load of a gate|up row)
+    bool waited = MODE == 0;
     const int w = static_cast<int>(threadIdx.x) - 64;
     const int quad = warp & 3;
     const int groups = args.K >> 4;
@@ -322,6 +350,10 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         if (new_expert || passes > 1) {
           // ---- build the token-side operand (the MMAs that read the previous one have
           // completed: their accumulators were awaited below before this point)
+          if (!waited) {
+            chain_wait();
+            waited = true;
+          }
           for (int item = w; item < rows * groups; item += kWorkers) {
             const int j = item / groups, g = item - j * groups;
             const int entry = bars.members[m0 + j];
