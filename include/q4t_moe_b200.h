@@ -188,13 +188,15 @@ int32_t q4t_moe_routed_workspace_layout(int32_t M, int32_t k, int32_t hs,
  * then (token,slot) ascending) and row_of_flat maps (token,slot) to its row.
  * Expert ids outside [0,E) are skipped.  flags: bit 0 = also materialise the
  * bf16 gate/up outputs in gu_out (parity/debug; slower).
- * Batches of at most 16 tokens (M <= 16, M*k <= 256) take a path of their own,
- * the counterpart of MoEDeviceDecode / MoEDeviceDecodeMulti
+ * Decode-sized batches (M <= 64 by default, M*k <= 2048, E <= 2048) take a
+ * path of their own, the counterpart of MoEDeviceDecode / MoEDeviceDecodeMulti
  * (include/q4t/quant/moe_decode.h:8-36): no permutation, rows kept in
  * (token,slot) order (row_of_flat is the identity, -1 for skipped entries;
  * gu_out always holds the bf16 gate|up rows; the grouped tables, a_packed and
  * the intermediate codes are not produced).  Same arithmetic, same bits in
- * dn_out rows and y.  flags bit 2 = take the general grouped path anyway.     */
+ * dn_out rows and y.  flags bit 2 = take the general grouped path anyway;
+ * flags bit 3 = take the decode-sized path up to its limit of 128 tokens
+ * (beyond 64 tokens the grouped path is as fast or faster).                   */
 int32_t q4t_moe_routed_forward(const uint16_t* x, const int32_t* expert_ids,
                                const float* router_w, float* y,
                                const q4t_routed_weights* weights,
@@ -269,7 +271,8 @@ int32_t q4t_moe_forward_workspace_layout(int32_t T, int32_t k, int32_t hs,
  * shared expert's), bit 1 = materialise the fp32 routed sum in the workspace's
  * `routed` region; both are what the reference always writes and only its
  * diagnostics read, so they are off unless asked for; bit 2 = no decode-sized
- * path for the routed experts (see q4t_moe_routed_forward).                   */
+ * path for the routed experts, bit 3 = that path up to 128 tokens (see
+ * q4t_moe_routed_forward).                                                    */
 int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
                         const q4t_extra_weights* extra, uint16_t* y, int32_t T,
                         int32_t k, void* workspace, size_t workspace_bytes,

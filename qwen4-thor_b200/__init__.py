@@ -91,7 +91,8 @@ CHECK_LIB_PATH = os.path.join(_HERE, "libq4t_moe_b200_check.so")
 # q4t_moe_forward / q4t_moe_routed_forward flags
 FLAG_DUMP_GATE_UP = 1      # materialise the bf16 gate|up projections
 FLAG_ROUTED_F32 = 2        # materialise the fp32 routed sum (q4t_moe_forward)
-FLAG_GENERAL_PATH = 4      # batches of at most 16 tokens: take the grouped path of larger batches anyway
+FLAG_GENERAL_PATH = 4      # decode-sized batches (at most 64 tokens): take the grouped path of larger batches anyway
+FLAG_DECODE_PATH = 8       # take the decode-sized path up to its limit of 128 tokens
 EP_MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
 EP_SYNC_IDS_OFFSET = 256

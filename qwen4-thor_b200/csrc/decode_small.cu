@@ -46,7 +46,9 @@ constexpr uint32_t kOpTileBytes = kSmallN * 128;  // 16 token rows x 128 bytes
 // bytes, and the other half (rows 16-31, never used with 16 token rows) overlaps the next atom.
 constexpr uint32_t kOpSfStride = 256;
 constexpr int kSmallMaxStages = 10;
-constexpr int kListTableExperts = 4096;           // expert ids the first-entry table (16 KB of the ring) can index
+constexpr int kSmallSharedStages = 5;             // ring depth when two CTAs share an SM ...
+constexpr size_t kSmallSharedBytes = 97 * 1024 + 512;   // ... and the dynamic shared memory each may then use, lists aside,
+constexpr size_t kSmallSharedMaxBytes = 112 * 1024;      // ... or at most
 
 struct SmallBars {
   uint64_t full[kSmallMaxStages];
@@ -57,11 +59,8 @@ struct SmallBars {
   uint32_t tmem_base;
   uint32_t abort_flag;
   int n_serving;
-  int32_t ids[kSmallMaxEntries];
-  uint8_t first[kSmallMaxEntries];     // entry i is the first that names its expert
-  int count[kSmallMaxEntries];         // for a serving entry: the entries that name its expert
-  int16_t serving[kSmallMaxEntries];   // the serving entries, ascending
-  int members[kSmallMaxEntries];       // entries of the expert being served, ascending
+  int n_found;                              // members collected for the expert being served
+  int scan[kSmallThreads / 32];             // per-warp totals of the compaction
 };
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -82,6 +81,12 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const uint32_t ntk = (static_cast<uint32_t>(args.K) + 63u) >> 6;
   const uint32_t op_base = smem_base + static_cast<uint32_t>(stages) * kSmallStage;   // token-side codes
   const uint32_t opsf_base = op_base + static_cast<uint32_t>(nkb) * kOpTileBytes;      // token-side scale atoms
+  // the lists, sized by the number of entries (behind the operand)
+  const int r_pad = (args.R + 7) & ~7;
+  int16_t* const l_ids = reinterpret_cast<int16_t*>(smem_gen + (opsf_base - smem_base) + ntk * kOpSfStride);   // expert of each entry, -1 = skipped
+  int16_t* const l_serving = l_ids + r_pad;      // the experts that have entries, by first entry
+  int16_t* const l_members = l_serving + r_pad;  // entries of the expert being served (any order)
+  uint8_t* const l_passes = reinterpret_cast<uint8_t*>(l_members + r_pad);   // ceil(entries / 16) of each serving expert
   volatile uint32_t* abort_flag = &bars.abort_flag;
 
   if (threadIdx.x == 0) {
@@ -102,6 +107,16 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     tmem_alloc(smem_u32(&bars.tmem_base), args.tmem_cols);
     tmem_relinquish();
   }
+  // Per-expert tables for the work list (entries of each expert, its first entry) live in the
+  // weight ring, which no copy has touched yet; they are cleared while the kernel still waits
+  // for its predecessor.
+  const int R = args.R, E = args.E;
+  int32_t* const count_of = reinterpret_cast<int32_t*>(smem_gen);
+  int32_t* const first_of = count_of + E;
+  for (int e = threadIdx.x; e < E; e += kSmallThreads) {
+    count_of[e] = 0;
+    first_of[e] = 0x7fffffff;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -116,63 +131,51 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     if (args.release_next) chain_release_next();
   }
 
-  // ---- the work list, the same in every CTA: which entries serve, how many entries each covers.
-  // A table of the first entry per expert lives in the weight ring, which no copy has touched yet.
-  const int R = args.R;
-  int32_t* const first_of = reinterpret_cast<int32_t*>(smem_gen);
-  const bool by_table = args.E <= kListTableExperts;
+  // ---- the work list, the same in every CTA: the experts that have entries, in the order of their first entry,
+  // with the number of 16-row passes each needs
   for (int i = threadIdx.x; i < R; i += kSmallThreads) {
     const int e = args.ids[i];
-    bars.ids[i] = e;
-    bars.count[i] = 0;
-    if (by_table && e >= 0 && e < args.E) first_of[e] = 0x7fffffff;
-  }
-  __syncthreads();
-  if (by_table) {
-    for (int i = threadIdx.x; i < R; i += kSmallThreads) {
-      const int e = bars.ids[i];
-      if (e >= 0 && e < args.E) atomicMin(&first_of[e], i);
+    const bool in_range = e >= 0 && e < E;
+    l_ids[i] = static_cast<int16_t>(in_range ? e : -1);
+    if (in_range) {
+      atomicAdd(&count_of[e], 1);
+      atomicMin(&first_of[e], i);
     }
-    __syncthreads();
-    for (int i = threadIdx.x; i < R; i += kSmallThreads) {
-      const int e = bars.ids[i];
-      const bool in_range = e >= 0 && e < args.E;
-      const int f = in_range ? first_of[e] : -1;
-      bars.first[i] = f == i ? 1 : 0;
-      if (in_range) atomicAdd(&bars.count[f], 1);
-      if (MODE == 0 && blockIdx.x == 0) args.row_of_flat[i] = in_range ? i : -1;
-    }
-    fence_async_smem();   // the ring is written by TMA from here on
-  } else {
-    for (int i = threadIdx.x; i < R; i += kSmallThreads) {
-      const int e = bars.ids[i];
-      const bool in_range = e >= 0 && e < args.E;
-      bool first = in_range;
-      int cnt = 0;
-      for (int j = 0; j < R; ++j) {
-        const bool same = bars.ids[j] == e;
-        if (same && j < i) first = false;
-        cnt += (same && j >= i) ? 1 : 0;
-      }
-      bars.first[i] = first ? 1 : 0;
-      bars.count[i] = cnt;
-      if (MODE == 0 && blockIdx.x == 0) args.row_of_flat[i] = in_range ? i : -1;
-    }
+    if (MODE == 0 && blockIdx.x == 0) args.row_of_flat[i] = in_range ? i : -1;
   }
   // the first CTA also clears the status word (it starts long before any bounded wait of this
   // launch could run out)
   if (MODE == 0 && blockIdx.x == 0 && threadIdx.x == 0 && args.status) *args.status = 0;
   __syncthreads();
-  if (warp == 0) {
-    int n = 0;
-    for (int b = 0; b < R; b += 32) {
-      const int i = b + lane;
-      const bool f = i < R && bars.first[i] != 0;
-      const uint32_t m = __ballot_sync(0xffffffffu, f);
-      if (f) bars.serving[n + __popc(m & ((1u << lane) - 1u))] = static_cast<int16_t>(i);
-      n += __popc(m);
+  {
+    // compaction in the order in which the experts first appear: thread t owns entries [t*c, (t+1)*c)
+    const int c = (R + kSmallThreads - 1) / kSmallThreads;
+    const int i0 = min(R, static_cast<int>(threadIdx.x) * c), i1 = min(R, i0 + c);
+    int mine = 0;
+    for (int i = i0; i < i1; ++i) {
+      const int e = l_ids[i];
+      mine += (e >= 0 && first_of[e] == i) ? 1 : 0;
     }
-    if (lane == 0) bars.n_serving = n;
+    int incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    if (lane == 31) bars.scan[warp] = incl;
+    __syncthreads();
+    int pos = incl - mine;
+    for (int wq = 0; wq < warp; ++wq) pos += bars.scan[wq];
+    for (int i = i0; i < i1; ++i) {
+      const int e = l_ids[i];
+      if (e >= 0 && first_of[e] == i) {
+        l_serving[pos] = static_cast<int16_t>(e);
+        l_passes[pos] = static_cast<uint8_t>((count_of[e] + kSmallN - 1) / kSmallN);
+        ++pos;
+      }
+    }
+    if (threadIdx.x == kSmallThreads - 1) bars.n_serving = pos;
+    fence_async_smem();   // the ring is written by TMA from here on
   }
   __syncthreads();
   // this CTA's share of the (serving entry, weight tile) pairs: contiguous, sizes differ by at most one
@@ -193,8 +196,8 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       bool ok = true;
       for (int t = t_begin; t < t_end && ok; ++t) {
         const int u = t / args.n_tiles, nt = t - u * args.n_tiles;
-        const int f = bars.serving[u], e = bars.ids[f];
-        const int passes = (bars.count[f] + kSmallN - 1) / kSmallN;
+        const int e = l_serving[u];
+        const int passes = l_passes[u];
         const int w_row0 = e * args.w_rows_per_expert + nt * 128;
         const uint8_t* w_sf = args.w_sf + static_cast<size_t>(e) * args.w_sf_stride + static_cast<size_t>(nt) * ntk * 512u;
         for (int p = 0; p < passes && ok; ++p) {
@@ -240,7 +243,7 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       int prev_u = -1;
       for (int t = t_begin; t < t_end && ok; ++t) {
         const int u = t / args.n_tiles;
-        const int passes = (bars.count[bars.serving[u]] + kSmallN - 1) / kSmallN;
+        const int passes = l_passes[u];
         for (int p = 0; p < passes && ok; ++p, ++unit) {
           if (u != prev_u || passes > 1) {   // a new token-side operand
             if (!mbar_wait(smem_u32(&bars.operand_ready), builds & 1u, abort_flag)) {
@@ -320,24 +323,19 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     int n_members = 0;
     for (int t = t_begin; t < t_end && ok; ++t) {
       const int u = t / args.n_tiles, nt = t - u * args.n_tiles;
-      const int f = bars.serving[u], e = bars.ids[f];
+      const int e = l_serving[u];
       const bool new_expert = u != prev_u;
       if (new_expert) {
-        // entries of this expert from f on, ascending (the previous expert's member list is
-        // no longer needed: its rows were stored before this point)
+        // the entries that name this expert, in whatever order the threads find them: an
+        // output row depends only on its own operand row, not on its position in the pass.
+        // (The previous expert's list is no longer needed: its rows were stored before this.)
         worker_sync();
-        if (warp == 2) {
-          int n = 0;
-          for (int b = f & ~31; b < R; b += 32) {
-            const int i = b + lane;
-            const bool hit = i >= f && i < R && bars.ids[i] == e;
-            const uint32_t m = __ballot_sync(0xffffffffu, hit);
-            if (hit) bars.members[n + __popc(m & ((1u << lane) - 1u))] = i;
-            n += __popc(m);
-          }
-        }
+        if (w == 0) bars.n_found = 0;
         worker_sync();
-        n_members = bars.count[f];
+        for (int i = w; i < R; i += kWorkers)
+          if (l_ids[i] == e) l_members[atomicAdd(&bars.n_found, 1)] = static_cast<int16_t>(i);
+        worker_sync();
+        n_members = bars.n_found;
       }
       prev_u = u;
       const float in_scale = args.in_scale[e];
@@ -356,7 +354,7 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           }
           for (int item = w; item < rows * groups; item += kWorkers) {
             const int j = item / groups, g = item - j * groups;
-            const int entry = bars.members[m0 + j];
+            const int entry = l_members[m0 + j];
             float a[16];
             if (MODE == 0) {
               const uint4* src = reinterpret_cast<const uint4*>(args.src + static_cast<size_t>(entry / args.k) * args.src_ld + g * 16);
@@ -415,7 +413,7 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
           for (int j = 0; j < kSmallN; ++j)
             if (j < rows)
-              args.out[static_cast<size_t>(bars.members[m0 + j]) * args.ldo + n_out] =
+              args.out[static_cast<size_t>(l_members[m0 + j]) * args.ldo + n_out] =
                   f32_to_bf16(alpha * __uint_as_float(v[j]));
         }
       }
@@ -431,26 +429,38 @@ small_batch_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   }
 }
 
-size_t small_smem_bytes(int K, int stages) {
+size_t small_list_bytes(int entries) { return static_cast<size_t>((entries + 7) & ~7) * 7; }
+
+size_t small_smem_bytes(int K, int stages, int entries) {
   const size_t nkb = (static_cast<size_t>(K) / 2 + 127) / 128, ntk = (static_cast<size_t>(K) + 63) / 64;
-  return 1024 + static_cast<size_t>(stages) * kSmallStage + nkb * kOpTileBytes + ntk * kOpSfStride + 256;
+  return 1024 + static_cast<size_t>(stages) * kSmallStage + nkb * kOpTileBytes + ntk * kOpSfStride +
+         small_list_bytes(entries) + 256;
 }
 
 }  // namespace
 
 // The ring holds a whole tile (every k-block in flight at once: with a handful of tiles the
 // kernel is one memory round trip long) when there are few enough tiles for one CTA per SM;
-// otherwise four stages, so that two CTAs share an SM and one streams while the other builds
-// its operand or stores its rows.
-int small_batch_stages(int K, int tiles) {
+// otherwise as many stages (at most a tile's worth) as leave room for two CTAs per SM, so that
+// one streams while the other builds its operand or stores its rows.  The down projection's
+// short tiles (two k-blocks at moe_is 512) give small CTAs, four to an SM, which measured
+// faster than fewer CTAs with deeper rings.
+int small_batch_stages(int K, int tiles, int entries) {
   const int nkb = (K / 2 + 127) / 128;
-  int stages = nkb < kSmallMaxStages ? nkb : kSmallMaxStages;
   constexpr int kDeepRingTiles = 148;  // one tile per SM of a B200
-  if (tiles > kDeepRingTiles && stages > 4) stages = 4;
-  if (tiles > kDeepRingTiles)
-    while (stages > 2 && small_smem_bytes(K, stages) > 112 * 1024) --stages;
-  while (stages > 2 && small_smem_bytes(K, stages) > 200 * 1024) --stages;
-  return small_smem_bytes(K, stages) <= 200 * 1024 ? stages : 0;
+  int stages;
+  if (tiles <= kDeepRingTiles) {
+    stages = nkb < kSmallMaxStages ? nkb : kSmallMaxStages;
+    while (stages > 2 && small_smem_bytes(K, stages, entries) > 200 * 1024) --stages;
+  } else {
+    // two CTAs per SM; with few entries they leave some shared memory to the kernels of the
+    // shared expert, which run beside this one
+    size_t budget = kSmallSharedBytes + small_list_bytes(entries);
+    if (budget > kSmallSharedMaxBytes) budget = kSmallSharedMaxBytes;
+    stages = nkb < kSmallSharedStages ? nkb : kSmallSharedStages;   // short reductions: more, smaller CTAs per SM
+    while (stages > 2 && small_smem_bytes(K, stages, entries) > budget) --stages;
+  }
+  return small_smem_bytes(K, stages, entries) <= 200 * 1024 ? stages : 0;
 }
 
 cudaError_t small_batch_set_attributes() {
@@ -462,12 +472,20 @@ cudaError_t small_batch_set_attributes() {
 
 cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallBatchArgs& a, int num_sms,
                                cudaStream_t stream) {
-  if (a.R <= 0 || a.R > kSmallMaxEntries || a.stages <= 0) return cudaErrorInvalidValue;
-  const size_t smem = small_smem_bytes(a.K, a.stages);
-  // as many CTAs as can be resident at once (shared memory, tensor-memory columns), but never
-  // more than there can be tiles; CTAs beyond the number of tiles that exist leave at once
-  int per_sm = static_cast<int>((227 * 1024) / (smem + 6 * 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+  if (a.R <= 0 || a.R > kSmallMaxEntries || a.E > kSmallMaxExperts || a.stages <= 0) return cudaErrorInvalidValue;
+  size_t smem = small_smem_bytes(a.K, a.stages, a.R);
+  // Never more CTAs on an SM than its 512 tensor-memory columns serve: one more would sit in
+  // its allocation until a whole neighbour had finished.  Shared memory is the resource that
+  // bounds residency, so each CTA asks for more than a (limit+1)-th of the SM's 228 KB.
+  const size_t tmem_limit = 512u / a.tmem_cols;
+  const size_t min_smem = ((228 * 1024) / (tmem_limit + 1) + 16) & ~static_cast<size_t>(15);
+  if (smem < min_smem) smem = min_smem;
+  // as many CTAs as can be resident at once (shared memory: 228 KB per SM, 1 KB of it reserved
+  // per CTA; tensor-memory columns), but never more than there can be tiles; CTAs beyond the
+  // number of tiles that exist leave at once
+  int per_sm = static_cast<int>((228 * 1024) / (smem + sizeof(SmallBars) + 64 + 1024));
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 4) per_sm = 4;
   if (static_cast<int>(512u / a.tmem_cols) < per_sm) per_sm = static_cast<int>(512u / a.tmem_cols);
   const int upper = a.R * a.n_tiles, resident = per_sm * num_sms;
   const dim3 grid(static_cast<unsigned>(upper < resident ? upper : resident));

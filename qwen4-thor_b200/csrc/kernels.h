@@ -185,8 +185,9 @@ cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_f
 
 // ---- routed experts for decode-sized batches (decode_small.cu)
 constexpr int kSmallN = 16;            // token rows per pass of one CTA (the N side of the MMA)
-constexpr int kSmallMaxTokens = 16;    // largest batch that takes this path
-constexpr int kSmallMaxEntries = 256;  // (token,slot) entries: 16 tokens x top-16
+constexpr int kSmallMaxTokens = 128;   // largest batch that may take this path
+constexpr int kSmallMaxEntries = 2048; // (token,slot) entries: 128 tokens x top-16
+constexpr int kSmallMaxExperts = 2048; // expert ids the per-expert tables (8 bytes each, inside one ring stage) can index
 struct SmallBatchArgs {
   const int32_t* ids;        // [R] expert (or slot) of each (token,slot) entry; outside [0,E) = skipped
   int R, k, E;
@@ -208,9 +209,9 @@ struct SmallBatchArgs {
   uint32_t tmem_cols;        // tensor-memory columns: 32 (accumulator) + 32 per stage, rounded up to a power of two
   int release_next;          // gate/up only: let the down kernel become resident while this one runs
 };
-// Ring depth for reduction length K and `tiles` CTAs, 0 when the token-side operand does not
-// fit shared memory.
-int small_batch_stages(int K, int tiles);
+// Ring depth for reduction length K, `tiles` weight tiles and `entries` (token,slot) entries,
+// 0 when the token-side operand does not fit shared memory.
+int small_batch_stages(int K, int tiles, int entries);
 cudaError_t small_batch_set_attributes();
 // mode 0 = gate/up, 1 = down.
 cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallBatchArgs& a, int num_sms,

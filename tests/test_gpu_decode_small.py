@@ -1,4 +1,4 @@
-"""The decode-sized path of the routed experts (at most 16 tokens; the counterpart of the
+"""The decode-sized path of the routed experts (at most 64 tokens by default, 128 on request; the counterpart of the
 reference's MoEDeviceDecode / MoEDeviceDecodeMulti, include/q4t/quant/moe_decode.h:8-36)
 against the general grouped path, bit for bit: the reference's own check of its grouped decode
 against its per-row decode asks for zero ulp (tests/moe_decode_grouped_test.cpp:328-411).  The
@@ -19,7 +19,7 @@ pytestmark = pytest.mark.gpu
 
 def _both_paths(q4t, dl, x, ids, rw, T, k):
     out = []
-    for flags in (q4t.FLAG_DUMP_GATE_UP | q4t.FLAG_GENERAL_PATH, 0):
+    for flags in (q4t.FLAG_DUMP_GATE_UP | q4t.FLAG_GENERAL_PATH, q4t.FLAG_DECODE_PATH):
         rf = q4t.RoutedForward(dl, T, k)
         rf.ws.fill_(0xEE)
         y = torch.zeros((T, dl.hs), dtype=torch.float32, device="cuda")
@@ -38,7 +38,10 @@ def _both_paths(q4t, dl, x, ids, rw, T, k):
     (16, 512, 256, 16, 4),                                 # few experts: up to 16 rows per expert
     (16, 256, 128, 16, 16),                                # 256 entries, 16 per expert
     (4, 256, 128, 16, 4),                                  # 16+ rows per expert: more than one pass per CTA
-    (64, 1024, 384, 3, 6), (32, 4096, 1024, 2, 8)])
+    (64, 1024, 384, 3, 6), (32, 4096, 1024, 2, 8),
+    (512, 2048, 512, 32, 10), (512, 2048, 512, 128, 10),   # larger batches: the lists hold up to 2048 entries
+    (16, 512, 256, 64, 4), (4, 256, 128, 100, 4),          # many rows per expert: several passes
+    (64, 512, 128, 128, 16)])                              # 2048 entries
 def test_decode_sized_path_equals_general_path(q4t, gpu_lib, E, hs, is_, T, k):
     if E >= 512:     # built on the device (seeded); the CPU oracle is left out at this size
         L = None
@@ -73,14 +76,15 @@ def test_decode_sized_path_equals_general_path(q4t, gpu_lib, E, hs, is_, T, k):
 
 
 def test_whole_layer_decode_sized_equals_general(q4t, gpu_lib):
-    """q4t_moe_forward at T = 1..16: same experts, same weights, same output bits on both paths."""
+    """q4t_moe_forward at T = 1..128: same experts, same weights, same output bits on both paths
+    (the decode-sized path by default up to 64 tokens, on request above)."""
     E, hs, is_, sis, k = 128, 1024, 256, 256, 8
     L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=77)
     dl = q4t.DeviceLayer.from_host(L)
-    for T in (1, 2, 7, 9, 16):
+    for T in (1, 2, 7, 9, 16, 33, 64, 128):
         x = dev(synth.make_x(T, hs, seed=T))
         ys = []
-        for flags in (q4t.FLAG_GENERAL_PATH, 0):
+        for flags in (q4t.FLAG_GENERAL_PATH, q4t.FLAG_DECODE_PATH if T > 64 else 0):
             fwd = q4t.MoEForward(dl, T, k)
             y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
             fwd(x, y, flags=flags)
