@@ -490,7 +490,10 @@ def main_single(args):
     if not args.quick:
         sweep = []
         for t in (1, 8, 16, 32, 64):
-            r = run_decode_point(torch, q4t, layers, t, max(args.steps, 20), args.warmup, with_stages=True)
+            # these steps are 35-150 us long: a timed region of 50 is over in a few milliseconds, so it is
+            # repeated (median reported) after a longer warm-up than the headline point needs
+            r = run_decode_point(torch, q4t, layers, t, max(args.steps, 20), max(args.warmup, 20), with_stages=True,
+                                 repeats=5)
             r["hbm_frac_of_measured"] = r["layer_gbs"] / peaks["hbm_gbs"]
             sweep.append(r)
         also["decode_sweep"] = sweep
