@@ -1,8 +1,8 @@
-// The routed experts for decode-sized batches (at most 16 tokens), the counterpart of the
-// reference's device-routed decode path (MoEDeviceDecode / MoEDeviceDecodeMulti,
-// include/q4t/quant/moe_decode.h:8-36, src/quant/moe_decode.cu:762-823): no permutation
-// step, no separate quantise step, and tiles shaped for streaming weights rather than for
-// arithmetic.
+// The routed experts for decode-sized batches (up to 128 tokens; the entry points send batches of
+// up to 64 here by default), the counterpart of the reference's device-routed decode path
+// (MoEDeviceDecode / MoEDeviceDecodeMulti, include/q4t/quant/moe_decode.h:8-36,
+// src/quant/moe_decode.cu:762-823): no permutation step, no separate quantise step, and tiles
+// shaped for streaming weights rather than for arithmetic.
 //
 // With a handful of tokens every selected expert has one or two rows, so the work is reading
 // each selected expert's weights once.  The general grouped GEMM puts the token rows on the
@@ -12,9 +12,9 @@
 // against up to 16 token rows (the N side), so an expert gives 2*is/128 gate/up tiles and hs/128
 // down tiles, and each CTA streams 128 x K/2 bytes of codes through a ring of TMA stages.
 //
-// The work is the list of (serving entry, weight tile) pairs, where an entry "serves" when it is
-// the first (token,slot) entry that names its expert; it then covers every later entry of that
-// expert too (16 per pass).  Every CTA derives the same list from the id table (at most 256
+// The work is the list of (expert, weight tile) pairs over the experts that have entries, in the
+// order of their first (token,slot) entry; an expert with more than 16 entries takes several
+// passes over its tiles.  Every CTA derives the same list from the id table (at most 2048
 // entries) and takes one contiguous share of it, so that its consecutive tiles mostly belong to
 // one expert and reuse the token-side operand; with few tiles that is one tile per CTA, with many
 // the CTAs are persistent and the weight ring keeps streaming across tiles while the previous

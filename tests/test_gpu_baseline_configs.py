@@ -53,11 +53,11 @@ def _check_rows(x_rows, ids, rw, L, got_y_rows, got_routed_rows=None):
     return err, routed
 
 
-@pytest.mark.parametrize("T,general", [(1, False), (1, True), (8, False), (8, True), (16, False), (32, True),
-                                       (64, True), (128, True)])
+@pytest.mark.parametrize("T,general", [(1, False), (1, True), (8, False), (8, True), (16, False), (32, False),
+                                       (32, True), (64, False), (64, True), (128, True)])
 def test_decode_points_vs_oracle(q4t, gpu_lib, uniform_layer, T, general):
     """The decode sweep of the benchmark: logits, selection, weights, routed sum and layer output.
-    Batches of at most 16 tokens run on their own path by default (rows in (token,slot) order)
+    Batches of at most 64 tokens run on their own path by default (rows in (token,slot) order)
     and once more on the grouped path of the larger batches."""
     dl, L = uniform_layer
     syn = importlib.import_module("qwen4-thor_b200.synthetic")
