@@ -92,3 +92,37 @@ def test_whole_layer_decode_sized_equals_general(q4t, gpu_lib):
             ys.append((host(y), host(fwd.region("expert_ids", torch.int32, T * k)), host(fwd.region("router_w", torch.float32, T * k))))
         assert np.array_equal(ys[0][1], ys[1][1]) and np.array_equal(ys[0][2], ys[1][2])
         assert np.array_equal(ys[0][0], ys[1][0]), f"T={T}"
+
+
+@pytest.mark.parametrize("T", [1, 8, 40])
+def test_decode_sized_layer_in_a_cuda_graph(q4t, gpu_lib, T):
+    """The layer on the decode-sized path (chained launches, the early release of the down kernel,
+    the side-stream shared expert) captured as one CUDA graph: every replay gives the eager bits."""
+    E, hs, is_, sis, k = 64, 1024, 256, 256, 6
+    L = synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=91)
+    dl = q4t.DeviceLayer.from_host(L)
+    xs = [dev(synth.make_x(T, hs, seed=T + i)) for i in range(3)]
+    fwd = q4t.MoEForward(dl, T, k)
+    x = torch.empty((T, hs), dtype=torch.int16, device="cuda")
+    y = torch.empty((T, hs), dtype=torch.bfloat16, device="cuda")
+    eager = []
+    for xi in xs:
+        x.copy_(xi.view(torch.int16).reshape(T, hs))
+        fwd(x, y)
+        fwd.status()
+        eager.append(host(y))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fwd(x, y)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            fwd(x, y)
+    torch.cuda.current_stream().wait_stream(side)
+    for rep in range(2):
+        for xi, want in zip(xs, eager):
+            x.copy_(xi.view(torch.int16).reshape(T, hs))
+            graph.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(host(y), want), f"T={T} replay {rep}"
+    fwd.status()
