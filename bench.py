@@ -10,7 +10,8 @@ forward; successive steps rotate over several independent layer weight sets
 and inputs so that no step finds its weights in L2.  The line also carries the
 sweep over T in {1, 8, 16, 32, 64}, the 16384-token Zipf-skewed prefill layer,
 the MTP draft layer's BF16-expert MoE and the 48-layer decode stack
-(x <- x + MoE(RMSNorm(x)), eager and as one CUDA graph) under "also".  "e2e" is the same step fed from pinned host memory with
+(x <- x + MoE(RMSNorm(x)), eager and as one CUDA graph, at T = 128 and at 1 and 8
+tokens) under "also".  "e2e" is the same step fed from pinned host memory with
 the result copied back, copies on their own streams.
 
 N > 1 (launched by torchrun, one rank per GPU): the expert-parallel prefill
@@ -546,6 +547,11 @@ def main_single(args):
         also["mtp_bf16_moe"] = run_mtp_bf16_point(torch, q4t)
     if not args.quick and args.stack_layers > 0:   # last: the graph capture attempt must not disturb the rest
         also["stack"] = run_stack_point(torch, q4t, syn, layers, args.stack_layers, T, 5, main["layer_bytes"])
+        # the same stack at decode-sized batches: eagerly these steps are close to what the host can
+        # launch (12 calls per layer), as one CUDA graph they show the device time per layer
+        by_t = {r["T"]: r for r in also.get("decode_sweep", [])}
+        also["stack_decode_sized"] = [run_stack_point(torch, q4t, syn, layers, args.stack_layers, t, 5,
+                                                      by_t[t]["layer_bytes"]) for t in (1, 8) if t in by_t]
 
     prefill_roofline = None
     if "prefill_T16384" in also:
