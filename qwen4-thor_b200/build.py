@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libq4t_moe_b200.so")
 CHECK_LIB = os.path.join(HERE, "libq4t_moe_b200_check.so")
-SOURCES = ["api.cu", "quant_kernels.cu", "routing_kernels.cu", "tc_gemm.cu", "tc_gemm_pair.cu", "decode_small.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "quant_kernels.cu", "routing_kernels.cu", "tc_gemm.cu", "tc_gemm_pair.cu", "decode_small.cu", "bf16_small_m.cu", "noalloc.cu"]
 CHECK_SOURCES = ["check/check_api.cu", "check/selftest.cu", "check/simt_check.cu"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

@@ -102,6 +102,7 @@ int device_state(const DeviceState** out) {
     if ((e = q4t::gemm_pair_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = q4t::routing_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     if ((e = q4t::small_batch_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
+    if ((e = q4t::bf16_small_m_set_attributes()) != cudaSuccess) return fail_cuda("cudaFuncSetAttribute", e);
     s.encode = reinterpret_cast<EncodeFn>(fn);
     s.num_sms = prop.multiProcessorCount;
     s.ready = true;
@@ -132,6 +133,41 @@ int make_tmap(const DeviceState* ds, CUtensorMap* tm, bool bf16, const void* bas
   CUresult r = ds->encode(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                           const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(Q4T_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+  return Q4T_OK;
+}
+
+// 3-D view of a K-major bf16 matrix, 64 elements x rows x K/64, whose box brings `depth`
+// consecutive k-blocks of `box_rows` rows with one load (bf16_small_m.cu); each k-block lands
+// 128-byte swizzled like a box of make_tmap.
+int make_tmap_kblocks(const DeviceState* ds, CUtensorMap* tm, const void* base, uint64_t K, uint64_t rows,
+                      uint32_t box_rows, uint32_t depth) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((K * 2) & 15u) || K % 64)
+    return fail(Q4T_ERR_INVALID, "operand base and row pitch must be 16-byte aligned");
+  cuuint64_t dims[3] = {64, rows, K / 64};
+  cuuint64_t strides[2] = {K * 2, 128};
+  cuuint32_t box[3] = {64, box_rows, depth};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = ds->encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(Q4T_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
+  return Q4T_OK;
+}
+
+// The same for a gate|up weight [2*N, K]: 64 elements x N rows x 2 halves x K/64, box 64 x 32 x 2 x depth,
+// so that every k-block lands as 32 gate rows followed by the 32 matching up rows.
+int make_tmap_kblocks_gate_up(const DeviceState* ds, CUtensorMap* tm, const void* base, uint64_t K, uint64_t N,
+                              uint32_t depth) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((K * 2) & 15u) || K % 64)
+    return fail(Q4T_ERR_INVALID, "operand base and row pitch must be 16-byte aligned");
+  cuuint64_t dims[4] = {64, N, 2, K / 64};
+  cuuint64_t strides[3] = {K * 2, N * K * 2, 128};
+  cuuint32_t box[4] = {64, 32, 2, depth};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = ds->encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(Q4T_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string(int(r)) + ")");
   return Q4T_OK;
@@ -600,6 +636,17 @@ int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w,
     return Q4T_OK;
   }
   if (K % 16 || N % 16) return fail(Q4T_ERR_INVALID, "K and N must be multiples of 16");
+  // one tile of token rows: a kernel that loads four k-blocks at a time (a handful of CTAs are
+  // bound by how fast one thread issues TMA loads, not by bandwidth)
+  static const bool no_small_m = std::getenv("Q4T_NO_SMALL_M_GEMM") != nullptr;
+  if (!no_small_m && q4t::bf16_small_m_fits(M, N, K)) {
+    CUtensorMap tx, tw;
+    int rc3;
+    if ((rc3 = make_tmap_kblocks(ds, &tx, x, K, M, q4t::bf16_small_m_box_rows(M), 4)) != Q4T_OK) return rc3;
+    if ((rc3 = make_tmap_kblocks(ds, &tw, w, K, N, 64, 4)) != Q4T_OK) return rc3;
+    if ((e = q4t::launch_bf16_small_m(tx, tw, y, M, N, K, st)) != cudaSuccess) return fail_cuda("bf16 small-M GEMM launch", e);
+    return Q4T_OK;
+  }
   // few wide tiles would leave most SMs idle: use 64-column tiles then
   const int m_tiles = (M + 127) / 128;
   const bool narrow = m_tiles * ((N + 255) / 256) < ds->num_sms / 2 && N % 64 == 0;
@@ -635,6 +682,13 @@ int run_shared_expert(const DeviceState* ds, const uint16_t* x, const q4t_extra_
   if (T <= 8) {
     if ((rc = run_bf16_linear(ds, x, extra->shared_gu, sgu, T, 2 * sis, hs, st)) != Q4T_OK) return rc;
     if ((e = q4t::launch_swiglu(sgu, sact, T, sis, st)) != cudaSuccess) return fail_cuda("swiglu launch", e);
+  } else if (std::getenv("Q4T_NO_SMALL_M_GEMM") == nullptr && q4t::bf16_small_m_swiglu_fits(T, sis, hs)) {
+    // one tile of token rows: the kernel that loads four k-blocks per TMA operation
+    CUtensorMap tx, tw;
+    if ((rc = make_tmap_kblocks(ds, &tx, x, hs, T, q4t::bf16_small_m_box_rows(T), 4)) != Q4T_OK) return rc;
+    if ((rc = make_tmap_kblocks_gate_up(ds, &tw, extra->shared_gu, hs, sis, 4)) != Q4T_OK) return rc;
+    if ((e = q4t::launch_bf16_small_m_swiglu(tx, tw, sact, T, sis, hs, (flags & 1u) ? sgu : nullptr, st)) != cudaSuccess)
+      return fail_cuda("shared gate/up launch", e);
   } else {
     const int m_tiles = (T + 127) / 128;
     const bool narrow = m_tiles * (sis / 128) < ds->num_sms / 2;
@@ -1618,6 +1672,7 @@ int32_t q4t_moe_workspace_status(const void* workspace, int32_t M, int32_t k, in
   cudaError_t e = cudaMemcpy(&word, static_cast<const uint8_t*>(workspace) + L.status, 4, cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return fail_cuda("status read", e);
   if (word != 0) return fail(Q4T_ERR_KERNEL, "a bounded device-side wait ran out (role " + std::to_string(word) + ")");
+  if (q4t::small_m_gemm_timed_out()) return fail(Q4T_ERR_KERNEL, "a bounded device-side wait ran out (bf16 linear)");
   return Q4T_OK;
 }
 

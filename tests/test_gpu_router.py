@@ -67,6 +67,22 @@ def test_tensor_core_linear(q4t, gpu_lib, M, N, K):
     assert (ulp > 0).mean() < 0.02
 
 
+@pytest.mark.parametrize("M,N,K", [(9, 512, 2048), (16, 512, 2048), (33, 512, 2048), (128, 512, 2048), (128, 2048, 512),
+                                   (100, 640, 2560), (17, 64, 64), (40, 128, 832)])
+def test_linear_of_one_row_tile_equals_the_general_kernel(q4t, gpu_lib, M, N, K):
+    """Batches of 9..128 rows run on the kernel that loads four k-blocks per TMA operation
+    (K = 832 and 2560/64 = 40 end in a short or exact group, K = 64 is a single k-block); the
+    same rows inside a 300-row batch run on the general GEMM kernel.  Same MMA sequence over K,
+    so the same bits: a token's logits do not depend on the size of the batch it arrives in."""
+    rng = np.random.default_rng(M + N + K)
+    x = O.f32_to_bf16(rng.standard_normal((300, K)).astype(np.float32))
+    w = O.f32_to_bf16((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    big = host(q4t.bf16_linear(dev(x), dev(w)))
+    small = host(q4t.bf16_linear(dev(np.ascontiguousarray(x[:M])), dev(w)))
+    assert small.shape == (M, N)
+    assert np.array_equal(small, big[:M])
+
+
 @pytest.mark.parametrize("T,k,E", [(1, 10, 512), (16, 10, 512), (700, 10, 512), (37, 4, 64)])
 def test_permutation_tables(q4t, gpu_lib, T, k, E):
     """Stable order (expert ascending, then (token,slot) ascending), read back
