@@ -159,10 +159,11 @@ int make_tmap_kblocks(const DeviceState* ds, CUtensorMap* tm, const void* base, 
 // The same for a gate|up weight [2*N, K]: 64 elements x N rows x 2 halves x K/64, box 64 x 32 x 2 x depth,
 // so that every k-block lands as 32 gate rows followed by the 32 matching up rows.
 int make_tmap_kblocks_gate_up(const DeviceState* ds, CUtensorMap* tm, const void* base, uint64_t K, uint64_t N,
-                              uint32_t depth) {
+                              uint32_t depth, uint64_t first_half_rows = 0) {
   if ((reinterpret_cast<uintptr_t>(base) & 15u) || ((K * 2) & 15u) || K % 64)
     return fail(Q4T_ERR_INVALID, "operand base and row pitch must be 16-byte aligned");
-  cuuint64_t dims[4] = {64, N, 2, K / 64};
+  // first_half_rows: rows a box may start at (a stack of [2*N, K] weights: all rows but the last N)
+  cuuint64_t dims[4] = {64, first_half_rows ? first_half_rows : N, 2, K / 64};
   cuuint64_t strides[3] = {K * 2, N * K * 2, 128};
   cuuint32_t box[4] = {64, 32, 2, depth};
   cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -573,6 +574,27 @@ int run_routed_core_bf16(const DeviceState* ds, const uint16_t* x, const int32_t
   uint16_t* inter = P.at<uint16_t>(L.gu_out);
   CUtensorMap tm_a, tm_b;
   int rc;
+  // draft-sized batches: every expert has at most M rows, so a tile is a handful of rows against
+  // 64 weight rows, loaded four k-blocks at a time (bf16_small_m.cu)
+  static const bool no_small_m = std::getenv("Q4T_NO_SMALL_M_GEMM") != nullptr;
+  if (!no_small_m && M <= 16 && hs % 64 == 0 && is % 64 == 0) {
+    const int box_rows = q4t::bf16_small_m_box_rows(M);
+    const int max_row_tiles = R < E ? R : E;
+    if ((rc = make_tmap_kblocks(ds, &tm_a, compact, hs, R, box_rows, 4)) != Q4T_OK) return rc;
+    if ((rc = make_tmap_kblocks_gate_up(ds, &tm_b, w->gu, hs, is, 4, static_cast<uint64_t>(E) * 2 * is - is)) != Q4T_OK)
+      return rc;
+    if ((e = q4t::launch_bf16_small_m_grouped(tm_a, tm_b, inter, true, box_rows, max_row_tiles, is, hs, pt.tile_expert,
+                                              pt.tile_row0, pt.tile_nrows, pt.ntiles, 2 * is, ds->num_sms, st)) != cudaSuccess)
+      return fail_cuda("bf16 gate/up launch", e);
+    stage_end(4, st);
+    if ((rc = make_tmap_kblocks(ds, &tm_a, inter, is, R, box_rows, 4)) != Q4T_OK) return rc;
+    if ((rc = make_tmap_kblocks(ds, &tm_b, w->down, is, static_cast<uint64_t>(E) * hs, 64, 4)) != Q4T_OK) return rc;
+    if ((e = q4t::launch_bf16_small_m_grouped(tm_a, tm_b, P.at<uint16_t>(L.dn_out), false, box_rows, max_row_tiles, hs, is,
+                                              pt.tile_expert, pt.tile_row0, pt.tile_nrows, pt.ntiles, hs, ds->num_sms, st)) != cudaSuccess)
+      return fail_cuda("bf16 down launch", e);
+    stage_end(5, st);
+    return Q4T_OK;
+  }
   if ((rc = make_tmap(ds, &tm_a, true, compact, hs, R, static_cast<uint64_t>(hs) * 2)) != Q4T_OK) return rc;
   if ((rc = make_tmap(ds, &tm_b, true, w->gu, hs, static_cast<uint64_t>(E) * 2 * is, static_cast<uint64_t>(hs) * 2)) !=
       Q4T_OK)
@@ -625,7 +647,7 @@ int run_routed_core_bf16(const DeviceState* ds, const uint16_t* x, const int32_t
 
 // y[M,N] = bf16(x . w^T): exact-order warp GEMV for M <= 8, tensor cores above.
 int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w, uint16_t* y, int M, int N,
-                    int K, cudaStream_t st) {
+                    int K, cudaStream_t st, bool beside_others = false) {
   cudaError_t e;
   // the exact-order GEMV keeps the M rows of x in shared memory (at most 96 KB); beyond
   // that, shapes the tensor-core kernel accepts fall through to it
@@ -644,7 +666,7 @@ int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w,
     int rc3;
     if ((rc3 = make_tmap_kblocks(ds, &tx, x, K, M, q4t::bf16_small_m_box_rows(M), 4)) != Q4T_OK) return rc3;
     if ((rc3 = make_tmap_kblocks(ds, &tw, w, K, N, 64, 4)) != Q4T_OK) return rc3;
-    if ((e = q4t::launch_bf16_small_m(tx, tw, y, M, N, K, st)) != cudaSuccess) return fail_cuda("bf16 small-M GEMM launch", e);
+    if ((e = q4t::launch_bf16_small_m(tx, tw, y, M, N, K, ds->num_sms, beside_others, st)) != cudaSuccess) return fail_cuda("bf16 small-M GEMM launch", e);
     return Q4T_OK;
   }
   // few wide tiles would leave most SMs idle: use 64-column tiles then
@@ -687,7 +709,7 @@ int run_shared_expert(const DeviceState* ds, const uint16_t* x, const q4t_extra_
     CUtensorMap tx, tw;
     if ((rc = make_tmap_kblocks(ds, &tx, x, hs, T, q4t::bf16_small_m_box_rows(T), 4)) != Q4T_OK) return rc;
     if ((rc = make_tmap_kblocks_gate_up(ds, &tw, extra->shared_gu, hs, sis, 4)) != Q4T_OK) return rc;
-    if ((e = q4t::launch_bf16_small_m_swiglu(tx, tw, sact, T, sis, hs, (flags & 1u) ? sgu : nullptr, st)) != cudaSuccess)
+    if ((e = q4t::launch_bf16_small_m_swiglu(tx, tw, sact, T, sis, hs, (flags & 1u) ? sgu : nullptr, ds->num_sms, st)) != cudaSuccess)
       return fail_cuda("shared gate/up launch", e);
   } else {
     const int m_tiles = (T + 127) / 128;
@@ -716,7 +738,7 @@ int run_shared_expert(const DeviceState* ds, const uint16_t* x, const q4t_extra_
                                           : q4t::launch_gemm_bf16(ta, tb, g, q4t::Epilogue::kSwigluBf16, ds->num_sms, st);
     if (e != cudaSuccess) return fail_cuda("shared gate/up GEMM launch", e);
   }
-  return run_bf16_linear(ds, sact, extra->shared_down, sdown, T, hs, sis, st);
+  return run_bf16_linear(ds, sact, extra->shared_down, sdown, T, hs, sis, st, true);
 }
 
 }  // namespace

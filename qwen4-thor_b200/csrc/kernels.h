@@ -220,17 +220,26 @@ cudaError_t launch_small_batch(int mode, const CUtensorMap& tmap_w, const SmallB
 // ---- bf16 linear for one tile of token rows (bf16_small_m.cu): M <= 128, N a multiple of 64, K a
 // multiple of 64.  tmap_x / tmap_w are 3-D maps (64 elements x rows x K/64) with boxes of
 // 64 x bf16_small_m_box_rows(M) x 4 and 64 x 64 x 4.
+// beside_others: the launch runs next to another stream's kernels (the shared expert beside the routed
+// experts): a shallow ring, so that it leaves them the SM's shared memory.
 cudaError_t bf16_small_m_set_attributes();
 bool bf16_small_m_fits(int M, int N, int K);
 int bf16_small_m_box_rows(int M);
 cudaError_t launch_bf16_small_m(const CUtensorMap& tmap_x, const CUtensorMap& tmap_w, uint16_t* y, int M, int N, int K,
-                                cudaStream_t stream);
+                                int num_sms, bool beside_others, cudaStream_t stream);
 // The shared expert's gate/up projection with SwiGLU: w has 2*N rows (gate rows, then up rows), tmap_w
 // is the 4-D map 64 elements x N rows x 2 halves x K/64 with a box of 64 x 32 x 2 x 4; act [M, N];
 // gu_dump (optional) receives the bf16 projections [M, 2*N].
 bool bf16_small_m_swiglu_fits(int M, int N, int K);
 cudaError_t launch_bf16_small_m_swiglu(const CUtensorMap& tmap_x, const CUtensorMap& tmap_w, uint16_t* act, int M, int N,
-                                       int K, uint16_t* gu_dump, cudaStream_t stream);
+                                       int K, uint16_t* gu_dump, int num_sms, cudaStream_t stream);
+// Grouped form: blockIdx.y runs over the row tiles of the permutation tables (the rows of one expert,
+// consecutive in x; at most max_row_tiles of them), the weights are [groups * w_rows_per_group, K];
+// x's box has box_rows rows (a tile with more rows takes several passes over its weights).
+cudaError_t launch_bf16_small_m_grouped(const CUtensorMap& tmap_x, const CUtensorMap& tmap_w, uint16_t* y, bool swiglu,
+                                        int box_rows, int max_row_tiles, int N, int K, const int32_t* tile_expert,
+                                        const int32_t* tile_row0, const int32_t* tile_nrows, const int32_t* ntiles,
+                                        int w_rows_per_group, int num_sms, cudaStream_t stream);
 bool small_m_gemm_timed_out();   // reads and clears the kernel's time-out flag
 
 // ---- tensor-core GEMMs (tc_gemm.cu)
