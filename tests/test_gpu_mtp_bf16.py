@@ -19,13 +19,17 @@ def _weights(E, hs, is_, seed):
     return gu, down
 
 
-@pytest.mark.parametrize("E,hs,is_,T,k", [(8, 256, 128, 5, 2), (16, 2560, 640, 40, 4), (32, 512, 256, 300, 6)])
+@pytest.mark.parametrize("E,hs,is_,T,k", [(8, 256, 128, 5, 2), (16, 2560, 640, 40, 4), (32, 512, 256, 300, 6),
+                                          (16, 2560, 640, 8, 4),      # the draft layer's shapes, draft-sized batch
+                                          (4, 512, 128, 12, 4)])      # one expert named three times per token
 def test_bf16_routed_vs_oracle(q4t, gpu_lib, E, hs, is_, T, k):
     gu, down = _weights(E, hs, is_, seed=E + T)
     x = synth.make_x(T, hs, seed=3)
     ids_h, rw_h = synth.random_routing(T, k, E, seed=5)
     if T > 10:
         ids_h[3, 0] = -1          # a skipped entry
+    if E == 4:
+        ids_h[:, 1:] = 0          # 36 rows for expert 0: more than the 16-row box of the draft-sized kernel (3 passes)
     moe = q4t.Bf16MoE(dev(gu).view(torch.bfloat16), dev(down).view(torch.bfloat16), None, T, k)
     y = torch.zeros((T, hs), dtype=torch.float32, device="cuda")
     moe.routed(dev(x), dev(ids_h), dev(rw_h), y)
