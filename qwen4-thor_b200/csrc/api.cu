@@ -556,6 +556,12 @@ int run_routed_core(const DeviceState* ds, const uint16_t* x, const int32_t* ids
 // 300-420): gather the token rows in expert order, gate/up GEMM with the SwiGLU epilogue
 // (bf16 projections, bf16((g*sigmoid(g))*u)), down GEMM to bf16 rows.  `compact` is the
 // [M*k, hs] bf16 row buffer; the intermediate reuses the gu_out region, the result dn_out.
+// Q4T_NO_SMALL_M_GEMM: the general GEMM kernel for every BF16 projection (A/B measurements).
+bool no_small_m_gemm() {
+  static const bool off = std::getenv("Q4T_NO_SMALL_M_GEMM") != nullptr;
+  return off;
+}
+
 int run_routed_core_bf16(const DeviceState* ds, const uint16_t* x, const int32_t* ids,
                          const q4t_bf16_expert_weights* w, const RoutedPtrs& P, uint16_t* compact, int M, int k,
                          cudaStream_t st, bool plan_done) {
@@ -576,8 +582,7 @@ int run_routed_core_bf16(const DeviceState* ds, const uint16_t* x, const int32_t
   int rc;
   // draft-sized batches: every expert has at most M rows, so a tile is a handful of rows against
   // 64 weight rows, loaded four k-blocks at a time (bf16_small_m.cu)
-  static const bool no_small_m = std::getenv("Q4T_NO_SMALL_M_GEMM") != nullptr;
-  if (!no_small_m && M <= 16 && hs % 64 == 0 && is % 64 == 0) {
+  if (!no_small_m_gemm() && M <= 16 && hs % 64 == 0 && is % 64 == 0) {
     const int box_rows = q4t::bf16_small_m_box_rows(M);
     const int max_row_tiles = R < E ? R : E;
     if ((rc = make_tmap_kblocks(ds, &tm_a, compact, hs, R, box_rows, 4)) != Q4T_OK) return rc;
@@ -660,8 +665,7 @@ int run_bf16_linear(const DeviceState* ds, const uint16_t* x, const uint16_t* w,
   if (K % 16 || N % 16) return fail(Q4T_ERR_INVALID, "K and N must be multiples of 16");
   // one tile of token rows: a kernel that loads four k-blocks at a time (a handful of CTAs are
   // bound by how fast one thread issues TMA loads, not by bandwidth)
-  static const bool no_small_m = std::getenv("Q4T_NO_SMALL_M_GEMM") != nullptr;
-  if (!no_small_m && q4t::bf16_small_m_fits(M, N, K)) {
+  if (!no_small_m_gemm() && q4t::bf16_small_m_fits(M, N, K)) {
     CUtensorMap tx, tw;
     int rc3;
     if ((rc3 = make_tmap_kblocks(ds, &tx, x, K, M, q4t::bf16_small_m_box_rows(M), 4)) != Q4T_OK) return rc3;
@@ -704,7 +708,7 @@ int run_shared_expert(const DeviceState* ds, const uint16_t* x, const q4t_extra_
   if (T <= 8) {
     if ((rc = run_bf16_linear(ds, x, extra->shared_gu, sgu, T, 2 * sis, hs, st)) != Q4T_OK) return rc;
     if ((e = q4t::launch_swiglu(sgu, sact, T, sis, st)) != cudaSuccess) return fail_cuda("swiglu launch", e);
-  } else if (std::getenv("Q4T_NO_SMALL_M_GEMM") == nullptr && q4t::bf16_small_m_swiglu_fits(T, sis, hs)) {
+  } else if (!no_small_m_gemm() && q4t::bf16_small_m_swiglu_fits(T, sis, hs)) {
     // one tile of token rows: the kernel that loads four k-blocks per TMA operation
     CUtensorMap tx, tw;
     if ((rc = make_tmap_kblocks(ds, &tx, x, hs, T, q4t::bf16_small_m_box_rows(T), 4)) != Q4T_OK) return rc;
