@@ -19,26 +19,33 @@ __global__ void __launch_bounds__(256) small_m_linear_kernel(const uint16_t* __r
                                                              const uint16_t* __restrict__ w,
                                                              uint16_t* __restrict__ y, int M, int N,
                                                              int K) {
-  chain_wait();
   extern __shared__ __align__(16) uint16_t s_x[];  // [M, K], loaded once per block
   const int k8 = K >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  const uint4* wrow = reinterpret_cast<const uint4*>(w + static_cast<size_t>(n < N ? n : 0) * K);
+  // The weights do not come from the kernel before this one: the first eight chunks of the
+  // row (all of it up to K = 2048) are requested before the wait and the staging of x.
+  uint4 wv[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+    if (n < N && lane + 32 * u < k8) wv[u] = __ldg(wrow + lane + 32 * u);
+  chain_wait();
   for (int i = threadIdx.x; i < M * k8; i += 256)
     reinterpret_cast<uint4*>(s_x)[i] = __ldg(reinterpret_cast<const uint4*>(x) + i);
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * 8 + warp;
   if (n >= N) return;
-  const uint4* wrow = reinterpret_cast<const uint4*>(w + static_cast<size_t>(n) * K);
   float ax[MAXM], ay[MAXM];
 #pragma unroll
   for (int m = 0; m < MAXM; ++m) ax[m] = ay[m] = 0.0f;
   // chunks lane, lane+32, ... in order; the weight loads of eight chunks are
   // issued together so that their latencies overlap
   for (int i0 = lane; i0 < k8; i0 += 32 * 8) {
-    uint4 wv[8];
+    if (i0 != lane) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
-      if (i0 + 32 * u < k8) wv[u] = __ldg(wrow + i0 + 32 * u);
+      for (int u = 0; u < 8; ++u)
+        if (i0 + 32 * u < k8) wv[u] = __ldg(wrow + i0 + 32 * u);
+    }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int i = i0 + 32 * u;
