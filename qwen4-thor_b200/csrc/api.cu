@@ -584,7 +584,8 @@ int run_routed_core_bf16(const DeviceState* ds, const uint16_t* x, const int32_t
   // 64 weight rows, loaded four k-blocks at a time (bf16_small_m.cu)
   if (!no_small_m_gemm() && M <= 16 && hs % 64 == 0 && is % 64 == 0) {
     const int box_rows = q4t::bf16_small_m_box_rows(M);
-    const int max_row_tiles = R < E ? R : E;
+    // one row tile per expert with rows, one more for every 128 rows an expert has beyond that
+    const int max_row_tiles = (R < E ? R : E) + R / 128;
     if ((rc = make_tmap_kblocks(ds, &tm_a, compact, hs, R, box_rows, 4)) != Q4T_OK) return rc;
     if ((rc = make_tmap_kblocks_gate_up(ds, &tm_b, w->gu, hs, is, 4, static_cast<uint64_t>(E) * 2 * is - is)) != Q4T_OK)
       return rc;
