@@ -308,6 +308,14 @@ int32_t q4t_moe_forward(const uint16_t* x, const q4t_routed_weights* routed,
  *                    bf16 [T, hc*hs] (16-byte aligned, may not overlap y),
  *                    hc_inject_gate is bf16 [T, hc] as ApplyInjectGateKernel
  *                    leaves it (2*sigmoid(inject/hc)).  y is still written.
+ * norm_*          : the step between two layers of a decode stack fused into the
+ *                    final combine: with norm_residual != NULL (bf16 [T,hs], the
+ *                    residual stream, read and written) norm_residual <-
+ *                    bf16(norm_residual + y) and norm_out (bf16 [T,hs], distinct
+ *                    from norm_residual; it may be the buffer x points to) <-
+ *                    RMSNorm(norm_residual) with eps norm_eps and no weight: bit
+ *                    for bit what q4t_residual_rmsnorm_bf16 computes after the
+ *                    layer.  hs a multiple of 8, at most 8192.  y is still written.
  * fixed_ids and flags as in q4t_moe_forward.                                   */
 typedef struct q4t_forward_options {
   const int32_t* fixed_ids;
@@ -318,6 +326,9 @@ typedef struct q4t_forward_options {
   const uint16_t* hc_residual;
   const uint16_t* hc_inject_gate;
   uint16_t* hc_out;
+  uint16_t* norm_residual;
+  uint16_t* norm_out;
+  float norm_eps;
 } q4t_forward_options;
 int32_t q4t_moe_forward_ex(const uint16_t* x, const q4t_routed_weights* routed,
                            const q4t_extra_weights* extra, uint16_t* y, int32_t T,

@@ -65,7 +65,8 @@ class ForwardOptions(C.Structure):
     """q4t_forward_options: the replay table, the router-trace observer and the slot-mode table."""
     _fields_ = [("fixed_ids", C.c_void_p), ("trace_ids_out", C.c_void_p), ("slot_of_expert", C.c_void_p),
                 ("flags", C.c_uint32), ("hc_count", C.c_int32), ("hc_residual", C.c_void_p),
-                ("hc_inject_gate", C.c_void_p), ("hc_out", C.c_void_p)]
+                ("hc_inject_gate", C.c_void_p), ("hc_out", C.c_void_p), ("norm_residual", C.c_void_p),
+                ("norm_out", C.c_void_p), ("norm_eps", C.c_float)]
 
 
 EXPORTS = [
@@ -390,13 +391,15 @@ class MoEForward:
         self.ws = torch.empty(self.layout.total, dtype=torch.uint8, device=device)
 
     def __call__(self, x, y, fixed_ids=None, flags=0, stream=None, trace_ids_out=None, slot_of_expert=None,
-                 hc_write=None):
+                 hc_write=None, norm_write=None):
         """trace_ids_out: CUDA int32 [T,k] that receives the selected expert ids (the router-trace
         observer); slot_of_expert: CUDA int32 [E] expert -> resident slot table (slot mode: the
         layer's routed weights then hold layer.E slots, the router chooses among layer.E_router);
         hc_write: (residual bf16 [T, hc*hs], inject_gate bf16 [T, hc], out bf16 [T, hc*hs]), the
-        layer's gated residual write fused into the final combine."""
-        if trace_ids_out is None and slot_of_expert is None and hc_write is None:
+        layer's gated residual write fused into the final combine; norm_write: (residual bf16 [T, hs]
+        read and written, out bf16 [T, hs], eps): residual <- bf16(residual + y), out <- RMSNorm(residual),
+        the step between two layers of a stack fused into the final combine."""
+        if trace_ids_out is None and slot_of_expert is None and hc_write is None and norm_write is None:
             check(load().q4t_moe_forward(_ptr(x), C.byref(self.layer.routed), C.byref(self.layer.extra), _ptr(y),
                                          self.T, self.k, _ptr(self.ws), self.layout.total, _ptr(fixed_ids),
                                          flags, _stream_ptr(stream)))
@@ -405,8 +408,9 @@ class MoEForward:
         if hc_write is not None:
             res, gate, out = hc_write
             hc = gate.shape[1]
+        nres, nout, neps = norm_write if norm_write is not None else (None, None, 0.0)
         opt = ForwardOptions(_ptr(fixed_ids), _ptr(trace_ids_out), _ptr(slot_of_expert), flags, hc, _ptr(res),
-                             _ptr(gate), _ptr(out))
+                             _ptr(gate), _ptr(out), _ptr(nres), _ptr(nout), float(neps))
         check(load().q4t_moe_forward_ex(_ptr(x), C.byref(self.layer.routed), C.byref(self.layer.extra), _ptr(y),
                                         self.T, self.k, _ptr(self.ws), self.layout.total, C.byref(opt),
                                         _stream_ptr(stream)))
@@ -476,19 +480,31 @@ class DecodeStack:
     """L MoE layers applied as x <- bf16(x + MoE_l(RMSNorm(x))), the decode-stack harness
     (eps 1e-6, no norm weight).  One workspace is shared by all layers."""
 
-    def __init__(self, layers, T: int, k: int, eps: float = 1e-6, device="cuda"):
+    def __init__(self, layers, T: int, k: int, eps: float = 1e-6, device="cuda", fused: bool = True):
         import torch
-        self.layers, self.T, self.k, self.eps = layers, T, k, eps
+        self.layers, self.T, self.k, self.eps, self.fused = layers, T, k, eps, fused
         self.fwd = MoEForward(layers[0], T, k, device)
         hs = layers[0].hs
         self.h = torch.empty((T, hs), dtype=torch.bfloat16, device=device)
+        self.h2 = torch.empty((T, hs), dtype=torch.bfloat16, device=device)
         self.y = torch.empty((T, hs), dtype=torch.bfloat16, device=device)
 
     def __call__(self, x, stream=None):
-        """Runs the stack in place on x (bf16 [T, hs]); returns x."""
+        """Runs the stack in place on x (bf16 [T, hs]); returns x.  fused (default): one residual +
+        RMSNorm launch in front of the first layer, after that every layer's combine adds its output
+        to x and writes the next layer's normalised input itself (same bits either way)."""
         L = load()
         sp = _stream_ptr(stream)
         fw = self.fwd
+        if self.fused:
+            check(L.q4t_residual_rmsnorm_bf16(_ptr(x), None, _ptr(self.h), self.T, self.layers[0].hs, float(self.eps), sp))
+            h_in, h_out = self.h, self.h2
+            for layer in self.layers:
+                opt = ForwardOptions(None, None, None, 0, 0, None, None, None, _ptr(x), _ptr(h_out), float(self.eps))
+                check(L.q4t_moe_forward_ex(_ptr(h_in), C.byref(layer.routed), C.byref(layer.extra), _ptr(self.y), self.T,
+                                           self.k, _ptr(fw.ws), fw.ws.numel(), C.byref(opt), sp))
+                h_in, h_out = h_out, h_in
+            return x
         for i, layer in enumerate(self.layers):
             check(L.q4t_residual_rmsnorm_bf16(_ptr(x), _ptr(self.y) if i else None, _ptr(self.h), self.T,
                                               layer.hs, float(self.eps), sp))

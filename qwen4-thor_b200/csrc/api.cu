@@ -953,7 +953,7 @@ int moe_forward_impl(const uint16_t* x, const q4t_routed_weights* routed, const 
                      const q4t_extra_weights* extra, uint16_t* y, int32_t T, int32_t k, void* workspace,
                      size_t workspace_bytes, const int32_t* fixed_ids, int32_t* trace_ids_out,
                      const int32_t* slot_of_expert, uint32_t flags, void* stream,
-                     const q4t::HcWrite& hcw = q4t::HcWrite{}) {
+                     const q4t::HcWrite& hcw = q4t::HcWrite{}, const q4t::NormWrite& nw = q4t::NormWrite{}) {
   if (T <= 0) return Q4T_OK;                                           // src/model/moe.cu:442
   if (k <= 0 || k > 16) return fail(Q4T_ERR_INVALID, "k out of range");  // moe.cu:443
   if ((!routed && !routed_bf16) || !extra) return fail(Q4T_ERR_INVALID, "null weights");
@@ -1081,7 +1081,7 @@ int moe_forward_impl(const uint16_t* x, const q4t_routed_weights* routed, const 
 
   // 7. routed sum + sigmoid-gated shared expert
   if ((e = q4t::launch_final_combine(P.at<uint16_t>(P.L.dn_out), P.at<int32_t>(P.L.row_of_flat), rw, sdown, x,
-                                     extra->shared_gate_scalar, routed_f32, y, T, k, hs, st, hcw)) != cudaSuccess)
+                                     extra->shared_gate_scalar, routed_f32, y, T, k, hs, st, hcw, nw)) != cudaSuccess)
     return fail_cuda("combine launch", e);
   stage_end(7, st);
   return Q4T_OK;
@@ -1111,8 +1111,18 @@ int32_t q4t_moe_forward_ex(const uint16_t* x, const q4t_routed_weights* routed, 
       return fail(Q4T_ERR_INVALID, "gated residual write: buffers must be 16-byte aligned");
     hcw = q4t::HcWrite{opt->hc_residual, opt->hc_inject_gate, opt->hc_out, opt->hc_count};
   }
+  q4t::NormWrite nw{};
+  if (opt->norm_residual) {
+    if (!opt->norm_out || opt->norm_out == opt->norm_residual)
+      return fail(Q4T_ERR_INVALID, "residual + RMSNorm write: two distinct non-null buffers");
+    if ((reinterpret_cast<uintptr_t>(opt->norm_residual) | reinterpret_cast<uintptr_t>(opt->norm_out)) & 15u)
+      return fail(Q4T_ERR_INVALID, "residual + RMSNorm write: buffers must be 16-byte aligned");
+    if (extra && (extra->hs > q4t::kNormWriteMaxHs || extra->hs % 8))
+      return fail(Q4T_ERR_INVALID, "residual + RMSNorm write: hs must be a multiple of 8, at most 8192");
+    nw = q4t::NormWrite{opt->norm_residual, opt->norm_out, opt->norm_eps};
+  }
   return moe_forward_impl(x, routed, nullptr, extra, y, T, k, workspace, workspace_bytes, opt->fixed_ids,
-                          opt->trace_ids_out, opt->slot_of_expert, opt->flags, stream, hcw);
+                          opt->trace_ids_out, opt->slot_of_expert, opt->flags, stream, hcw, nw);
 }
 
 // ---- BF16 routed experts (the MTP draft layer)

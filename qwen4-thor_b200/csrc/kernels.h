@@ -178,10 +178,19 @@ struct HcWrite {
   uint16_t* out;                // [T, hc, hs] bf16
   int hc;
 };
+// The step between two layers of a decode stack fused into the combine: residual <- bf16(residual + y),
+// out <- RMSNorm(residual) without a weight, bit for bit what launch_residual_rmsnorm computes.
+constexpr int kNormWriteMaxHs = 8192;
+struct NormWrite {
+  uint16_t* residual;   // [T, hs] bf16, read and written (null = off)
+  uint16_t* out;        // [T, hs] bf16
+  float eps;
+};
 cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,
                                  const uint16_t* shared_down, const uint16_t* x,
                                  const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
-                                 int k, int hs, cudaStream_t stream, const HcWrite& hcw = HcWrite{});
+                                 int k, int hs, cudaStream_t stream, const HcWrite& hcw = HcWrite{},
+                                 const NormWrite& nw = NormWrite{});
 
 // ---- routed experts for decode-sized batches (decode_small.cu)
 constexpr int kSmallN = 16;            // token rows per pass of one CTA (the N side of the MMA)

@@ -764,9 +764,12 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
     const uint16_t* __restrict__ dn_out, const int32_t* __restrict__ row_of_flat,
     const float* __restrict__ rw, const uint16_t* __restrict__ shared_down,
     const uint16_t* __restrict__ x, const uint16_t* __restrict__ gate_scalar,
-    float* __restrict__ routed, uint16_t* __restrict__ y, int T, int k, int hs, const HcWrite hcw) {
+    float* __restrict__ routed, uint16_t* __restrict__ y, int T, int k, int hs, const HcWrite hcw,
+    const NormWrite nw) {
   chain_wait();
   __shared__ float part[256];
+  __shared__ float s_sq[kNormWriteMaxHs / 8];   // per 8-column group: sum of squares of the new residual row
+  __shared__ float s_rnorm;
   __shared__ int s_row[16];
   __shared__ float s_w[16];
   const int t = blockIdx.x;
@@ -862,6 +865,44 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
       for (int j = 0; j < 4; ++j)
         w[j] = f32x2_to_bf16x2(fmaf(bf16x2_lo(o[j]), inj, bf16x2_lo(r[j])), fmaf(bf16x2_hi(o[j]), inj, bf16x2_hi(r[j])));
       *(reinterpret_cast<uint4*>(hcw.out + at) + c8) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // The step between two layers of a decode stack, x <- bf16(x + y) and h = RMSNorm(x), with
+    // the arithmetic of residual_rmsnorm_kernel: the sum from the bf16-rounded y, and a sum of
+    // squares per 8-column group that is folded below in that kernel's order.
+    if (nw.residual) {
+      uint4* xr = reinterpret_cast<uint4*>(nw.residual + static_cast<size_t>(t) * hs) + c8;
+      const uint4 xv = *xr;
+      const uint32_t xa[4] = {xv.x, xv.y, xv.z, xv.w};
+      uint32_t xn[4];
+      float sq = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        xn[j] = f32x2_to_bf16x2(bf16x2_lo(xa[j]) + bf16x2_lo(o[j]), bf16x2_hi(xa[j]) + bf16x2_hi(o[j]));
+        sq = fmaf(bf16x2_lo(xn[j]), bf16x2_lo(xn[j]), sq);
+        sq = fmaf(bf16x2_hi(xn[j]), bf16x2_hi(xn[j]), sq);
+      }
+      *xr = make_uint4(xn[0], xn[1], xn[2], xn[3]);
+      s_sq[c8] = sq;
+    }
+  }
+  if (nw.residual) {
+    __syncthreads();
+    if (threadIdx.x < 32) {   // residual_rmsnorm_kernel: lane l adds groups l, l+32, ... in order, then a butterfly
+      float sum = 0.0f;
+      for (int i = threadIdx.x; i < n8; i += 32) sum += s_sq[i];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      if (threadIdx.x == 0) s_rnorm = __frsqrt_rn(__fdiv_rn(sum, static_cast<float>(hs)) + nw.eps);
+    }
+    __syncthreads();
+    const float r = s_rnorm;
+    for (int c8 = threadIdx.x; c8 < n8; c8 += 256) {   // each thread reads back the groups it has just written
+      const uint4 xv = *(reinterpret_cast<const uint4*>(nw.residual + static_cast<size_t>(t) * hs) + c8);
+      const uint32_t xa[4] = {xv.x, xv.y, xv.z, xv.w};
+      uint32_t h[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = f32x2_to_bf16x2(bf16x2_lo(xa[j]) * r, bf16x2_hi(xa[j]) * r);
+      *(reinterpret_cast<uint4*>(nw.out + static_cast<size_t>(t) * hs) + c8) = make_uint4(h[0], h[1], h[2], h[3]);
     }
   }
 }
@@ -1007,12 +1048,13 @@ cudaError_t launch_residual_rmsnorm(uint16_t* x, const uint16_t* y, uint16_t* h,
 cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_flat, const float* rw,
                                  const uint16_t* shared_down, const uint16_t* x,
                                  const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
-                                 int k, int hs, cudaStream_t stream, const HcWrite& hcw) {
+                                 int k, int hs, cudaStream_t stream, const HcWrite& hcw, const NormWrite& nw) {
+  if (nw.residual && (hs > kNormWriteMaxHs || hs % 8 || !nw.out)) return cudaErrorInvalidValue;
   if (T <= 1024)
     return launch_chained(final_combine_kernel<true>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
-                          shared_down, x, gate_scalar, routed, y, T, k, hs, hcw);
+                          shared_down, x, gate_scalar, routed, y, T, k, hs, hcw, nw);
   return launch_chained(final_combine_kernel<false>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
-                        shared_down, x, gate_scalar, routed, y, T, k, hs, hcw);
+                        shared_down, x, gate_scalar, routed, y, T, k, hs, hcw, nw);
 }
 
 }  // namespace q4t

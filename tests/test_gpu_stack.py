@@ -86,3 +86,33 @@ def test_gated_residual_write_fused_into_combine(q4t, gpu_lib, T):
     assert torch.equal(y0.view(torch.int16), y1.view(torch.int16))
     want = O.gated_residual_write(host(y1), res, gate)
     assert np.array_equal(host(out), want)
+
+
+@pytest.mark.parametrize("T,hs", [(1, 1024), (9, 512), (70, 2560), (130, 512)])
+def test_stack_with_the_norm_step_fused_into_the_combine(q4t, gpu_lib, T, hs):
+    """x <- bf16(x + y), h <- RMSNorm(x) between two layers: as a launch of its own and fused into
+    the layer's final combine (q4t_forward_options.norm_*): the same bits in x after three layers."""
+    E, is_, sis, k, nl = 32, 256, 128, 4, 3
+    layers = [synth.make_layer(E=E, hs=hs, moe_is=is_, shared_is=sis, seed=40 + i) for i in range(nl)]
+    dls = [q4t.DeviceLayer.from_host(L) for L in layers]
+    x0 = synth.make_x(T, hs, seed=T)
+    xa = dev(x0).view(torch.bfloat16).clone()
+    xb = dev(x0).view(torch.bfloat16).clone()
+    q4t.DecodeStack(dls, T, k, fused=False)(xa)
+    q4t.DecodeStack(dls, T, k, fused=True)(xb)
+    torch.cuda.synchronize()
+    assert torch.equal(xa.view(torch.int16), xb.view(torch.int16))
+
+
+def test_norm_write_rejects_bad_arguments(q4t, gpu_lib):
+    L = synth.make_layer(E=8, hs=256, moe_is=128, shared_is=128, seed=1)
+    dl = q4t.DeviceLayer.from_host(L)
+    T, k = 4, 2
+    fwd = q4t.MoEForward(dl, T, k)
+    x = dev(synth.make_x(T, 256, seed=2))
+    y = torch.empty((T, 256), dtype=torch.bfloat16, device="cuda")
+    res = torch.zeros((T, 256), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(q4t.Q4TError, match="two distinct"):
+        fwd(x, y, norm_write=(res, res, 1e-6))
+    with pytest.raises(q4t.Q4TError, match="two distinct"):
+        fwd(x, y, norm_write=(res, None, 1e-6))
