@@ -98,11 +98,21 @@ struct GatedResidualWrite {
   int hc = 0;
 };
 
+// The step between this layer and the next in a decode stack without hyper-connections,
+// residual <- bf16(residual + y) and out <- RMSNorm(residual) (no weight), when it is to be
+// fused into the layer's last kernel instead of running as a launch of its own.
+struct ResidualNormWrite {
+  uint16_t* residual = nullptr;   // [T, hs] bf16, the residual stream (read and written)
+  uint16_t* out = nullptr;        // [T, hs] bf16, the next layer's normalised input
+  float eps = 1e-6f;
+};
+
 namespace detail {
 inline Status RunMoEForward(const uint16_t* x, const quant::MoEWeightLayout& routed, const MoEExtraWeights& extra,
                             uint16_t* y, int T, int k, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                             trace::RouterCollector* trace, int layer_id, const quant::MoEResidency* residency,
-                            MoEForwardDiagnostics* diagnostics, const GatedResidualWrite* write) {
+                            MoEForwardDiagnostics* diagnostics, const GatedResidualWrite* write,
+                            const ResidualNormWrite* norm = nullptr) {
   if (diagnostics) *diagnostics = {};
   const q4t_routed_weights rw = routed.Abi();
   const q4t_extra_weights ew = extra.Abi();
@@ -119,7 +129,12 @@ inline Status RunMoEForward(const uint16_t* x, const quant::MoEWeightLayout& rou
     opt.hc_inject_gate = write->inject_gate;
     opt.hc_out = write->out;
   }
-  if (residency != nullptr || opt.hc_count > 0) {
+  if (norm != nullptr && norm->residual != nullptr) {
+    opt.norm_residual = norm->residual;
+    opt.norm_out = norm->out;
+    opt.norm_eps = norm->eps;
+  }
+  if (residency != nullptr || opt.hc_count > 0 || opt.norm_residual != nullptr) {
     if (q4t_moe_forward_ex(x, &rw, &ew, y, T, k, workspace, workspace_bytes, &opt, stream) != Q4T_OK)
       return Status::Fail(q4t_last_error());
   } else if (q4t_moe_forward(x, &rw, &ew, y, T, k, workspace, workspace_bytes, nullptr, 0, stream) != Q4T_OK) {
@@ -158,6 +173,17 @@ inline Status MoEForwardAndWrite(const uint16_t* x, const quant::MoEWeightLayout
     return Status::Fail("gated residual write needs a residual, a gate and an output");
   return detail::RunMoEForward(x, routed, extra, y, T, k, workspace, workspace_bytes, stream, trace, layer_id, residency,
                                nullptr, &write);
+}
+
+// MoEForward followed by the residual add and the next layer's RMSNorm in one call.
+inline Status MoEForwardAndNorm(const uint16_t* x, const quant::MoEWeightLayout& routed, const MoEExtraWeights& extra,
+                                uint16_t* y, int T, int k, void* workspace, size_t workspace_bytes,
+                                const ResidualNormWrite& norm, cudaStream_t stream,
+                                trace::RouterCollector* trace = nullptr, int layer_id = -1,
+                                const quant::MoEResidency* residency = nullptr) {
+  if (!norm.residual || !norm.out) return Status::Fail("residual + RMSNorm write needs a residual and an output");
+  return detail::RunMoEForward(x, routed, extra, y, T, k, workspace, workspace_bytes, stream, trace, layer_id, residency,
+                               nullptr, nullptr, &norm);
 }
 
 }  // namespace q4t::model

@@ -304,6 +304,32 @@ int main() {
     wr.hc = 0;
     CHECK(!model::MoEForwardAndWrite(d_x, L, X, d_y, T, k, ws, ws_bytes, wr, 0).ok());
   }
+  // ---- MoEForward with the stack's residual + RMSNorm step fused in, against the layer followed
+  // by q4t_residual_rmsnorm_bf16: the same residual stream and the same normalised row, bit for bit
+  {
+    std::vector<uint16_t> res_h(size_t(T) * hs), x_a(res_h.size()), x_b(res_h.size()), h_a(res_h.size()), h_b(res_h.size());
+    for (size_t i = 0; i < res_h.size(); ++i) res_h[i] = static_cast<uint16_t>(0x3c00u + (i * 53u) % 0x400u);
+    uint16_t *d_xa, *d_xb, *d_ha, *d_hb;
+    for (uint16_t** ptr : {&d_xa, &d_xb, &d_ha, &d_hb}) cudaMalloc(reinterpret_cast<void**>(ptr), res_h.size() * 2);
+    cudaMemcpy(d_xa, res_h.data(), res_h.size() * 2, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_xb, res_h.data(), res_h.size() * 2, cudaMemcpyHostToDevice);
+    CHECK(model::MoEForward(d_x, L, X, d_y, T, k, ws, ws_bytes, nullptr, 0, 0).ok());
+    CHECK(q4t_residual_rmsnorm_bf16(d_xa, d_y, d_ha, T, hs, 1e-6f, nullptr) == Q4T_OK);
+    model::ResidualNormWrite nw;
+    nw.residual = d_xb; nw.out = d_hb; nw.eps = 1e-6f;
+    s = model::MoEForwardAndNorm(d_x, L, X, d_y, T, k, ws, ws_bytes, nw, 0);
+    if (!s.ok()) std::printf("MoEForwardAndNorm: %s\n", s.message().c_str());
+    CHECK(s.ok());
+    CHECK(cudaDeviceSynchronize() == cudaSuccess);
+    cudaMemcpy(x_a.data(), d_xa, x_a.size() * 2, cudaMemcpyDeviceToHost);
+    cudaMemcpy(x_b.data(), d_xb, x_b.size() * 2, cudaMemcpyDeviceToHost);
+    cudaMemcpy(h_a.data(), d_ha, h_a.size() * 2, cudaMemcpyDeviceToHost);
+    cudaMemcpy(h_b.data(), d_hb, h_b.size() * 2, cudaMemcpyDeviceToHost);
+    CHECK(std::memcmp(x_a.data(), x_b.data(), x_a.size() * 2) == 0);
+    CHECK(std::memcmp(h_a.data(), h_b.data(), h_a.size() * 2) == 0);
+    nw.out = nullptr;
+    CHECK(!model::MoEForwardAndNorm(d_x, L, X, d_y, T, k, ws, ws_bytes, nw, 0).ok());
+  }
   // the MTP draft layer's BF16 experts through the reference-shaped calls
   mtp::MoeBf16Weights B;
   B.E = E; B.hs = hs; B.moe_is = is;
