@@ -759,7 +759,9 @@ __global__ void __launch_bounds__(256) residual_rmsnorm_kernel(uint16_t* __restr
 // PRELOAD: request all of the token's rows before the first is used (k <= 16), so that the
 // slot-order sum costs one memory round trip instead of k: 3 us of a 13 us decode launch; at
 // 16 K tokens the extra registers cost more than the latency they hide (254 vs 175 us).
-template <bool PRELOAD>
+// NORM: the stack's residual + RMSNorm step rides on the kernel (a separate instantiation, so that the
+// plain combine, which is at the HBM bound at prefill sizes, keeps its registers and shared memory).
+template <bool PRELOAD, bool NORM>
 __global__ void __launch_bounds__(256) final_combine_kernel(
     const uint16_t* __restrict__ dn_out, const int32_t* __restrict__ row_of_flat,
     const float* __restrict__ rw, const uint16_t* __restrict__ shared_down,
@@ -768,7 +770,7 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
     const NormWrite nw) {
   chain_wait();
   __shared__ float part[256];
-  __shared__ float s_sq[kNormWriteMaxHs / 8];   // per 8-column group: sum of squares of the new residual row
+  __shared__ float s_sq[NORM ? kNormWriteMaxHs / 8 : 1];   // per 8-column group: sum of squares of the new residual row
   __shared__ float s_rnorm;
   __shared__ int s_row[16];
   __shared__ float s_w[16];
@@ -869,7 +871,7 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
     // The step between two layers of a decode stack, x <- bf16(x + y) and h = RMSNorm(x), with
     // the arithmetic of residual_rmsnorm_kernel: the sum from the bf16-rounded y, and a sum of
     // squares per 8-column group that is folded below in that kernel's order.
-    if (nw.residual) {
+    if constexpr (NORM) {
       uint4* xr = reinterpret_cast<uint4*>(nw.residual + static_cast<size_t>(t) * hs) + c8;
       const uint4 xv = *xr;
       const uint32_t xa[4] = {xv.x, xv.y, xv.z, xv.w};
@@ -885,7 +887,7 @@ __global__ void __launch_bounds__(256) final_combine_kernel(
       s_sq[c8] = sq;
     }
   }
-  if (nw.residual) {
+  if constexpr (NORM) {
     __syncthreads();
     if (threadIdx.x < 32) {   // residual_rmsnorm_kernel: lane l adds groups l, l+32, ... in order, then a butterfly
       float sum = 0.0f;
@@ -1050,10 +1052,17 @@ cudaError_t launch_final_combine(const uint16_t* dn_out, const int32_t* row_of_f
                                  const uint16_t* gate_scalar, float* routed, uint16_t* y, int T,
                                  int k, int hs, cudaStream_t stream, const HcWrite& hcw, const NormWrite& nw) {
   if (nw.residual && (hs > kNormWriteMaxHs || hs % 8 || !nw.out)) return cudaErrorInvalidValue;
-  if (T <= 1024)
-    return launch_chained(final_combine_kernel<true>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
+  if (nw.residual) {
+    if (T <= 1024)
+      return launch_chained(final_combine_kernel<true, true>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
+                            shared_down, x, gate_scalar, routed, y, T, k, hs, hcw, nw);
+    return launch_chained(final_combine_kernel<false, true>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
                           shared_down, x, gate_scalar, routed, y, T, k, hs, hcw, nw);
-  return launch_chained(final_combine_kernel<false>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
+  }
+  if (T <= 1024)
+    return launch_chained(final_combine_kernel<true, false>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
+                          shared_down, x, gate_scalar, routed, y, T, k, hs, hcw, nw);
+  return launch_chained(final_combine_kernel<false, false>, dim3(T), dim3(256), 0, stream, dn_out, row_of_flat, rw,
                         shared_down, x, gate_scalar, routed, y, T, k, hs, hcw, nw);
 }
 
